@@ -1,0 +1,290 @@
+"""CUDA-graph decode engine for llama-architecture decoders (llama / mistral / qwen2 / yi ...).
+
+The reference decodes through the Hugging Face module tree, one Python call and several device kernels per
+sub-module, synchronising every token (python/llm/src/ipex_llm/utils/benchmark_util_4_47.py:3297-3378,
+models/llama.py:56-206).  Decode at batch 1 on a B200 moves only ~3.6 GB per token for a 7B int4 model, so the
+step is bounded by how tightly the weight stream is kept busy, not by arithmetic.  This engine therefore
+
+* flattens the converted model into five fused kernels per layer
+    1. RMSNorm + qkv GEMV (+bias)
+    2. RoPE + KV-cache append (+e5m2 quantization) + split-KV attention
+    3. o_proj GEMV + residual
+    4. RMSNorm + gate/up GEMV + SiLU*mul
+    5. down_proj GEMV + residual
+  plus embedding gather, final-norm + lm_head GEMV and argmax;
+* chains them with programmatic dependent launch (each kernel prefetches its weights into L2 while its
+  predecessor drains) and captures the whole step in one CUDA graph;
+* keeps the position in device memory so the same graph replays for every token;
+* shares KV storage with the module path (prefill, speculative verification) through the package's cache
+  classes, whose pre-allocated tensors it reads and appends to in place.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+from typing import List, Optional
+
+import torch
+
+from ..native import cuda_api as api
+from ..native.lib import cuda_lib, current_stream, ptr
+from ..ops import cuda_ops
+from ..ops.kv_cache import DynamicFp8Cache, DynamicNormalCache
+from ..ops.linear import BF16Linear, FP16Linear, LowBitLinear
+from ..quant import qtypes as qt
+from ..quant.params import device_nbytes
+
+
+class _W:
+    """One linear of the flattened model: tiled low-bit bytes or a dense half matrix."""
+
+    def __init__(self, data, wf, qtype, N, K, bias=None):
+        self.data, self.wf, self.qtype, self.N, self.K, self.bias = data, wf, qtype, N, K, bias
+
+    @staticmethod
+    def from_module(mod, dtype):
+        bias = mod.bias.data.to(dtype) if getattr(mod, "bias", None) is not None else None
+        if isinstance(mod, LowBitLinear):
+            w = mod.weight
+            if not cuda_ops.is_tiled(w.qtype):
+                raise NotImplementedError(f"decode engine needs a tiled qtype, got {qt.qtype_name(w.qtype)}")
+            return _W(w.data, cuda_ops.QTYPE_TO_WF[w.qtype], w.qtype, int(w._shape[0]), int(w._shape[1]), bias)
+        w = mod.weight.data.to(dtype).contiguous()
+        wf = api.WF_F16 if dtype == torch.float16 else api.WF_BF16
+        return _W(w, wf, None, w.shape[0], w.shape[1], bias)
+
+
+def _interleave_row_tiles(a: _W, b: _W) -> _W:
+    """Merge two tiled weights of equal shape so that row tile 2i comes from ``a`` and 2i+1 from ``b``
+    (gate / up), which lets one CTA produce act(gate) * up for 16 output features."""
+    assert a.wf == b.wf and a.N == b.N and a.K == b.K and a.N % 16 == 0
+    if a.wf in (api.WF_F16, api.WF_BF16):
+        t = a.N // 16
+        w = torch.stack([a.data.view(t, 16, a.K), b.data.view(t, 16, a.K)], dim=1).reshape(2 * a.N, a.K).contiguous()
+        return _W(w, a.wf, None, 2 * a.N, a.K)
+    Np, Kp = a.N, (a.K + 127) // 128 * 128
+    T = Np // 16
+    four_bit = a.wf in (api.WF_SYM_INT4, api.WF_ASYM_INT4, api.WF_LUT4)
+    code_bytes = Np * Kp // 2 if four_bit else Np * Kp
+    if four_bit:
+        plane_sizes = [code_bytes] + [Np * (Kp // 64) * 2] * (2 if a.wf == api.WF_ASYM_INT4 else 1)
+    elif a.wf == api.WF_INT8:
+        plane_sizes = [code_bytes, Np * (Kp // 64) * 2]
+    else:
+        plane_sizes = [code_bytes, Np * (Kp // 128) * 4]
+    out_planes = []
+    off = 0
+    for sz in plane_sizes:
+        pa = a.data[off:off + sz].view(T, -1)
+        pb = b.data[off:off + sz].view(T, -1)
+        out_planes.append(torch.stack([pa, pb], dim=1).reshape(-1))
+        off += sz
+    return _W(torch.cat(out_planes).contiguous(), a.wf, a.qtype, 2 * a.N, a.K)
+
+
+class _Layer:
+    pass
+
+
+class DecoderEngine:
+    """Flattened llama-architecture decoder with graph-captured decode steps."""
+
+    def __init__(self, model, max_batch: int = 1, max_len: int = 2048, kv_fp8: Optional[bool] = None):
+        cfg = model.config
+        self.model = model
+        self.cfg = cfg
+        base = model.model
+        first = next(model.parameters())
+        self.device = base.embed_tokens.weight.device
+        self.dtype = base.norm.weight.dtype if base.norm.weight.dtype in (torch.float16, torch.bfloat16) \
+            else torch.float16
+        self.H = cfg.hidden_size
+        self.n_heads_cfg = cfg.num_attention_heads
+        self.n_kv_cfg = getattr(cfg, "num_key_value_heads", None) or cfg.num_attention_heads
+        self.hd = getattr(cfg, "head_dim", None) or cfg.hidden_size // cfg.num_attention_heads
+        self.eps = float(getattr(cfg, "rms_norm_eps", 1e-6))
+        self.vocab = cfg.vocab_size
+        self.max_batch = max_batch
+        self.max_len = max_len
+        if kv_fp8 is None:
+            from ..models.utils import use_quantize_kv_cache
+            kv_fp8 = use_quantize_kv_cache(None, torch.empty(max_batch, 1, device=self.device), 1, 1)
+        self.kv_fp8 = bool(kv_fp8)
+        self.use_pdl = os.environ.get("IPEX_LLM_PDL", "1") != "0"
+        dt = self.dtype
+
+        self.embed = base.embed_tokens.weight.data
+        if self.embed.dtype != dt:
+            self.embed = self.embed.to(dt)
+        self.final_norm = base.norm.weight.data.to(dt)
+        self.lm_head = _W.from_module(model.lm_head, dt)
+        self.layers: List[_Layer] = []
+        for blk in base.layers:
+            L = _Layer()
+            attn, mlp = blk.self_attn, blk.mlp
+            if not hasattr(attn, "qkv_proj"):
+                raise NotImplementedError("decode engine expects merged qkv_proj (optimize_model=True)")
+            L.qkv = _W.from_module(attn.qkv_proj, dt)
+            L.o = _W.from_module(attn.o_proj, dt)
+            g, u = _W.from_module(mlp.gate_proj, dt), _W.from_module(mlp.up_proj, dt)
+            L.gate_up = _interleave_row_tiles(g, u)
+            L.down = _W.from_module(mlp.down_proj, dt)
+            L.ln1 = blk.input_layernorm.weight.data.to(dt)
+            L.ln2 = blk.post_attention_layernorm.weight.data.to(dt)
+            L.layer_idx = attn.layer_idx
+            self.layers.append(L)
+        # local (possibly tensor-parallel) head counts follow the fused qkv shape
+        groups = self.n_heads_cfg // self.n_kv_cfg
+        total_heads = self.layers[0].qkv.N // self.hd
+        self.n_kv = total_heads // (groups + 2)
+        self.n_heads = total_heads - 2 * self.n_kv
+        self.inter = self.layers[0].gate_up.N // 2
+        self.tp_group = getattr(self.layers[0], "tp", None)
+
+        # rotary table (fp32) from the model's own rotary module, so every rope-scaling flavour is honoured
+        pos = torch.arange(max_len, device=self.device).unsqueeze(0)
+        dummy = torch.zeros(1, max_len, self.H, device=self.device, dtype=torch.float32)
+        cos, sin = base.rotary_emb(dummy, position_ids=pos)
+        R = cos.shape[-1]
+        self.rot_dim = R
+        self.cos = cos[0, :, : R // 2].float().contiguous()
+        self.sin = sin[0, :, : R // 2].float().contiguous()
+
+        B = max_batch
+        dev = self.device
+        self.tokens = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.past_len = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.h = [torch.zeros(B, self.H, dtype=dt, device=dev) for _ in range(2)]
+        self.qkv_buf = torch.zeros(B, self.layers[0].qkv.N, dtype=dt, device=dev)
+        self.attn_buf = torch.zeros(B, self.n_heads * self.hd, dtype=dt, device=dev)
+        self.act_buf = torch.zeros(B, self.inter, dtype=dt, device=dev)
+        self.logits = torch.zeros(B, self.vocab, dtype=dt, device=dev)
+        self.cache = None
+        self._graphs = {}
+        self._lib = cuda_lib()
+        self._nsplit = None
+        self.kernel_launches_per_step = 1 + 5 * len(self.layers) + 2
+
+    # ------------------------------------------------------------------------------------------------
+    def new_cache(self, batch: int):
+        """A cache of the package's own class whose storage is pre-allocated to ``max_len`` tokens."""
+        pool = self.__dict__.setdefault("_cache_pool", {})
+        if batch in pool:
+            cache = pool[batch]
+            for layer in cache.layers:
+                layer.set_length(0)
+            return cache
+        cls = DynamicFp8Cache if self.kv_fp8 else DynamicNormalCache
+        cache = cls(self.cfg)
+        pool[batch] = cache
+        for _ in self.layers:
+            layer = cache.layer_class_to_replicate()
+            layer.preallocate(batch, self.n_kv, self.max_len, self.hd, self.hd, self.dtype, self.device)
+            cache.layers.append(layer)
+        return cache
+
+    def bind_cache(self, cache, batch: int):
+        self.cache = cache
+        self.batch = batch
+        self._graphs = {k: v for k, v in self._graphs.items() if v[1] is cache}
+
+    # ------------------------------------------------------------------------------------------------
+    def _gemv(self, w: _W, x, out, norm_w=None, bias=None, residual=None, act=0):
+        M = x.shape[0]
+        for s in range(0, M, 8):
+            e = min(M, s + 8)
+            cuda_ops.gemv_lowbit(x[s:e], w.data, w.qtype, w.N, w.K, out=out[s:e], norm_weight=norm_w, eps=self.eps,
+                                 bias=bias if bias is not None else w.bias,
+                                 residual=residual[s:e] if residual is not None else None, act=act,
+                                 pdl=self.use_pdl, wf=w.wf)
+
+    def _attention(self, L: _Layer, B: int):
+        lib = self._lib
+        layer = self.cache.layers[L.layer_idx]
+        kc, vc = layer._k, layer._v
+        D, Hq, Hkv = self.hd, self.n_heads, self.n_kv
+        q_off_k = Hq * D
+        q_off_v = (Hq + Hkv) * D
+        qkv = self.qkv_buf[:B]
+        ld = qkv.stride(0)
+        knew = qkv[:, q_off_k:]
+        vnew = qkv[:, q_off_v:]
+        out = self.attn_buf[:B]
+        G = Hq // Hkv
+        nsplit = self._nsplit
+        floats = lib.ipex_attn_decode_scratch_floats(B, Hkv, G, 1, D, nsplit)
+        ints = lib.ipex_attn_decode_counter_ints(B, Hkv, G, 1)
+        scratch, counters = cuda_ops.attn_workspace(self.device, floats, ints)
+        strides = (ctypes.c_int64 * 12)(ld, ld, D, ld, ld, D, kc.stride(0), kc.stride(1), kc.stride(2),
+                                        out.stride(0), out.stride(0), D)
+        rc = lib.ipex_attn_decode(ptr(qkv), ptr(knew), ptr(vnew), ptr(kc), ptr(vc), ptr(out), ptr(self.past_len), 0,
+                                  ptr(self.cos), ptr(self.sin), ptr(scratch), ptr(counters), strides, B, 1, Hq, Hkv,
+                                  D, nsplit, 1, self.rot_dim, 1, 0, 1.0 / math.sqrt(D), 0.0, int(self.kv_fp8),
+                                  api.dtype_code(self.dtype), int(self.use_pdl), current_stream())
+        api.check(rc, "attn_decode")
+
+    def _step_kernels(self, B: int):
+        """Issue one decode step for ``B`` sequences on the current stream: tokens[:B] -> tokens[:B]."""
+        lib = self._lib
+        dtc = api.dtype_code(self.dtype)
+        pdl = int(self.use_pdl)
+        h0, h1 = self.h[0][:B], self.h[1][:B]
+        rc = lib.ipex_embedding(ptr(self.tokens), ptr(self.embed), ptr(h0), B, self.H, 1.0, dtc, 0, current_stream())
+        api.check(rc, "embedding")
+        for L in self.layers:
+            self._gemv(L.qkv, h0, self.qkv_buf[:B], norm_w=L.ln1)
+            self._attention(L, B)
+            self._gemv(L.o, self.attn_buf[:B], h1, residual=h0)
+            self._gemv(L.gate_up, h1, self.act_buf[:B], norm_w=L.ln2, act=1)
+            self._gemv(L.down, self.act_buf[:B], h0, residual=h1)
+        self._gemv(self.lm_head, h0, self.logits[:B], norm_w=self.final_norm)
+        rc = lib.ipex_argmax(ptr(self.logits), ptr(self.tokens), B, self.vocab, self.logits.stride(0), dtc, pdl,
+                             current_stream())
+        api.check(rc, "argmax")
+        self.past_len[:B].add_(1)
+
+    def decode_step(self, B: int, use_graph: bool = True):
+        """One token for every sequence.  The step is captured once per (batch, cache) and replayed."""
+        if self._nsplit is None:
+            self._nsplit = cuda_ops.pick_nsplit(B, self.n_kv, self.max_len)
+        if not use_graph or os.environ.get("IPEX_LLM_ENGINE_GRAPH", "1") == "0":
+            self._step_kernels(B)
+            return
+        entry = self._graphs.get(B)
+        if entry is None:
+            # warm up outside capture (lazy allocations, cudaFuncSetAttribute), restoring the state it advances
+            saved_tok, saved_len = self.tokens.clone(), self.past_len.clone()
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._step_kernels(B)
+            torch.cuda.current_stream().wait_stream(s)
+            self.tokens.copy_(saved_tok)
+            self.past_len.copy_(saved_len)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._step_kernels(B)
+            # capture does not execute: state is unchanged
+            entry = (g, self.cache)
+            self._graphs[B] = entry
+        entry[0].replay()
+
+    # ------------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def prefill(self, input_ids: torch.Tensor, attention_mask=None):
+        """Prompt pass through the module path (tensor-core GEMMs + prefill attention), writing K/V into the
+        engine's cache; returns the logits of the last position ``[B, V]``."""
+        B, S = input_ids.shape
+        if S + 1 > self.max_len:
+            raise ValueError(f"prompt of {S} tokens does not fit max_len={self.max_len}")
+        cache = self.new_cache(B)
+        self.bind_cache(cache, B)
+        out = self.model(input_ids=input_ids, attention_mask=attention_mask, past_key_values=cache, use_cache=True)
+        logits = out.logits[:, -1, :]
+        self.past_len[:B] = S
+        return logits
+
+    def sync_cache_length(self, n: int):
+        for layer in self.cache.layers:
+            layer.set_length(n)

@@ -1,0 +1,242 @@
+"""Fused-op façade shared by every model forward replacement.
+
+Counterpart of python/llm/src/ipex_llm/transformers/models/common.py:22-305 of the reference
+(``merge_qkv_base``, ``fuse_mlp_base`` / ``mlp_silu_forward`` / ``mlp_gelu_forward``, ``rms_norm_forward``,
+``layer_norm_forward``, ``attention_softmax``, ``scaled_dot_product_attention``, head-dim padding helpers).
+On a CUDA tensor every function calls the package's own sm_100a kernel; on the CPU it is plain PyTorch in fp32.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from ..ops.kv_cache import fp8_e5m2_dequantize
+
+SILU = 0
+GELU = 1
+
+
+# ------------------------------------------------------------------------------------------------
+# weight surgery helpers
+# ------------------------------------------------------------------------------------------------
+def merge_linear(linears):
+    """Concatenate several ``nn.Linear`` along the output dimension into one."""
+    if hasattr(linears[0], "weight"):
+        new_weight = torch.cat([lin.weight.data for lin in linears], dim=0)
+        if linears[0].bias is not None:
+            new_linear = nn.Linear(0, 0, bias=True)
+            new_linear.bias = nn.Parameter(torch.cat([lin.bias.data for lin in linears], dim=0), requires_grad=False)
+        else:
+            new_linear = nn.Linear(0, 0, bias=False)
+        new_linear.weight = nn.Parameter(new_weight, requires_grad=False)
+        new_linear.in_features = new_weight.size(1)
+        new_linear.out_features = new_weight.size(0)
+        return new_linear
+    raise TypeError("merge_linear expects nn.Linear-like modules")
+
+
+def merge_qkv_base(module: nn.Module, attention_class):
+    """Replace q_proj/k_proj/v_proj of ``attention_class`` modules by one ``qkv_proj``
+    (reference models/common.py:40-52).  ``attention_class`` may be a class or a class name."""
+    hit = (module.__class__.__name__ == attention_class) if isinstance(attention_class, str) \
+        else isinstance(module, attention_class)
+    if hit and hasattr(module, "q_proj") and hasattr(module, "k_proj") and hasattr(module, "v_proj"):
+        module.qkv_proj = merge_linear([module.q_proj, module.k_proj, module.v_proj])
+        del module.q_proj, module.k_proj, module.v_proj
+
+
+def padding_linear_hd(linear: nn.Linear, old_hd: int, new_hd: int) -> nn.Linear:
+    in_features, out_features = linear.in_features, linear.out_features
+    weight = linear.weight.data.view(-1, old_hd, in_features)
+    new_weight = torch.zeros(weight.shape[0], new_hd, in_features, dtype=weight.dtype, device=weight.device)
+    new_weight[:, :old_hd] = weight
+    new_linear = nn.Linear(0, 0, bias=linear.bias is not None)
+    new_linear.weight = nn.Parameter(new_weight.view(-1, in_features), requires_grad=False)
+    if linear.bias is not None:
+        bias = linear.bias.data.view(-1, old_hd)
+        nb = torch.zeros(bias.shape[0], new_hd, dtype=bias.dtype, device=bias.device)
+        nb[:, :old_hd] = bias
+        new_linear.bias = nn.Parameter(nb.flatten(), requires_grad=False)
+    new_linear.in_features = in_features
+    new_linear.out_features = out_features // old_hd * new_hd
+    return new_linear
+
+
+def padding_states_hd(states: torch.Tensor, old_hd: int, new_hd: int):
+    return F.pad(states, (0, new_hd - old_hd))
+
+
+# ------------------------------------------------------------------------------------------------
+# norms
+# ------------------------------------------------------------------------------------------------
+def rms_norm_forward(self, hidden_states: torch.Tensor, residual: torch.Tensor = None):
+    weight = self.weight
+    eps = getattr(self, "variance_epsilon", None)
+    if eps is None:
+        eps = getattr(self, "eps", None)
+    if eps is None:
+        eps = getattr(self, "epsilon", 1e-6)
+    offset = getattr(self, "_ipex_weight_offset", 0.0)  # Gemma: weight + 1
+    if hidden_states.is_cuda and not hidden_states.requires_grad and \
+            hidden_states.dtype in (torch.float16, torch.bfloat16):
+        from ..ops import cuda_ops
+        return cuda_ops.rms_norm(hidden_states, weight, eps, offset)
+    input_dtype = hidden_states.dtype
+    h = hidden_states.to(torch.float32)
+    variance = h.pow(2).mean(-1, keepdim=True)
+    h = h * torch.rsqrt(variance + eps)
+    return ((weight.float() + offset) * h).to(input_dtype)
+
+
+def gemma_rms_norm_forward(self, hidden_states):
+    self._ipex_weight_offset = 1.0
+    return rms_norm_forward(self, hidden_states)
+
+
+def layer_norm_forward(self, hidden_states: torch.Tensor):
+    if hidden_states.is_cuda and not hidden_states.requires_grad and self.weight is not None and \
+            hidden_states.dtype in (torch.float16, torch.bfloat16):
+        from ..ops import cuda_ops
+        return cuda_ops.layer_norm(hidden_states, self.weight, self.bias, self.eps)
+    return F.layer_norm(hidden_states, self.normalized_shape, self.weight, self.bias, self.eps)
+
+
+# ------------------------------------------------------------------------------------------------
+# MLP
+# ------------------------------------------------------------------------------------------------
+def _act_mul(gate: torch.Tensor, up: torch.Tensor, act: int):
+    if gate.is_cuda and not gate.requires_grad and gate.dtype in (torch.float16, torch.bfloat16):
+        from ..ops import cuda_ops
+        return cuda_ops.act_mul(gate, up, act)
+    if act == SILU:
+        return F.silu(gate) * up
+    return F.gelu(gate, approximate="tanh") * up
+
+
+def fuse_mlp_base(module: nn.Module, act: int, x: torch.Tensor):
+    """down(act(gate(x)) * up(x)); a merged ``gate_up_proj`` (if the converter built one) is used as one GEMM."""
+    if hasattr(module, "gate_up_proj") and isinstance(module.gate_up_proj, nn.Module):
+        gu = module.gate_up_proj(x)
+        gate, up = gu.chunk(2, dim=-1)
+        return module.down_proj(_act_mul(gate.contiguous(), up.contiguous(), act))
+    return module.down_proj(_act_mul(module.gate_proj(x), module.up_proj(x), act))
+
+
+def mlp_silu_forward(self, x: torch.Tensor, *args, **kwargs):
+    return fuse_mlp_base(self, SILU, x)
+
+
+def mlp_gelu_forward(self, x: torch.Tensor, *args, **kwargs):
+    return fuse_mlp_base(self, GELU, x)
+
+
+# ------------------------------------------------------------------------------------------------
+# rotary embedding
+# ------------------------------------------------------------------------------------------------
+def rotate_half(x):
+    x1 = x[..., : x.shape[-1] // 2]
+    x2 = x[..., x.shape[-1] // 2:]
+    return torch.cat((-x2, x1), dim=-1)
+
+
+def apply_rotary_pos_emb(q, k, cos, sin, unsqueeze_dim=1, interleaved=False):
+    """RoPE on q and k (``[B, H, S, D]``); ``cos``/``sin`` are ``[B, S, R]`` with R <= D (partial rotary).
+    ``interleaved`` selects the GPT-J "two" pairing instead of the NeoX "half" pairing."""
+    if q.is_cuda and not q.requires_grad and q.dtype in (torch.float16, torch.bfloat16) and cos.dim() == 3:
+        from ..ops import cuda_ops
+        return cuda_ops.rotary_inplace(q, k, cos, sin, interleaved)
+    cos = cos.unsqueeze(unsqueeze_dim)
+    sin = sin.unsqueeze(unsqueeze_dim)
+    rot = cos.shape[-1]
+
+    def _apply(x):
+        xr, xp = x[..., :rot], x[..., rot:]
+        if interleaved:
+            x1 = xr[..., 0::2]
+            x2 = xr[..., 1::2]
+            c = cos[..., : rot // 2]
+            s = sin[..., : rot // 2]
+            o = torch.stack((x1 * c - x2 * s, x2 * c + x1 * s), dim=-1).flatten(-2)
+        else:
+            o = xr * cos + rotate_half(xr) * sin
+        return torch.cat((o.to(x.dtype), xp), dim=-1) if xp.shape[-1] else o.to(x.dtype)
+
+    return _apply(q), _apply(k)
+
+
+# ------------------------------------------------------------------------------------------------
+# attention
+# ------------------------------------------------------------------------------------------------
+def attention_softmax(attn_weights: torch.Tensor):
+    if attn_weights.is_cuda and attn_weights.is_contiguous() and not attn_weights.requires_grad and \
+            attn_weights.dtype in (torch.float16, torch.bfloat16, torch.float32):
+        from ..ops import cuda_ops
+        return cuda_ops.softmax_inplace(attn_weights)
+    return F.softmax(attn_weights, dim=-1, dtype=torch.float32).to(attn_weights.dtype)
+
+
+def repeat_kv(hidden_states: torch.Tensor, n_rep: int) -> torch.Tensor:
+    if n_rep == 1:
+        return hidden_states
+    b, h, s, d = hidden_states.shape
+    return hidden_states[:, :, None, :, :].expand(b, h, n_rep, s, d).reshape(b, h * n_rep, s, d)
+
+
+def scaled_dot_product_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                                 mask: torch.Tensor = None, is_causal: bool = False, scale: float = None,
+                                 softcap: float = None, sliding_window: int = None) -> torch.Tensor:
+    """softmax(q k^T * scale + mask) v with GQA handled inside.
+
+    ``query`` is ``[B, Hq, Sq, D]``; ``key``/``value`` are ``[B, Hkv, Skv, D]`` in the activation dtype or packed
+    e5m2 bytes (uint8).  Routing (reference models/common.py:249-305): short queries against a long cache
+    (decode, speculative verification, lookup: Sq <= 32) go to the split-KV decode kernel, which reads fp8 KV
+    directly; everything else goes to the prefill path."""
+    bsz, n_heads, q_len, head_dim = query.shape
+    kv_len = key.shape[2]
+    n_kv = key.shape[1]
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim)
+    fp8 = key.dtype == torch.uint8
+
+    if query.is_cuda and not query.requires_grad and query.dtype in (torch.float16, torch.bfloat16):
+        from ..ops import cuda_ops
+        if q_len <= 32 and cuda_ops.sdpa_decode_supported(head_dim, value.shape[-1]):
+            return cuda_ops.sdpa_decode(query, key, value, mask, scale, softcap, sliding_window,
+                                        causal=is_causal or (mask is None and q_len > 1))
+        if fp8:
+            key = fp8_e5m2_dequantize(key, query.dtype)
+            value = fp8_e5m2_dequantize(value, query.dtype)
+        return cuda_ops.sdpa_prefill(query, key, value, mask, scale, softcap, sliding_window,
+                                     causal=is_causal or (mask is None and q_len > 1))
+
+    if fp8:
+        key = fp8_e5m2_dequantize(key, query.dtype)
+        value = fp8_e5m2_dequantize(value, query.dtype)
+    key = repeat_kv(key, n_heads // n_kv)
+    value = repeat_kv(value, n_heads // n_kv)
+    if softcap is None and sliding_window is None:
+        if mask is not None:
+            mask = mask[..., :kv_len]
+            if mask.dtype != torch.bool and mask.dtype != query.dtype:
+                mask = mask.to(query.dtype)
+        return F.scaled_dot_product_attention(query, key, value, attn_mask=mask, scale=scale,
+                                              is_causal=(mask is None and q_len > 1 and q_len == kv_len))
+    # eager path (soft-capped logits, sliding window)
+    w = torch.matmul(query.float(), key.float().transpose(2, 3)) * scale
+    if softcap is not None:
+        w = torch.tanh(w / softcap) * softcap
+    if mask is not None:
+        m = mask[..., :kv_len]
+        w = w.masked_fill(~m, float("-inf")) if m.dtype == torch.bool else w + m.float()
+    else:
+        qi = torch.arange(kv_len - q_len, kv_len, device=w.device).view(-1, 1)
+        ki = torch.arange(kv_len, device=w.device).view(1, -1)
+        allowed = ki <= qi
+        if sliding_window is not None:
+            allowed = allowed & (ki > qi - sliding_window)
+        w = w.masked_fill(~allowed, float("-inf"))
+    w = torch.softmax(w, dim=-1)
+    return torch.matmul(w, value.float()).to(query.dtype)

@@ -1,0 +1,445 @@
+"""Python entry points of the sm_100a kernels (torch tensors in, torch tensors out).
+
+This is the layer the reference fills with ``xe_linear`` / ``xe_batch`` / ``xe_addons`` calls
+(python/llm/src/ipex_llm/transformers/xpu_ops.py:23-162).  Every function launches on the current CUDA stream
+through the C ABI of ``libipex_llm_cuda.so`` and raises if the library is missing — there is no eager
+fallback on a GPU.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+
+import torch
+
+from ..native import cuda_api as api
+from ..native.lib import cuda_lib, current_stream, ptr
+from ..quant import qtypes as qt
+from ..quant.params import FP4Params, get_block_size, get_type_size
+
+_NF4 = [-1.0, -0.6961928009986877, -0.5250730514526367, -0.39491748809814453, -0.28444138169288635,
+        -0.18477343022823334, -0.09105003625154495, 0.0, 0.07958029955625534, 0.16093020141124725,
+        0.24611230194568634, 0.33791524171829224, 0.44070982933044434, 0.5626170039176941,
+        0.7229568362236023, 1.0]
+_FP4 = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0]
+
+QTYPE_TO_WF = {
+    qt.SYM_INT4: api.WF_SYM_INT4, qt.ASYM_INT4: api.WF_ASYM_INT4, qt.NF4: api.WF_LUT4, qt.FP4: api.WF_LUT4,
+    qt.FP8E4: api.WF_FP8_E4M3, qt.FP8E5: api.WF_FP8_E5M2, qt.SYM_INT8: api.WF_INT8,
+}
+
+_lut_cache = {}
+_USE_PDL = os.environ.get("IPEX_LLM_PDL", "1") != "0"
+GEMV_MAX_M = 8
+_SMEM_LIMIT = 200 * 1024
+
+
+def lut_for(qtype: int, device) -> torch.Tensor | None:
+    if qtype not in (qt.NF4, qt.FP4):
+        return None
+    key = (qtype, str(device))
+    if key not in _lut_cache:
+        _lut_cache[key] = torch.tensor(_NF4 if qtype == qt.NF4 else _FP4, dtype=torch.float32, device=device)
+    return _lut_cache[key]
+
+
+def _dt(t: torch.Tensor) -> int:
+    return api.dtype_code(t.dtype)
+
+
+def is_tiled(qtype: int) -> bool:
+    return qtype in QTYPE_TO_WF
+
+
+# ------------------------------------------------------------------------------------------------
+# linear
+# ------------------------------------------------------------------------------------------------
+def gemv_lowbit(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K: int, out: torch.Tensor = None,
+                norm_weight: torch.Tensor = None, eps: float = 1e-6, norm_offset: float = 0.0,
+                bias: torch.Tensor = None, residual: torch.Tensor = None, act: int = 0, pdl: bool = False,
+                wf: int = None) -> torch.Tensor:
+    """``x [M<=8, K]`` times a tiled low-bit (or dense half) weight.  ``act``: 0 none, 1 SiLU(gate)*up,
+    2 GELU(gate)*up with gate/up row tiles interleaved in ``w_data`` (then the output has N/2 columns)."""
+    lib = cuda_lib()
+    M = x.shape[0]
+    assert 1 <= M <= GEMV_MAX_M and x.stride(-1) == 1
+    if wf is None:
+        wf = QTYPE_TO_WF[qtype]
+    n_out = N // 2 if act else N
+    if out is None:
+        out = torch.empty((M, n_out), dtype=x.dtype, device=x.device)
+    lut = lut_for(qtype, x.device) if wf == api.WF_LUT4 else None
+    rc = lib.ipex_gemv_lowbit(ptr(w_data), wf, ptr(x), ptr(out), M, N, K, x.stride(0), out.stride(0),
+                              ptr(norm_weight), eps, norm_offset, ptr(bias), ptr(residual),
+                              residual.stride(0) if residual is not None else 0, act, ptr(lut), _dt(x),
+                              int(pdl and _USE_PDL), current_stream())
+    api.check(rc, "gemv_lowbit")
+    return out
+
+
+def _gemv_rows_per_call(K: int, dtype_size: int = 2) -> int:
+    kp = (K + 127) // 128 * 128
+    return max(1, min(GEMV_MAX_M, (_SMEM_LIMIT - 8192) // ((kp + 8) * 2)))
+
+
+def lowbit_linear(x: torch.Tensor, weight: FP4Params) -> torch.Tensor:
+    """``x [M, K] @ dequant(weight).T`` for any qtype, any M."""
+    N, K = int(weight._shape[0]), int(weight._shape[1])
+    qtype = weight.qtype
+    M = x.shape[0]
+    if x.dtype == torch.float32:
+        return lowbit_linear(x.to(torch.float16), weight).to(torch.float32)
+    if is_tiled(qtype):
+        if M <= GEMV_MAX_M:
+            per = _gemv_rows_per_call(K)
+            if M <= per:
+                return gemv_lowbit(x, weight.data, qtype, N, K)
+            out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+            for s in range(0, M, per):
+                gemv_lowbit(x[s:s + per], weight.data, qtype, N, K, out=out[s:s + per])
+            return out
+        return gemm_lowbit(x, weight.data, qtype, N, K)
+    # qtypes without a tile layout: dequantize the canonical blocks, then the dense GEMM / GEMV
+    w = dequantize_device(weight.data, (N, K), qtype, x.dtype)
+    return dense_linear(x, w)
+
+
+def gemm_lowbit(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K: int, out: torch.Tensor = None,
+                bias: torch.Tensor = None, residual: torch.Tensor = None) -> torch.Tensor:
+    """M > 8: tcgen05 GEMM with in-kernel dequantization when the kernel is built; otherwise dequantize to the
+    activation dtype and run the dense tensor-core GEMM."""
+    lib = cuda_lib()
+    M = x.shape[0]
+    fn = getattr(lib, "ipex_gemm_lowbit_tcgen05", None)
+    if fn is not None and os.environ.get("IPEX_LLM_TCGEN05", "1") != "0" and x.dtype in (torch.float16, torch.bfloat16):
+        from . import tcgen05_gemm
+        if tcgen05_gemm.supported(M, N, K, qtype):
+            return tcgen05_gemm.gemm_lowbit(x, w_data, qtype, N, K, out=out, bias=bias, residual=residual)
+    w = dequantize_device(w_data, (N, K), qtype, x.dtype)
+    y = dense_linear(x, w)
+    if bias is not None:
+        y = y + bias
+    if residual is not None:
+        y = y + residual
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def dense_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x [M, K] @ w[N, K].T`` for half-precision weights: own GEMV for M <= 8, own tcgen05 GEMM above when
+    available, cuBLAS as the plain library GEMM otherwise."""
+    M, K = x.shape
+    N = w.shape[0]
+    if M <= GEMV_MAX_M and K % 64 == 0 and w.is_contiguous() and x.dtype == w.dtype and \
+            x.dtype in (torch.float16, torch.bfloat16) and M <= _gemv_rows_per_call(K):
+        wf = api.WF_F16 if w.dtype == torch.float16 else api.WF_BF16
+        return gemv_lowbit(x, w, None, N, K, wf=wf)
+    lib = cuda_lib()
+    if getattr(lib, "ipex_gemm_bf16_tcgen05", None) is not None and os.environ.get("IPEX_LLM_TCGEN05", "1") != "0":
+        from . import tcgen05_gemm
+        if tcgen05_gemm.dense_supported(M, N, K, x.dtype) and x.dtype == w.dtype:
+            return tcgen05_gemm.gemm_dense(x, w)
+    return torch.matmul(x, w.t())
+
+
+def lowbit_linear_backward(grad_output: torch.Tensor, weight: FP4Params) -> torch.Tensor:
+    """``grad_x = grad_y @ dequant(W)`` (QLoRA backward, reference low_bit_linear.py:522-540)."""
+    N, K = int(weight._shape[0]), int(weight._shape[1])
+    go = grad_output.reshape(-1, N)
+    w = dequantize_device(weight.data, (N, K), weight.qtype, go.dtype if go.dtype != torch.float32
+                          else torch.bfloat16)
+    return torch.matmul(go.to(w.dtype), w).to(grad_output.dtype).view(*grad_output.shape[:-1], K)
+
+
+def dequantize_device(w_data: torch.Tensor, shape, qtype: int, dtype=torch.float16) -> torch.Tensor:
+    """Full dense weight from device-resident packed bytes."""
+    lib = cuda_lib()
+    N, K = int(shape[0]), int(shape[1])
+    out = torch.empty((N, K), dtype=dtype, device=w_data.device)
+    if is_tiled(qtype):
+        rc = lib.ipex_dequantize_tiles(ptr(w_data), ptr(out), N, K, K, QTYPE_TO_WF[qtype],
+                                       ptr(lut_for(qtype, w_data.device)), api.dtype_code(dtype), current_stream())
+        api.check(rc, "dequantize_tiles")
+    else:
+        qk, ts = get_block_size(qtype), get_type_size(qtype)
+        raw = w_data.view(torch.uint8)
+        rc = lib.ipex_dequantize_blocks(ptr(raw), ptr(out), N * K // qk, qk, ts, qtype, api.dtype_code(dtype),
+                                        current_stream())
+        api.check(rc, "dequantize_blocks")
+    return out
+
+
+def dequantize_rows(ids: torch.Tensor, weight: FP4Params, dim: int, vocab: int, dtype) -> torch.Tensor:
+    lib = cuda_lib()
+    flat = ids.reshape(-1).to(torch.int64).contiguous()
+    out_dtype = dtype if dtype in (torch.float16, torch.bfloat16, torch.float32) else torch.float32
+    out = torch.empty((flat.numel(), dim), dtype=out_dtype, device=ids.device)
+    qk, ts = get_block_size(weight.qtype), get_type_size(weight.qtype)
+    raw = weight.data.view(torch.uint8)
+    rc = lib.ipex_dequantize_rows(ptr(flat), ptr(raw), ptr(out), flat.numel(), dim, qk, ts, weight.qtype,
+                                  api.dtype_code(out_dtype), current_stream())
+    api.check(rc, "dequantize_rows")
+    return out.view(*ids.shape, dim)
+
+
+# ------------------------------------------------------------------------------------------------
+# norms / activations / softmax / rope
+# ------------------------------------------------------------------------------------------------
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: float = 0.0, residual: torch.Tensor = None,
+             residual_out: torch.Tensor = None, pdl: bool = False) -> torch.Tensor:
+    lib = cuda_lib()
+    xc = x.contiguous()
+    H = xc.shape[-1]
+    rows = xc.numel() // H
+    out = torch.empty_like(xc)
+    w = weight if weight.dtype == xc.dtype else weight.to(xc.dtype)
+    rc = lib.ipex_rms_norm(ptr(xc), ptr(w), ptr(residual), ptr(out), ptr(residual_out), rows, H, eps, offset, _dt(xc),
+                           int(pdl and _USE_PDL), current_stream())
+    api.check(rc, "rms_norm")
+    return out
+
+
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float) -> torch.Tensor:
+    lib = cuda_lib()
+    xc = x.contiguous()
+    H = xc.shape[-1]
+    out = torch.empty_like(xc)
+    w = weight.to(xc.dtype) if weight is not None else None
+    b = bias.to(xc.dtype) if bias is not None else None
+    rc = lib.ipex_layer_norm(ptr(xc), ptr(w), ptr(b), ptr(out), xc.numel() // H, H, eps, _dt(xc), current_stream())
+    api.check(rc, "layer_norm")
+    return out
+
+
+def act_mul(gate: torch.Tensor, up: torch.Tensor, act: int) -> torch.Tensor:
+    lib = cuda_lib()
+    g, u = gate.contiguous(), up.contiguous()
+    out = torch.empty_like(g)
+    rc = lib.ipex_act_mul(ptr(g), ptr(u), ptr(out), g.numel(), act, _dt(g), 0, current_stream())
+    api.check(rc, "act_mul")
+    return out
+
+
+def softmax_inplace(x: torch.Tensor) -> torch.Tensor:
+    lib = cuda_lib()
+    cols = x.shape[-1]
+    rc = lib.ipex_softmax_inplace(ptr(x), x.numel() // cols, cols, _dt(x), current_stream())
+    api.check(rc, "softmax_inplace")
+    return x
+
+
+def rotary_inplace(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, interleaved=False):
+    """RoPE in place on ``q [B,Hq,S,D]`` / ``k [B,Hk,S,D]`` (arbitrary outer strides, unit inner stride);
+    ``cos``/``sin`` ``[B or 1, S, R]``.  Returns (q, k)."""
+    lib = cuda_lib()
+    if q.stride(-1) != 1:
+        q = q.contiguous()
+    if k.stride(-1) != 1:
+        k = k.contiguous()
+    B, Hq, S, D = q.shape
+    Hk = k.shape[1]
+    R = cos.shape[-1]
+    # transformers passes cos/sin duplicated over the two halves ([.., R] with R = rotary dim): use the first half
+    cosc = cos[..., : R // 2].contiguous() if not interleaved else cos[..., 0::2].contiguous()
+    sinc = sin[..., : R // 2].contiguous() if not interleaved else sin[..., 0::2].contiguous()
+    cs_b = cosc.stride(0) if cosc.shape[0] == B and B > 1 else 0
+    cos_dt = api.DT_F32 if cosc.dtype == torch.float32 else _dt(cosc)
+    if cos_dt != api.DT_F32 and cosc.dtype != q.dtype:
+        cosc, sinc, cos_dt = cosc.float(), sinc.float(), api.DT_F32
+    rc = lib.ipex_rope_inplace(ptr(q), ptr(k), ptr(cosc), ptr(sinc), B, Hq, Hk, S, R, q.stride(0), q.stride(1),
+                               q.stride(2), k.stride(0), k.stride(1), k.stride(2), cs_b, cosc.stride(1),
+                               int(interleaved), _dt(q), cos_dt, current_stream())
+    api.check(rc, "rope_inplace")
+    return q, k
+
+
+def quantize_kv_e5m2(x: torch.Tensor) -> torch.Tensor:
+    lib = cuda_lib()
+    xc = x.contiguous()
+    D = xc.shape[-1]
+    out = torch.empty(xc.shape, dtype=torch.uint8, device=xc.device)
+    rc = lib.ipex_kv_quant_e5m2(ptr(xc), ptr(out), xc.numel() // D, D, D, _dt(xc), current_stream())
+    api.check(rc, "kv_quant_e5m2")
+    return out
+
+
+def dequantize_kv_e5m2(x: torch.Tensor, dtype) -> torch.Tensor:
+    lib = cuda_lib()
+    D = x.shape[-1]
+    if x.stride(-1) != 1 or not _rows_uniform(x):
+        x = x.contiguous()
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    if x.is_contiguous():
+        rc = lib.ipex_kv_dequant_e5m2(ptr(x), ptr(out), x.numel() // D, D, D, api.dtype_code(dtype), current_stream())
+        api.check(rc, "kv_dequant_e5m2")
+        return out
+    # [B, H, S, D] view into a larger [B, H, cap, D] buffer: convert per (b, h) slab
+    B, H, S, _ = x.shape
+    for b in range(B):
+        for h in range(H):
+            src = x[b, h]
+            rc = lib.ipex_kv_dequant_e5m2(ptr(src), ptr(out[b, h]), S, D, src.stride(0), api.dtype_code(dtype),
+                                          current_stream())
+            api.check(rc, "kv_dequant_e5m2")
+    return out
+
+
+def _rows_uniform(x):
+    return x.dim() == 4
+
+
+def repetition_penalty_inplace(logits: torch.Tensor, input_ids: torch.Tensor, penalty: float):
+    lib = cuda_lib()
+    B, V = logits.shape
+    ids = input_ids.to(torch.int64).contiguous()
+    rc = lib.ipex_repetition_penalty(ptr(logits), ptr(ids), B, V, ids.shape[1], penalty, _dt(logits),
+                                     current_stream())
+    api.check(rc, "repetition_penalty")
+    return logits
+
+
+# ------------------------------------------------------------------------------------------------
+# attention
+# ------------------------------------------------------------------------------------------------
+_attn_ws = {}
+
+
+def sdpa_decode_supported(head_dim: int, v_head_dim: int) -> bool:
+    return head_dim == v_head_dim and head_dim in (64, 128, 256)
+
+
+def pick_nsplit(B: int, Hkv: int, kv_len: int, n_sm: int = 148) -> int:
+    ctas = max(1, B * Hkv)
+    want = max(1, (2 * n_sm) // ctas)
+    by_len = max(1, kv_len // 128)
+    return int(max(1, min(want, by_len, 64)))
+
+
+def attn_workspace(device, floats: int, ints: int):
+    """Per-device scratch of the split-KV kernel (grown on demand, tickets zeroed once)."""
+    key = str(device)
+    ws = _attn_ws.get(key)
+    if ws is None or ws[0].numel() < floats or ws[1].numel() < ints:
+        ws = (torch.empty(max(floats, 1 << 16), dtype=torch.float32, device=device),
+              torch.zeros(max(ints, 4096), dtype=torch.int32, device=device))
+        _attn_ws[key] = ws
+    return ws
+
+
+def sdpa_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask, scale: float, softcap, sliding_window,
+                causal: bool = True) -> torch.Tensor:
+    """Module-path decode attention: the cache views ``k``/``v`` ``[B,Hkv,Skv,D]`` (activation dtype or e5m2
+    bytes) already hold every token; ``q [B,Hq,Sq<=32,D]`` is already rotated."""
+    if mask is not None and (mask.dtype == torch.bool and not bool(mask.all()) or
+                             mask.dtype != torch.bool and bool((mask != 0).any()) and
+                             not _is_causal_mask(mask, q.shape[2], k.shape[2])):
+        # arbitrary masks (padding) take the generic path
+        from .kv_cache import fp8_e5m2_dequantize
+        from ..models.common import repeat_kv
+        if k.dtype == torch.uint8:
+            k, v = fp8_e5m2_dequantize(k, q.dtype), fp8_e5m2_dequantize(v, q.dtype)
+        kk, vv = repeat_kv(k, q.shape[1] // k.shape[1]), repeat_kv(v, q.shape[1] // k.shape[1])
+        m = mask[..., : k.shape[2]]
+        return torch.nn.functional.scaled_dot_product_attention(q, kk, vv, attn_mask=m.to(q.dtype) if
+                                                                m.dtype != torch.bool else m, scale=scale)
+    lib = cuda_lib()
+    B, Hq, Sq, D = q.shape
+    Hkv, Skv = k.shape[1], k.shape[2]
+    fp8 = k.dtype == torch.uint8
+    if k.stride(-1) != 1 or v.stride(-1) != 1 or k.stride() != v.stride():
+        k, v = k.contiguous(), v.contiguous()
+    if q.stride(-1) != 1:
+        q = q.contiguous()
+    out = torch.empty((B, Sq, Hq, D), dtype=q.dtype, device=q.device)
+    nsplit = pick_nsplit(B, Hkv, Skv)
+    G = Hq // Hkv
+    floats = lib.ipex_attn_decode_scratch_floats(B, Hkv, G, Sq, D, nsplit)
+    ints = lib.ipex_attn_decode_counter_ints(B, Hkv, G, Sq)
+    scratch, counters = attn_workspace(q.device, floats, ints)
+    strides = (ctypes.c_int64 * 12)(q.stride(0), q.stride(2), q.stride(1), 0, 0, 0,
+                                    k.stride(0), k.stride(1), k.stride(2),
+                                    out.stride(0), out.stride(1), out.stride(2))
+    rc = lib.ipex_attn_decode(ptr(q), None, None, ptr(k), ptr(v), ptr(out), None, Skv, None, None, ptr(scratch),
+                              ptr(counters), strides, B, Sq, Hq, Hkv, D, nsplit, 0, 0, int(causal),
+                              int(sliding_window or 0), float(scale), float(softcap or 0.0), int(fp8), _dt(q), 0,
+                              current_stream())
+    api.check(rc, "attn_decode")
+    return out.transpose(1, 2)
+
+
+def _is_causal_mask(mask, q_len, kv_len) -> bool:
+    """True when an additive/bool mask is exactly the causal pattern for the last ``q_len`` positions."""
+    m = mask[..., :kv_len]
+    if m.shape[-2] != q_len:
+        return False
+    allowed = (m if m.dtype == torch.bool else (m == 0))
+    qi = torch.arange(kv_len - q_len, kv_len, device=m.device).view(-1, 1)
+    ki = torch.arange(kv_len, device=m.device).view(1, -1)
+    return bool((allowed == (ki <= qi)).all())
+
+
+def sdpa_prefill(q, k, v, mask, scale, softcap, sliding_window, causal=True):
+    """Prefill attention.  Uses the package's tcgen05 flash kernel when built and applicable; otherwise the
+    library SDPA (flash) on repeated KV heads — the same fallback the reference takes off its own device
+    (models/common.py:288-305)."""
+    from ..models.common import repeat_kv
+    n_rep = q.shape[1] // k.shape[1]
+    if softcap or sliding_window:
+        kk, vv = repeat_kv(k, n_rep), repeat_kv(v, n_rep)
+        w = torch.matmul(q, kk.transpose(2, 3)).float() * scale
+        if softcap:
+            w = torch.tanh(w / softcap) * softcap
+        q_len, kv_len = q.shape[2], k.shape[2]
+        if mask is not None:
+            m = mask[..., :kv_len]
+            w = w.masked_fill(~m, float("-inf")) if m.dtype == torch.bool else w + m.float()
+        else:
+            qi = torch.arange(kv_len - q_len, kv_len, device=w.device).view(-1, 1)
+            ki = torch.arange(kv_len, device=w.device).view(1, -1)
+            allowed = ki <= qi if causal else torch.ones_like(ki <= qi)
+            if sliding_window:
+                allowed = allowed & (ki > qi - sliding_window)
+            w = w.masked_fill(~allowed, float("-inf"))
+        return torch.matmul(torch.softmax(w, dim=-1).to(q.dtype), vv)
+    if mask is not None:
+        m = mask[..., : k.shape[2]]
+        if m.dtype != torch.bool and m.dtype != q.dtype:
+            m = m.to(q.dtype)
+        return torch.nn.functional.scaled_dot_product_attention(q, k, v, attn_mask=m, scale=scale,
+                                                                enable_gqa=n_rep > 1)
+    return torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=causal and q.shape[2] > 1,
+                                                            scale=scale, enable_gqa=n_rep > 1)
+
+
+# ------------------------------------------------------------------------------------------------
+# MoE (the fused kernels register themselves here when built)
+# ------------------------------------------------------------------------------------------------
+def moe_supported(experts) -> bool:
+    return False
+
+
+def moe_softmax_topk(router_logits, top_k, renormalize):
+    lib = cuda_lib()
+    fn = getattr(lib, "ipex_moe_softmax_topk", None)
+    T, E = router_logits.shape
+    if fn is None or E > 256 or top_k > 8:
+        probs = torch.softmax(router_logits.float(), dim=-1)
+        w, idx = torch.topk(probs, top_k, dim=-1)
+        if renormalize:
+            w = w / w.sum(dim=-1, keepdim=True)
+        return probs, w, idx
+    logits = router_logits.contiguous()
+    probs = torch.empty((T, E), dtype=torch.float32, device=logits.device)
+    w = torch.empty((T, top_k), dtype=torch.float32, device=logits.device)
+    idx = torch.empty((T, top_k), dtype=torch.int64, device=logits.device)
+    rc = fn(ptr(logits), ptr(probs), ptr(w), ptr(idx), T, E, top_k, int(renormalize), _dt(logits), current_stream())
+    api.check(rc, "moe_softmax_topk")
+    return probs, w, idx
+
+
+def moe_group_topk(scores, bias, n_group, topk_group, top_k, norm_topk_prob, routed_scaling_factor):
+    from .moe import moe_group_topk as ref
+    return ref(scores.cpu(), bias.cpu(), n_group, topk_group, top_k, norm_topk_prob, routed_scaling_factor)

@@ -1,0 +1,237 @@
+"""CPU plumbing: tiny Llama through the public API (from_pretrained / generate / save_low_bit / load_low_bit /
+optimize_model), family forward replacements, caches."""
+import json
+import os
+
+import pytest
+import torch
+
+
+def _cos(a, b):
+    return torch.nn.functional.cosine_similarity(a.flatten().float(), b.flatten().float(), dim=0).item()
+
+
+@pytest.fixture(scope="module")
+def fp32_model(tiny_llama_dir):
+    from transformers import LlamaForCausalLM
+    return LlamaForCausalLM.from_pretrained(tiny_llama_dir).eval()
+
+
+@pytest.fixture(scope="module")
+def int4_model(tiny_llama_dir):
+    from ipex_llm.transformers import AutoModelForCausalLM
+    return AutoModelForCausalLM.from_pretrained(tiny_llama_dir, load_in_4bit=True)
+
+
+def test_conversion_structure(int4_model):
+    from ipex_llm_b200.ops.linear import LowBitLinear
+    attn = int4_model.model.layers[0].self_attn
+    assert isinstance(attn.qkv_proj, LowBitLinear) and not hasattr(attn, "q_proj")
+    assert attn.qkv_proj.out_len == 768 and attn.qkv_proj.weight.data.dtype == torch.uint8
+    # K = 688 is not a multiple of 64: the layer stays unquantized (reference convert.py:611-613)
+    assert type(int4_model.model.layers[0].mlp.down_proj) is torch.nn.Linear
+    assert isinstance(int4_model.lm_head, LowBitLinear) and int4_model.lm_head.optimize_lm_head
+    assert int4_model.config.bigdl_transformers_low_bit == "sym_int4"
+
+
+def test_logits_vs_fp32(int4_model, fp32_model, tiny_llama_dir):
+    from ipex_llm.transformers import AutoModelForCausalLM
+    torch.manual_seed(0)
+    ids = torch.randint(0, 32000, (1, 32))
+    os.environ["IPEX_LLM_LAST_LM_HEAD"] = "0"
+    try:
+        with torch.no_grad():
+            ref = fp32_model(ids).logits
+            out = int4_model(ids).logits
+            # an unquantized random-weight model amplifies 4-bit noise layer by layer (there is no learned
+            # structure to average it out): the same weights in 8 bits must be near exact, 4 bits well aligned
+            int8 = AutoModelForCausalLM.from_pretrained(tiny_llama_dir, load_in_low_bit="sym_int8")
+            out8 = int8(ids).logits
+    finally:
+        os.environ.pop("IPEX_LLM_LAST_LM_HEAD")
+    assert out.shape == ref.shape
+    assert _cos(ref, out8) > 0.999
+    assert _cos(ref, out) > 0.95
+    # against an fp32 model that holds exactly the dequantized weights the converted model must agree (> 0.99
+    # with a wide margin): the forward replacements and the low-bit matmul add no error of their own
+    import copy
+    deq = copy.deepcopy(fp32_model)
+    for (n, mod) in int4_model.named_modules():
+        if hasattr(mod, "weight") and getattr(mod.weight, "quantized", False):
+            w = mod.weight.dequantize()
+            if n.endswith("qkv_proj"):
+                parent = deq.get_submodule(n.rsplit(".", 1)[0])
+                q, k, v = w.split([256, 256, 256], dim=0)
+                parent.q_proj.weight.data, parent.k_proj.weight.data, parent.v_proj.weight.data = q, k, v
+            else:
+                deq.get_submodule(n).weight.data = w
+    with torch.no_grad():
+        ref_deq = deq(ids).logits
+    assert _cos(ref_deq[:, -1], int4_model(ids).logits[:, -1]) > 0.9999
+
+
+def test_generate_32_tokens_matches_dequantized_reference(int4_model):
+    torch.manual_seed(1)
+    ids = torch.randint(0, 32000, (1, 32))
+    out = int4_model.generate(ids, max_new_tokens=32, do_sample=False)
+    assert out.shape == (1, 64)
+    again = int4_model.generate(ids, max_new_tokens=32, do_sample=False)
+    assert torch.equal(out, again)
+
+
+def test_save_load_low_bit_roundtrip(int4_model, tmp_path):
+    from ipex_llm.transformers import AutoModelForCausalLM
+    d = str(tmp_path / "lowbit")
+    int4_model.save_low_bit(d)
+    for f in ("pytorch_model.bin", "config.json", "load_keys.json", "generation_config.json"):
+        assert os.path.exists(os.path.join(d, f)), f
+    cfg = json.load(open(os.path.join(d, "config.json")))
+    assert cfg["bigdl_transformers_low_bit"] == "sym_int4" and cfg["tie_word_embeddings"] is False
+    keys = json.load(open(os.path.join(d, "load_keys.json")))["all_checkpoint_keys"]
+    assert "model.layers.0.self_attn.qkv_proj.weight" in keys
+    sd = torch.load(os.path.join(d, "pytorch_model.bin"), weights_only=True)
+    w = sd["model.layers.0.self_attn.qkv_proj.weight"]
+    assert w.dtype == torch.uint8 and w.dim() == 1 and w.numel() == 768 * 256 // 64 * 34
+    loaded = AutoModelForCausalLM.load_low_bit(d)
+    ids = torch.randint(0, 32000, (1, 16))
+    with torch.no_grad():
+        assert torch.equal(int4_model(ids).logits, loaded(ids).logits)
+    with pytest.raises(RuntimeError):
+        AutoModelForCausalLM.from_pretrained(d, load_in_4bit=True)   # low-bit dirs go through load_low_bit
+
+
+def test_load_low_bit_detects_missing_shard(int4_model, tmp_path):
+    from ipex_llm.transformers import AutoModelForCausalLM
+    d = str(tmp_path / "sharded")
+    int4_model.save_low_bit(d, max_shard_size="4MB")
+    idx = json.load(open(os.path.join(d, "pytorch_model.bin.index.json")))
+    files = sorted(set(idx["weight_map"].values()))
+    assert len(files) > 1
+    loaded = AutoModelForCausalLM.load_low_bit(d)
+    ids = torch.randint(0, 32000, (1, 8))
+    with torch.no_grad():
+        assert torch.equal(int4_model(ids).logits, loaded(ids).logits)
+    os.remove(os.path.join(d, files[0]))
+    with pytest.raises(RuntimeError):
+        AutoModelForCausalLM.load_low_bit(d)
+
+
+def test_optimize_model_api_and_low_memory_init(fp32_model, tmp_path):
+    import copy
+    from ipex_llm import optimize_model
+    from ipex_llm.optimize import load_low_bit, low_memory_init
+    m = optimize_model(copy.deepcopy(fp32_model), low_bit="sym_int8")
+    d = str(tmp_path / "opt")
+    m.save_low_bit(d)
+    assert json.load(open(os.path.join(d, "bigdl_config.json")))["bigdl_transformers_low_bit"] == "sym_int8"
+    from transformers import LlamaForCausalLM
+    with low_memory_init():
+        shell = LlamaForCausalLM(fp32_model.config)
+    assert next(shell.parameters()).device.type == "meta"
+    m2 = load_low_bit(shell, d)
+    ids = torch.randint(0, 32000, (1, 12))
+    with torch.no_grad():
+        assert torch.allclose(m(ids).logits, m2(ids).logits, atol=1e-5)
+
+
+def test_optimize_model_true_vs_false(tiny_llama_dir):
+    """Forward replacements must not change the numerics of the low-bit model (reference test:
+    test_transformers_api.py:151-169, mean relative difference < 5%)."""
+    from ipex_llm.transformers import AutoModelForCausalLM
+    a = AutoModelForCausalLM.from_pretrained(tiny_llama_dir, load_in_low_bit="sym_int8", optimize_model=True)
+    b = AutoModelForCausalLM.from_pretrained(tiny_llama_dir, load_in_low_bit="sym_int8", optimize_model=False)
+    ids = torch.randint(0, 32000, (2, 24))
+    with torch.no_grad():
+        la, lb = a(ids).logits, b(ids).logits
+    la = la[:, -1] if la.shape[1] == 1 else la[:, -1]
+    lb = lb[:, -1]
+    assert _cos(la, lb) > 0.9999
+
+
+def test_modules_to_not_convert_and_mixed_precision(tiny_llama_dir):
+    from ipex_llm.transformers import AutoModelForCausalLM
+    from ipex_llm_b200.ops.linear import LowBitLinear
+    from ipex_llm_b200.quant import qtypes as qt
+    m = AutoModelForCausalLM.from_pretrained(tiny_llama_dir, load_in_4bit=True, modules_to_not_convert=["lm_head", "o_proj"])
+    assert type(m.lm_head) is torch.nn.Linear
+    assert type(m.model.layers[0].self_attn.o_proj) is torch.nn.Linear
+    m = AutoModelForCausalLM.from_pretrained(tiny_llama_dir, load_in_4bit=True, mixed_precision=True)
+    assert isinstance(m.lm_head, LowBitLinear) and m.lm_head.weight.qtype == qt.Q6_K
+
+
+FAMILY_CONFIGS = {
+    "mistral": ("MistralConfig", dict(sliding_window=None)),
+    "qwen2": ("Qwen2Config", dict()),
+    "qwen3": ("Qwen3Config", dict(head_dim=32)),
+    "gemma": ("GemmaConfig", dict(head_dim=32)),
+    "gemma2": ("Gemma2Config", dict(head_dim=32, sliding_window=16, query_pre_attn_scalar=32)),
+    "phi3": ("Phi3Config", dict(pad_token_id=0)),
+    "mixtral": ("MixtralConfig", dict(num_local_experts=4, num_experts_per_tok=2)),
+    "qwen2_moe": ("Qwen2MoeConfig", dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=128,
+                                        shared_expert_intermediate_size=128)),
+}
+
+
+@pytest.mark.parametrize("family", list(FAMILY_CONFIGS))
+def test_family_forward_replacement(family):
+    """optimize_model on/off agree for every registered family (tiny random model, 8-bit weights)."""
+    import copy
+    import transformers
+    from ipex_llm import optimize_model
+    cls_name, extra = FAMILY_CONFIGS[family]
+    cfg = getattr(transformers, cls_name)(hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                                          num_attention_heads=4, num_key_value_heads=2, vocab_size=1000,
+                                          max_position_embeddings=256, **extra)
+    torch.manual_seed(0)
+    base = transformers.AutoModelForCausalLM.from_config(cfg).eval()
+    a = optimize_model(copy.deepcopy(base), low_bit="sym_int8", optimize_llm=True)
+    b = optimize_model(copy.deepcopy(base), low_bit="sym_int8", optimize_llm=False)
+    ids = torch.randint(0, 1000, (2, 20))
+    with torch.no_grad():
+        la, lb = a(ids).logits[:, -1], b(ids).logits[:, -1]
+        ref = base(ids).logits[:, -1]
+    assert _cos(la, lb) > 0.9995, family
+    assert _cos(la, ref) > 0.99, family
+    # incremental decoding through the package's caches agrees with a full forward
+    out = a.generate(ids, max_new_tokens=4, do_sample=False)
+    with torch.no_grad():
+        full = a(out[:, :-1]).logits[:, -1].argmax(-1)
+    assert torch.equal(full, out[:, -1]), family
+
+
+def test_kv_caches():
+    from ipex_llm_b200.ops.kv_cache import (DynamicCompressCache, DynamicFp8Cache, DynamicNormalCache,
+                                            fp8_e5m2_dequantize)
+    c = DynamicNormalCache()
+    k, v = torch.randn(1, 2, 5, 16), torch.randn(1, 2, 5, 16)
+    kk, vv = c.update(k, v, 0)
+    assert kk.shape == (1, 2, 5, 16) and c.get_seq_length() == 5
+    kk, _ = c.update(k[:, :, :1], v[:, :, :1], 0)
+    assert kk.shape[2] == 6 and torch.equal(kk[:, :, :5], k)
+    storage = c.layers[0]._k
+    c.crop(4)
+    assert c.get_seq_length() == 4 and c.layers[0]._k is storage      # O(1) crop keeps the allocation
+    c.update(k[:, :, :3], v[:, :, :3], 0)
+    assert c.get_seq_length() == 7
+    f = DynamicFp8Cache()
+    kq, vq = f.update(k, v, 0)
+    assert kq.dtype == torch.uint8
+    assert torch.allclose(fp8_e5m2_dequantize(kq, torch.float32), k, atol=0.13, rtol=0.13)
+    s = DynamicCompressCache()
+    q = torch.randn(1, 2, 2000, 16)
+    kl, vl = torch.randn(1, 2, 2000, 16), torch.randn(1, 2, 2000, 16)
+    s.layers.append(s.layer_class_to_replicate())
+    k_ret, _ = s.update(kl, vl, 0, query_states=q, attention_mask=None, num_key_value_groups=1)
+    assert k_ret.shape[2] == 2000 and s.get_seq_length() == 1024 and s.real_kv_len == 2000
+
+
+def test_env_flags(monkeypatch):
+    from ipex_llm_b200 import config as cfg
+    monkeypatch.setenv("IPEX_LLM_QUANTIZE_KV_CACHE", "1")
+    assert cfg.quantize_kv_cache_flag() is True
+    monkeypatch.setenv("IPEX_LLM_QUANTIZE_KV_CACHE", "0")
+    assert cfg.quantize_kv_cache_flag() is False
+    monkeypatch.delenv("IPEX_LLM_QUANTIZE_KV_CACHE")
+    assert cfg.quantize_kv_cache_flag() is None
+    monkeypatch.setenv("IPEX_LLM_LOW_MEM", "1")
+    assert cfg.low_mem()
