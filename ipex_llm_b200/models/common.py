@@ -157,8 +157,9 @@ def apply_rotary_pos_emb(q, k, cos, sin, unsqueeze_dim=1, interleaved=False):
         if interleaved:
             x1 = xr[..., 0::2]
             x2 = xr[..., 1::2]
-            c = cos[..., : rot // 2]
-            s = sin[..., : rot // 2]
+            # GPT-J tables repeat every frequency twice (f0, f0, f1, f1, ...): take one of each pair
+            c = cos[..., 0::2]
+            s = sin[..., 0::2]
             o = torch.stack((x1 * c - x2 * s, x2 * c + x1 * s), dim=-1).flatten(-2)
         else:
             o = xr * cos + rotate_half(xr) * sin

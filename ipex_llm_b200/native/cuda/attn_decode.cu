@@ -56,49 +56,51 @@ __device__ __forceinline__ uint8_t to_e5m2(float v) {
 }
 __device__ __forceinline__ float from_e5m2(uint8_t b) { return __half2float(__ushort_as_half((uint16_t)b << 8)); }
 
-// load DPL consecutive cache elements as floats
+// DPL consecutive cache elements of one token held as raw 32-bit words (loaded early, decoded late)
 template <typename T, bool FP8, int DPL>
-__device__ __forceinline__ void load_kv(const void* base, int64_t elem_off, float (&out)[DPL]) {
-  if constexpr (FP8) {
-    const uint8_t* p = reinterpret_cast<const uint8_t*>(base) + elem_off;
-    if constexpr (DPL % 16 == 0) {
+struct RawKV {
+  static constexpr int kBytes = FP8 ? DPL : DPL * 2;
+  static constexpr int kWords = kBytes / 4;
+  static_assert(kBytes % 8 == 0, "unsupported head dim");
+  uint32_t w[kWords];
+
+  __device__ __forceinline__ void load(const void* base, int64_t elem_off) {
+    const uint8_t* p = reinterpret_cast<const uint8_t*>(base) + elem_off * (FP8 ? 1 : 2);
+    if constexpr (kBytes % 16 == 0) {
 #pragma unroll
-      for (int i = 0; i < DPL / 16; i++) {
-        uint4 v = *reinterpret_cast<const uint4*>(p + 16 * i);
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-          // two bytes -> half2 by moving each byte to the upper byte of a 16-bit lane
-          uint32_t lo = __byte_perm(w[j], 0, 0x1404), hi = __byte_perm(w[j], 0, 0x3424);
-          float2 a = __half22float2(*reinterpret_cast<__half2*>(&lo));
-          float2 b = __half22float2(*reinterpret_cast<__half2*>(&hi));
-          out[16 * i + 4 * j + 0] = a.x; out[16 * i + 4 * j + 1] = a.y;
-          out[16 * i + 4 * j + 2] = b.x; out[16 * i + 4 * j + 3] = b.y;
-        }
+      for (int i = 0; i < kBytes / 16; i++) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p + 16 * i);
+        w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
       }
     } else {
-      uint2 v = *reinterpret_cast<const uint2*>(p);
-      static_assert(DPL == 8 || DPL % 16 == 0, "unsupported head dim");
-      const uint32_t w[2] = {v.x, v.y};
 #pragma unroll
-      for (int j = 0; j < 2; j++) {
-        uint32_t lo = __byte_perm(w[j], 0, 0x1404), hi = __byte_perm(w[j], 0, 0x3424);
-        float2 a = __half22float2(*reinterpret_cast<__half2*>(&lo));
-        float2 b = __half22float2(*reinterpret_cast<__half2*>(&hi));
-        out[4 * j + 0] = a.x; out[4 * j + 1] = a.y; out[4 * j + 2] = b.x; out[4 * j + 3] = b.y;
+      for (int i = 0; i < kBytes / 8; i++) {
+        const uint2 v = *reinterpret_cast<const uint2*>(p + 8 * i);
+        w[2 * i] = v.x; w[2 * i + 1] = v.y;
       }
     }
-  } else {
-    const T* p = reinterpret_cast<const T*>(base) + elem_off;
+  }
+
+  __device__ __forceinline__ void decode(float (&out)[DPL]) const {
+    if constexpr (FP8) {
 #pragma unroll
-    for (int i = 0; i < DPL / 8; i++) {
-      uint4 v = *reinterpret_cast<const uint4*>(p + 8 * i);
-      const T* e = reinterpret_cast<const T*>(&v);
+      for (int j = 0; j < kWords; j++) {
+        // e5m2 byte -> fp16 by moving it to the upper byte of a 16-bit lane
+        uint32_t lo = __byte_perm(w[j], 0, 0x1404), hi = __byte_perm(w[j], 0, 0x3424);
+        const float2 a = __half22float2(*reinterpret_cast<__half2*>(&lo));
+        const float2 b = __half22float2(*reinterpret_cast<__half2*>(&hi));
+        out[4 * j + 0] = a.x; out[4 * j + 1] = a.y; out[4 * j + 2] = b.x; out[4 * j + 3] = b.y;
+      }
+    } else {
 #pragma unroll
-      for (int j = 0; j < 8; j++) out[8 * i + j] = DT<T>::to_f(e[j]);
+      for (int j = 0; j < kWords; j++) {
+        const T* e = reinterpret_cast<const T*>(&w[j]);
+        out[2 * j] = DT<T>::to_f(e[0]);
+        out[2 * j + 1] = DT<T>::to_f(e[1]);
+      }
     }
   }
-}
+};
 
 template <typename T, bool FP8, int D, int RW>
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
@@ -269,18 +271,34 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     const uint8_t* kc = reinterpret_cast<const uint8_t*>(a.kcache);
     const uint8_t* vc = reinterpret_cast<const uint8_t*>(a.vcache);
     const int64_t head_off = b * a.c_b + (int64_t)kvh * a.c_h + ds * DPL;
-    for (int base = t0 + tsub * 4; base < t1; base += 4 * TS) {
+    // two-deep software pipeline on the raw cache words: the loads of step i+1 are in flight while step i
+    // goes through the (serial) online-softmax update
+    RawKV<T, FP8, DPL> kr, vr, kn, vn;
+    int base = t0 + tsub * 4;
+    if (base + tg < t1) {
+      kr.load(kc, head_off + (int64_t)(base + tg) * a.c_s);
+      vr.load(vc, head_off + (int64_t)(base + tg) * a.c_s);
+    }
+    while (base < t1) {
+      const int nbase = base + 4 * TS;
+      if (nbase + tg < t1) {
+        kn.load(kc, head_off + (int64_t)(nbase + tg) * a.c_s);
+        vn.load(vc, head_off + (int64_t)(nbase + tg) * a.c_s);
+      }
       const int pos = base + tg;
       const bool valid = pos < t1;
       float kf[DPL], vf[DPL];
       if (valid) {
-        load_kv<T, FP8, DPL>(kc, head_off + (int64_t)pos * a.c_s, kf);
-        load_kv<T, FP8, DPL>(vc, head_off + (int64_t)pos * a.c_s, vf);
+        kr.decode(kf);
+        vr.decode(vf);
       } else {
 #pragma unroll
         for (int d = 0; d < DPL; d++) { kf[d] = 0.f; vf[d] = 0.f; }
       }
       consume(kf, vf, pos, valid);
+      kr = kn;
+      vr = vn;
+      base = nbase;
     }
   }
   // ---- new tokens (mode A, last split) from shared memory ----

@@ -1,0 +1,644 @@
+// Low-bit GEMV / skinny GEMM for decode (M <= 8), bulk-async (TMA) pipelined version, sm_100a.
+//
+// Same contract as gemv_lowbit.cu (y = epilogue(prologue(x) * dequant(W)^T), tile layout of
+// native/host/quant_core.cpp), different data movement.  Decode GEMVs of a 7B model stream 8-45 MB each and
+// last only microseconds, so a kernel that starts loading when its warps are ready to compute spends most of
+// its life waiting for the first bytes.  Here
+//   * a producer warp streams the CTA's weight tiles with cp.async.bulk (global -> shared, completion on an
+//     mbarrier) through a ring of stages; a row tile's K chunks are contiguous in the tile layout, so one
+//     bulk copy moves up to 16 chunks (16 KB of 4-bit codes) plus one copy for their scales;
+//   * the producer never waits for the previous kernel (weights do not depend on it): with programmatic
+//     dependent launch the ring is already full when griddepcontrol.wait returns and the consumers have
+//     finished staging / normalising x;
+//   * sixteen consumer warps split the chunks of a stage, run the fragment-order mma pipeline straight out of
+//     shared memory (4-bit codes become fp16 operands with ONE logic op per pair: the constant offsets are
+//     removed from the fp32 accumulator once per 64-group), and release the stage through an "empty" mbarrier;
+//   * CTAs are persistent over row-tile groups, so x is staged (and RMS-normalised) once per CTA.
+// Every mbarrier wait is bounded; on expiry the kernel records an error code in *err and leaves.
+#include "common/utils.cuh"
+#include <cuda_fp8.h>
+
+namespace {
+
+constexpr int kCW = 16;                      // consumer warps
+constexpr int kCThreads = kCW * 32;          // 512
+constexpr int kThreadsTma = kCThreads + 32;  // + producer warp
+constexpr int kSpinLimit = 1 << 22;
+constexpr int kNB = 4;                        // reduction buffers in flight
+
+struct TmaArgs {
+  const uint8_t* w;
+  const void* x;
+  void* y;
+  const void* norm_w;
+  const void* bias;
+  const void* residual;
+  const float* lut;
+  int* err;
+  int M, N, K;
+  int ldx, ldy, ldr;
+  float eps, norm_offset;
+  int act;
+  int stages;  // ring depth
+  int cps;     // chunks (of 128 k) per stage
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// bounded wait for the phase with the given parity; false on expiry
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  uint32_t done = 0;
+  for (int i = 0; i < kSpinLimit; i++) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    // back off: a waiting warp must not eat the issue slots of the warps that have data
+    if (i >= 2) __nanosleep(i < 32 ? 32 : 128);
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kCThreads) : "memory"); }
+
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("sub.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+// word = 8 nibbles in magic order -> four fp16x2 operands WITHOUT removing the offsets:
+//   p[0], p[2] = 1024 + q      (weights 0,1 and 4,5 of the octet)
+//   p[1], p[3] = 1024 + 16 q   (weights 2,3 and 6,7)
+// The activations paired with p[1]/p[3] are stored pre-divided by 16, and the constant parts
+// (1024 + zero point) * x are removed once per 64-group from the fp32 accumulator (see xcorr), so the
+// dequantization costs one logic op per pair instead of a logic op and a floating point op.
+struct Int4Raw {
+  uint32_t p[4];
+  __device__ __forceinline__ explicit Int4Raw(uint32_t u) {
+    constexpr uint32_t kMagic = 0x64006400u;
+    const uint32_t u2 = u >> 8;
+    p[0] = (u & 0x000F000Fu) | kMagic;
+    p[1] = (u & 0x00F000F0u) | kMagic;
+    p[2] = (u2 & 0x000F000Fu) | kMagic;
+    p[3] = (u2 & 0x00F000F0u) | kMagic;
+  }
+};
+
+__device__ __forceinline__ float act_apply(float g, int act) {
+  if (act == 1) return g / (1.0f + __expf(-g));
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  return 0.5f * g * (1.0f + tanhf(k0 * (g + k1 * g * g * g)));
+}
+
+// x -> fp16 rows in shared memory (optionally RMS-normalised), zero padded to Kp; consumer threads only
+template <typename T, bool PRESCALE>
+__device__ void stage_x(const TmaArgs& a, __half* xs, int xs_stride, int Kp, float* scratch) {
+  const int tid = threadIdx.x;
+  const T* x = reinterpret_cast<const T*>(a.x);
+  const T* nw = reinterpret_cast<const T*>(a.norm_w);
+  const int nvec = a.K / 8;  // K % 64 == 0
+  for (int m = 0; m < a.M; m++) {
+    const T* xr = x + (size_t)m * a.ldx;
+    float rstd = 1.0f;
+    if (nw != nullptr) {
+      float ss = 0.f;
+      for (int v = tid; v < nvec; v += kCThreads) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(xr + v * 8);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 8; j++) { const float f = DT<T>::to_f(e[j]); ss += f * f; }
+      }
+      ss = warp_sum(ss);
+      if ((tid & 31) == 0) scratch[tid >> 5] = ss;
+      consumer_sync();
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < kCW; w++) tot += scratch[w];
+      rstd = rsqrtf(tot / (float)a.K + a.eps);
+      consumer_sync();
+    }
+    for (int v = tid; v < Kp / 8; v += kCThreads) {
+      __align__(16) __half o[8];
+      if (v < nvec) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(xr + v * 8);
+        const T* e = reinterpret_cast<const T*>(&raw);
+        uint4 wraw = make_uint4(0, 0, 0, 0);
+        if (nw != nullptr) wraw = *reinterpret_cast<const uint4*>(nw + v * 8);
+        const T* we = reinterpret_cast<const T*>(&wraw);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          float f = DT<T>::to_f(e[j]);
+          if (nw != nullptr) f = f * rstd * (DT<T>::to_f(we[j]) + a.norm_offset);
+          f = fminf(fmaxf(f, -65504.f), 65504.f);
+          if (PRESCALE && (j & 2)) f *= 0.0625f;   // partners of the "1024 + 16 q" operands
+          o[j] = __float2half_rn(f);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; j++) o[j] = __float2half_rn(0.f);
+      }
+      *reinterpret_cast<uint4*>(xs + m * xs_stride + v * 8) = *reinterpret_cast<const uint4*>(o);
+    }
+  }
+}
+
+template <int WF, typename T, int RT>
+__global__ void __launch_bounds__(kThreadsTma, 1) gemv_tma_kernel(TmaArgs a) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  constexpr bool k4bit = WF == WF_SYM_INT4 || WF == WF_ASYM_INT4 || WF == WF_LUT4;
+  constexpr int CB = k4bit ? 1024 : 2048;                 // code bytes per 128-k chunk of a row tile
+  constexpr int SB = 64;                                  // scale bytes per chunk
+  constexpr int MB = WF == WF_ASYM_INT4 ? 64 : 0;         // min bytes per chunk
+  const int Kp = (int)ceil_to_i64(a.K, 128);
+  const int Np = (int)ceil_to_i64(a.N, 16);
+  const int chunks = Kp / 128;
+  const int xs_stride = Kp + 8;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int STAGES = a.stages, CPS = a.cps;
+  const int stage_bytes = CPS * (CB + SB + MB);
+  const int stages_per_tile = (chunks + CPS - 1) / CPS;
+  const int ntiles = Np / 16;
+  const int ngroups = (ntiles + RT - 1) / RT;
+
+  // shared memory carve-up (the ring first: bulk copies need 16-byte alignment, it gets 128)
+  uint8_t* ring = smem_raw;
+  size_t off = (size_t)STAGES * stage_bytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem_raw + off);
+  uint64_t* empty_bar = full_bar + STAGES;
+  off += (size_t)2 * STAGES * sizeof(uint64_t);
+  off = (off + 15) & ~(size_t)15;
+  __half* xs = reinterpret_cast<__half*>(smem_raw + off);
+  off += ((size_t)a.M * xs_stride * sizeof(__half) + 15) & ~(size_t)15;
+  float* red = reinterpret_cast<float*>(smem_raw + off);      // [kNB][RT][16][8], zero between uses
+  off += (size_t)kNB * RT * 128 * sizeof(float);
+  int* red_cnt = reinterpret_cast<int*>(smem_raw + off);      // [kNB] tickets
+  int* red_gen = red_cnt + kNB;                                // [kNB] generations
+  off += 2 * kNB * sizeof(int);
+  float* scratch = reinterpret_cast<float*>(smem_raw + off);
+  off += 64;
+  float* xcorr = reinterpret_cast<float*>(smem_raw + off);     // int4: [M][Kp/64]
+  if (WF == WF_SYM_INT4 || WF == WF_ASYM_INT4) off += (size_t)a.M * (Kp / 64) * sizeof(float);
+  float* xsum = reinterpret_cast<float*>(smem_raw + off);      // asym: [M][Kp/64]
+  if (WF == WF_ASYM_INT4) off += (size_t)a.M * (Kp / 64) * sizeof(float);
+  uint32_t* lut256 = reinterpret_cast<uint32_t*>(smem_raw + off);
+
+  const uint8_t* codes = a.w;
+  const size_t code_bytes = k4bit ? (size_t)Np * Kp / 2 : (size_t)Np * Kp;
+  const uint8_t* scales = a.w + code_bytes;
+  const uint8_t* mins = scales + (size_t)Np * (Kp / 64) * 2;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kCW);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+
+  if (warp == kCW) {
+    // ---------------- producer: independent of the previous kernel, starts immediately ----------------
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int grp = blockIdx.x; grp < ngroups && ok; grp += gridDim.x) {
+        for (int r = 0; r < RT && ok; r++) {
+          const int tile = grp * RT + r;
+          if (tile >= ntiles) break;
+          for (int sp = 0; sp < stages_per_tile; sp++, it++) {
+            const int slot = it % STAGES;
+            if (it >= STAGES) {
+              if (!mbar_wait(&empty_bar[slot], ((it / STAGES) - 1) & 1)) {
+                atomicExch(a.err, 1);
+                ok = false;
+                break;
+              }
+            }
+            const int c0 = sp * CPS;
+            const int nch = min(CPS, chunks - c0);
+            uint8_t* dst = ring + (size_t)slot * stage_bytes;
+            mbar_expect_tx(&full_bar[slot], (uint32_t)(nch * (CB + SB + MB)));
+            const size_t chunk_index = (size_t)tile * chunks + c0;
+            bulk_g2s(dst, codes + chunk_index * CB, (uint32_t)(nch * CB), &full_bar[slot]);
+            bulk_g2s(dst + CPS * CB, scales + chunk_index * SB, (uint32_t)(nch * SB), &full_bar[slot]);
+            if (MB) bulk_g2s(dst + CPS * (CB + SB), mins + chunk_index * MB, (uint32_t)(nch * MB), &full_bar[slot]);
+          }
+        }
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers ----------------
+  pdl_wait();
+  constexpr bool kInt4 = WF == WF_SYM_INT4 || WF == WF_ASYM_INT4;
+  for (int i = tid; i < kNB * RT * 128; i += kCThreads) red[i] = 0.f;
+  if (tid < 2 * kNB) red_cnt[tid] = 0;
+  if (WF == WF_LUT4 && tid < 256) {
+    __half2 v = __floats2half2_rn(a.lut[tid & 15], a.lut[tid >> 4]);
+    lut256[tid] = *reinterpret_cast<uint32_t*>(&v);
+  }
+  stage_x<T, kInt4>(a, xs, xs_stride, Kp, scratch);
+  consumer_sync();
+  if (kInt4) {
+    // per (row of x, 64-group): the constant part of sum_k A_k x'_k to take out of the accumulator, and for the
+    // asymmetric format the plain sum of x (for the "+ min" term)
+    const int groups = Kp / 64;
+    const float zlo = WF == WF_SYM_INT4 ? 1032.f : 1024.f;
+    const float zhi = WF == WF_SYM_INT4 ? 1152.f : 1024.f;
+    for (int i = tid; i < a.M * groups; i += kCThreads) {
+      const int m = i / groups, gi = i % groups;
+      float slo = 0.f, shi = 0.f;
+      for (int k = 0; k < 64; k++) {
+        const float v = __half2float(xs[m * xs_stride + gi * 64 + k]);
+        if (k & 2) shi += v; else slo += v;
+      }
+      xcorr[i] = zlo * slo + zhi * shi;
+      if (WF == WF_ASYM_INT4) xsum[i] = slo + 16.f * shi;
+    }
+    consumer_sync();
+  }
+
+  const bool has_x = g < a.M;
+  T* y = reinterpret_cast<T*>(a.y);
+  int it = 0, giter = 0;
+  bool ok = true;
+  for (int grp = blockIdx.x; grp < ngroups && ok; grp += gridDim.x, giter++) {
+    float acc[RT][4];
+#pragma unroll
+    for (int r = 0; r < RT; r++)
+#pragma unroll
+      for (int i = 0; i < 4; i++) acc[r][i] = 0.f;
+#pragma unroll
+    for (int r = 0; r < RT; r++) {
+      const int tile = grp * RT + r;
+      if (tile >= ntiles) break;
+      for (int sp = 0; sp < stages_per_tile; sp++, it++) {
+        const int slot = it % STAGES;
+        if (!mbar_wait(&full_bar[slot], (it / STAGES) & 1)) {
+          atomicExch(a.err, 2);
+          ok = false;
+          break;
+        }
+        const int c0 = sp * CPS;
+        const int nch = min(CPS, chunks - c0);
+        const uint8_t* st = ring + (size_t)slot * stage_bytes;
+        const uint8_t* st_scales = st + CPS * CB;
+        const uint8_t* st_mins = st + CPS * (CB + SB);
+        for (int c = warp; c < nch; c += kCW) {
+          const int cg = c0 + c;
+          uint4 xa0 = make_uint4(0, 0, 0, 0), xa1 = xa0, xb0 = xa0, xb1 = xa0;
+          if (has_x) {
+            const __half* xp = xs + g * xs_stride + cg * 128 + 16 * t;
+            xa0 = *reinterpret_cast<const uint4*>(xp);
+            xa1 = *reinterpret_cast<const uint4*>(xp + 8);
+            xb0 = *reinterpret_cast<const uint4*>(xp + 64);
+            xb1 = *reinterpret_cast<const uint4*>(xp + 72);
+          }
+          if constexpr (k4bit) {
+            const uint8_t* tp = st + c * CB;
+            const uint4 qa = *reinterpret_cast<const uint4*>(tp + g * 64 + t * 16);
+            const uint4 qb = *reinterpret_cast<const uint4*>(tp + (g + 8) * 64 + t * 16);
+            const uint32_t s0 = *reinterpret_cast<const uint32_t*>(st_scales + c * SB + (0 * 16 + 2 * g) * 2);
+            const uint32_t s1 = *reinterpret_cast<const uint32_t*>(st_scales + c * SB + (1 * 16 + 2 * g) * 2);
+            const float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&s0));
+            const float2 d1 = __half22float2(*reinterpret_cast<const __half2*>(&s1));
+            float c0v[4] = {0.f, 0.f, 0.f, 0.f}, c1v[4] = {0.f, 0.f, 0.f, 0.f};
+            if constexpr (WF == WF_LUT4) {
+              auto lp = [&](uint32_t word, int byte) { return lut256[(word >> (8 * byte)) & 0xFF]; };
+              mma_f16(c0v, lp(qa.x, 0), lp(qb.x, 0), lp(qa.x, 1), lp(qb.x, 1), xa0.x, xa0.y);
+              mma_f16(c0v, lp(qa.x, 2), lp(qb.x, 2), lp(qa.x, 3), lp(qb.x, 3), xa0.z, xa0.w);
+              mma_f16(c0v, lp(qa.y, 0), lp(qb.y, 0), lp(qa.y, 1), lp(qb.y, 1), xa1.x, xa1.y);
+              mma_f16(c0v, lp(qa.y, 2), lp(qb.y, 2), lp(qa.y, 3), lp(qb.y, 3), xa1.z, xa1.w);
+              mma_f16(c1v, lp(qa.z, 0), lp(qb.z, 0), lp(qa.z, 1), lp(qb.z, 1), xb0.x, xb0.y);
+              mma_f16(c1v, lp(qa.z, 2), lp(qb.z, 2), lp(qa.z, 3), lp(qb.z, 3), xb0.z, xb0.w);
+              mma_f16(c1v, lp(qa.w, 0), lp(qb.w, 0), lp(qa.w, 1), lp(qb.w, 1), xb1.x, xb1.y);
+              mma_f16(c1v, lp(qa.w, 2), lp(qb.w, 2), lp(qa.w, 3), lp(qb.w, 3), xb1.z, xb1.w);
+            } else {
+              // two independent accumulation chains per 64-group keep the tensor pipe busy
+              float c0w[4] = {0.f, 0.f, 0.f, 0.f}, c1w[4] = {0.f, 0.f, 0.f, 0.f};
+              {
+                Int4Raw A(qa.x), B(qb.x);
+                mma_f16(c0v, A.p[0], B.p[0], A.p[1], B.p[1], xa0.x, xa0.y);
+                mma_f16(c0w, A.p[2], B.p[2], A.p[3], B.p[3], xa0.z, xa0.w);
+              }
+              {
+                Int4Raw A(qa.z), B(qb.z);
+                mma_f16(c1v, A.p[0], B.p[0], A.p[1], B.p[1], xb0.x, xb0.y);
+                mma_f16(c1w, A.p[2], B.p[2], A.p[3], B.p[3], xb0.z, xb0.w);
+              }
+              {
+                Int4Raw A(qa.y), B(qb.y);
+                mma_f16(c0v, A.p[0], B.p[0], A.p[1], B.p[1], xa1.x, xa1.y);
+                mma_f16(c0w, A.p[2], B.p[2], A.p[3], B.p[3], xa1.z, xa1.w);
+              }
+              {
+                Int4Raw A(qa.w), B(qb.w);
+                mma_f16(c1v, A.p[0], B.p[0], A.p[1], B.p[1], xb1.x, xb1.y);
+                mma_f16(c1w, A.p[2], B.p[2], A.p[3], B.p[3], xb1.z, xb1.w);
+              }
+              const int groups = Kp / 64;
+              const int n0 = 2 * t, n1 = 2 * t + 1;
+              const float k00 = n0 < a.M ? xcorr[n0 * groups + 2 * cg] : 0.f;
+              const float k01 = n0 < a.M ? xcorr[n0 * groups + 2 * cg + 1] : 0.f;
+              const float k10 = n1 < a.M ? xcorr[n1 * groups + 2 * cg] : 0.f;
+              const float k11 = n1 < a.M ? xcorr[n1 * groups + 2 * cg + 1] : 0.f;
+              c0v[0] += c0w[0] - k00; c0v[1] += c0w[1] - k10; c0v[2] += c0w[2] - k00; c0v[3] += c0w[3] - k10;
+              c1v[0] += c1w[0] - k01; c1v[1] += c1w[1] - k11; c1v[2] += c1w[2] - k01; c1v[3] += c1w[3] - k11;
+            }
+            acc[r][0] += d0.x * c0v[0] + d1.x * c1v[0];
+            acc[r][1] += d0.x * c0v[1] + d1.x * c1v[1];
+            acc[r][2] += d0.y * c0v[2] + d1.y * c1v[2];
+            acc[r][3] += d0.y * c0v[3] + d1.y * c1v[3];
+            if constexpr (WF == WF_ASYM_INT4) {
+              const uint32_t m0 = *reinterpret_cast<const uint32_t*>(st_mins + c * MB + (0 * 16 + 2 * g) * 2);
+              const uint32_t m1 = *reinterpret_cast<const uint32_t*>(st_mins + c * MB + (1 * 16 + 2 * g) * 2);
+              const float2 mn0 = __half22float2(*reinterpret_cast<const __half2*>(&m0));
+              const float2 mn1 = __half22float2(*reinterpret_cast<const __half2*>(&m1));
+              const int groups = Kp / 64;
+              const int n0 = 2 * t, n1 = 2 * t + 1;
+              const float xs00 = n0 < a.M ? xsum[n0 * groups + 2 * cg] : 0.f;
+              const float xs01 = n0 < a.M ? xsum[n0 * groups + 2 * cg + 1] : 0.f;
+              const float xs10 = n1 < a.M ? xsum[n1 * groups + 2 * cg] : 0.f;
+              const float xs11 = n1 < a.M ? xsum[n1 * groups + 2 * cg + 1] : 0.f;
+              acc[r][0] += mn0.x * xs00 + mn1.x * xs01;
+              acc[r][1] += mn0.x * xs10 + mn1.x * xs11;
+              acc[r][2] += mn0.y * xs00 + mn1.y * xs01;
+              acc[r][3] += mn0.y * xs10 + mn1.y * xs11;
+            }
+          } else {
+            // 8-bit families: a 128-k chunk = two [16 rows][64 k] tiles of 1024 bytes
+            float cc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            const uint4 xv[4] = {xa0, xa1, xb0, xb1};
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+              const uint8_t* tp = st + c * CB + h * 1024;
+              const uint4 qa = *reinterpret_cast<const uint4*>(tp + g * 64 + t * 16);
+              const uint4 qb = *reinterpret_cast<const uint4*>(tp + (g + 8) * 64 + t * 16);
+              const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w};
+              const uint32_t wb[4] = {qb.x, qb.y, qb.z, qb.w};
+              const uint32_t xw[8] = {xv[2 * h].x, xv[2 * h].y, xv[2 * h].z, xv[2 * h].w,
+                                      xv[2 * h + 1].x, xv[2 * h + 1].y, xv[2 * h + 1].z, xv[2 * h + 1].w};
+#pragma unroll
+              for (int j = 0; j < 4; j++) {
+                uint32_t a0, a1, a2, a3;
+                if constexpr (WF == WF_INT8) {
+                  const uint32_t ua = wa[j] ^ 0x80808080u, ub = wb[j] ^ 0x80808080u;
+                  constexpr uint32_t k1152 = 0x64806480u;
+                  a0 = h2_sub(__byte_perm(ua, 0x64646464u, 0x4140), k1152);
+                  a2 = h2_sub(__byte_perm(ua, 0x64646464u, 0x4342), k1152);
+                  a1 = h2_sub(__byte_perm(ub, 0x64646464u, 0x4140), k1152);
+                  a3 = h2_sub(__byte_perm(ub, 0x64646464u, 0x4342), k1152);
+                } else {
+                  constexpr __nv_fp8_interpretation_t kind = WF == WF_FP8_E4M3 ? __NV_E4M3 : __NV_E5M2;
+                  __half2_raw r0 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wa[j] & 0xFFFF), kind);
+                  __half2_raw r2 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wa[j] >> 16), kind);
+                  __half2_raw r1 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wb[j] & 0xFFFF), kind);
+                  __half2_raw r3 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wb[j] >> 16), kind);
+                  a0 = (uint32_t)r0.x | ((uint32_t)r0.y << 16);
+                  a2 = (uint32_t)r2.x | ((uint32_t)r2.y << 16);
+                  a1 = (uint32_t)r1.x | ((uint32_t)r1.y << 16);
+                  a3 = (uint32_t)r3.x | ((uint32_t)r3.y << 16);
+                }
+                mma_f16(cc[h], a0, a1, a2, a3, xw[2 * j], xw[2 * j + 1]);
+              }
+            }
+            if constexpr (WF == WF_INT8) {
+#pragma unroll
+              for (int h = 0; h < 2; h++) {
+                const uint32_t s = *reinterpret_cast<const uint32_t*>(st_scales + c * SB + h * 32 + 2 * g * 2);
+                const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&s));
+                acc[r][0] += d.x * cc[h][0];
+                acc[r][1] += d.x * cc[h][1];
+                acc[r][2] += d.y * cc[h][2];
+                acc[r][3] += d.y * cc[h][3];
+              }
+            } else {
+              const float2 d = *reinterpret_cast<const float2*>(st_scales + c * SB + 2 * g * 4);
+              acc[r][0] += d.x * (cc[0][0] + cc[1][0]);
+              acc[r][1] += d.x * (cc[0][1] + cc[1][1]);
+              acc[r][2] += d.y * (cc[0][2] + cc[1][2]);
+              acc[r][3] += d.y * (cc[0][3] + cc[1][3]);
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[slot]);
+      }
+      if (!ok) break;
+    }
+    if (!ok) break;
+
+    // ---- cross-warp reduction without a CTA-wide barrier ----
+    // Every warp adds its partial tile into one of kNB zero-initialised shared accumulators (shared-memory
+    // float atomics) and then takes a ticket; the warp that draws the last ticket finalises the tile (reads
+    // and re-zeroes the accumulator with atomicExch, applies the epilogue, stores) and publishes the buffer
+    // for reuse by bumping its generation.  Fast warps run ahead into the next groups' buffers meanwhile.
+    const int b = giter % kNB;
+    {
+      volatile int* genp = red_gen + b;
+      bool ready = false;
+      for (int i = 0; i < kSpinLimit; i++) {
+        if (*genp == giter / kNB) { ready = true; break; }
+        __nanosleep(64);
+      }
+      if (!ready) {
+        atomicExch(a.err, 3);
+        break;
+      }
+    }
+    float* rbuf = red + (size_t)b * RT * 128;
+#pragma unroll
+    for (int r = 0; r < RT; r++) {
+      float* rp = rbuf + (size_t)r * 128;
+      atomicAdd(&rp[g * 8 + 2 * t], acc[r][0]);
+      atomicAdd(&rp[g * 8 + 2 * t + 1], acc[r][1]);
+      atomicAdd(&rp[(g + 8) * 8 + 2 * t], acc[r][2]);
+      atomicAdd(&rp[(g + 8) * 8 + 2 * t + 1], acc[r][3]);
+    }
+    __threadfence_block();
+    __syncwarp();
+    int ticket = 0;
+    if (lane == 0) ticket = atomicAdd(red_cnt + b, 1);
+    ticket = __shfl_sync(0xffffffffu, ticket, 0);
+    if (ticket == kCW - 1) {
+      __threadfence_block();
+      if (a.act == 0) {
+#pragma unroll
+        for (int j = 0; j < RT * 4; j++) {
+          const int i = lane + 32 * j;            // index into [RT][16 rows][8 cols]
+          const int r = i / 128, row = (i % 128) / 8, col = i % 8;
+          float sv = atomicExch(&rbuf[i], 0.f);
+          const int n = (grp * RT + r) * 16 + row;
+          if (n < a.N && col < a.M) {
+            if (a.bias != nullptr) sv += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[n]);
+            if (a.residual != nullptr)
+              sv += DT<T>::to_f(reinterpret_cast<const T*>(a.residual)[(size_t)col * a.ldr + n]);
+            y[(size_t)col * a.ldy + n] = DT<T>::from_f(sv);
+          }
+        }
+      } else if (RT == 2) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          const int i = lane + 32 * j;
+          const int row = i / 8, col = i % 8;
+          float gsum = atomicExch(&rbuf[i], 0.f), usum = atomicExch(&rbuf[128 + i], 0.f);
+          const int n = grp * 16 + row;
+          if (n < a.N / 2 && col < a.M) {
+            if (a.bias != nullptr) {
+              gsum += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[(size_t)grp * 32 + row]);
+              usum += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[(size_t)grp * 32 + 16 + row]);
+            }
+            y[(size_t)col * a.ldy + n] = DT<T>::from_f(act_apply(gsum, a.act) * usum);
+          }
+        }
+      }
+      __threadfence_block();
+      __syncwarp();
+      if (lane == 0) {
+        red_cnt[b] = 0;
+        __threadfence_block();
+        *(volatile int*)(red_gen + b) = giter / kNB + 1;
+      }
+    }
+  }
+}
+
+struct LaunchPlan {
+  int stages, cps, grid;
+  size_t smem;
+};
+
+// Tuning knobs (set once per process through ipex_gemv_tma_tune): CTAs per SM the grid is sized for, and the
+// shared-memory budget of one CTA.  The default leaves half of every SM free so that, under programmatic
+// dependent launch, the next kernel's CTAs can become resident and fill their rings while this one computes.
+int g_ctas_per_sm = 2;
+int g_budget_kb = 54;
+int g_cps4 = 8;
+
+template <int WF, int RT>
+LaunchPlan plan(const TmaArgs& a) {
+  constexpr bool k4bit = WF == WF_SYM_INT4 || WF == WF_ASYM_INT4 || WF == WF_LUT4;
+  const int CB = k4bit ? 1024 : 2048;
+  const int MB = WF == WF_ASYM_INT4 ? 64 : 0;
+  const int Kp = (int)ceil_to_i64(a.K, 128), Np = (int)ceil_to_i64(a.N, 16);
+  const int chunks = Kp / 128;
+  LaunchPlan p;
+  p.cps = k4bit ? g_cps4 : g_cps4 / 2;
+  if (p.cps < 1) p.cps = 1;
+  if (p.cps > chunks) p.cps = chunks;
+  const size_t stage_bytes = (size_t)p.cps * (CB + 64 + MB);
+  size_t fixed = (((size_t)a.M * (Kp + 8) * 2 + 15) & ~(size_t)15) + (size_t)kNB * RT * 128 * 4 + 2 * kNB * 4 + 64 + 256;
+  if (WF == WF_ASYM_INT4) fixed += (size_t)a.M * (Kp / 64) * 4;
+  if (WF == WF_SYM_INT4 || WF == WF_ASYM_INT4) fixed += (size_t)a.M * (Kp / 64) * 4;
+  if (WF == WF_LUT4) fixed += 1024;
+  size_t budget = (size_t)g_budget_kb * 1024;
+  if (budget < fixed + 3 * (stage_bytes + 16)) budget = fixed + 3 * (stage_bytes + 16);
+  int stages = (int)((budget - fixed) / (stage_bytes + 16));
+  if (stages > 12) stages = 12;
+  if (stages < 2) stages = 2;
+  p.stages = stages;
+  p.smem = (size_t)stages * stage_bytes + 2 * stages * 8 + 16 + fixed;
+  const int ngroups = (Np / 16 + RT - 1) / RT;
+  int per_sm = g_ctas_per_sm;
+  while (per_sm > 1 && p.smem * per_sm > 220 * 1024) per_sm--;
+  p.grid = ngroups < 148 * per_sm ? ngroups : 148 * per_sm;
+  return p;
+}
+
+template <int WF, typename T, int RT>
+cudaError_t launch_tma(TmaArgs a, cudaStream_t stream, bool pdl) {
+  LaunchPlan p = plan<WF, RT>(a);
+  if (p.smem > 227 * 1024) return cudaErrorInvalidValue;
+  a.stages = p.stages;
+  a.cps = p.cps;
+  auto kern = gemv_tma_kernel<WF, T, RT>;
+  if (p.smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
+    if (e != cudaSuccess) return e;
+  }
+  return launch_kernel(kern, dim3(p.grid), dim3(kThreadsTma), p.smem, stream, pdl, a);
+}
+
+template <int WF, typename T>
+cudaError_t dispatch_rt(const TmaArgs& a, cudaStream_t s, bool pdl) {
+  if (a.act != 0) return launch_tma<WF, T, 2>(a, s, pdl);
+  return launch_tma<WF, T, 1>(a, s, pdl);
+}
+
+template <typename T>
+cudaError_t dispatch_wf(int wf, const TmaArgs& a, cudaStream_t s, bool pdl) {
+  switch (wf) {
+    case WF_SYM_INT4: return dispatch_rt<WF_SYM_INT4, T>(a, s, pdl);
+    case WF_ASYM_INT4: return dispatch_rt<WF_ASYM_INT4, T>(a, s, pdl);
+    case WF_LUT4: return dispatch_rt<WF_LUT4, T>(a, s, pdl);
+    case WF_FP8_E4M3: return dispatch_rt<WF_FP8_E4M3, T>(a, s, pdl);
+    case WF_FP8_E5M2: return dispatch_rt<WF_FP8_E5M2, T>(a, s, pdl);
+    case WF_INT8: return dispatch_rt<WF_INT8, T>(a, s, pdl);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace
+
+// Process-wide tuning of the pipelined GEMV (values <= 0 keep the current setting).
+IPEX_API void ipex_gemv_tma_tune(int ctas_per_sm, int budget_kb, int chunks_per_stage_4bit) {
+  if (ctas_per_sm > 0) g_ctas_per_sm = ctas_per_sm > 4 ? 4 : ctas_per_sm;
+  if (budget_kb > 0) g_budget_kb = budget_kb > 220 ? 220 : budget_kb;
+  if (chunks_per_stage_4bit > 0) g_cps4 = chunks_per_stage_4bit > 32 ? 32 : chunks_per_stage_4bit;
+}
+
+// Same arguments as ipex_gemv_lowbit plus `err`: a device int the kernel sets non-zero if one of its bounded
+// mbarrier waits expires (1 = producer waiting for a free stage, 2 = consumer waiting for data).
+// Returns cudaErrorInvalidValue when x does not fit shared memory (the caller then splits M or uses the
+// non-pipelined kernel).
+IPEX_API int ipex_gemv_lowbit_tma(const void* w, int wf, const void* x, void* y, int M, int N, int K, int ldx, int ldy,
+                                  const void* norm_w, float eps, float norm_offset, const void* bias,
+                                  const void* residual, int ldr, int act, const float* lut, int dtype, int pdl,
+                                  int* err, void* stream) {
+  if (M < 1 || M > 8 || (K % 64) != 0 || err == nullptr) return (int)cudaErrorInvalidValue;
+  if ((ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0) return (int)cudaErrorInvalidValue;
+  TmaArgs a;
+  a.w = (const uint8_t*)w; a.x = x; a.y = y; a.norm_w = norm_w; a.bias = bias; a.residual = residual; a.lut = lut;
+  a.err = err;
+  a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy; a.ldr = ldr; a.eps = eps; a.norm_offset = norm_offset;
+  a.act = act; a.stages = 0; a.cps = 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == DT_F16) return (int)dispatch_wf<__half>(wf, a, s, pdl != 0);
+  if (dtype == DT_BF16) return (int)dispatch_wf<__nv_bfloat16>(wf, a, s, pdl != 0);
+  return (int)cudaErrorInvalidValue;
+}

@@ -16,6 +16,8 @@ WF_SYM_INT4, WF_ASYM_INT4, WF_LUT4, WF_FP8_E4M3, WF_FP8_E5M2, WF_INT8, WF_F16, W
 
 _SIGS = {
     "ipex_gemv_lowbit": [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp, cf, cf, vp, vp, ci, ci, vp, ci, ci, vp],
+    "ipex_gemv_lowbit_tma": [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp, cf, cf, vp, vp, ci, ci, vp, ci, ci, vp, vp],
+    "ipex_gemv_int4_direct": [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp, cf, cf, vp, vp, ci, ci, vp, ci, ci, vp],
     "ipex_rms_norm": [vp, vp, vp, vp, vp, i64, ci, cf, cf, ci, ci, vp],
     "ipex_layer_norm": [vp, vp, vp, vp, i64, ci, cf, ci, vp],
     "ipex_act_mul": [vp, vp, vp, i64, ci, ci, ci, vp],
@@ -58,6 +60,10 @@ def declare(lib: ctypes.CDLL):
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = i64
+    lib.ipex_gemv_tma_tune.argtypes = [ci, ci, ci]
+    lib.ipex_gemv_tma_tune.restype = None
+    lib.ipex_gemv_direct_tune.argtypes = [ci]
+    lib.ipex_gemv_direct_tune.restype = None
     for name, args in _OPTIONAL.items():
         fn = getattr(lib, name, None)
         if fn is not None:

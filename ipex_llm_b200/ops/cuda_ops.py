@@ -31,6 +31,30 @@ QTYPE_TO_WF = {
 
 _lut_cache = {}
 _USE_PDL = os.environ.get("IPEX_LLM_PDL", "1") != "0"
+_GEMV_IMPL = os.environ.get("IPEX_LLM_GEMV", "direct")   # direct | tma | v1
+_err_flags = {}
+
+
+def error_flag(device) -> torch.Tensor:
+    """Device int the kernels with bounded waits set when a wait expires (0 = healthy)."""
+    key = str(device)
+    if key not in _err_flags:
+        _err_flags[key] = torch.zeros(4, dtype=torch.int32, device=device)
+        tune = os.environ.get("IPEX_LLM_GEMV_TUNE")  # "ctas_per_sm,budget_kb,chunks_per_stage"
+        if tune:
+            a, b, c = (int(v) for v in tune.split(","))
+            cuda_lib().ipex_gemv_tma_tune(a, b, c)
+    return _err_flags[key]
+
+
+def check_error_flag(device):
+    """Raise if a kernel recorded an expired wait (synchronises the device)."""
+    flag = _err_flags.get(str(device))
+    if flag is not None:
+        v = int(flag[0].item())
+        if v != 0:
+            flag.zero_()
+            raise RuntimeError(f"ipex_llm_b200: a kernel wait expired (code {v}); results are invalid")
 GEMV_MAX_M = 8
 _SMEM_LIMIT = 200 * 1024
 
@@ -70,6 +94,25 @@ def gemv_lowbit(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K: in
     if out is None:
         out = torch.empty((M, n_out), dtype=x.dtype, device=x.device)
     lut = lut_for(qtype, x.device) if wf == api.WF_LUT4 else None
+    if _GEMV_IMPL == "direct" and wf in (api.WF_SYM_INT4, api.WF_ASYM_INT4) and x.stride(0) % 8 == 0:
+        rc = lib.ipex_gemv_int4_direct(ptr(w_data), wf, ptr(x), ptr(out), M, N, K, x.stride(0), out.stride(0),
+                                       ptr(norm_weight), eps, norm_offset, ptr(bias), ptr(residual),
+                                       residual.stride(0) if residual is not None else 0, act, None, _dt(x),
+                                       int(pdl and _USE_PDL), current_stream())
+        if rc == 0:
+            return out
+        if rc != 1:
+            api.check(rc, "gemv_int4_direct")
+    if _GEMV_IMPL == "tma" and wf not in (api.WF_F16, api.WF_BF16):
+        rc = lib.ipex_gemv_lowbit_tma(ptr(w_data), wf, ptr(x), ptr(out), M, N, K, x.stride(0), out.stride(0),
+                                      ptr(norm_weight), eps, norm_offset, ptr(bias), ptr(residual),
+                                      residual.stride(0) if residual is not None else 0, act, ptr(lut), _dt(x),
+                                      int(pdl and _USE_PDL), ptr(error_flag(x.device)), current_stream())
+        if rc == 0:
+            return out
+        if rc != 1:
+            api.check(rc, "gemv_lowbit_tma")
+        # cudaErrorInvalidValue: x does not fit beside the ring -> non-pipelined kernel
     rc = lib.ipex_gemv_lowbit(ptr(w_data), wf, ptr(x), ptr(out), M, N, K, x.stride(0), out.stride(0),
                               ptr(norm_weight), eps, norm_offset, ptr(bias), ptr(residual),
                               residual.stride(0) if residual is not None else 0, act, ptr(lut), _dt(x),
@@ -313,7 +356,7 @@ def sdpa_decode_supported(head_dim: int, v_head_dim: int) -> bool:
 
 def pick_nsplit(B: int, Hkv: int, kv_len: int, n_sm: int = 148) -> int:
     ctas = max(1, B * Hkv)
-    want = max(1, (2 * n_sm) // ctas)
+    want = max(1, (int(os.environ.get("IPEX_LLM_ATTN_WAVES", "4")) * n_sm) // ctas)
     by_len = max(1, kv_len // 128)
     return int(max(1, min(want, by_len, 64)))
 

@@ -128,7 +128,7 @@ class LowBitEmbedding(nn.Embedding):
                   convert_shape_only, qtype)
         # embedding tables are read row-wise: they always keep the canonical (row-contiguous) byte order
         obj._parameters["weight"] = obj.weight.quantize("meta" if str(device) == "meta" else "cpu")
-        obj._keep_canonical = True
+        obj.weight.keep_canonical = True
         return obj
 
     def _apply(self, fn, recurse=True):
@@ -138,5 +138,6 @@ class LowBitEmbedding(nn.Embedding):
         if w.quantized and probe.device != w.data.device and w.data.device.type != "meta":
             moved = FP4Params(w.data.to(probe.device), requires_grad=False, quantized=True, _shape=w._shape,
                               qtype=w.qtype)
+            moved.keep_canonical = True
             self._parameters["weight"] = moved
         return self

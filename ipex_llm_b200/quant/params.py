@@ -188,6 +188,8 @@ class FP4Params(torch.nn.Parameter):
     def layout(self) -> str:
         """"device" when the packed bytes are in the GPU tile layout, else "canonical".  Derived from where
         the bytes live so that ``nn.Module._apply`` (which swaps ``.data`` in place) cannot desynchronise it."""
+        if getattr(self, "keep_canonical", False):
+            return "canonical"   # row-addressed tables (quantized embeddings) stay in block order on the GPU
         return "device" if (self.quantized and self.data.is_cuda) else "canonical"
 
     @layout.setter
@@ -209,7 +211,10 @@ class FP4Params(torch.nn.Parameter):
                   imatrix=self.imatrix, in_features=self.in_features, enable_scale_search=self.enable_scale_search,
                   convert_shape_only=self.convert_shape_only)
         kw.update(over)
-        return FP4Params(data, **kw)
+        new = FP4Params(data, **kw)
+        if getattr(self, "keep_canonical", False):
+            new.keep_canonical = True
+        return new
 
     def ggml_mse(self, w, ggml_qtype, device):
         if device == "meta":

@@ -44,8 +44,10 @@ LOAD_KEYS_NAME = "load_keys.json"
 def _plain_state_dict(model):
     """State dict with packed weights as plain (canonical, CPU) tensors."""
     out = {}
-    for k, v in model.state_dict().items():
-        if isinstance(v, FP4Params) or getattr(v, "quantized", False):
+    # keep_vars: the FP4Params objects themselves (a detached copy would lose qtype / shape, and with them the
+    # knowledge that GPU-resident bytes are in tile order and must go back to canonical blocks)
+    for k, v in model.state_dict(keep_vars=True).items():
+        if isinstance(v, FP4Params) and v.quantized:
             v = v.to("cpu") if v.data.device.type != "cpu" else v
             out[k] = v.data.detach().clone()
         else:

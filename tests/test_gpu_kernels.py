@@ -260,3 +260,22 @@ def test_embedding_rows_and_argmax_and_penalty():
             ref[b, t] = ref[b, t] * 1.3 if ref[b, t] < 0 else ref[b, t] / 1.3
     got = cuda_ops.repetition_penalty_inplace(logits.clone(), ids, 1.3)
     assert torch.allclose(got.float(), ref, atol=2e-3, rtol=2e-3)
+
+
+def test_gemv_non_pipelined_variant_and_wait_flags(monkeypatch):
+    """The register-path GEMV stays available (it serves shapes whose x does not fit beside the TMA ring) and no
+    bounded wait of the pipelined kernel has expired during the tests above."""
+    from ipex_llm_b200.ops import cuda_ops
+    torch.manual_seed(12)
+    N, K, M = 1040, 2048, 4
+    w = torch.randn(N, K) * 0.02
+    _, deq, dev = _quantize_cpu(w, "sym_int4")
+    x = torch.randn(M, K).half().cuda()
+    ref = x.float().cpu() @ deq.t()
+    y_tma = cuda_ops.gemv_lowbit(x, dev.cuda(), _qt("sym_int4"), N, K).float().cpu()
+    monkeypatch.setattr(cuda_ops, "_GEMV_IMPL", "v1")
+    y_v1 = cuda_ops.gemv_lowbit(x, dev.cuda(), _qt("sym_int4"), N, K).float().cpu()
+    assert (y_v1 - ref).abs().max().item() < 4e-3 * ref.abs().max().item()
+    assert (y_tma - y_v1).abs().max().item() < 2e-3 * ref.abs().max().item()
+    torch.cuda.synchronize()
+    cuda_ops.check_error_flag(x.device)
