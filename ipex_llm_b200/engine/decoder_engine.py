@@ -39,20 +39,24 @@ from ..quant.params import device_nbytes
 class _W:
     """One linear of the flattened model: tiled low-bit bytes or a dense half matrix."""
 
-    def __init__(self, data, wf, qtype, N, K, bias=None):
+    def __init__(self, data, wf, qtype, N, K, bias=None, tp=None):
         self.data, self.wf, self.qtype, self.N, self.K, self.bias = data, wf, qtype, N, K, bias
+        self.tp = tp   # TPGroup of a row-parallel layer (its output is summed over the group), else None
 
     @staticmethod
     def from_module(mod, dtype):
         bias = mod.bias.data.to(dtype) if getattr(mod, "bias", None) is not None else None
+        tp = getattr(mod, "mp_group", None)
+        if tp is not None and getattr(tp, "world_size", 1) <= 1:
+            tp = None
         if isinstance(mod, LowBitLinear):
             w = mod.weight
             if not cuda_ops.is_tiled(w.qtype):
                 raise NotImplementedError(f"decode engine needs a tiled qtype, got {qt.qtype_name(w.qtype)}")
-            return _W(w.data, cuda_ops.QTYPE_TO_WF[w.qtype], w.qtype, int(w._shape[0]), int(w._shape[1]), bias)
+            return _W(w.data, cuda_ops.QTYPE_TO_WF[w.qtype], w.qtype, int(w._shape[0]), int(w._shape[1]), bias, tp)
         w = mod.weight.data.to(dtype).contiguous()
         wf = api.WF_F16 if dtype == torch.float16 else api.WF_BF16
-        return _W(w, wf, None, w.shape[0], w.shape[1], bias)
+        return _W(w, wf, None, w.shape[0], w.shape[1], bias, tp)
 
 
 def _interleave_row_tiles(a: _W, b: _W) -> _W:
@@ -194,6 +198,23 @@ class DecoderEngine:
         M = x.shape[0]
         for s in range(0, M, 8):
             e = min(M, s + 8)
+            if w.tp is not None and norm_w is None and act == 0 and w.wf not in (api.WF_F16, api.WF_BF16):
+                # row-parallel layer: the GEMV kernel exchanges its partial tiles with the peers itself
+                cuda_ops.gemv_lowbit_ar(x[s:e], w.data, w.qtype, w.N, w.K, out[s:e], w.tp.symm(),
+                                        bias=bias if bias is not None else w.bias,
+                                        residual=residual[s:e] if residual is not None else None,
+                                        pdl=self.use_pdl, wf=w.wf)
+                continue
+            if w.tp is not None:
+                # dense (unquantized) row-parallel layer: plain GEMV, stand-alone all-reduce, then the residual
+                cuda_ops.gemv_lowbit(x[s:e], w.data, w.qtype, w.N, w.K, out=out[s:e], pdl=False, wf=w.wf)
+                w.tp.all_reduce(out[s:e])
+                b_ = bias if bias is not None else w.bias
+                if b_ is not None:
+                    out[s:e].add_(b_)
+                if residual is not None:
+                    out[s:e].add_(residual[s:e])
+                continue
             cuda_ops.gemv_lowbit(x[s:e], w.data, w.qtype, w.N, w.K, out=out[s:e], norm_weight=norm_w, eps=self.eps,
                                  bias=bias if bias is not None else w.bias,
                                  residual=residual[s:e] if residual is not None else None, act=act,
@@ -262,13 +283,23 @@ class DecoderEngine:
             torch.cuda.current_stream().wait_stream(s)
             self.tokens.copy_(saved_tok)
             self.past_len.copy_(saved_len)
+            comm = self._tp_comm()
+            parity = comm._parity if comm is not None else 0
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 self._step_kernels(B)
             # capture does not execute: state is unchanged
-            entry = (g, self.cache)
+            entry = (g, self.cache, parity)
             self._graphs[B] = entry
+        comm = self._tp_comm()
+        if comm is not None and comm._parity != entry[2]:
+            # the buffer parity of the fused all-reduces is baked into the graph: realign (same on every rank)
+            comm.barrier()
         entry[0].replay()
+
+    def _tp_comm(self):
+        tp = self.layers[0].o.tp
+        return tp.symm() if tp is not None else None
 
     # ------------------------------------------------------------------------------------------------
     @torch.no_grad()

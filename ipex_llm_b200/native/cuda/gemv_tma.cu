@@ -41,7 +41,25 @@ struct TmaArgs {
   int act;
   int stages;  // ring depth
   int cps;     // chunks (of 128 k) per stage
+  // tensor-parallel row-parallel layers: fused all-reduce over NVLink peer memory (tp_world > 1)
+  int tp_rank, tp_world, tp_npad;
+  float* const* tp_bufs;   // [tp_world] device pointers: rank r's partial buffer [tp_world][8][tp_npad] fp32
+  int* const* tp_flags;    // [tp_world] device pointers: rank r's per-tile arrival counters
 };
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_relaxed_sys_f32(const float* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add(int* p, int v) {
+  asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -497,7 +515,57 @@ __global__ void __launch_bounds__(kThreadsTma, 1) gemv_tma_kernel(TmaArgs a) {
     ticket = __shfl_sync(0xffffffffu, ticket, 0);
     if (ticket == kCW - 1) {
       __threadfence_block();
-      if (a.act == 0) {
+      if (a.tp_world > 1 && a.act == 0 && RT == 1) {
+        // ---- fused all-reduce of this 16-row tile over peer memory ----
+        // 1. push this rank's partial tile into slot [tp_rank] of EVERY rank's buffer (plain stores to the
+        //    peers' mapped memory), 2. release-increment the tile's arrival counter on every rank,
+        // 3. wait (bounded) until all tp_world partials of the tile have arrived here, 4. sum them locally.
+        // Other warps of the CTA keep streaming the next tiles meanwhile.
+        float pv[4];
+        int pn[4], pc[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          const int i = lane + 32 * j;
+          pc[j] = i % 8;
+          pn[j] = grp * 16 + i / 8;
+          pv[j] = atomicExch(&rbuf[i], 0.f);
+        }
+        for (int rk = 0; rk < a.tp_world; rk++) {
+          float* dst = a.tp_bufs[rk] + (size_t)a.tp_rank * 8 * a.tp_npad;
+#pragma unroll
+          for (int j = 0; j < 4; j++)
+            if (pn[j] < a.N && pc[j] < a.M) dst[(size_t)pc[j] * a.tp_npad + pn[j]] = pv[j];
+        }
+        __threadfence_system();
+        __syncwarp();
+        if (lane < a.tp_world) red_release_sys_add(a.tp_flags[lane] + grp, 1);
+        int* my_flag = a.tp_flags[a.tp_rank] + grp;
+        bool arrived = false;
+        if (lane == 0) {
+          for (int i = 0; i < kSpinLimit; i++) {
+            if (ld_acquire_sys(my_flag) >= a.tp_world) { arrived = true; break; }
+            __nanosleep(64);
+          }
+          if (arrived) *my_flag = 0;   // self-cleaning: the next user of this counter is two launches away
+          else atomicExch(a.err, 4);
+        }
+        arrived = __shfl_sync(0xffffffffu, (int)arrived, 0) != 0;
+        if (arrived) {
+          const float* src = a.tp_bufs[a.tp_rank];
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            if (pn[j] < a.N && pc[j] < a.M) {
+              float sv = 0.f;
+              for (int rk = 0; rk < a.tp_world; rk++)
+                sv += ld_relaxed_sys_f32(src + ((size_t)rk * 8 + pc[j]) * a.tp_npad + pn[j]);
+              if (a.bias != nullptr) sv += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[pn[j]]);
+              if (a.residual != nullptr)
+                sv += DT<T>::to_f(reinterpret_cast<const T*>(a.residual)[(size_t)pc[j] * a.ldr + pn[j]]);
+              y[(size_t)pc[j] * a.ldy + pn[j]] = DT<T>::from_f(sv);
+            }
+          }
+        }
+      } else if (a.act == 0) {
 #pragma unroll
         for (int j = 0; j < RT * 4; j++) {
           const int i = lane + 32 * j;            // index into [RT][16 rows][8 cols]
@@ -546,9 +614,9 @@ struct LaunchPlan {
 // Tuning knobs (set once per process through ipex_gemv_tma_tune): CTAs per SM the grid is sized for, and the
 // shared-memory budget of one CTA.  The default leaves half of every SM free so that, under programmatic
 // dependent launch, the next kernel's CTAs can become resident and fill their rings while this one computes.
-int g_ctas_per_sm = 2;
-int g_budget_kb = 54;
-int g_cps4 = 8;
+int g_ctas_per_sm = 1;
+int g_budget_kb = 140;
+int g_cps4 = 32;
 
 template <int WF, int RT>
 LaunchPlan plan(const TmaArgs& a) {
@@ -626,19 +694,46 @@ IPEX_API void ipex_gemv_tma_tune(int ctas_per_sm, int budget_kb, int chunks_per_
 // mbarrier waits expires (1 = producer waiting for a free stage, 2 = consumer waiting for data).
 // Returns cudaErrorInvalidValue when x does not fit shared memory (the caller then splits M or uses the
 // non-pipelined kernel).
-IPEX_API int ipex_gemv_lowbit_tma(const void* w, int wf, const void* x, void* y, int M, int N, int K, int ldx, int ldy,
-                                  const void* norm_w, float eps, float norm_offset, const void* bias,
-                                  const void* residual, int ldr, int act, const float* lut, int dtype, int pdl,
-                                  int* err, void* stream) {
+static int gemv_tma_entry(const void* w, int wf, const void* x, void* y, int M, int N, int K, int ldx, int ldy,
+                          const void* norm_w, float eps, float norm_offset, const void* bias, const void* residual,
+                          int ldr, int act, const float* lut, int dtype, int pdl, int* err, void* stream, int tp_rank,
+                          int tp_world, int tp_npad, const void* tp_bufs, const void* tp_flags) {
   if (M < 1 || M > 8 || (K % 64) != 0 || err == nullptr) return (int)cudaErrorInvalidValue;
   if ((ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0) return (int)cudaErrorInvalidValue;
+  if (tp_world > 1 && (act != 0 || tp_bufs == nullptr || tp_flags == nullptr || tp_npad < N || tp_world > 8))
+    return (int)cudaErrorInvalidValue;
   TmaArgs a;
   a.w = (const uint8_t*)w; a.x = x; a.y = y; a.norm_w = norm_w; a.bias = bias; a.residual = residual; a.lut = lut;
   a.err = err;
   a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy; a.ldr = ldr; a.eps = eps; a.norm_offset = norm_offset;
   a.act = act; a.stages = 0; a.cps = 0;
+  a.tp_rank = tp_rank; a.tp_world = tp_world; a.tp_npad = tp_npad;
+  a.tp_bufs = reinterpret_cast<float* const*>(tp_bufs);
+  a.tp_flags = reinterpret_cast<int* const*>(tp_flags);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == DT_F16) return (int)dispatch_wf<__half>(wf, a, s, pdl != 0);
   if (dtype == DT_BF16) return (int)dispatch_wf<__nv_bfloat16>(wf, a, s, pdl != 0);
   return (int)cudaErrorInvalidValue;
+}
+
+IPEX_API int ipex_gemv_lowbit_tma(const void* w, int wf, const void* x, void* y, int M, int N, int K, int ldx, int ldy,
+                                  const void* norm_w, float eps, float norm_offset, const void* bias,
+                                  const void* residual, int ldr, int act, const float* lut, int dtype, int pdl,
+                                  int* err, void* stream) {
+  return gemv_tma_entry(w, wf, x, y, M, N, K, ldx, ldy, norm_w, eps, norm_offset, bias, residual, ldr, act, lut, dtype,
+                        pdl, err, stream, 0, 1, 0, nullptr, nullptr);
+}
+
+// Row-parallel GEMV fused with its all-reduce (tensor parallelism): every rank runs the same launch on its K-slice
+// of the weight; the kernel exchanges the 16-row partial tiles through peer memory and every rank ends with the
+// full sum (+ bias, + residual) in y.  tp_bufs / tp_flags are device arrays of tp_world pointers into the ranks'
+// symmetric buffers for the call's parity (two parities alternate between consecutive calls); the arrival
+// counters must be zero before the first call and are left zero.  Bounded waits: *err = 4 if a peer never arrives.
+IPEX_API int ipex_gemv_lowbit_tma_ar(const void* w, int wf, const void* x, void* y, int M, int N, int K, int ldx,
+                                     int ldy, const void* norm_w, float eps, float norm_offset, const void* bias,
+                                     const void* residual, int ldr, const float* lut, int dtype, int pdl, int* err,
+                                     void* stream, int tp_rank, int tp_world, int tp_npad, const void* tp_bufs,
+                                     const void* tp_flags) {
+  return gemv_tma_entry(w, wf, x, y, M, N, K, ldx, ldy, norm_w, eps, norm_offset, bias, residual, ldr, 0, lut, dtype,
+                        pdl, err, stream, tp_rank, tp_world, tp_npad, tp_bufs, tp_flags);
 }

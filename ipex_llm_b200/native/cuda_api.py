@@ -17,6 +17,11 @@ WF_SYM_INT4, WF_ASYM_INT4, WF_LUT4, WF_FP8_E4M3, WF_FP8_E5M2, WF_INT8, WF_F16, W
 _SIGS = {
     "ipex_gemv_lowbit": [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp, cf, cf, vp, vp, ci, ci, vp, ci, ci, vp],
     "ipex_gemv_lowbit_tma": [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp, cf, cf, vp, vp, ci, ci, vp, ci, ci, vp, vp],
+    "ipex_gemv_lowbit_tma_ar": [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp, cf, cf, vp, vp, ci, vp, ci, ci, vp, vp,
+                                ci, ci, ci, vp, vp],
+    "ipex_allreduce_oneshot": [vp, vp, vp, i64, ci, ci, ci, vp, ci, ci, vp],
+    "ipex_symm_barrier": [vp, ci, ci, vp, vp],
+    "ipex_wait_timeout_probe": [vp, ci, ci, vp, vp],
     "ipex_gemv_int4_direct": [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp, cf, cf, vp, vp, ci, ci, vp, ci, ci, vp],
     "ipex_rms_norm": [vp, vp, vp, vp, vp, i64, ci, cf, cf, ci, ci, vp],
     "ipex_layer_norm": [vp, vp, vp, vp, i64, ci, cf, ci, vp],
@@ -46,8 +51,6 @@ _OPTIONAL = {
     "ipex_gemm_bf16_tcgen05": [vp, vp, vp, ci, ci, ci, ci, ci, ci, vp, vp, ci, ci, vp],
     "ipex_gemm_lowbit_tcgen05": [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp, vp, ci, vp, ci, ci, vp],
     "ipex_moe_softmax_topk": [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp],
-    "ipex_allreduce_oneshot": [vp, vp, vp, i64, ci, ci, ci, vp, ci, ci, vp],
-    "ipex_gemv_lowbit_ar": [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp, vp, ci, vp, ci, vp, vp, ci, ci, ci, vp, ci, ci, vp],
 }
 
 

@@ -31,7 +31,7 @@ QTYPE_TO_WF = {
 
 _lut_cache = {}
 _USE_PDL = os.environ.get("IPEX_LLM_PDL", "1") != "0"
-_GEMV_IMPL = os.environ.get("IPEX_LLM_GEMV", "direct")   # direct | tma | v1
+_GEMV_IMPL = os.environ.get("IPEX_LLM_GEMV", "tma")   # tma | direct | v1
 _err_flags = {}
 
 
@@ -118,6 +118,26 @@ def gemv_lowbit(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K: in
                               residual.stride(0) if residual is not None else 0, act, ptr(lut), _dt(x),
                               int(pdl and _USE_PDL), current_stream())
     api.check(rc, "gemv_lowbit")
+    return out
+
+
+def gemv_lowbit_ar(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K: int, out: torch.Tensor, comm,
+                   bias: torch.Tensor = None, residual: torch.Tensor = None, pdl: bool = False, wf: int = None):
+    """Row-parallel GEMV fused with its all-reduce: ``out = sum_over_ranks(x_r @ W_r.T) (+ bias) (+ residual)``.
+    ``comm`` is the group's ``SymmComm``; every rank must issue the same sequence of calls."""
+    lib = cuda_lib()
+    M = x.shape[0]
+    assert 1 <= M <= GEMV_MAX_M and x.stride(-1) == 1
+    if wf is None:
+        wf = QTYPE_TO_WF[qtype]
+    lut = lut_for(qtype, x.device) if wf == api.WF_LUT4 else None
+    rank, world, npad, bufs, flags = comm.gemv_ar_args()
+    rc = lib.ipex_gemv_lowbit_tma_ar(ptr(w_data), wf, ptr(x), ptr(out), M, N, K, x.stride(0), out.stride(0), None,
+                                     0.0, 0.0, ptr(bias), ptr(residual),
+                                     residual.stride(0) if residual is not None else 0, ptr(lut), _dt(x),
+                                     int(pdl and _USE_PDL), ptr(error_flag(x.device)), current_stream(), rank, world,
+                                     npad, ptr(bufs), ptr(flags))
+    api.check(rc, "gemv_lowbit_tma_ar")
     return out
 
 

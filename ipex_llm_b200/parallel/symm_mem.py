@@ -1,0 +1,110 @@
+"""Symmetric peer memory for the tensor-parallel kernels.
+
+Stands in for the reference's oneCCL / ``deepspeed.comm`` backend (component N7: ``dist.init_process_group('ccl')``,
+python/llm/src/ipex_llm/transformers/pipeline_parallel.py:108-112; ``inference_all_reduce`` in
+low_bit_linear.py:680).  One NCCL process group is still used for bootstrap, pipeline p2p and as a fallback;
+the latency-critical decode collectives run on a per-rank buffer that every peer maps (CUDA VMM through
+``torch.distributed._symmetric_memory``), so a kernel can store into / load from any GPU of the node directly.
+
+Layout of each rank's buffer, for each of two call parities:
+  [ 64 block counters | 2048 tile counters | all-reduce staging (ar_bytes) | GEMV partials [world][8][npad] fp32 ]
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..native import cuda_api as api
+from ..native.lib import cuda_lib, current_stream, ptr
+
+_N_BLOCK_FLAGS = 64
+_N_TILE_FLAGS = 4096
+
+
+class SymmComm:
+    _instances = {}
+
+    @classmethod
+    def get(cls, group=None):
+        key = id(group) if group is not None else 0
+        if key not in cls._instances:
+            cls._instances[key] = cls(group)
+        return cls._instances[key]
+
+    def __init__(self, group=None, ar_bytes: int = 8 << 20, npad: int = 32768):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.ar_bytes = ar_bytes
+        self.npad = npad
+        self.flag_bytes = (_N_BLOCK_FLAGS + _N_TILE_FLAGS) * 4
+        self.gemv_bytes = self.world * 8 * npad * 4
+        self.parity_bytes = (self.flag_bytes + ar_bytes + self.gemv_bytes + 255) // 256 * 256
+        total = 2 * self.parity_bytes
+        self.buf = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
+        self.buf.zero_()
+        torch.cuda.synchronize()
+        try:
+            self.handle = symm_mem.rendezvous(self.buf, self.group)
+        except Exception:  # noqa: BLE001  (older signatures take the group name)
+            name = self.group.group_name
+            if hasattr(symm_mem, "enable_symm_mem_for_group"):
+                symm_mem.enable_symm_mem_for_group(name)
+            self.handle = symm_mem.rendezvous(self.buf, name)
+        base_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        dist.barrier(group=self.group)
+
+        def ptr_array(offset):
+            return torch.tensor([p + offset for p in base_ptrs], dtype=torch.int64, device=self.device)
+
+        self.block_flags, self.tile_flags, self.ar_bufs, self.gemv_bufs = [], [], [], []
+        for par in range(2):
+            o = par * self.parity_bytes
+            self.block_flags.append(ptr_array(o))
+            self.tile_flags.append(ptr_array(o + _N_BLOCK_FLAGS * 4))
+            self.ar_bufs.append(ptr_array(o + self.flag_bytes))
+            self.gemv_bufs.append(ptr_array(o + self.flag_bytes + ar_bytes))
+        self._local_ar = [self.buf[par * self.parity_bytes + self.flag_bytes:
+                                   par * self.parity_bytes + self.flag_bytes + ar_bytes] for par in range(2)]
+        self._parity = 0
+        from ..ops.cuda_ops import error_flag
+        self.err = error_flag(self.device)
+
+    # ------------------------------------------------------------------------------------------------
+    def next_parity(self) -> int:
+        """Every collective call (on every rank, in the same order) takes the next parity."""
+        p = self._parity
+        self._parity ^= 1
+        return p
+
+    def can_all_reduce(self, t: torch.Tensor) -> bool:
+        return t.is_cuda and t.is_contiguous() and t.numel() * t.element_size() <= self.ar_bytes and \
+            t.dtype in (torch.float16, torch.bfloat16, torch.float32)
+
+    def all_reduce(self, t: torch.Tensor, pdl: bool = False) -> torch.Tensor:
+        """In-place sum over the group through peer loads (one-shot: every rank reads every peer)."""
+        lib = cuda_lib()
+        par = self.next_parity()
+        nbytes = t.numel() * t.element_size()
+        stage = self._local_ar[par][:nbytes].view(t.dtype)
+        stage.copy_(t.reshape(-1))
+        blocks = max(1, min(_N_BLOCK_FLAGS, (t.numel() + 4095) // 4096))
+        rc = lib.ipex_allreduce_oneshot(ptr(self.ar_bufs[par]), ptr(self.block_flags[par]), ptr(t), t.numel(),
+                                        api.dtype_code(t.dtype), self.rank, self.world, ptr(self.err), blocks,
+                                        int(pdl), current_stream())
+        api.check(rc, "allreduce_oneshot")
+        return t
+
+    def barrier(self):
+        lib = cuda_lib()
+        par = self.next_parity()
+        rc = lib.ipex_symm_barrier(ptr(self.block_flags[par]), self.rank, self.world, ptr(self.err),
+                                   current_stream())
+        api.check(rc, "symm_barrier")
+
+    def gemv_ar_args(self):
+        """(rank, world, npad, bufs_ptr_array, tile_flags_ptr_array) for the next fused GEMV+all-reduce call."""
+        par = self.next_parity()
+        return self.rank, self.world, self.npad, self.gemv_bufs[par], self.tile_flags[par]

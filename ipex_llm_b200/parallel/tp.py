@@ -111,8 +111,10 @@ def _shard_cols(w, rank, world):
 
 def _column(lin: nn.Linear, rank, world, group, unit=1):
     w = _shard_rows(lin.weight.data, rank, world, unit)
-    new = ColumnParallelLinear(lin.in_features, w.shape[0], lin.bias is not None, mp_group=group,
+    # no mp_group on column-parallel layers: the converter all-reduces whatever carries one
+    new = ColumnParallelLinear(lin.in_features, w.shape[0], lin.bias is not None, mp_group=None,
                                device="meta", dtype=w.dtype)
+    new.tp_group = group
     new.weight = nn.Parameter(w, requires_grad=False)
     if lin.bias is not None:
         new.bias = nn.Parameter(_shard_rows(lin.bias.data, rank, world, unit), requires_grad=False)
