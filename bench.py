@@ -117,6 +117,8 @@ def main():
     ap.add_argument("--prompt", type=int, default=None)
     ap.add_argument("--low-bit", default=None)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--layers", type=int, default=None,
+                    help="profiling only: truncate the model to this many layers (the JSON line then names it)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -154,6 +156,9 @@ def main():
     from ipex_llm.transformers import AutoModelForCausalLM
     from ipex_llm_b200.engine import get_engine
 
+    if args.layers:
+        spec["num_hidden_layers"] = args.layers
+        name = f"{name}-{args.layers}layers-PROFILING-ONLY"
     cfg = LlamaConfig(tie_word_embeddings=False, **spec)
     tp_group = None
     if n_gpus > 1:

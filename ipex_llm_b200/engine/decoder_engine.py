@@ -268,7 +268,7 @@ class DecoderEngine:
     def decode_step(self, B: int, use_graph: bool = True):
         """One token for every sequence.  The step is captured once per (batch, cache) and replayed."""
         if self._nsplit is None:
-            self._nsplit = cuda_ops.pick_nsplit(B, self.n_kv, self.max_len)
+            self._nsplit = cuda_ops.pick_nsplit(B, self.n_kv, self.max_len, rows=self.n_heads // self.n_kv)
         if not use_graph or os.environ.get("IPEX_LLM_ENGINE_GRAPH", "1") == "0":
             self._step_kernels(B)
             return

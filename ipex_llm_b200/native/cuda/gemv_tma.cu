@@ -193,7 +193,10 @@ __device__ void stage_x(const TmaArgs& a, __half* xs, int xs_stride, int Kp, flo
 }
 
 template <int WF, typename T, int RT>
-__global__ void __launch_bounds__(kThreadsTma, 1) gemv_tma_kernel(TmaArgs a) {
+#ifndef IPEX_GEMV_MIN_BLOCKS
+#define IPEX_GEMV_MIN_BLOCKS 1
+#endif
+__global__ void __launch_bounds__(kThreadsTma, IPEX_GEMV_MIN_BLOCKS) gemv_tma_kernel(TmaArgs a) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   constexpr bool k4bit = WF == WF_SYM_INT4 || WF == WF_ASYM_INT4 || WF == WF_LUT4;
   constexpr int CB = k4bit ? 1024 : 2048;                 // code bytes per 128-k chunk of a row tile

@@ -78,7 +78,7 @@ def cuda_lib() -> ctypes.CDLL:
     if _cuda is None:
         with _lock:
             if _cuda is None:
-                path = _build.CUDA_LIB
+                path = os.environ.get("IPEX_LLM_CUDA_LIB") or _build.CUDA_LIB
                 if not os.path.exists(path):
                     try:
                         path = _build.build_cuda()

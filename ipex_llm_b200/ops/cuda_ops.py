@@ -374,11 +374,19 @@ def sdpa_decode_supported(head_dim: int, v_head_dim: int) -> bool:
     return head_dim == v_head_dim and head_dim in (64, 128, 256)
 
 
-def pick_nsplit(B: int, Hkv: int, kv_len: int, n_sm: int = 148) -> int:
-    ctas = max(1, B * Hkv)
-    want = max(1, (int(os.environ.get("IPEX_LLM_ATTN_WAVES", "4")) * n_sm) // ctas)
-    by_len = max(1, kv_len // 128)
-    return int(max(1, min(want, by_len, 64)))
+def pick_nsplit(B: int, Hkv: int, kv_len: int, n_sm: int = 148, rows: int = 1) -> int:
+    """Number of KV splits.  A warp walks its tokens serially (4 per step, one step prefetched), so the split
+    count is chosen to keep that chain short: about ``IPEX_LLM_ATTN_STEPS`` steps per warp.  ``rows`` = q rows
+    per kv head (GQA group x query length): with more rows the warps of a CTA divide rows, not tokens."""
+    steps = int(os.environ.get("IPEX_LLM_ATTN_STEPS", "8"))
+    rows_blk = min(16, max(1, rows))
+    rw = 1 if rows_blk <= 1 else (2 if rows_blk <= 8 else 4)
+    row_groups = -(-rows_blk // rw)
+    rg_p2 = 1 if row_groups <= 1 else (2 if row_groups <= 2 else 4)
+    ts = 4 // rg_p2                      # warps sharing a row group split the tokens
+    tokens_per_split = 4 * ts * steps
+    by_len = max(1, -(-kv_len // tokens_per_split))
+    return int(max(1, min(by_len, 128)))
 
 
 def attn_workspace(device, floats: int, ints: int):
@@ -417,8 +425,8 @@ def sdpa_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask, scale: 
     if q.stride(-1) != 1:
         q = q.contiguous()
     out = torch.empty((B, Sq, Hq, D), dtype=q.dtype, device=q.device)
-    nsplit = pick_nsplit(B, Hkv, Skv)
     G = Hq // Hkv
+    nsplit = pick_nsplit(B, Hkv, Skv, rows=G * Sq)
     floats = lib.ipex_attn_decode_scratch_floats(B, Hkv, G, Sq, D, nsplit)
     ints = lib.ipex_attn_decode_counter_ints(B, Hkv, G, Sq)
     scratch, counters = attn_workspace(q.device, floats, ints)

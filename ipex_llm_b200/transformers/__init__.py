@@ -9,6 +9,9 @@ from .model import (AutoModel, AutoModelForCausalLM, AutoModelForMaskedLM, AutoM
 
 def __getattr__(name):
     if name in ("init_pipeline_parallel", "PPModelWorker", "pipeline_parallel"):
-        from . import pipeline_parallel as _pp
-        return getattr(_pp, name)
+        import importlib
+        _pp = importlib.import_module(__name__ + ".pipeline_parallel")
+        # the submodule and the function share the name ``pipeline_parallel``: attribute access gives the
+        # submodule once it is imported, as in the reference package
+        return _pp if name == "pipeline_parallel" else getattr(_pp, name)
     raise AttributeError(name)

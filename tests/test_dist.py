@@ -62,6 +62,37 @@ def test_tensor_parallel_gpu(tp_llama_dir):
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
 
 
+@pytest.fixture(scope="module")
+def pp_llama_dir(tmp_path_factory):
+    """Tiny Llama with 5 layers, so that 2 stages get 3 + 2 layers."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(hidden_size=128, intermediate_size=256, num_hidden_layers=5, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=32000, max_position_embeddings=512, tie_word_embeddings=False)
+    torch.manual_seed(1)
+    m = LlamaForCausalLM(cfg)
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() > 1:
+                p.normal_(0.0, 0.05)
+    d = tmp_path_factory.mktemp("pp_llama")
+    m.save_pretrained(d)
+    return str(d)
+
+
+def test_pipeline_parallel_cpu_gloo(pp_llama_dir):
+    res = run_workers("pp_worker.py", 2, ["--device", "cpu", "--model-dir", pp_llama_dir])
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert res.stdout.count(": ok") == 2
+
+
+@pytest.mark.gpu
+def test_pipeline_parallel_gpu(pp_llama_dir):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    res = run_workers("pp_worker.py", 2, ["--device", "cuda", "--model-dir", pp_llama_dir])
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+
+
 @pytest.mark.gpu
 def test_device_wait_times_out_cleanly():
     """A bounded device-side wait that nothing satisfies returns an error status and leaves the context usable."""
