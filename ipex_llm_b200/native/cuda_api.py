@@ -48,7 +48,8 @@ _I64_RET = {
 
 # optional entry points: declared when the library exports them (kernels added over time)
 _OPTIONAL = {
-    "ipex_gemm_bf16_tcgen05": [vp, vp, vp, ci, ci, ci, ci, ci, ci, vp, vp, ci, ci, vp],
+    "ipex_gemm_tcgen05": [vp, vp, vp, vp, vp, ci, ci, ci, i64, i64, i64, i64, ci, vp, vp],
+    "ipex_gemm_tcgen05_token_tile": [ci],
     "ipex_gemm_lowbit_tcgen05": [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp, vp, ci, vp, ci, ci, vp],
     "ipex_moe_softmax_topk": [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp],
 }

@@ -201,7 +201,7 @@ def dense_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         wf = api.WF_F16 if w.dtype == torch.float16 else api.WF_BF16
         return gemv_lowbit(x, w, None, N, K, wf=wf)
     lib = cuda_lib()
-    if getattr(lib, "ipex_gemm_bf16_tcgen05", None) is not None and os.environ.get("IPEX_LLM_TCGEN05", "1") != "0":
+    if getattr(lib, "ipex_gemm_tcgen05", None) is not None and os.environ.get("IPEX_LLM_TCGEN05", "1") != "0":
         from . import tcgen05_gemm
         if tcgen05_gemm.dense_supported(M, N, K, x.dtype) and x.dtype == w.dtype:
             return tcgen05_gemm.gemm_dense(x, w)

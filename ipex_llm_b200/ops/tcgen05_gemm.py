@@ -1,0 +1,82 @@
+"""Python front of the tcgen05 (5th-gen tensor core) GEMM kernels used for prompts and batches.
+
+``gemm_dense``  : ``x[M,K] @ w[N,K].T`` for fp16/bf16 weights (TMA -> swizzled shared memory -> tcgen05.mma -> TMEM).
+``gemm_lowbit`` : the same contraction with packed low-bit weights dequantized inside the kernel's producer warps.
+
+Reference counterpart: the GEMM branch of ``xe_linear.forward_new`` that the reference takes for prompts
+(python/llm/src/ipex_llm/transformers/low_bit_linear.py:640-668) and ``xe_batch.batch_forward``.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..native import cuda_api as api
+from ..native.lib import cuda_lib, current_stream, ptr
+from ..quant import qtypes as qt
+
+
+def _err(device):
+    from . import cuda_ops
+    return cuda_ops.error_flag(device)
+
+
+def dense_supported(M: int, N: int, K: int, dtype) -> bool:
+    return dtype in (torch.float16, torch.bfloat16) and K % 8 == 0 and M >= 1 and N >= 8
+
+
+def gemm_dense(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor = None, residual: torch.Tensor = None,
+               out: torch.Tensor = None) -> torch.Tensor:
+    """``x [M, K] @ w[N, K].T (+ bias) (+ residual)``; ``x``/``w`` row strides must be multiples of 8 elements."""
+    lib = cuda_lib()
+    M, K = x.shape
+    N = w.shape[0]
+    if x.stride(1) != 1 or x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0:
+        x = x.contiguous()
+    if w.stride(1) != 1 or w.stride(0) % 8 != 0 or w.data_ptr() % 16 != 0:
+        w = w.contiguous()
+    if out is None:
+        out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    if residual is not None and residual.stride(1) != 1:
+        residual = residual.contiguous()
+    rc = lib.ipex_gemm_tcgen05(ptr(x), ptr(w), ptr(out), ptr(bias), ptr(residual), M, N, K, x.stride(0), w.stride(0),
+                               out.stride(0), residual.stride(0) if residual is not None else 0,
+                               api.dtype_code(x.dtype), ptr(_err(x.device)), current_stream())
+    if rc == -1:
+        raise RuntimeError("ipex_llm_b200: the driver's tensor-map encoder rejected the GEMM operands")
+    api.check(rc, "gemm_tcgen05")
+    return out
+
+
+# weight families the in-kernel dequantizer handles (codes of native/cuda/common/utils.cuh)
+_LOWBIT_FAMILIES = ("WF_SYM_INT4", "WF_ASYM_INT4", "WF_LUT4", "WF_FP8_E4M3", "WF_FP8_E5M2", "WF_INT8")
+
+
+def supported(M: int, N: int, K: int, qtype: int) -> bool:
+    from .cuda_ops import QTYPE_TO_WF
+    lib = cuda_lib()
+    if getattr(lib, "ipex_gemm_lowbit_tcgen05", None) is None or qtype not in QTYPE_TO_WF:
+        return False
+    ok = {getattr(api, n) for n in _LOWBIT_FAMILIES if hasattr(api, n)}
+    return QTYPE_TO_WF[qtype] in ok and K % 128 == 0 and N % 16 == 0
+
+
+def gemm_lowbit(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K: int, out: torch.Tensor = None,
+                bias: torch.Tensor = None, residual: torch.Tensor = None) -> torch.Tensor:
+    from .cuda_ops import QTYPE_TO_WF, lut_for
+    lib = cuda_lib()
+    M = x.shape[0]
+    if x.stride(1) != 1 or x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0:
+        x = x.contiguous()
+    if out is None:
+        out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    if residual is not None and residual.stride(1) != 1:
+        residual = residual.contiguous()
+    rc = lib.ipex_gemm_lowbit_tcgen05(ptr(x), ptr(w_data), ptr(out), ptr(bias), ptr(residual),
+                                      ptr(lut_for(qtype, x.device)), M, N, K, x.stride(0), out.stride(0),
+                                      residual.stride(0) if residual is not None else 0, QTYPE_TO_WF[qtype],
+                                      api.dtype_code(x.dtype), ptr(_err(x.device)), current_stream())
+    if rc == -1:
+        raise RuntimeError("ipex_llm_b200: the driver's tensor-map encoder rejected the GEMM operands")
+    api.check(rc, "gemm_lowbit_tcgen05")
+    return out
+
