@@ -179,13 +179,17 @@ def main():
     # ---- prompt pass (1st token), timed on the device ----
     ids = ids_host.to(dev)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    ev0.record()
-    logits = eng.prefill(ids)
-    nxt = torch.argmax(logits, dim=-1)
-    ev1.record()
-    torch.cuda.synchronize()
-    first_ms = ev0.elapsed_time(ev1)
+    first_cold_ms = first_ms = 0.0
+    for attempt in range(2):       # the first pass pays one-time set-up (module load, workspaces); report the second
+        torch.cuda.synchronize()
+        ev0.record()
+        logits = eng.prefill(ids)
+        nxt = torch.argmax(logits, dim=-1)
+        ev1.record()
+        torch.cuda.synchronize()
+        if attempt == 0:
+            first_cold_ms = ev0.elapsed_time(ev1)
+        first_ms = ev0.elapsed_time(ev1)
     eng.tokens[:batch] = nxt
 
     def barrier():
@@ -249,6 +253,7 @@ def main():
                                     f"({sum(p.numel() * p.element_size() for p in model.parameters()) / 1e9:.2f} GB)",
                        "decode_engine": "cuda-graph + programmatic dependent launch"},
             "first_token_ms": round(first_ms, 3),
+            "first_token_cold_ms": round(first_cold_ms, 3),
             "model_build_s": round(load_s, 2),
             "gpu_launches": int(args.steps * eng.kernel_launches_per_step),
             "clocks": clocks,

@@ -72,7 +72,8 @@ class MatMulLowBitCPU(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, A, weight):
-        result = ggml_matmul_src1_x_src0_t(weight.data, A, weight._shape, weight.qtype).to(A.dtype)
+        raw = weight.data if weight.data.dtype == torch.uint8 else weight.data.view(torch.uint8)
+        result = ggml_matmul_src1_x_src0_t(raw, A.detach(), weight._shape, weight.qtype).to(A.dtype)
         if any(ctx.needs_input_grad[:2]):
             ctx.weight = weight
         else:

@@ -61,19 +61,24 @@ def supported(M: int, N: int, K: int, qtype: int) -> bool:
 
 
 def gemm_lowbit(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K: int, out: torch.Tensor = None,
-                bias: torch.Tensor = None, residual: torch.Tensor = None) -> torch.Tensor:
+                bias: torch.Tensor = None, residual: torch.Tensor = None, act: int = 0, wf: int = None) -> torch.Tensor:
+    """``x [M, K] @ dequant(w).T`` with the packed device tiles of ``qtype`` (or of family ``wf``).  ``act`` 1/2
+    (silu / gelu-tanh) treats the rows as 16-row-interleaved gate/up and returns ``[M, N/2]``."""
     from .cuda_ops import QTYPE_TO_WF, lut_for
     lib = cuda_lib()
     M = x.shape[0]
     if x.stride(1) != 1 or x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0:
         x = x.contiguous()
     if out is None:
-        out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+        out = torch.empty((M, N // 2 if act else N), dtype=x.dtype, device=x.device)
     if residual is not None and residual.stride(1) != 1:
         residual = residual.contiguous()
-    rc = lib.ipex_gemm_lowbit_tcgen05(ptr(x), ptr(w_data), ptr(out), ptr(bias), ptr(residual),
-                                      ptr(lut_for(qtype, x.device)), M, N, K, x.stride(0), out.stride(0),
-                                      residual.stride(0) if residual is not None else 0, QTYPE_TO_WF[qtype],
+    if wf is None:
+        wf = QTYPE_TO_WF[qtype]
+    lut = lut_for(qtype, x.device) if qtype is not None else None
+    rc = lib.ipex_gemm_lowbit_tcgen05(ptr(x), ptr(w_data), ptr(out), ptr(bias), ptr(residual), ptr(lut), M, N, K,
+                                      x.stride(0), out.stride(0),
+                                      residual.stride(0) if residual is not None else 0, wf, int(act),
                                       api.dtype_code(x.dtype), ptr(_err(x.device)), current_stream())
     if rc == -1:
         raise RuntimeError("ipex_llm_b200: the driver's tensor-map encoder rejected the GEMM operands")

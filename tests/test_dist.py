@@ -93,6 +93,21 @@ def test_pipeline_parallel_gpu(pp_llama_dir):
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
 
 
+def test_dp_fused_optimizer_cpu_gloo():
+    res = run_workers("dp_worker.py", 2, ["--device", "cpu"])
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert res.stdout.count(": ok") == 2
+
+
+@pytest.mark.gpu
+def test_dp_fused_optimizer_gpu():
+    """reduce-scatter + AdamW + all-gather in one kernel over peer memory."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    res = run_workers("dp_worker.py", 2, ["--device", "cuda"])
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+
+
 @pytest.mark.gpu
 def test_device_wait_times_out_cleanly():
     """A bounded device-side wait that nothing satisfies returns an error status and leaves the context usable."""

@@ -52,6 +52,66 @@ def test_gemm_dense_bias_residual_strided():
     assert _rel_err(out, ref) < 3e-3
 
 
+TILED = ["sym_int4", "asym_int4", "nf4", "fp4", "fp8_e4m3", "fp8_e5m2", "sym_int8"]
+
+
+@pytest.mark.parametrize("name", TILED)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(40, 144, 256), (300, 1008, 1024), (1024, 4096, 4096)])
+def test_gemm_lowbit_vs_dequantized(name, dtype, shape):
+    """In-kernel dequantization: compare with fp32 matmul over the weights the tile dequantizer produces."""
+    from ipex_llm_b200.ops import cuda_ops, tcgen05_gemm
+    from ipex_llm_b200.ops.cuda_quant import quantize_to_device_layout
+    from ipex_llm_b200.quant import qtypes as qt
+    M, N, K = shape
+    if shape[0] == 1024 and name not in ("sym_int4", "fp8_e4m3", "nf4"):
+        pytest.skip("large shape covered by three families")
+    q = qt.qtype_from_name(name)
+    torch.manual_seed(N + K)
+    w = torch.randn(N, K, device="cuda") * 0.05
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dtype)
+    packed = quantize_to_device_layout(w.half(), q)
+    deq = cuda_ops.dequantize_device(packed, (N, K), q, torch.float32)
+    assert tcgen05_gemm.supported(M, N, K, q)
+    out = tcgen05_gemm.gemm_lowbit(x, packed, q, N, K)
+    torch.cuda.synchronize()
+    cuda_ops.check_error_flag(x.device)
+    ref = x.float() @ deq.t()
+    # the kernel rounds each dequantized weight (and its scale) to the activation dtype before the MMA
+    tol = 4e-3 if dtype == torch.float16 else 1.5e-2
+    assert _rel_err(out, ref) < tol, (name, dtype, _rel_err(out, ref))
+    out2 = tcgen05_gemm.gemm_lowbit(x, packed, q, N, K)
+    assert torch.equal(out, out2)
+
+
+def test_gemm_lowbit_bias_residual_and_gate_up_act():
+    from ipex_llm_b200.engine.decoder_engine import _W, _interleave_row_tiles
+    from ipex_llm_b200.ops import cuda_ops, tcgen05_gemm
+    from ipex_llm_b200.ops.cuda_quant import quantize_to_device_layout
+    from ipex_llm_b200.quant import qtypes as qt
+    torch.manual_seed(5)
+    M, N, K = 150, 512, 768
+    q = qt.qtype_from_name("sym_int4")
+    x = (torch.randn(M, K, device="cuda") * 0.5).half()
+    wg, wu = torch.randn(N, K, device="cuda") * 0.05, torch.randn(N, K, device="cuda") * 0.05
+    pg, pu = quantize_to_device_layout(wg.half(), q), quantize_to_device_layout(wu.half(), q)
+    dg = cuda_ops.dequantize_device(pg, (N, K), q, torch.float32)
+    du = cuda_ops.dequantize_device(pu, (N, K), q, torch.float32)
+    # bias + residual
+    bias, res = torch.randn(N, device="cuda").half(), torch.randn(M, N, device="cuda").half()
+    out = tcgen05_gemm.gemm_lowbit(x, pg, q, N, K, bias=bias, residual=res)
+    assert _rel_err(out, x.float() @ dg.t() + bias.float() + res.float()) < 4e-3
+    # silu(gate) * up over 16-row-interleaved tiles
+    wf = cuda_ops.QTYPE_TO_WF[q]
+    merged = _interleave_row_tiles(_W(pg, wf, q, N, K), _W(pu, wf, q, N, K))
+    out = tcgen05_gemm.gemm_lowbit(x, merged.data, q, 2 * N, K, act=1)
+    g = x.float() @ dg.t()
+    ref = torch.nn.functional.silu(g) * (x.float() @ du.t())
+    assert out.shape == (M, N)
+    assert _rel_err(out, ref) < 6e-3
+    cuda_ops.check_error_flag(x.device)
+
+
 def test_dense_linear_routes_to_tcgen05():
     from ipex_llm_b200.ops import cuda_ops
     torch.manual_seed(4)
