@@ -192,20 +192,122 @@ __device__ void stage_x(const TmaArgs& a, __half* xs, int xs_stride, int Kp, flo
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Integer path for symmetric int4 (internal family code WF_I8): the activations of a token become 15-bit integers
+// xi = hi * 128 + lo (hi, lo int8, one fp32 scale per token), the 4-bit codes become int8 operands with one logic
+// op per FOUR weights, and the products run on the s8 tensor-core instruction (m16n8k32).  Exact integer
+// accumulation per 64-group, then one int->float conversion and one FMA with the group's weight scale per output.
+// The "- 8" of the codes is applied by starting the accumulators at -8 * sum(x) of the group (precomputed when x is
+// staged), so it costs nothing in the loop.  Operand order: a word of 8 codes masks into bytes (k0,k4,k1,k5) and
+// (k2,k6,k3,k7); x is stored in the same order, so no byte shuffles are needed on either side.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int WF_I8 = 100;
+constexpr int kI8Pad = 64;  // extra bytes per staged token row: 8 rows x 4 lanes x 16 B hit 32 distinct 16-byte banks
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// x -> (hi, lo) int8 rows in the octet order above, per-token scale, per-(group, token) accumulator seeds.
+//   xh / xl : [M][Kp + kI8Pad] bytes      dxs : [8] floats      seeds : [Kp/64][8 tokens] int2 = (-8 sum hi, -8 sum lo)
+template <typename T>
+__device__ void stage_x_i8(const TmaArgs& a, int8_t* xh, int8_t* xl, int stride, int Kp, float* dxs, int2* seeds,
+                           float* scratch) {
+  const int tid = threadIdx.x;
+  const T* x = reinterpret_cast<const T*>(a.x);
+  const T* nw = reinterpret_cast<const T*>(a.norm_w);
+  const int nvec = a.K / 8;  // K % 64 == 0
+  const int groups = Kp / 64;
+  for (int i = tid; i < groups * 8; i += kCThreads)
+    if ((i & 7) >= a.M) seeds[i] = make_int2(0, 0);
+  if (tid < 8) dxs[tid] = 0.f;
+  for (int m = 0; m < a.M; m++) {
+    const T* xr = x + (size_t)m * a.ldx;
+    float ss = 0.f, mx = 0.f;
+    for (int v = tid; v < nvec; v += kCThreads) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(xr + v * 8);
+      const T* e = reinterpret_cast<const T*>(&raw);
+      uint4 wraw = make_uint4(0, 0, 0, 0);
+      if (nw != nullptr) wraw = *reinterpret_cast<const uint4*>(nw + v * 8);
+      const T* we = reinterpret_cast<const T*>(&wraw);
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        float f = DT<T>::to_f(e[j]);
+        ss += f * f;
+        if (nw != nullptr) f *= DT<T>::to_f(we[j]) + a.norm_offset;
+        mx = fmaxf(mx, fabsf(f));
+      }
+    }
+    ss = warp_sum(ss);
+    mx = warp_max(mx);
+    if ((tid & 31) == 0) { scratch[tid >> 5] = ss; scratch[kCW + (tid >> 5)] = mx; }
+    consumer_sync();
+    float tot = 0.f, amax = 0.f;
+#pragma unroll
+    for (int w = 0; w < kCW; w++) { tot += scratch[w]; amax = fmaxf(amax, scratch[kCW + w]); }
+    const float rstd = nw != nullptr ? rsqrtf(tot / (float)a.K + a.eps) : 1.0f;
+    amax *= rstd;
+    const float dx = amax > 0.f ? amax / 16383.f : 1.0f;
+    const float inv = rstd / dx;   // value * weight * inv = integer
+    if (tid == 0) dxs[m] = dx;
+    consumer_sync();
+    for (int v0 = 0; v0 < Kp / 8; v0 += kCThreads) {
+      const int v = v0 + tid;
+      int sh = 0, sl = 0;
+      if (v < Kp / 8) {
+        uint32_t ph[2] = {0, 0}, pl[2] = {0, 0};
+        if (v < nvec) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(xr + v * 8);
+          const T* e = reinterpret_cast<const T*>(&raw);
+          uint4 wraw = make_uint4(0, 0, 0, 0);
+          if (nw != nullptr) wraw = *reinterpret_cast<const uint4*>(nw + v * 8);
+          const T* we = reinterpret_cast<const T*>(&wraw);
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            float f = DT<T>::to_f(e[j]);
+            if (nw != nullptr) f *= DT<T>::to_f(we[j]) + a.norm_offset;
+            int xi = __float2int_rn(f * inv);
+            xi = max(-16383, min(16383, xi));
+            const int hi = xi >> 7, lo = xi & 127;
+            sh += hi;
+            sl += lo;
+            // element j of the octet -> byte position in (k0,k4,k1,k5 | k2,k6,k3,k7)
+            const int pos = ((j & 2) ? 4 : 0) + ((j & 1) ? 2 : 0) + ((j & 4) ? 1 : 0);
+            ph[pos >> 2] |= (uint32_t)(hi & 0xFF) << (8 * (pos & 3));
+            pl[pos >> 2] |= (uint32_t)lo << (8 * (pos & 3));
+          }
+        }
+        *reinterpret_cast<uint2*>(xh + (size_t)m * stride + v * 8) = make_uint2(ph[0], ph[1]);
+        *reinterpret_cast<uint2*>(xl + (size_t)m * stride + v * 8) = make_uint2(pl[0], pl[1]);
+      }
+      // 8 consecutive octets (= 8 consecutive lanes) form a 64-group
+      sh += __shfl_xor_sync(0xffffffffu, sh, 1); sl += __shfl_xor_sync(0xffffffffu, sl, 1);
+      sh += __shfl_xor_sync(0xffffffffu, sh, 2); sl += __shfl_xor_sync(0xffffffffu, sl, 2);
+      sh += __shfl_xor_sync(0xffffffffu, sh, 4); sl += __shfl_xor_sync(0xffffffffu, sl, 4);
+      if ((tid & 7) == 0 && v < Kp / 8) seeds[(v >> 3) * 8 + m] = make_int2(-8 * sh, -8 * sl);
+    }
+  }
+}
+
 template <int WF, typename T, int RT>
 #ifndef IPEX_GEMV_MIN_BLOCKS
 #define IPEX_GEMV_MIN_BLOCKS 1
 #endif
 __global__ void __launch_bounds__(kThreadsTma, IPEX_GEMV_MIN_BLOCKS) gemv_tma_kernel(TmaArgs a) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  constexpr bool k4bit = WF == WF_SYM_INT4 || WF == WF_ASYM_INT4 || WF == WF_LUT4;
+  constexpr bool kI8 = WF == WF_I8;
+  constexpr bool k4bit = WF == WF_SYM_INT4 || WF == WF_ASYM_INT4 || WF == WF_LUT4 || kI8;
   constexpr int CB = k4bit ? 1024 : 2048;                 // code bytes per 128-k chunk of a row tile
   constexpr int SB = 64;                                  // scale bytes per chunk
   constexpr int MB = WF == WF_ASYM_INT4 ? 64 : 0;         // min bytes per chunk
   const int Kp = (int)ceil_to_i64(a.K, 128);
   const int Np = (int)ceil_to_i64(a.N, 16);
   const int chunks = Kp / 128;
-  const int xs_stride = Kp + 8;
+  const int xs_stride = kI8 ? Kp + kI8Pad : Kp + 8;   // elements of xs (fp16) / bytes of each int8 plane
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int STAGES = a.stages, CPS = a.cps;
@@ -229,7 +331,11 @@ __global__ void __launch_bounds__(kThreadsTma, IPEX_GEMV_MIN_BLOCKS) gemv_tma_ke
   int* red_gen = red_cnt + kNB;                                // [kNB] generations
   off += 2 * kNB * sizeof(int);
   float* scratch = reinterpret_cast<float*>(smem_raw + off);
-  off += 64;
+  off += 128;
+  float* dxs = reinterpret_cast<float*>(smem_raw + off);       // integer path: per-token activation scale
+  off += 32;
+  int2* seeds = reinterpret_cast<int2*>(smem_raw + off);       // integer path: [Kp/64][8] accumulator seeds
+  if (kI8) off += (size_t)(Kp / 64) * 8 * sizeof(int2);
   float* xcorr = reinterpret_cast<float*>(smem_raw + off);     // int4: [M][Kp/64]
   if (WF == WF_SYM_INT4 || WF == WF_ASYM_INT4) off += (size_t)a.M * (Kp / 64) * sizeof(float);
   float* xsum = reinterpret_cast<float*>(smem_raw + off);      // asym: [M][Kp/64]
@@ -293,7 +399,10 @@ __global__ void __launch_bounds__(kThreadsTma, IPEX_GEMV_MIN_BLOCKS) gemv_tma_ke
     __half2 v = __floats2half2_rn(a.lut[tid & 15], a.lut[tid >> 4]);
     lut256[tid] = *reinterpret_cast<uint32_t*>(&v);
   }
-  stage_x<T, kInt4>(a, xs, xs_stride, Kp, scratch);
+  int8_t* xh = reinterpret_cast<int8_t*>(xs);
+  int8_t* xl = xh + (size_t)a.M * xs_stride;
+  if constexpr (kI8) stage_x_i8<T>(a, xh, xl, xs_stride, Kp, dxs, seeds, scratch);
+  else stage_x<T, kInt4>(a, xs, xs_stride, Kp, scratch);
   consumer_sync();
   if (kInt4) {
     // per (row of x, 64-group): the constant part of sum_k A_k x'_k to take out of the accumulator, and for the
@@ -342,6 +451,55 @@ __global__ void __launch_bounds__(kThreadsTma, IPEX_GEMV_MIN_BLOCKS) gemv_tma_ke
         const uint8_t* st_mins = st + CPS * (CB + SB);
         for (int c = warp; c < nch; c += kCW) {
           const int cg = c0 + c;
+          if constexpr (kI8) {
+            const uint8_t* tp = st + c * CB;
+            const uint4 qa = *reinterpret_cast<const uint4*>(tp + g * 64 + t * 16);
+            const uint4 qb = *reinterpret_cast<const uint4*>(tp + (g + 8) * 64 + t * 16);
+            const uint32_t s0 = *reinterpret_cast<const uint32_t*>(st_scales + c * SB + (0 * 16 + 2 * g) * 2);
+            const uint32_t s1 = *reinterpret_cast<const uint32_t*>(st_scales + c * SB + (1 * 16 + 2 * g) * 2);
+            uint4 h0 = make_uint4(0, 0, 0, 0), h1 = h0, l0 = h0, l1 = h0;
+            if (has_x) {
+              const int8_t* ph = xh + (size_t)g * xs_stride + cg * 128 + 16 * t;
+              const int8_t* pl = xl + (size_t)g * xs_stride + cg * 128 + 16 * t;
+              h0 = *reinterpret_cast<const uint4*>(ph);
+              h1 = *reinterpret_cast<const uint4*>(ph + 64);
+              l0 = *reinterpret_cast<const uint4*>(pl);
+              l1 = *reinterpret_cast<const uint4*>(pl + 64);
+            }
+            const int4 sd0 = *reinterpret_cast<const int4*>(seeds + (2 * cg) * 8 + 2 * t);
+            const int4 sd1 = *reinterpret_cast<const int4*>(seeds + (2 * cg + 1) * 8 + 2 * t);
+            constexpr uint32_t kM = 0x0F0F0F0Fu;
+            // group 0 (words x, y), group 1 (words z, w)
+            int ah0[4] = {sd0.x, sd0.z, sd0.x, sd0.z}, al0[4] = {sd0.y, sd0.w, sd0.y, sd0.w};
+            int ah1[4] = {sd1.x, sd1.z, sd1.x, sd1.z}, al1[4] = {sd1.y, sd1.w, sd1.y, sd1.w};
+            {
+              const uint32_t a0 = qa.x & kM, a1 = qb.x & kM, a2 = (qa.x >> 4) & kM, a3 = (qb.x >> 4) & kM;
+              mma_s8(ah0, a0, a1, a2, a3, h0.x, h0.y);
+              mma_s8(al0, a0, a1, a2, a3, l0.x, l0.y);
+            }
+            {
+              const uint32_t a0 = qa.z & kM, a1 = qb.z & kM, a2 = (qa.z >> 4) & kM, a3 = (qb.z >> 4) & kM;
+              mma_s8(ah1, a0, a1, a2, a3, h1.x, h1.y);
+              mma_s8(al1, a0, a1, a2, a3, l1.x, l1.y);
+            }
+            {
+              const uint32_t a0 = qa.y & kM, a1 = qb.y & kM, a2 = (qa.y >> 4) & kM, a3 = (qb.y >> 4) & kM;
+              mma_s8(ah0, a0, a1, a2, a3, h0.z, h0.w);
+              mma_s8(al0, a0, a1, a2, a3, l0.z, l0.w);
+            }
+            {
+              const uint32_t a0 = qa.w & kM, a1 = qb.w & kM, a2 = (qa.w >> 4) & kM, a3 = (qb.w >> 4) & kM;
+              mma_s8(ah1, a0, a1, a2, a3, h1.z, h1.w);
+              mma_s8(al1, a0, a1, a2, a3, l1.z, l1.w);
+            }
+            const float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&s0));
+            const float2 d1 = __half22float2(*reinterpret_cast<const __half2*>(&s1));
+            acc[r][0] += d0.x * (float)(ah0[0] * 128 + al0[0]) + d1.x * (float)(ah1[0] * 128 + al1[0]);
+            acc[r][1] += d0.x * (float)(ah0[1] * 128 + al0[1]) + d1.x * (float)(ah1[1] * 128 + al1[1]);
+            acc[r][2] += d0.y * (float)(ah0[2] * 128 + al0[2]) + d1.y * (float)(ah1[2] * 128 + al1[2]);
+            acc[r][3] += d0.y * (float)(ah0[3] * 128 + al0[3]) + d1.y * (float)(ah1[3] * 128 + al1[3]);
+            continue;
+          }
           uint4 xa0 = make_uint4(0, 0, 0, 0), xa1 = xa0, xb0 = xa0, xb1 = xa0;
           if (has_x) {
             const __half* xp = xs + g * xs_stride + cg * 128 + 16 * t;
@@ -483,6 +641,13 @@ __global__ void __launch_bounds__(kThreadsTma, IPEX_GEMV_MIN_BLOCKS) gemv_tma_ke
       if (!ok) break;
     }
     if (!ok) break;
+    if constexpr (kI8) {
+      const float dxa = dxs[2 * t], dxb = dxs[2 * t + 1];
+#pragma unroll
+      for (int r = 0; r < RT; r++) {
+        acc[r][0] *= dxa; acc[r][1] *= dxb; acc[r][2] *= dxa; acc[r][3] *= dxb;
+      }
+    }
 
     // ---- cross-warp reduction without a CTA-wide barrier ----
     // Every warp adds its partial tile into one of kNB zero-initialised shared accumulators (shared-memory
@@ -620,10 +785,11 @@ struct LaunchPlan {
 int g_ctas_per_sm = 1;
 int g_budget_kb = 140;
 int g_cps4 = 32;
+int g_int_path = 1;   // symmetric int4: integer tensor-core path (0 = fp16 operands)
 
 template <int WF, int RT>
 LaunchPlan plan(const TmaArgs& a) {
-  constexpr bool k4bit = WF == WF_SYM_INT4 || WF == WF_ASYM_INT4 || WF == WF_LUT4;
+  constexpr bool k4bit = WF == WF_SYM_INT4 || WF == WF_ASYM_INT4 || WF == WF_LUT4 || WF == WF_I8;
   const int CB = k4bit ? 1024 : 2048;
   const int MB = WF == WF_ASYM_INT4 ? 64 : 0;
   const int Kp = (int)ceil_to_i64(a.K, 128), Np = (int)ceil_to_i64(a.N, 16);
@@ -633,7 +799,10 @@ LaunchPlan plan(const TmaArgs& a) {
   if (p.cps < 1) p.cps = 1;
   if (p.cps > chunks) p.cps = chunks;
   const size_t stage_bytes = (size_t)p.cps * (CB + 64 + MB);
-  size_t fixed = (((size_t)a.M * (Kp + 8) * 2 + 15) & ~(size_t)15) + (size_t)kNB * RT * 128 * 4 + 2 * kNB * 4 + 64 + 256;
+  const size_t xrow = WF == WF_I8 ? (size_t)(Kp + kI8Pad) : (size_t)(Kp + 8);   // x 2 bytes (fp16, or two int8 planes)
+  size_t fixed = (((size_t)a.M * xrow * 2 + 15) & ~(size_t)15) + (size_t)kNB * RT * 128 * 4 + 2 * kNB * 4 + 128 + 32 +
+                 256;
+  if (WF == WF_I8) fixed += (size_t)(Kp / 64) * 8 * 8;
   if (WF == WF_ASYM_INT4) fixed += (size_t)a.M * (Kp / 64) * 4;
   if (WF == WF_SYM_INT4 || WF == WF_ASYM_INT4) fixed += (size_t)a.M * (Kp / 64) * 4;
   if (WF == WF_LUT4) fixed += 1024;
@@ -674,7 +843,8 @@ cudaError_t dispatch_rt(const TmaArgs& a, cudaStream_t s, bool pdl) {
 template <typename T>
 cudaError_t dispatch_wf(int wf, const TmaArgs& a, cudaStream_t s, bool pdl) {
   switch (wf) {
-    case WF_SYM_INT4: return dispatch_rt<WF_SYM_INT4, T>(a, s, pdl);
+    case WF_SYM_INT4:
+      return g_int_path ? dispatch_rt<WF_I8, T>(a, s, pdl) : dispatch_rt<WF_SYM_INT4, T>(a, s, pdl);
     case WF_ASYM_INT4: return dispatch_rt<WF_ASYM_INT4, T>(a, s, pdl);
     case WF_LUT4: return dispatch_rt<WF_LUT4, T>(a, s, pdl);
     case WF_FP8_E4M3: return dispatch_rt<WF_FP8_E4M3, T>(a, s, pdl);
@@ -685,6 +855,9 @@ cudaError_t dispatch_wf(int wf, const TmaArgs& a, cudaStream_t s, bool pdl) {
 }
 
 }  // namespace
+
+// Symmetric int4: 1 = integer (s8 tensor core) path, 0 = fp16-operand path.
+IPEX_API void ipex_gemv_tma_int_path(int on) { g_int_path = on != 0; }
 
 // Process-wide tuning of the pipelined GEMV (values <= 0 keep the current setting).
 IPEX_API void ipex_gemv_tma_tune(int ctas_per_sm, int budget_kb, int chunks_per_stage_4bit) {

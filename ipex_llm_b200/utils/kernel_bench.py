@@ -18,10 +18,27 @@ import os
 import torch
 
 
+_GRAPH = False
+
+
 def _time(fn, iters, warmup):
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
+    if _GRAPH:
+        # replay `iters` launches from one CUDA graph: removes the host's per-launch cost from the measurement
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(iters):
+                fn(i)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters * 1e3
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(iters):
@@ -131,7 +148,10 @@ def main(argv=None):
     ap.add_argument("--copies", type=int, default=0)
     ap.add_argument("--iters", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--graph", action="store_true", help="time a CUDA-graph replay of the launches")
     a = ap.parse_args(argv)
+    global _GRAPH
+    _GRAPH = a.graph
     if not torch.cuda.is_available():
         raise SystemExit("kernel_bench needs a CUDA device")
     res = {"gemv": bench_gemv, "gemm": bench_gemm, "attn": bench_attn, "rmsnorm": bench_rmsnorm}[a.op](a)

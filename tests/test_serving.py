@@ -1,0 +1,90 @@
+"""HTTP serving on CPU: tiny random Llama + a word-level tokenizer built in the test, FastAPI TestClient."""
+import json
+
+import pytest
+import torch
+
+
+@pytest.fixture(scope="module")
+def worker():
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import LlamaConfig, PreTrainedTokenizerFast
+    from ipex_llm.transformers import AutoModelForCausalLM
+    from ipex_llm_b200.serving import ModelWorker
+    words = ["<pad>", "<s>", "</s>", "<unk>"] + [f"w{i}" for i in range(60)]
+    tk = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tk.pre_tokenizer = pre_tokenizers.Whitespace()
+    tok = PreTrainedTokenizerFast(tokenizer_object=tk, pad_token="<pad>", bos_token="<s>", eos_token="</s>",
+                                  unk_token="<unk>", padding_side="left")
+    cfg = LlamaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=64, max_position_embeddings=256, tie_word_embeddings=False,
+                      eos_token_id=2, pad_token_id=0, bos_token_id=1)
+    model = AutoModelForCausalLM.from_config(cfg, load_in_low_bit="sym_int8", torch_dtype=torch.float32, device="cpu")
+    w = ModelWorker(model=model.eval(), tokenizer=tok, max_num_seqs=4)
+    yield w
+    w.shutdown()
+
+
+def test_batch_streamer_incremental_text():
+    from ipex_llm.transformers.streamer import BatchTextIteratorStreamer
+
+    class Tok:
+        def decode(self, ids, **kw):
+            return " ".join(f"w{i}" for i in ids)
+    s = BatchTextIteratorStreamer(2, Tok(), skip_prompt=True)
+    s.put(torch.tensor([[1, 2], [3, 4]]))          # prompt: skipped
+    s.put(torch.tensor([5, 6]))
+    s.put(torch.tensor([7, 8]))
+    s.end()
+    chunks = list(s)
+    assert "".join(c[0] for c in chunks) == "w5 w7" and "".join(c[1] for c in chunks) == "w6 w8"
+
+
+def test_generate_and_openai_endpoints(worker):
+    from fastapi.testclient import TestClient
+    from ipex_llm_b200.serving import FastApp
+    with TestClient(FastApp(worker, served_model_name="tiny").app) as c:
+        assert c.get("/health").text == "OK"
+        assert c.get("/v1/models").json()["data"][0]["id"] == "tiny"
+        r = c.post("/generate", json={"inputs": "w1 w2 w3", "parameters": {"max_new_tokens": 6}}).json()
+        assert r["generated_tokens"] <= 6 and r["prompt_tokens"] == 3 and isinstance(r["generated_text"], str)
+        ref = worker.submit_blocking("w1 w2 w3", __import__("ipex_llm_b200.serving", fromlist=["SamplingParams"])
+                                     .SamplingParams(max_new_tokens=6))
+        assert ref.text == r["generated_text"]          # batching / streaming does not change greedy output
+        r = c.post("/v1/completions", json={"model": "tiny", "prompt": ["w4 w5", "w6 w7 w8 w9"], "max_tokens": 5,
+                                            "temperature": 1.0}).json()
+        assert len(r["choices"]) == 2 and r["usage"]["prompt_tokens"] == 6
+        r = c.post("/v1/chat/completions", json={"model": "tiny", "max_tokens": 4, "messages": [
+            {"role": "user", "content": "w1 w2"}]}).json()
+        assert r["choices"][0]["message"]["role"] == "assistant" and r["usage"]["completion_tokens"] <= 4
+        m = c.get("/metrics").text
+        assert "ipex_llm_requests_total" in m
+
+
+def test_streaming_endpoints(worker):
+    from fastapi.testclient import TestClient
+    from ipex_llm_b200.serving import FastApp
+    with TestClient(FastApp(worker, served_model_name="tiny").app) as c:
+        full = c.post("/generate", json={"inputs": "w9 w8", "parameters": {"max_new_tokens": 8}}).json()
+        with c.stream("POST", "/generate_stream", json={"inputs": "w9 w8", "parameters": {"max_new_tokens": 8}}) as r:
+            events = [json.loads(l[6:]) for l in r.iter_lines() if l.startswith("data: ")]
+        assert "".join(e["token"]["text"] for e in events) == full["generated_text"]
+        assert events[-1]["finish_reason"] in ("length", "stop")
+        with c.stream("POST", "/v1/chat/completions", json={"model": "tiny", "stream": True, "max_tokens": 5,
+                                                            "messages": [{"role": "user", "content": "w3"}]}) as r:
+            lines = [l[6:] for l in r.iter_lines() if l.startswith("data: ")]
+        assert lines[-1] == "[DONE]"
+        chunks = [json.loads(l) for l in lines[:-1]]
+        assert chunks[0]["choices"][0]["delta"]["role"] == "assistant"
+        assert chunks[-1]["choices"][0]["finish_reason"] in ("stop", "length")
+
+
+def test_stop_string_truncates(worker):
+    from ipex_llm_b200.serving import SamplingParams
+    base = worker.submit_blocking("w1 w2", SamplingParams(max_new_tokens=10))
+    words = base.text.split()
+    if len(words) >= 3:
+        stop = words[2]
+        cut = worker.submit_blocking("w1 w2", SamplingParams(max_new_tokens=10, stop=[stop]))
+        assert stop not in cut.text and base.text.startswith(cut.text)
+        assert cut.finish_reason == "stop"
