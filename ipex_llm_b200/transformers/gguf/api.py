@@ -1,0 +1,190 @@
+"""``load_gguf_model``: build a low-bit model (and a tokenizer) straight from a ``.gguf`` file.
+
+Counterpart of python/llm/src/ipex_llm/transformers/gguf/api.py:30-75 and the per-family loaders under
+``gguf/models/`` (llama, mistral, mixtral, baichuan, bloom, falcon, mpt, yuan2).  One table-driven loader covers the
+llama-shaped families (llama, mistral, mixtral, qwen2, gemma, baichuan, yuan2's llama base): the GGUF tensor names are
+mapped to Hugging Face module names, q/k projections are un-permuted (llama.cpp stores them in the interleaved
+rotary order), every matrix is re-quantized to ``low_bit`` as it is read, and nothing of the model is ever held in
+full precision beyond one tensor.
+"""
+from __future__ import annotations
+
+import re
+from typing import Optional
+
+import torch
+
+from ...utils.common import invalidInputError
+
+# GGUF file_type -> the qtype the file was exported with (informational; tensors are decoded individually)
+qtype_map = {2: "sym_int4", 3: "asym_int4", 7: "sym_int8", 8: "sym_int5", 9: "asym_int5", 0: "fp32", 1: "fp16",
+             15: "q4_k", 17: "q5_k", 18: "q6_k", 10: "q2_k"}
+
+_LLAMA_LIKE = ("llama", "mistral", "mixtral", "qwen2", "gemma", "baichuan", "yuan")
+
+_BLOCK_MAP = {
+    "attn_norm.weight": "input_layernorm.weight",
+    "ffn_norm.weight": "post_attention_layernorm.weight",
+    "attn_q.weight": "self_attn.q_proj.weight", "attn_q.bias": "self_attn.q_proj.bias",
+    "attn_k.weight": "self_attn.k_proj.weight", "attn_k.bias": "self_attn.k_proj.bias",
+    "attn_v.weight": "self_attn.v_proj.weight", "attn_v.bias": "self_attn.v_proj.bias",
+    "attn_output.weight": "self_attn.o_proj.weight",
+    "ffn_gate.weight": "mlp.gate_proj.weight", "ffn_up.weight": "mlp.up_proj.weight",
+    "ffn_down.weight": "mlp.down_proj.weight",
+    "ffn_gate_inp.weight": "block_sparse_moe.gate.weight",
+}
+
+
+def get_llama_module_name(name: str) -> Optional[str]:
+    """GGUF tensor name -> Hugging Face parameter name (None for tensors that have no counterpart)."""
+    if name == "token_embd.weight":
+        return "model.embed_tokens.weight"
+    if name == "output_norm.weight":
+        return "model.norm.weight"
+    if name == "output.weight":
+        return "lm_head.weight"
+    m = re.match(r"blk\.(\d+)\.(.+)", name)
+    if not m:
+        return None
+    layer, rest = m.group(1), m.group(2)
+    if rest in _BLOCK_MAP:
+        return f"model.layers.{layer}.{_BLOCK_MAP[rest]}"
+    e = re.match(r"ffn_(gate|up|down)\.(\d+)\.weight", rest)     # mixtral experts stored one by one
+    if e:
+        w = {"gate": "w1", "down": "w2", "up": "w3"}[e.group(1)]
+        return f"model.layers.{layer}.block_sparse_moe.experts.{e.group(2)}.{w}.weight"
+    return None
+
+
+def _unpermute(t: torch.Tensor, n_head: int) -> torch.Tensor:
+    """Undo llama.cpp's q/k row permutation (pairs interleaved for its rotary kernel)."""
+    rows = t.shape[0]
+    return t.reshape(n_head, rows // n_head // 2, 2, *t.shape[1:]).swapaxes(1, 2).reshape(t.shape)
+
+
+def _hf_config(cfg: dict, arch: str, vocab: int):
+    import transformers
+    g = lambda k, d=None: cfg.get(f"{arch}.{k}", d)  # noqa: E731
+    common = dict(vocab_size=vocab, hidden_size=g("embedding_length"), intermediate_size=g("feed_forward_length"),
+                  num_hidden_layers=g("block_count"), num_attention_heads=g("attention.head_count"),
+                  num_key_value_heads=g("attention.head_count_kv", g("attention.head_count")),
+                  max_position_embeddings=g("context_length", 4096),
+                  rms_norm_eps=g("attention.layer_norm_rms_epsilon", 1e-5),
+                  bos_token_id=cfg.get("tokenizer.ggml.bos_token_id"), eos_token_id=cfg.get("tokenizer.ggml.eos_token_id"),
+                  tie_word_embeddings=False, use_cache=True)
+    rope = g("rope.freq_base")
+    if rope:
+        common["rope_theta"] = float(rope)
+    name = str(cfg.get("general.name", "")).lower()
+    if arch == "qwen2":
+        return transformers.Qwen2Config(**common), "qwen2"
+    if arch == "gemma":
+        common["head_dim"] = g("attention.key_length", common["hidden_size"] // common["num_attention_heads"])
+        return transformers.GemmaConfig(**common), "gemma"
+    if g("expert_count"):
+        return transformers.MixtralConfig(num_local_experts=g("expert_count"),
+                                          num_experts_per_tok=g("expert_used_count", 2), **common), "mixtral"
+    if "mistral" in name:
+        return transformers.MistralConfig(**common), "mistral"
+    return transformers.LlamaConfig(**common), "llama"
+
+
+class GGUFTokenizer:
+    """Minimal tokenizer over the vocabulary stored in the file (sentencepiece pieces rebuilt into a processor)."""
+
+    def __init__(self, loader):
+        import sentencepiece as spm
+        from transformers.convert_slow_tokenizer import import_protobuf
+        spm_pb2 = import_protobuf("Failed to import protobuf")
+        trainer = spm_pb2.TrainerSpec(byte_fallback=True, model_type=spm_pb2.TrainerSpec.ModelType.BPE)
+        proto = spm_pb2.ModelProto(pieces=loader.tokenizer_pieces(), trainer_spec=trainer)
+        self.sp = spm.SentencePieceProcessor(model_proto=proto.SerializeToString())
+        self.bos_token_id = loader.config.get("tokenizer.ggml.bos_token_id")
+        self.eos_token_id = loader.config.get("tokenizer.ggml.eos_token_id")
+        self.pad_token_id = loader.config.get("tokenizer.ggml.padding_token_id", self.eos_token_id)
+        self.padding_side = "left"
+        self.vocab_size = self.sp.get_piece_size()
+
+    def encode(self, text, add_special_tokens=True):
+        ids = self.sp.encode(text)
+        return ([self.bos_token_id] if add_special_tokens and self.bos_token_id is not None else []) + ids
+
+    def decode(self, ids, skip_special_tokens=True, **kw):
+        ids = [int(i) for i in (ids.tolist() if hasattr(ids, "tolist") else ids)]
+        if skip_special_tokens:
+            ids = [i for i in ids if i not in (self.bos_token_id, self.eos_token_id, self.pad_token_id)]
+        return self.sp.decode(ids)
+
+    def __call__(self, text, return_tensors=None, padding=False, **kw):
+        batch = [text] if isinstance(text, str) else list(text)
+        enc = [self.encode(t) for t in batch]
+        n = max(len(e) for e in enc)
+        pad = self.pad_token_id if self.pad_token_id is not None else 0
+        ids = [[pad] * (n - len(e)) + e for e in enc]
+        mask = [[0] * (n - len(e)) + [1] * len(e) for e in enc]
+        if return_tensors == "pt":
+            return {"input_ids": torch.tensor(ids), "attention_mask": torch.tensor(mask)}
+        return {"input_ids": ids if not isinstance(text, str) else ids[0],
+                "attention_mask": mask if not isinstance(text, str) else mask[0]}
+
+
+def load_gguf_model(fpath: str, dtype: torch.dtype = torch.float, low_bit: str = "sym_int4"):
+    """Returns ``(model, tokenizer)``; ``model`` is a low-bit model ready for ``.to('cuda')`` / ``generate``."""
+    from ..convert import ggml_convert_low_bit
+    from ..model import _attach_api
+    from ...quant import qtypes as qt
+    from .gguf import GGUFFileLoader
+    import transformers
+
+    loader = GGUFFileLoader(fpath)
+    cfg = loader.config
+    arch = cfg.get("general.architecture")
+    print("model_family:" + str(arch))
+    invalidInputError(arch in _LLAMA_LIKE, f"Unsupported model family: {arch}")
+    vocab = len(cfg["tokenizer.ggml.tokens"]) if "tokenizer.ggml.tokens" in cfg else None
+    names = loader.tensor_loader.names()
+    if vocab is None:
+        vocab = loader.tensor_loader.infos[names.index("token_embd.weight")][1][1]
+    hf_cfg, family = _hf_config(cfg, arch, vocab)
+    n_head, n_kv = hf_cfg.num_attention_heads, hf_cfg.num_key_value_heads
+    if "output.weight" not in names:
+        hf_cfg.tie_word_embeddings = True
+
+    try:
+        from transformers.initialization import no_init_weights
+    except ImportError:  # older layouts
+        from transformers.modeling_utils import no_init_weights
+    with no_init_weights(), torch.device("meta"):
+        model = transformers.AutoModelForCausalLM.from_config(hf_cfg, dtype=dtype)
+    model.to_empty(device="cpu")
+    params = dict(model.named_parameters())
+    loaded = set()
+
+    def process(name, tensor):
+        target = get_llama_module_name(name)
+        if target is None or target not in params:
+            return
+        if target.endswith("q_proj.weight") or target.endswith("q_proj.bias"):
+            tensor = _unpermute(tensor, n_head)
+        elif target.endswith("k_proj.weight") or target.endswith("k_proj.bias"):
+            tensor = _unpermute(tensor, n_kv)
+        with torch.no_grad():
+            params[target].copy_(tensor.to(params[target].dtype).reshape(params[target].shape))
+        loaded.add(target)
+
+    loader.tensor_loader.load_while_process(process)
+    missing = [n for n in params if n not in loaded and not (hf_cfg.tie_word_embeddings and n == "lm_head.weight")]
+    invalidInputError(not missing, f"GGUF file lacks tensors for: {missing[:5]}{' ...' if len(missing) > 5 else ''}")
+    if hf_cfg.tie_word_embeddings:
+        model.tie_weights()
+    # buffers created on meta (rotary tables) are rebuilt by re-instantiating them
+    from ..model import _rebuild_nonpersistent
+    _rebuild_nonpersistent(model)
+    model = ggml_convert_low_bit(model.eval(), qt.qtype_from_name(low_bit), optimize_model=True)
+    model = _attach_api(model, low_bit)
+    try:
+        tokenizer = GGUFTokenizer(loader) if "tokenizer.ggml.tokens" in cfg else None
+    except Exception:  # noqa: BLE001 - vocabulary kinds without a sentencepiece form (byte-level BPE): model only
+        tokenizer = None
+    loader.close()
+    return model, tokenizer

@@ -480,11 +480,11 @@ class _BaseAutoModelClass:
         """Load a ``.gguf`` file (llama / mistral / mixtral / baichuan / bloom / falcon / mpt / yuan2 families) and
         return ``(model, tokenizer)``."""
         from .gguf.api import load_gguf_model
-        model, tokenizer = load_gguf_model(fpath, dtype=torch.half, low_bit=low_bit)
-        model = ggml_convert_low_bit(model, qt.qtype_from_name(low_bit), optimize_model,
-                                     cpu_embedding=cpu_embedding)
+        # the loader quantizes each matrix as it is read, so the model arrives converted
+        model, tokenizer = load_gguf_model(fpath, dtype=torch.float32 if not torch.cuda.is_available() else torch.half,
+                                           low_bit=low_bit)
         model.config.update({"bigdl_transformers_low_bit": low_bit})
-        return _attach_api(model), tokenizer
+        return model, tokenizer
 
 
 def _strip_private(kwargs):
