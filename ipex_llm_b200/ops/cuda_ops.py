@@ -121,6 +121,51 @@ def gemv_lowbit(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K: in
     return out
 
 
+class _ChainOpDesc(ctypes.Structure):
+    _fields_ = [("w", ctypes.c_void_p), ("x", ctypes.c_void_p), ("y", ctypes.c_void_p), ("norm_w", ctypes.c_void_p),
+                ("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("N", ctypes.c_int), ("K", ctypes.c_int),
+                ("ldx", ctypes.c_int), ("ldy", ctypes.c_int), ("ldr", ctypes.c_int), ("act", ctypes.c_int),
+                ("eps", ctypes.c_float), ("norm_offset", ctypes.c_float)]
+
+
+_chain_barriers = {}
+
+
+def chain_barrier(device) -> torch.Tensor:
+    """Arrival / exit counters of the chained-GEMV kernel's grid barrier (zero between launches)."""
+    key = str(device)
+    if key not in _chain_barriers:
+        _chain_barriers[key] = torch.zeros(2, dtype=torch.int32, device=device)
+    return _chain_barriers[key]
+
+
+def gemv_chain(ops, M: int, dtype, device, pdl: bool = False):
+    """Up to four dependent symmetric-int4 GEMVs in one persistent kernel.  ``ops``: dicts with ``w`` (packed
+    tiles), ``x`` ``[M, K]``, ``y``, ``N``, ``K`` and optional ``norm_w``, ``bias``, ``residual``, ``act``, ``eps``,
+    ``norm_offset``; op ``i + 1`` may read what op ``i`` wrote."""
+    lib = cuda_lib()
+    arr = (_ChainOpDesc * len(ops))()
+    for d, o in zip(arr, ops):
+        x, y, res = o["x"], o["y"], o.get("residual")
+        d.w, d.x, d.y = o["w"].data_ptr(), x.data_ptr(), y.data_ptr()
+        d.norm_w = o["norm_w"].data_ptr() if o.get("norm_w") is not None else None
+        d.bias = o["bias"].data_ptr() if o.get("bias") is not None else None
+        d.residual = res.data_ptr() if res is not None else None
+        d.N, d.K = int(o["N"]), int(o["K"])
+        d.ldx, d.ldy = x.stride(0), y.stride(0)
+        d.ldr = res.stride(0) if res is not None else 0
+        d.act = int(o.get("act", 0))
+        d.eps = float(o.get("eps", 1e-6))
+        d.norm_offset = float(o.get("norm_offset", 0.0))
+    fn = lib.ipex_gemv_chain
+    fn.argtypes = [ctypes.POINTER(_ChainOpDesc), ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+                   ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+    fn.restype = ctypes.c_int
+    rc = fn(arr, len(ops), M, api.dtype_code(dtype), ptr(chain_barrier(device)), int(pdl), ptr(error_flag(device)),
+            current_stream())
+    api.check(rc, "gemv_chain")
+
+
 def gemv_lowbit_ar(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K: int, out: torch.Tensor, comm,
                    bias: torch.Tensor = None, residual: torch.Tensor = None, pdl: bool = False, wf: int = None):
     """Row-parallel GEMV fused with its all-reduce: ``out = sum_over_ranks(x_r @ W_r.T) (+ bias) (+ residual)``.
