@@ -53,7 +53,7 @@ def llm_convert(model, outfile, model_family, outtype="int4", model_format="pth"
     else:
         invalidInputError(False, f"Unsupported input model_type: {model_format}")
     cls = AutoModel if model_family == "chatglm" else AutoModelForCausalLM
-    m = cls.from_pretrained(model, load_in_low_bit=low_bit, trust_remote_code=True, optimize_model=False)
+    m = cls.from_pretrained(model, load_in_low_bit=low_bit, trust_remote_code=True)
     out = os.path.join(outfile, f"bigdl_llm_{model_family}_{outtype.lower()}" +
                        ("_from_gptq" if model_format == "gptq" else ""))
     m.save_low_bit(out)

@@ -38,6 +38,12 @@ struct GemvArgs {
   int ldx, ldy, ldr;
   float eps, norm_offset;
   int act;  // 0 none, 1 silu(gate)*up, 2 gelu_tanh(gate)*up  (row tiles interleaved gate, up)
+  // mixture-of-experts mode (w_list != null): blockIdx.y is a (token, choice) slot; the slot's expert id selects the
+  // weight matrix on the device, x row = slot / x_div, y row = slot, one token per slot (M = 1)
+  const uint8_t* const* w_list;
+  const int64_t* expert_ids;
+  int x_div;
+  int x_div_slots;  // number of slots (grid.y)
 };
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -139,6 +145,12 @@ __global__ void __launch_bounds__(kThreads) gemv_tiled_kernel(GemvArgs a) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int tile_row0 = blockIdx.x * RT;
+  if (a.w_list != nullptr) {
+    const int slot = blockIdx.y;
+    a.w = a.w_list[a.expert_ids[slot]];
+    a.x = reinterpret_cast<const T*>(a.x) + (size_t)(slot / a.x_div) * a.ldx;
+    a.y = reinterpret_cast<T*>(a.y) + (size_t)slot * a.ldy;
+  }
 
   __half* xs = reinterpret_cast<__half*>(smem_raw);
   size_t off = ((size_t)a.M * xs_stride * sizeof(__half) + 15) & ~(size_t)15;
@@ -540,7 +552,7 @@ cudaError_t launch_tiled(const GemvArgs& a, cudaStream_t stream, bool pdl) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  dim3 grid((Np / 16 + RT - 1) / RT);
+  dim3 grid((Np / 16 + RT - 1) / RT, a.w_list != nullptr ? a.x_div_slots : 1);
   return launch_kernel(kern, grid, dim3(kThreads), smem, stream, pdl, a);
 }
 
@@ -577,6 +589,7 @@ IPEX_API int ipex_gemv_lowbit(const void* w, int wf, const void* x, void* y, int
   a.w = (const uint8_t*)w; a.x = x; a.y = y; a.norm_w = norm_w; a.bias = bias; a.residual = residual; a.lut = lut;
   a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy; a.ldr = ldr; a.eps = eps; a.norm_offset = norm_offset;
   a.act = act;
+  a.w_list = nullptr; a.expert_ids = nullptr; a.x_div = 1; a.x_div_slots = 1;
   cudaStream_t s = (cudaStream_t)stream;
   if (wf == WF_F16 || wf == WF_BF16) {
     if (act != 0) return (int)cudaErrorInvalidValue;
@@ -595,6 +608,28 @@ IPEX_API int ipex_gemv_lowbit(const void* w, int wf, const void* x, void* y, int
       return (int)launch_kernel(kern, grid, dim3(kThreads), smem, s, pdl != 0, a);
     }
   }
+  if (dtype == DT_F16) return (int)dispatch_wf<__half>(wf, a, s, pdl != 0);
+  if (dtype == DT_BF16) return (int)dispatch_wf<__nv_bfloat16>(wf, a, s, pdl != 0);
+  return (int)cudaErrorInvalidValue;
+}
+
+// Mixture-of-experts GEMV for decode: `nslots` = tokens x experts-per-token independent GEMVs in one launch.
+// Slot s uses the weight matrix w_list[expert_ids[s]] (all of family `wf`, shape [N, K], device tile layout), reads
+// x row s / x_div and writes y row s.  The expert choice never leaves the device.  act != 0: gate/up interleaved
+// row tiles, N/2 output columns.
+IPEX_API int ipex_moe_gemv(const void* w_list, int wf, const void* expert_ids, int nslots, const void* x, int x_div,
+                           void* y, int N, int K, int ldx, int ldy, int act, const float* lut, int dtype, int pdl,
+                           void* stream) {
+  if (nslots < 1 || nslots > 65535 || x_div < 1 || (K % 64) != 0 || wf == WF_F16 || wf == WF_BF16)
+    return (int)cudaErrorInvalidValue;
+  GemvArgs a;
+  a.w = nullptr; a.x = x; a.y = y; a.norm_w = nullptr; a.bias = nullptr; a.residual = nullptr; a.lut = lut;
+  a.M = 1; a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy; a.ldr = 0; a.eps = 0.f; a.norm_offset = 0.f;
+  a.act = act;
+  a.w_list = reinterpret_cast<const uint8_t* const*>(w_list);
+  a.expert_ids = reinterpret_cast<const int64_t*>(expert_ids);
+  a.x_div = x_div; a.x_div_slots = nslots;
+  cudaStream_t s = (cudaStream_t)stream;
   if (dtype == DT_F16) return (int)dispatch_wf<__half>(wf, a, s, pdl != 0);
   if (dtype == DT_BF16) return (int)dispatch_wf<__nv_bfloat16>(wf, a, s, pdl != 0);
   return (int)cudaErrorInvalidValue;

@@ -1,0 +1,119 @@
+// Mixture-of-experts routing on the device (the expert GEMVs themselves are ipex_moe_gemv in gemv_lowbit.cu).
+//
+// Reference counterparts: xe_addons.moe_softmax_topk and xe_addons.moe_group_topk as used by
+// python/llm/src/ipex_llm/transformers/models/common.py:343-361 (Mixtral / Qwen-MoE routing: softmax over the experts
+// in fp32, top-k, optional renormalisation) and models/deepseek.py:274-346 (grouped top-k with a score bias).
+// One warp per token; experts are spread over the lanes (E <= 256), top-k (k <= 8) by repeated warp arg-max.
+#include "common/utils.cuh"
+
+namespace {
+
+constexpr int kMaxPerLane = 8;  // 256 experts / 32 lanes
+
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+  }
+}
+
+template <typename T>
+__global__ void moe_softmax_topk_kernel(const T* __restrict__ logits, float* __restrict__ probs, float* __restrict__ w,
+                                        int64_t* __restrict__ idx, int tokens, int E, int k, int renorm) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= tokens) return;
+  const T* row = logits + (size_t)warp * E;
+  float v[kMaxPerLane];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < kMaxPerLane; j++) {
+    const int e = lane + 32 * j;
+    v[j] = e < E ? DT<T>::to_f(row[e]) : -INFINITY;
+    mx = fmaxf(mx, v[j]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < kMaxPerLane; j++) {
+    v[j] = (lane + 32 * j) < E ? __expf(v[j] - mx) : 0.f;
+    sum += v[j];
+  }
+  sum = warp_sum(sum);
+  const float inv = 1.0f / sum;
+#pragma unroll
+  for (int j = 0; j < kMaxPerLane; j++) {
+    v[j] *= inv;
+    const int e = lane + 32 * j;
+    if (e < E && probs != nullptr) probs[(size_t)warp * E + e] = v[j];
+    if (e >= E) v[j] = -1.f;
+  }
+  float chosen[8];
+  int chosen_i[8];
+  float tot = 0.f;
+  for (int r = 0; r < k; r++) {
+    float bv = -1.f;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; j++)
+      if (v[j] > bv) { bv = v[j]; bi = lane + 32 * j; }
+    warp_argmax(bv, bi);
+    chosen[r] = bv;
+    chosen_i[r] = bi;
+    tot += bv;
+    if ((bi & 31) == lane) v[bi >> 5] = -1.f;   // remove the winner
+  }
+  if (lane == 0) {
+    const float s = renorm ? 1.0f / tot : 1.0f;
+    for (int r = 0; r < k; r++) {
+      w[(size_t)warp * k + r] = chosen[r] * s;
+      idx[(size_t)warp * k + r] = chosen_i[r];
+    }
+  }
+}
+
+// out[t] = sum_r weights[t, r] * y[t * k + r]   (combining the experts' outputs)
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ y, const float* __restrict__ w, T* __restrict__ out, int tokens,
+                                   int k, int H) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)tokens * H) return;
+  const int t = (int)(i / H), h = (int)(i % H);
+  float acc = 0.f;
+  for (int r = 0; r < k; r++) acc += w[(size_t)t * k + r] * DT<T>::to_f(y[((size_t)t * k + r) * H + h]);
+  out[i] = DT<T>::from_f(acc);
+}
+
+}  // namespace
+
+// logits [tokens, E] (dtype) -> probs [tokens, E] fp32 (may be null), w [tokens, k] fp32, idx [tokens, k] int64.
+IPEX_API int ipex_moe_softmax_topk(const void* logits, float* probs, float* w, int64_t* idx, int tokens, int E, int k,
+                                   int renorm, int dtype, void* stream) {
+  if (E < 1 || E > 32 * kMaxPerLane || k < 1 || k > 8 || k > E || tokens < 1) return (int)cudaErrorInvalidValue;
+  const int threads = 128, blocks = (tokens * 32 + threads - 1) / threads;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == DT_F16)
+    moe_softmax_topk_kernel<__half><<<blocks, threads, 0, s>>>((const __half*)logits, probs, w, idx, tokens, E, k, renorm);
+  else if (dtype == DT_BF16)
+    moe_softmax_topk_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)logits, probs, w, idx,
+                                                                       tokens, E, k, renorm);
+  else if (dtype == DT_F32)
+    moe_softmax_topk_kernel<float><<<blocks, threads, 0, s>>>((const float*)logits, probs, w, idx, tokens, E, k, renorm);
+  else return (int)cudaErrorInvalidValue;
+  return (int)cudaGetLastError();
+}
+
+IPEX_API int ipex_moe_combine(const void* y, const float* w, void* out, int tokens, int k, int H, int dtype,
+                              void* stream) {
+  const int64_t n = (int64_t)tokens * H;
+  const int threads = 256, blocks = (int)((n + threads - 1) / threads);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == DT_F16)
+    moe_combine_kernel<__half><<<blocks, threads, 0, s>>>((const __half*)y, w, (__half*)out, tokens, k, H);
+  else if (dtype == DT_BF16)
+    moe_combine_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)y, w, (__nv_bfloat16*)out,
+                                                                  tokens, k, H);
+  else return (int)cudaErrorInvalidValue;
+  return (int)cudaGetLastError();
+}

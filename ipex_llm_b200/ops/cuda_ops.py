@@ -533,8 +533,104 @@ def sdpa_prefill(q, k, v, mask, scale, softcap, sliding_window, causal=True):
 # ------------------------------------------------------------------------------------------------
 # MoE (the fused kernels register themselves here when built)
 # ------------------------------------------------------------------------------------------------
+_MOE_MAX_SLOTS = 64       # tokens x experts-per-token handled by the per-slot GEMV launch (decode / small batches)
+
+
+class _MoeBank:
+    """Device-side view of a ``LowBitExperts`` bank: per-expert gate/up merged into interleaved 16-row tiles (so
+    the GEMV epilogue can apply act(gate) * up) and pointer tables indexed by expert id."""
+
+    def __init__(self, experts):
+        from ..engine.decoder_engine import _W, _interleave_row_tiles
+        q = experts.qtype
+        wf = QTYPE_TO_WF[q]
+        H, I = experts.hidden_dim, experts.intermediate_dim
+        self.gate_up, gu_ptrs, dn_ptrs = [], [], []
+        for i in range(experts.num_experts):     # (an activation module may be registered beside the experts)
+            e = experts[i]
+            merged = _interleave_row_tiles(_W(e.w1.weight.data, wf, q, I, H), _W(e.w3.weight.data, wf, q, I, H))
+            self.gate_up.append(merged.data)
+            gu_ptrs.append(merged.data.data_ptr())
+            dn_ptrs.append(e.w2.weight.data.data_ptr())
+        dev = experts[0].w1.weight.data.device
+        self.gu_ptrs = torch.tensor(gu_ptrs, dtype=torch.int64, device=dev)
+        self.dn_ptrs = torch.tensor(dn_ptrs, dtype=torch.int64, device=dev)
+        self.wf, self.qtype, self.H, self.I = wf, q, H, I
+
+
 def moe_supported(experts) -> bool:
-    return False
+    lib = cuda_lib()
+    if getattr(lib, "ipex_moe_gemv", None) is None or not is_tiled(experts.qtype):
+        return False
+    w = experts[0].w1.weight
+    return bool(getattr(w, "quantized", False)) and w.data.is_cuda and experts.hidden_dim % 64 == 0 and \
+        experts.intermediate_dim % 64 == 0 and experts.intermediate_dim % 16 == 0
+
+
+def moe_forward(experts, hidden_states, top_k_index, top_k_weights):
+    """Sparse-MoE block for few tokens: every (token, choice) slot is one GEMV whose expert is picked on the device
+    (no host synchronisation, two launches for all slots).  Larger token counts run expert by expert through the
+    tcgen05 GEMM."""
+    lib = cuda_lib()
+    T, k = top_k_index.shape
+    slots = T * k
+    if slots > _MOE_MAX_SLOTS:
+        return _moe_forward_grouped(experts, hidden_states, top_k_index, top_k_weights)
+    bank = experts.__dict__.get("_cuda_bank")
+    if bank is None:
+        bank = _MoeBank(experts)
+        experts.__dict__["_cuda_bank"] = bank
+    x = hidden_states.contiguous()
+    dt = x.dtype
+    act_code = 1 if getattr(experts.act_fn, "__name__", "silu") in ("silu", "SiLU") or \
+        type(experts.act_fn).__name__ in ("SiLU", "SiLUActivation") else 2
+    ids = top_k_index.reshape(-1).to(torch.int64).contiguous()
+    act = torch.empty((slots, bank.I), dtype=dt, device=x.device)
+    y = torch.empty((slots, bank.H), dtype=dt, device=x.device)
+    lut = lut_for(bank.qtype, x.device)
+    fn = lib.ipex_moe_gemv
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                   ctypes.c_void_p] + [ctypes.c_int] * 5 + [ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                                            ctypes.c_void_p]
+    fn.restype = ctypes.c_int
+    rc = fn(ptr(bank.gu_ptrs), bank.wf, ptr(ids), slots, ptr(x), k, ptr(act), 2 * bank.I, bank.H, x.stride(0),
+            act.stride(0), act_code, ptr(lut), _dt(x), 0, current_stream())
+    api.check(rc, "moe_gemv(gate_up)")
+    rc = fn(ptr(bank.dn_ptrs), bank.wf, ptr(ids), slots, ptr(act), 1, ptr(y), bank.H, bank.I, act.stride(0),
+            y.stride(0), 0, ptr(lut), _dt(x), 0, current_stream())
+    api.check(rc, "moe_gemv(down)")
+    out = torch.empty_like(x)
+    w = top_k_weights.to(torch.float32).contiguous()
+    cfn = lib.ipex_moe_combine
+    cfn.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 4 + [ctypes.c_void_p]
+    cfn.restype = ctypes.c_int
+    rc = cfn(ptr(y), ptr(w), ptr(out), T, k, bank.H, _dt(x), current_stream())
+    api.check(rc, "moe_combine")
+    return out
+
+
+def _moe_forward_grouped(experts, hidden_states, top_k_index, top_k_weights):
+    """Prompt-sized inputs: tokens grouped per expert, each group through the low-bit tensor-core GEMM."""
+    from ..models.common import SILU, _act_mul
+    final = torch.zeros_like(hidden_states)
+    E = experts.num_experts
+    flat = top_k_index.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=E).tolist()       # one host sync per MoE block
+    k = top_k_index.shape[1]
+    start = 0
+    for e, c in enumerate(counts):
+        if c == 0:
+            continue
+        sel = order[start:start + c]
+        start += c
+        tok, pos = sel // k, sel % k
+        x = hidden_states[tok]
+        exp = experts[e]
+        h = _act_mul(exp.w1(x), exp.w3(x), SILU)
+        yy = exp.w2(h) * top_k_weights[tok, pos, None].to(h.dtype)
+        final.index_add_(0, tok, yy.to(final.dtype))
+    return final
 
 
 def moe_softmax_topk(router_logits, top_k, renormalize):
@@ -557,5 +653,6 @@ def moe_softmax_topk(router_logits, top_k, renormalize):
 
 
 def moe_group_topk(scores, bias, n_group, topk_group, top_k, norm_topk_prob, routed_scaling_factor):
-    from .moe import moe_group_topk as ref
-    return ref(scores.cpu(), bias.cpu(), n_group, topk_group, top_k, norm_topk_prob, routed_scaling_factor)
+    """DeepSeek-V3 grouped routing on the device (tensor ops; no host round trip)."""
+    from .moe import _group_topk_impl
+    return _group_topk_impl(scores, bias, n_group, topk_group, top_k, norm_topk_prob, routed_scaling_factor)

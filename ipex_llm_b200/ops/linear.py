@@ -118,7 +118,8 @@ class LowBitLinear(nn.Linear):
     def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys,
                               error_msgs):
         key = prefix + "weight"
-        if key in state_dict and isinstance(self.weight, FP4Params):
+        found = key in state_dict
+        if found and isinstance(self.weight, FP4Params):
             data = state_dict[key]
             w = self.weight
             shape = w._shape if w._shape is not None else torch.Size(self.weight_shape)
@@ -127,7 +128,7 @@ class LowBitLinear(nn.Linear):
             state_dict = {k: v for k, v in state_dict.items() if k != key}
         super()._load_from_state_dict(state_dict, prefix, local_metadata, False, missing_keys, unexpected_keys,
                                       error_msgs)
-        if key in missing_keys:
+        if found and key in missing_keys:     # a packed weight that is absent from the checkpoint stays "missing"
             missing_keys.remove(key)
 
     def forward(self, x: torch.Tensor):

@@ -153,6 +153,12 @@ def ggml_matmul_src1_x_src0_t(src0: torch.Tensor, src1: torch.Tensor, src0_shape
     ne0 = (ctypes.c_int64 * 4)(K, N, 1, 1)
     ne1 = (ctypes.c_int64 * 4)(K, M, 1, 1)
     w = src0.contiguous()
+    need = N * K // get_block_size(src0_qtype) * get_type_size(src0_qtype)
+    have = w.numel() * w.element_size()
+    if have < need or w.device.type != "cpu":
+        raise RuntimeError(f"packed weight holds {have} bytes on {w.device}, a [{N}, {K}] "
+                           f"{qt.qtype_name(src0_qtype)} matrix needs {need} on cpu: the checkpoint does not match "
+                           "the module layout (was it saved with another `optimize_model` setting?)")
     lib.ggml_compute_forward_mul_mat_q_fp32(ne0, w.data_ptr(), src0_qtype, ne1, src1.data_ptr(), out.data_ptr())
     return out.view(*lead, N)
 

@@ -1,0 +1,87 @@
+"""Integration shims on CPU: LangChain / LlamaIndex wrappers, NPU-named entry point, JSON-constrained decoding,
+llm_convert + CLI, BenchmarkWrapper."""
+import json
+import os
+
+import pytest
+import torch
+
+
+@pytest.fixture(scope="module")
+def tiny(tmp_path_factory):
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import LlamaConfig, LlamaForCausalLM, PreTrainedTokenizerFast
+    d = tmp_path_factory.mktemp("tiny_ckpt")
+    words = ["<pad>", "<s>", "</s>", "<unk>", "{", "}", "[", "]", ":", ",", '"a"', '"b"', "1", "2", "true", "null"] + \
+        [f"w{i}" for i in range(48)]
+    tk = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tk.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    tok = PreTrainedTokenizerFast(tokenizer_object=tk, pad_token="<pad>", bos_token="<s>", eos_token="</s>",
+                                  unk_token="<unk>")
+    cfg = LlamaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=64, max_position_embeddings=256, tie_word_embeddings=False,
+                      eos_token_id=2, pad_token_id=0, bos_token_id=1)
+    torch.manual_seed(0)
+    LlamaForCausalLM(cfg).save_pretrained(d)
+    tok.save_pretrained(d)
+    return str(d)
+
+
+def test_langchain_and_llamaindex(tiny):
+    from ipex_llm.langchain.embeddings import TransformersEmbeddings
+    from ipex_llm.langchain.llms import TransformersLLM
+    from ipex_llm.llamaindex.llms import IpexLLM
+    llm = TransformersLLM.from_model_id(tiny, model_kwargs={"torch_dtype": torch.float32}, device_map="cpu")
+    out = llm.invoke("w1 w2 w3", max_new_tokens=5)
+    assert isinstance(out, str)
+    emb = TransformersEmbeddings.from_model_id(tiny, model_kwargs={"torch_dtype": torch.float32}, device_map="cpu")
+    v = emb.embed_query("w1 w2")
+    assert len(v) == 64 and len(emb.embed_documents(["w1", "w2 w3"])) == 2
+    li = IpexLLM(model_name=tiny, device_map="cpu", max_new_tokens=4, model_kwargs={"torch_dtype": torch.float32})
+    r = li.complete("w5 w6")
+    assert isinstance(r.text, str)
+    chunks = list(li.stream_complete("w5 w6"))
+    assert chunks and chunks[-1].text == r.text
+
+
+def test_npu_named_entry_point(tiny):
+    from ipex_llm.transformers.npu_model import AutoModelForCausalLM
+    m = AutoModelForCausalLM.from_pretrained(tiny, load_in_low_bit="sym_int4_rtn", max_context_len=1024,
+                                             max_prompt_len=512, transpose_value_cache=True,
+                                             torch_dtype=torch.float32)
+    out = m.generate(torch.tensor([[5, 6, 7]]), max_new_tokens=3, do_sample=False)
+    assert out.shape == (1, 6)
+
+
+def test_json_prefix_checker_and_processor(tiny):
+    from transformers import AutoTokenizer
+    from ipex_llm.transformers.xgrammar import _JsonPrefix, create_json_logits_processor
+    good = ['{"a": [1, 2.5e3, true, null], "b": {"c": "x\\n\\u00e9"}}', "[]", '"s"', "-0.5", "{}"]
+    for g in good:
+        s = _JsonPrefix()
+        assert s.feed(g) and s.complete, g
+        for cut in range(1, len(g)):
+            assert _JsonPrefix().feed(g[:cut]), g[:cut]
+    for bad in ['{"a" 1}', "[1,,2]", "{,}", "tru e", '{"a":}', "01", "[1 2]"]:
+        assert not _JsonPrefix().feed(bad) or not _JsonPrefix().feed(bad + " "), bad
+    tok = AutoTokenizer.from_pretrained(tiny)
+    proc = create_json_logits_processor(tok, 64)
+    ids = torch.tensor([[5, 6]])
+    scores = torch.zeros(1, 64)
+    out = proc(ids, scores)
+    allowed = {tok.decode([i]) for i in torch.nonzero(torch.isfinite(out[0])).flatten().tolist()}
+    assert "{" in allowed and "[" in allowed and "}" not in allowed and "," not in allowed
+
+
+def test_llm_convert_cli_and_benchmark_wrapper(tiny, tmp_path, capsys):
+    from ipex_llm import llm_convert
+    from ipex_llm.transformers import AutoModelForCausalLM
+    from ipex_llm.utils import BenchmarkWrapper
+    from ipex_llm_b200.cli.llm_cli import main as cli_main
+    out = llm_convert(tiny, str(tmp_path / "out"), model_family="llama", outtype="int8")
+    assert os.path.isdir(out) and "bigdl_transformers_low_bit" in json.load(open(os.path.join(out, "config.json")))
+    m = AutoModelForCausalLM.load_low_bit(out)
+    bw = BenchmarkWrapper(m, do_print=False)
+    bw.generate(torch.tensor([[5, 6, 7, 8]]), max_new_tokens=6, do_sample=False)
+    assert bw.first_cost > 0 and bw.rest_cost_mean > 0
+    assert cli_main(["-m", out, "-p", "w1 w2", "-n", "4", "--device", "cpu"]) == 0
