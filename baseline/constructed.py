@@ -1,0 +1,202 @@
+"""Constructed stand-in for the reference on NVIDIA hardware: the reference's semantics on stock cuBLAS + NCCL.
+
+The reference itself cannot run on this machine (its kernels are closed Intel binaries), so the comparison arm is
+what its algorithm amounts to with library calls only:
+  * low-bit weights are dequantized ONCE to the activation dtype and every projection is ``torch.matmul`` (cuBLAS);
+  * attention is ``torch.nn.functional.scaled_dot_product_attention`` over a pre-allocated KV cache;
+  * RMSNorm / RoPE / SiLU*mul are eager PyTorch ops;
+  * tensor parallelism = column/row sharded weights + ``torch.distributed.all_reduce`` (NCCL) after o_proj / down_proj.
+Same synthetic inputs, same timing rules as ``bench.py`` (CUDA events around K decode steps after W warm-ups,
+max over ranks).  The decode step is captured in a CUDA graph too, so the comparison is kernel-for-kernel and not
+against Python overhead.  Nothing of ``ipex_llm_b200`` is imported here.
+
+    python baseline/constructed.py --model llama2-7b --steps 64 --warmup 8
+    torchrun --nproc-per-node 8 --master-addr 127.0.0.1 baseline/constructed.py --model llama3-70b
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+MODELS = {
+    "llama2-7b": dict(hidden=4096, inter=11008, layers=32, heads=32, kv_heads=32, vocab=32000, theta=10000.0,
+                      prompt=1024, dtype=torch.float16),
+    "llama3-70b": dict(hidden=8192, inter=28672, layers=80, heads=64, kv_heads=8, vocab=128256, theta=500000.0,
+                       prompt=2048, dtype=torch.bfloat16),
+}
+
+
+class Layer:
+    pass
+
+
+class ConstructedLlama:
+    def __init__(self, spec, rank, world, device, batch, max_len, n_layers=None):
+        s = spec
+        self.s, self.rank, self.world, self.dev = s, rank, world, device
+        dt = s["dtype"]
+        self.dt = dt
+        H, I = s["hidden"], s["inter"]
+        self.hd = H // s["heads"]
+        self.nh, self.nkv = s["heads"] // world, max(1, s["kv_heads"] // world)
+        g = torch.Generator(device=device).manual_seed(1234 + rank)
+
+        def w(n, k):
+            return (torch.randn(n, k, device=device, dtype=torch.float32, generator=g) * 0.02).to(dt)
+        self.embed = w(s["vocab"], H)
+        self.lm_head = w(s["vocab"], H)
+        self.norm = torch.ones(H, device=device, dtype=dt)
+        self.layers = []
+        for _ in range(n_layers or s["layers"]):
+            L = Layer()
+            L.qkv = w((self.nh + 2 * self.nkv) * self.hd, H)
+            L.o = w(H, self.nh * self.hd)
+            L.gate_up = w(2 * I // world, H)
+            L.down = w(H, I // world)
+            L.ln1 = torch.ones(H, device=device, dtype=dt)
+            L.ln2 = torch.ones(H, device=device, dtype=dt)
+            L.k = torch.zeros(batch, self.nkv, max_len, self.hd, device=device, dtype=dt)
+            L.v = torch.zeros_like(L.k)
+            self.layers.append(L)
+        pos = torch.arange(max_len, device=device, dtype=torch.float32)
+        inv = 1.0 / (s["theta"] ** (torch.arange(0, self.hd, 2, device=device, dtype=torch.float32) / self.hd))
+        fr = torch.outer(pos, inv)
+        self.cos, self.sin = fr.cos().to(dt), fr.sin().to(dt)
+        self.batch, self.max_len = batch, max_len
+        self.pos = torch.zeros(1, dtype=torch.long, device=device)
+        self.tokens = torch.zeros(batch, dtype=torch.long, device=device)
+        self.mask_idx = torch.arange(max_len, device=device).view(1, 1, 1, max_len)
+
+    def _norm(self, x, w, eps=1e-5):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+    def _rope(self, x, cos, sin):
+        x1, x2 = x[..., : self.hd // 2], x[..., self.hd // 2:]
+        return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
+
+    def forward(self, ids, start: int = None):
+        """ids [B, S]; ``start`` = python int for the prompt pass, None = decode at device position ``self.pos``."""
+        B, S = ids.shape
+        h = self.embed[ids]
+        if start is not None:
+            cos, sin = self.cos[start:start + S], self.sin[start:start + S]
+        else:
+            cos, sin = self.cos[self.pos], self.sin[self.pos]
+        cos, sin = cos.view(1, 1, S, -1), sin.view(1, 1, S, -1)
+        for L in self.layers:
+            x = self._norm(h, L.ln1)
+            qkv = torch.matmul(x, L.qkv.t())
+            q, k, v = qkv.split([self.nh * self.hd, self.nkv * self.hd, self.nkv * self.hd], dim=-1)
+            q = self._rope(q.view(B, S, self.nh, self.hd).transpose(1, 2), cos, sin)
+            k = self._rope(k.view(B, S, self.nkv, self.hd).transpose(1, 2), cos, sin)
+            v = v.view(B, S, self.nkv, self.hd).transpose(1, 2)
+            if start is not None:
+                L.k[:, :, start:start + S] = k
+                L.v[:, :, start:start + S] = v
+                a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.nh != self.nkv)
+            else:
+                L.k.index_copy_(2, self.pos, k)
+                L.v.index_copy_(2, self.pos, v)
+                mask = self.mask_idx <= self.pos
+                a = F.scaled_dot_product_attention(q, L.k, L.v, attn_mask=mask, enable_gqa=self.nh != self.nkv)
+            o = torch.matmul(a.transpose(1, 2).reshape(B, S, -1), L.o.t())
+            if self.world > 1:
+                dist.all_reduce(o)
+            h = h + o
+            x = self._norm(h, L.ln2)
+            gu = torch.matmul(x, L.gate_up.t())
+            g_, u_ = gu.chunk(2, dim=-1)
+            d = torch.matmul(F.silu(g_) * u_, L.down.t())
+            if self.world > 1:
+                dist.all_reduce(d)
+            h = h + d
+        x = self._norm(h[:, -1], self.norm)
+        return torch.matmul(x, self.lm_head.t())
+
+    def decode_step(self):
+        logits = self.forward(self.tokens.view(-1, 1))
+        self.tokens.copy_(logits.argmax(-1))
+        self.pos.add_(1)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="llama2-7b", choices=list(MODELS))
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--no-graph", action="store_true")
+    a = ap.parse_args()
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    spec = MODELS[a.model]
+    max_len = spec["prompt"] + 2 * (a.steps + a.warmup) + 16
+    m = ConstructedLlama(spec, rank, world, dev, a.batch, max_len, a.layers or None)
+    g = torch.Generator(device="cpu").manual_seed(1234)
+    ids = torch.randint(0, spec["vocab"], (a.batch, spec["prompt"]), generator=g).to(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    first_ms = 0.0
+    with torch.no_grad():
+        for _ in range(2):
+            torch.cuda.synchronize()
+            e0.record()
+            logits = m.forward(ids, start=0)
+            m.tokens.copy_(logits.argmax(-1))
+            e1.record()
+            torch.cuda.synchronize()
+            first_ms = e0.elapsed_time(e1)
+        m.pos.fill_(spec["prompt"])
+        step = m.decode_step
+        if not a.no_graph:
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                for _ in range(2):
+                    m.decode_step()
+            torch.cuda.current_stream().wait_stream(s)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                m.decode_step()
+            step = graph.replay
+        for _ in range(a.warmup):
+            step()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(a.steps):
+            step()
+        e1.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / a.steps
+    t = torch.tensor([ms, first_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        print(json.dumps({"impl": "constructed cuBLAS+NCCL stand-in", "model": a.model, "n_gpus": world,
+                          "batch": a.batch, "ms_per_step": round(float(t[0]), 4),
+                          "tokens_per_s": round(a.batch * 1000.0 / float(t[0]), 2),
+                          "first_token_ms": round(float(t[1]), 2), "steps": a.steps, "warmup": a.warmup,
+                          "weights": str(spec["dtype"]).replace("torch.", "") + " (dequantized once)",
+                          "cuda_graph": not a.no_graph}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

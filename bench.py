@@ -111,7 +111,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "constructed"],
+                    help="reference: the unmodified reference (unavailable offline); constructed: its semantics on "
+                         "stock cuBLAS + NCCL (baseline/constructed.py)")
     ap.add_argument("--model", default="auto")
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--prompt", type=int, default=None)
@@ -122,6 +124,15 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.impl == "constructed":
+        import runpy
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        model = args.model if args.model != "auto" else ("llama2-7b" if world == 1 else "llama3-70b")
+        sys.argv = [os.path.join(ROOT, "baseline", "constructed.py"), "--model", model, "--steps", str(args.steps),
+                    "--warmup", str(max(args.warmup, 3))] + (["--batch", str(args.batch)] if args.batch else []) + \
+                   (["--layers", str(args.layers)] if args.layers else [])
+        runpy.run_path(sys.argv[0], run_name="__main__")
+        return 0
     args.warmup = max(args.warmup, 3)
 
     import torch

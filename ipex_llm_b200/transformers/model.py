@@ -391,6 +391,11 @@ class _BaseAutoModelClass:
                                     modules_to_not_convert or [], tp_group)
         model.config.update({"bigdl_transformers_low_bit": q_k, "bigdl_disk_embedding": False,
                              "tie_word_embeddings": False})
+        stages = kwargs.pop("pipeline_parallel_stages", 1)
+        if stages > 1:
+            # every rank builds the same seeded model and keeps its own slice of layers
+            from ..parallel.pp import pipeline_parallel
+            model = pipeline_parallel(model, stages, torch_dtype, device=torch.device(device))
         model = _attach_api(model)
         if speculative:
             from .speculative import attach_draft_model

@@ -85,3 +85,20 @@ def test_llm_convert_cli_and_benchmark_wrapper(tiny, tmp_path, capsys):
     bw.generate(torch.tensor([[5, 6, 7, 8]]), max_new_tokens=6, do_sample=False)
     assert bw.first_cost > 0 and bw.rest_cost_mean > 0
     assert cli_main(["-m", out, "-p", "w1 w2", "-n", "4", "--device", "cpu"]) == 0
+
+
+def test_native_style_classes_and_legacy_names(tiny):
+    import bigdl.llm  # noqa: F401
+    from bigdl.llm.transformers import AutoModelForCausalLM as Legacy
+    from ipex_llm.models import Llama
+    from ipex_llm.transformers import AutoModelForCausalLM
+    assert Legacy is AutoModelForCausalLM
+    llm = Llama(tiny, low_bit="sym_int8", device="cpu")
+    res = llm("w1 w2 w3", max_tokens=5)
+    assert res["object"] == "text_completion" and res["usage"]["completion_tokens"] <= 5
+    toks = llm.tokenize("w1 w2")
+    assert llm.detokenize(toks).decode().split() == ["w1", "w2"]
+    pieces = list(llm("w1 w2", max_tokens=4, stream=True))
+    assert pieces[-1]["choices"][0]["finish_reason"] in ("length", "stop")
+    emb = llm.create_embedding("w3 w4")
+    assert len(emb["data"][0]["embedding"]) == 64

@@ -88,3 +88,21 @@ def test_stop_string_truncates(worker):
         cut = worker.submit_blocking("w1 w2", SamplingParams(max_new_tokens=10, stop=[stop]))
         assert stop not in cut.text and base.text.startswith(cut.text)
         assert cut.finish_reason == "stop"
+
+
+def test_fastchat_protocol_worker(worker):
+    from fastapi.testclient import TestClient
+    from ipex_llm_b200.serving.fastchat.ipex_llm_worker import BigDLLLMWorker, create_app
+    w = BigDLLLMWorker(None, "http://localhost:21002", "w0", "tiny", worker=worker, no_register=True,
+                       stream_interval=1)
+    with TestClient(create_app(w)) as c:
+        st = c.post("/worker_get_status").json()
+        assert st["model_names"] == ["tiny"]
+        assert c.post("/count_token", json={"prompt": "w1 w2 w3"}).json()["count"] == 3
+        r = c.post("/worker_generate", json={"prompt": "w1 w2", "max_new_tokens": 5, "temperature": 0.0,
+                                             "echo": False}).json()
+        assert r["error_code"] == 0 and r["usage"]["completion_tokens"] <= 5
+        with c.stream("POST", "/worker_generate_stream", json={"prompt": "w1 w2", "max_new_tokens": 5,
+                                                              "temperature": 0.0, "echo": False}) as resp:
+            chunks = [json.loads(x) for x in resp.read().split(b"\0") if x]
+        assert chunks[-1]["text"] == r["text"] and chunks[-1]["finish_reason"] in ("length", "stop")
