@@ -119,3 +119,40 @@ def test_dense_linear_routes_to_tcgen05():
     w = (torch.randn(768, 1024, device="cuda") * 0.05).half()
     out = cuda_ops.dense_linear(x, w)
     assert _rel_err(out, x.float() @ w.float().t()) < 2e-3
+
+
+@pytest.mark.parametrize("low_bit", ["sym_int4", "fp8_e4m3"])
+def test_flat_prefill_matches_module_path(low_bit, monkeypatch):
+    """The engine's flattened prompt pass (tcgen05 GEMMs with fused residual / act) against the module-tree pass."""
+    from transformers import LlamaConfig
+    from ipex_llm.transformers import AutoModelForCausalLM
+    from ipex_llm_b200.engine import get_engine
+    cfg = LlamaConfig(hidden_size=512, intermediate_size=1408 if low_bit == "sym_int4" else 1536, num_hidden_layers=2,
+                      num_attention_heads=8, num_key_value_heads=2, vocab_size=2000, max_position_embeddings=512,
+                      tie_word_embeddings=False)
+    # unquantized KV cache: the module path attends over what the cache returns (e5m2-rounded when quantized), the
+    # flat path over the exact K/V of the prompt, so only with a half-precision cache are the two comparable
+    monkeypatch.setenv("IPEX_LLM_QUANTIZE_KV_CACHE", "0")
+    model = AutoModelForCausalLM.from_config(cfg, load_in_low_bit=low_bit, device="cuda", torch_dtype=torch.float16)
+    ids = torch.randint(0, 2000, (2, 37), device="cuda")
+    eng = get_engine(model, 2, 128)
+    if not eng._flat_prefill_ok():
+        pytest.skip("shapes outside the flat path")
+    flat = eng.prefill(ids).float()
+    k_flat = eng.cache.layers[1].keys.clone()
+    monkeypatch.setenv("IPEX_LLM_FLAT_PREFILL", "0")
+    eng._flat_ok = None
+    ref = eng.prefill(ids).float()
+    k_ref = eng.cache.layers[1].keys
+    cos = torch.nn.functional.cosine_similarity(flat.flatten(), ref.flatten(), dim=0).item()
+    assert cos > 0.9995, cos
+    assert k_flat.shape == k_ref.shape
+    if k_flat.dtype == torch.uint8:
+        assert (k_flat != k_ref).float().mean().item() < 0.02      # e5m2 codes may differ by rounding ties
+    else:
+        assert torch.allclose(k_flat.float(), k_ref.float(), atol=2e-2)
+    # decoding continues from the flat pass
+    eng._flat_ok = None
+    monkeypatch.delenv("IPEX_LLM_FLAT_PREFILL")
+    out = model.generate(ids, max_new_tokens=5, do_sample=False)
+    assert out.shape == (2, 42)
