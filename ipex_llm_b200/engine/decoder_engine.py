@@ -382,6 +382,11 @@ class DecoderEngine:
         Row-parallel layers sum their partial outputs over the tensor-parallel group before the residual."""
         from ..ops import tcgen05_gemm
         if w.tp is not None:
+            comm = w.tp.symm()
+            if comm is not None and os.environ.get("IPEX_LLM_TP_FUSED_GEMM_AR", "1") != "0":
+                # the all-reduce runs inside the GEMM's epilogue (peer stores + arrival counters over NVLink)
+                return tcgen05_gemm.gemm_lowbit_ar(x, w.data, w.qtype, w.N, w.K, comm, bias=w.bias,
+                                                   residual=residual, wf=w.wf)
             out = tcgen05_gemm.gemm_lowbit(x, w.data, w.qtype, w.N, w.K, wf=w.wf)
             w.tp.all_reduce(out)
             if w.bias is not None:

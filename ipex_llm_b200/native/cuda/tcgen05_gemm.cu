@@ -53,6 +53,11 @@ struct GemmArgs {
   int m_tiles, n_tiles;
   int act;  // 0: none; 1 silu, 2 gelu(tanh): rows come as 16-row tiles gate, up, gate, up ... and out has N/2 columns
   int* err;
+  // tensor parallel (tp_world > 1): the output is the sum of every rank's product.  tp_stage[r] / tp_flags[r] point
+  // at rank r's staging buffer [tp_world][tiles][128][BT] of T and its per-(tile, lane quarter) arrival counters.
+  int tp_rank, tp_world;
+  void* const* tp_stage;
+  int* const* tp_flags;
 };
 
 __device__ __forceinline__ int pair_row(int r) { return (r & 7) * 2 + (r >> 3); }
@@ -246,18 +251,22 @@ __device__ __forceinline__ void dequant_role(const GemmArgs& a, uint8_t* sA, uin
       if (valid && u < units) asm volatile("prefetch.global.L2 [%0];" ::"l"(wrow + (int64_t)u * tile_stride));
     };
 
-    uint4 n0, n1;
-    float nd0 = 0.f, nd1 = 0.f, nm0 = 0.f, nm1 = 0.f;
+    // two units are always in flight in registers (the loads of unit u+2 are issued before unit u is expanded), later
+    // ones are pulled into L2: the dequantizers must never wait for DRAM
+    uint4 n0, n1, p0, p1;
+    float nd0 = 0.f, nd1 = 0.f, nm0 = 0.f, nm1 = 0.f, pd0 = 0.f, pd1 = 0.f, pm0 = 0.f, pm1 = 0.f;
     load_unit(0, n0, n1, nd0, nd1, nm0, nm1);
+    load_unit(1, p0, p1, pd0, pd1, pm0, pm1);
 #pragma unroll 1
-    for (int u = 1; u <= kPrefetchUnits; ++u) prefetch_unit(u);
+    for (int u = 2; u <= 1 + kPrefetchUnits; ++u) prefetch_unit(u);
 
 #pragma unroll 1
     for (int u = 0; u < units && ok; ++u) {
       const uint4 q0 = n0, q1 = n1;
       const float d0 = nd0, d1 = nd1, m0 = nm0, m1 = nm1;
-      load_unit(u + 1, n0, n1, nd0, nd1, nm0, nm1);
-      prefetch_unit(u + 1 + kPrefetchUnits);
+      n0 = p0; n1 = p1; nd0 = pd0; nd1 = pd1; nm0 = pm0; nm1 = pm1;
+      load_unit(u + 2, p0, p1, pd0, pd1, pm0, pm1);
+      prefetch_unit(u + 2 + kPrefetchUnits);
       constexpr int kSub = k4 ? 2 : 1;  // stages fed by one unit
 #pragma unroll
       for (int g = 0; g < kSub; ++g) {
@@ -295,6 +304,76 @@ __device__ __forceinline__ void dequant_role(const GemmArgs& a, uint8_t* sA, uin
       }
     }
   }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// tensor-parallel epilogue, second half: wait (bounded) until every rank's partial of (tile, lane quarter) has
+// arrived in the local staging buffer, sum them in fp32, add bias / residual and store the finished rows.
+// The counter is reset by its only reader, so a completed launch leaves all counters zero.
+// ------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add(int* p, int v) {
+  asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+template <typename T, int BT>
+__device__ bool tp_finalize(const GemmArgs& a, int t, int qd, int lane, int ntiles, volatile int* abort_flag) {
+  int* flag = a.tp_flags[a.tp_rank] + t * 4 + qd;
+  int arrived = 0;
+  if (lane == 0) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+      if (ld_acquire_sys(flag) >= a.tp_world) { arrived = 1; break; }
+      __nanosleep(64);
+      if ((i & 255) == 255 && *abort_flag) break;
+    }
+    if (arrived) *flag = 0;
+    else {
+      report(a.err, 14);
+      *abort_flag = 1;
+    }
+  }
+  arrived = __shfl_sync(0xffffffffu, arrived, 0);
+  if (!arrived) return false;
+  const int nb = t / a.m_tiles, mb = t % a.m_tiles;
+  const int n = nb * kBM + qd * 32 + lane;
+  if (n >= a.N) return true;
+  T* out = reinterpret_cast<T*>(a.out);
+  const T* res = reinterpret_cast<const T*>(a.residual);
+  const float bv = a.bias != nullptr ? to_float(reinterpret_cast<const T*>(a.bias)[n]) : 0.f;
+  const size_t tile_elems = (size_t)kBM * BT;
+  const T* mine = reinterpret_cast<const T*>(a.tp_stage[a.tp_rank]);
+#pragma unroll 1
+  for (int c = 0; c < BT / 32; ++c) {
+    float acc[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) acc[j] = bv;
+    for (int rk = 0; rk < a.tp_world; ++rk) {
+      const uint4* src = reinterpret_cast<const uint4*>(mine + ((size_t)rk * ntiles + t) * tile_elems +
+                                                        (size_t)(qd * 32 + lane) * BT + c * 32);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 raw = __ldcg(src + q);   // written by peers: read through L2
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[q * 8 + j] += to_float(e[j]);
+      }
+    }
+    const int m0 = mb * BT + c * 32;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int m = m0 + j;
+      if (m < a.M) {
+        float f = acc[j];
+        if (res != nullptr) f += to_float(res[(int64_t)m * a.ldr + n]);
+        out[(int64_t)m * a.ldo + n] = from_float<T>(f);
+      }
+    }
+  }
+  return true;
 }
 
 // ------------------------------------------------------------------------------------------------------------------
@@ -409,17 +488,51 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     const T* res = reinterpret_cast<const T*>(a.residual);
     const T* bias = reinterpret_cast<const T*>(a.bias);
     int it = 0;
+    int prev_t = -1;      // tensor-parallel mode: tile whose partials are pushed but not yet reduced
+    bool ok_tp = true;
     for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
       const int nb = t / a.m_tiles, mb = t % a.m_tiles;
       const int acc = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
       if (!mbar_wait(&acc_full[acc], acc_ph, abort_flag)) {
         if (lane == 0) report(a.err, 10);
+        prev_t = -1;
         break;
       }
       tcgen05_fence_after();
       const int n = nb * kBM + qd * 32 + lane;
       const float bv = (bias != nullptr && n < a.N) ? to_float(bias[n]) : 0.f;
+      if (a.tp_world > 1) {
+        // ---- row-parallel layer: all-reduce fused into the epilogue, over NVLink peer memory ----
+        // push: this rank's partial tile goes, as T, into slot [tp_rank][tile] of EVERY rank's staging buffer
+        // (layout [weight row][token], so each lane writes 64 contiguous bytes per 32-token chunk), then the
+        // (tile, lane-quarter) arrival counter of every rank is bumped with release semantics.
+        const size_t tile_elems = (size_t)kBM * BT;
+        const size_t slot = ((size_t)a.tp_rank * ntiles + t) * tile_elems + (size_t)(qd * 32 + lane) * BT;
+#pragma unroll 1
+        for (int c = 0; c < BT / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_base + (uint32_t(qd * 32) << 16) + acc * BT + c * 32, v);
+          __align__(16) T packed[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) packed[j] = from_float<T>(__uint_as_float(v[j]));
+          for (int rk = 0; rk < a.tp_world; ++rk) {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.tp_stage[rk]) + slot + c * 32);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) dst[q] = reinterpret_cast<const uint4*>(packed)[q];
+          }
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);      // TMEM is free again: the MMA of the next tile may start
+        __threadfence_system();
+        __syncwarp();
+        if (lane < a.tp_world) red_release_sys_add(a.tp_flags[lane] + t * 4 + qd, 1);
+        // finalize the PREVIOUS tile: its partials had a whole tile time to arrive
+        if (prev_t >= 0) ok_tp = ok_tp && tp_finalize<T, BT>(a, prev_t, qd, lane, ntiles, abort_flag);
+        prev_t = t;
+        continue;
+      }
       // activation mode: lanes 0..15 hold gate rows, lanes 16..31 the matching up rows; 16 outputs per warp
       const int n_out = a.act != 0 ? (nb * kBM + qd * 32) / 2 + (lane & 15) : n;
       const int n_lim = a.act != 0 ? a.N / 2 : a.N;
@@ -453,6 +566,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
     }
+    if (a.tp_world > 1 && prev_t >= 0 && ok_tp) tp_finalize<T, BT>(a, prev_t, qd, lane, ntiles, abort_flag);
   } else {
     if constexpr (!kDense) dequant_role<T, BT, WF>(a, sA, full, empty, abort_flag, lut2);
   }
@@ -561,6 +675,53 @@ IPEX_API int ipex_gemm_lowbit_tcgen05(const void* x, const void* w, void* out, c
   a.n_tiles = (N + kBM - 1) / kBM;
   a.act = act;
   a.err = err;
+  cudaStream_t st = (cudaStream_t)stream;
+  return (int)(dtype == DT_F16 ? dispatch_wf<__half>(wf, bt, tx, tx, a, sm_count(), st)
+                               : dispatch_wf<__nv_bfloat16>(wf, bt, tx, tx, a, sm_count(), st));
+}
+
+// Bytes of staging every rank must provide for ipex_gemm_lowbit_tcgen05_ar (one parity), and number of counters.
+IPEX_API int64_t ipex_gemm_tcgen05_ar_stage_bytes(int M, int N, int world) {
+  const int bt = ipex_gemm_tcgen05_token_tile(M);
+  const int64_t tiles = (int64_t)((M + bt - 1) / bt) * ((N + kBM - 1) / kBM);
+  return (int64_t)world * tiles * kBM * bt * 2;
+}
+IPEX_API int64_t ipex_gemm_tcgen05_ar_counters(int M, int N) {
+  const int bt = ipex_gemm_tcgen05_token_tile(M);
+  return (int64_t)((M + bt - 1) / bt) * ((N + kBM - 1) / kBM) * 4;
+}
+
+// Row-parallel layer of a tensor-parallel model: out = sum over ranks of x_r . W_r^T (+ bias) (+ residual), the
+// all-reduce running inside the GEMM's epilogue over NVLink peer memory (plain peer stores + release / acquire
+// counters; no multicast).  Every rank launches the same shape.  tp_stage / tp_flags: device arrays of `world`
+// pointers into the ranks' symmetric buffers for this call's parity (two parities alternate between consecutive
+// calls); counters zero before the first call, left zero.  Bounded waits: *err = 14 when a peer never arrives.
+IPEX_API int ipex_gemm_lowbit_tcgen05_ar(const void* x, const void* w, void* out, const void* bias,
+                                         const void* residual, const float* lut, int M, int N, int K, int64_t ldx,
+                                         int64_t ldo, int64_t ldr, int wf, int dtype, int* err, void* stream,
+                                         int tp_rank, int tp_world, const void* tp_stage, const void* tp_flags) {
+  if (M < 1 || N < 1 || K < 1 || (ldx % 8) != 0) return (int)cudaErrorInvalidValue;
+  if (reinterpret_cast<uintptr_t>(x) & 15) return (int)cudaErrorInvalidValue;
+  if (dtype != DT_F16 && dtype != DT_BF16) return (int)cudaErrorInvalidValue;
+  if (tp_world < 2 || tp_world > 8 || tp_rank < 0 || tp_rank >= tp_world || tp_stage == nullptr || tp_flags == nullptr)
+    return (int)cudaErrorInvalidValue;
+  if (wf == WF_LUT4 && lut == nullptr) return (int)cudaErrorInvalidValue;
+  const int bt = ipex_gemm_tcgen05_token_tile(M);
+  const CUtensorMapDataType tdt = dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap tx;
+  if (!tc5::encode_2d_sw128(&tx, tdt, x, (uint64_t)K, (uint64_t)M, (uint64_t)ldx * 2, kBK, bt)) return -1;
+  GemmArgs a = {};
+  a.w = reinterpret_cast<const uint8_t*>(w); a.lut = lut;
+  a.out = out; a.bias = bias; a.residual = residual; a.ldo = ldo; a.ldr = ldr;
+  a.Np = ceil_to_i64(N, 16); a.Kp = ceil_to_i64(K, 128);
+  a.M = M; a.N = N; a.K = K;
+  a.m_tiles = (M + bt - 1) / bt;
+  a.n_tiles = (N + kBM - 1) / kBM;
+  a.act = 0;
+  a.err = err;
+  a.tp_rank = tp_rank; a.tp_world = tp_world;
+  a.tp_stage = reinterpret_cast<void* const*>(tp_stage);
+  a.tp_flags = reinterpret_cast<int* const*>(tp_flags);
   cudaStream_t st = (cudaStream_t)stream;
   return (int)(dtype == DT_F16 ? dispatch_wf<__half>(wf, bt, tx, tx, a, sm_count(), st)
                                : dispatch_wf<__nv_bfloat16>(wf, bt, tx, tx, a, sm_count(), st));

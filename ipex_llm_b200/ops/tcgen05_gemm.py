@@ -8,6 +8,8 @@ Reference counterpart: the GEMM branch of ``xe_linear.forward_new`` that the ref
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from ..native import cuda_api as api
@@ -85,3 +87,40 @@ def gemm_lowbit(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K: in
     api.check(rc, "gemm_lowbit_tcgen05")
     return out
 
+
+
+def gemm_lowbit_ar(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K: int, comm, out: torch.Tensor = None,
+                   bias: torch.Tensor = None, residual: torch.Tensor = None, wf: int = None) -> torch.Tensor:
+    """Row-parallel projection of a tensor-parallel model: ``sum_over_ranks(x_r @ dequant(W_r).T) (+ bias)
+    (+ residual)`` with the all-reduce fused into the GEMM's epilogue (peer stores over NVLink).  ``comm`` is the
+    group's ``SymmComm``; every rank issues the same calls in the same order."""
+    from .cuda_ops import QTYPE_TO_WF, lut_for
+    lib = cuda_lib()
+    M = x.shape[0]
+    if x.stride(1) != 1 or x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0:
+        x = x.contiguous()
+    if out is None:
+        out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    if residual is not None and residual.stride(1) != 1:
+        residual = residual.contiguous()
+    if wf is None:
+        wf = QTYPE_TO_WF[qtype]
+    lut = lut_for(qtype, x.device) if qtype is not None else None
+    sb = lib.ipex_gemm_tcgen05_ar_stage_bytes
+    sb.argtypes, sb.restype = [ctypes.c_int] * 3, ctypes.c_int64
+    cn = lib.ipex_gemm_tcgen05_ar_counters
+    cn.argtypes, cn.restype = [ctypes.c_int] * 2, ctypes.c_int64
+    rank, world, stage, flags = comm.gemm_ar_args(int(sb(M, N, comm.world)), int(cn(M, N)))
+    fn = lib.ipex_gemm_lowbit_tcgen05_ar
+    fn.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int] * 3 + [ctypes.c_int64] * 3 + [ctypes.c_int, ctypes.c_int,
+                                                                                    ctypes.c_void_p, ctypes.c_void_p,
+                                                                                    ctypes.c_int, ctypes.c_int,
+                                                                                    ctypes.c_void_p, ctypes.c_void_p]
+    fn.restype = ctypes.c_int
+    rc = fn(ptr(x), ptr(w_data), ptr(out), ptr(bias), ptr(residual), ptr(lut), M, N, K, x.stride(0), out.stride(0),
+            residual.stride(0) if residual is not None else 0, wf, api.dtype_code(x.dtype), ptr(_err(x.device)),
+            current_stream(), rank, world, ptr(stage), ptr(flags))
+    if rc == -1:
+        raise RuntimeError("ipex_llm_b200: the driver's tensor-map encoder rejected the GEMM operands")
+    api.check(rc, "gemm_lowbit_tcgen05_ar")
+    return out

@@ -108,3 +108,40 @@ class SymmComm:
         """(rank, world, npad, bufs_ptr_array, tile_flags_ptr_array) for the next fused GEMV+all-reduce call."""
         par = self.next_parity()
         return self.rank, self.world, self.npad, self.gemv_bufs[par], self.tile_flags[par]
+
+    # ------------------------------------------------------------------------------------------------
+    def gemm_ar_args(self, stage_bytes: int, n_counters: int):
+        """Staging + counters for the next GEMM fused with its all-reduce (``ipex_gemm_lowbit_tcgen05_ar``): returns
+        ``(rank, world, stage_ptr_array, flag_ptr_array)`` for this call's parity.  The symmetric buffer is created
+        on first use and grown when a larger product comes along; both are collective, so every rank must call this
+        with the same sizes in the same order (they do: the ranks run the same layers on the same token count)."""
+        import torch.distributed._symmetric_memory as symm_mem
+        need_stage = (stage_bytes + 255) // 256 * 256
+        need_flags = (n_counters * 4 + 255) // 256 * 256
+        cur = getattr(self, "_gemm_cap", (0, 0))
+        if need_stage > cur[0] or need_flags > cur[1]:
+            cap_stage = max(need_stage, cur[0], 32 << 20)
+            cap_flags = max(need_flags, cur[1], 64 << 10)
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+            per = cap_stage + cap_flags
+            buf = symm_mem.empty(2 * per, dtype=torch.uint8, device=self.device)
+            buf.zero_()
+            torch.cuda.synchronize()
+            try:
+                handle = symm_mem.rendezvous(buf, self.group)
+            except Exception:  # noqa: BLE001 (older signatures take the group name)
+                handle = symm_mem.rendezvous(buf, self.group.group_name)
+            bases = [int(p) for p in handle.buffer_ptrs]
+            dist.barrier(group=self.group)
+            self._gemm_buf, self._gemm_handle, self._gemm_cap = buf, handle, (cap_stage, cap_flags)
+            self._gemm_stage, self._gemm_flags = [], []
+            for par in range(2):
+                o = par * per
+                self._gemm_stage.append(torch.tensor([b + o for b in bases], dtype=torch.int64, device=self.device))
+                self._gemm_flags.append(torch.tensor([b + o + cap_stage for b in bases], dtype=torch.int64,
+                                                     device=self.device))
+            self._gemm_parity = 0
+        par = self._gemm_parity
+        self._gemm_parity ^= 1
+        return self.rank, self.world, self._gemm_stage[par], self._gemm_flags[par]

@@ -78,6 +78,28 @@ def main():
             err = (out.float() - ref).abs().max().item() / ref.abs().max().item()
             assert err < 5e-3, (name, err)
         cuda_ops.check_error_flag(dev)
+        # 2b. row-parallel GEMM (prompt sized) with the all-reduce fused into the tcgen05 epilogue
+        from ipex_llm_b200.ops import tcgen05_gemm
+        for Mtok, Nout in ((70, 384), (300, 1024)):
+            xg = torch.randn(Mtok, K, device=dev).half()
+            rg = torch.randn(Mtok, Nout, device=dev).half()
+            bg = torch.randn(Nout, device=dev).half()
+            wg = torch.randn(Nout, K, device=dev) * 0.05
+            for name in ("sym_int4", "fp8_e4m3"):
+                q = qt.qtype_from_name(name)
+                w_r = wg[:, rank * ks:(rank + 1) * ks].contiguous()
+                packed = quantize_to_device_layout(w_r.half(), q)
+                deq = cuda_ops.dequantize_device(packed, (Nout, ks), q, torch.float32)
+                part = xg[:, rank * ks:(rank + 1) * ks].float() @ deq.t()
+                dist.all_reduce(part)
+                ref = part + rg.float() + bg.float()
+                for _ in range(3):     # both staging parities and the self-cleaning counters
+                    out = tcgen05_gemm.gemm_lowbit_ar(xg[:, rank * ks:(rank + 1) * ks].contiguous(), packed, q, Nout,
+                                                      ks, comm, bias=bg, residual=rg)
+                torch.cuda.synchronize()
+                err = (out.float() - ref).abs().max().item() / ref.abs().max().item()
+                assert err < 1e-2, ("gemm_ar", name, Mtok, err)
+        cuda_ops.check_error_flag(dev)
 
     # 3. tiny llama, tensor parallel
     torch.manual_seed(0)
