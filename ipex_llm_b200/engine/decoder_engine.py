@@ -158,6 +158,8 @@ class DecoderEngine:
         B = max_batch
         dev = self.device
         self.tokens = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.vtokens = torch.zeros(8, dtype=torch.int64, device=dev)      # verify_step: tokens in, arg-max out
+        self.vout = torch.zeros(8, dtype=torch.int64, device=dev)
         self.past_len = torch.zeros(B, dtype=torch.int32, device=dev)
         self.h = [torch.zeros(B, self.H, dtype=dt, device=dev) for _ in range(2)]
         self.qkv_buf = torch.zeros(B, self.layers[0].qkv.N, dtype=dt, device=dev)
@@ -250,30 +252,85 @@ class DecoderEngine:
         return {"w": w.data, "x": x, "y": y, "N": w.N, "K": w.K, "norm_w": norm_w, "bias": w.bias,
                 "residual": residual, "act": act, "eps": self.eps}
 
-    def _attention(self, L: _Layer, B: int):
+    def _attention(self, L: _Layer, B: int, Sq: int = 1):
+        """Rope + cache append + attention for ``B`` sequences of ``Sq`` new tokens each; rows of the activation
+        buffers are ordered (sequence, position)."""
         lib = self._lib
         layer = self.cache.layers[L.layer_idx]
         kc, vc = layer._k, layer._v
         D, Hq, Hkv = self.hd, self.n_heads, self.n_kv
         q_off_k = Hq * D
         q_off_v = (Hq + Hkv) * D
-        qkv = self.qkv_buf[:B]
+        qkv = self.qkv_buf[:B * Sq]
         ld = qkv.stride(0)
         knew = qkv[:, q_off_k:]
         vnew = qkv[:, q_off_v:]
-        out = self.attn_buf[:B]
+        out = self.attn_buf[:B * Sq]
+        ldo = out.stride(0)
         G = Hq // Hkv
         nsplit = self._nsplit
-        floats = lib.ipex_attn_decode_scratch_floats(B, Hkv, G, 1, D, nsplit)
-        ints = lib.ipex_attn_decode_counter_ints(B, Hkv, G, 1)
+        floats = lib.ipex_attn_decode_scratch_floats(B, Hkv, G, Sq, D, nsplit)
+        ints = lib.ipex_attn_decode_counter_ints(B, Hkv, G, Sq)
         scratch, counters = cuda_ops.attn_workspace(self.device, floats, ints)
-        strides = (ctypes.c_int64 * 12)(ld, ld, D, ld, ld, D, kc.stride(0), kc.stride(1), kc.stride(2),
-                                        out.stride(0), out.stride(0), D)
+        strides = (ctypes.c_int64 * 12)(Sq * ld, ld, D, Sq * ld, ld, D, kc.stride(0), kc.stride(1), kc.stride(2),
+                                        Sq * ldo, ldo, D)
         rc = lib.ipex_attn_decode(ptr(qkv), ptr(knew), ptr(vnew), ptr(kc), ptr(vc), ptr(out), ptr(self.past_len), 0,
-                                  ptr(self.cos), ptr(self.sin), ptr(scratch), ptr(counters), strides, B, 1, Hq, Hkv,
+                                  ptr(self.cos), ptr(self.sin), ptr(scratch), ptr(counters), strides, B, Sq, Hq, Hkv,
                                   D, nsplit, 1, self.rot_dim, 1, 0, 1.0 / math.sqrt(D), 0.0, int(self.kv_fp8),
                                   api.dtype_code(self.dtype), int(self.use_pdl), current_stream())
         api.check(rc, "attn_decode")
+
+    # ------------------------------------------------------------------------------------------------
+    # multi-token scoring of ONE sequence (self-speculative verification, prompt lookup)
+    # ------------------------------------------------------------------------------------------------
+    def _verify_kernels(self, S: int):
+        lib = self._lib
+        dtc = api.dtype_code(self.dtype)
+        pdl = int(self.use_pdl)
+        h0, h1 = self.h[0][:S], self.h[1][:S]
+        rc = lib.ipex_embedding(ptr(self.vtokens), ptr(self.embed), ptr(h0), S, self.H, 1.0, dtc, 0, current_stream())
+        api.check(rc, "embedding")
+        for L in self.layers:
+            self._gemv(L.qkv, h0, self.qkv_buf[:S], norm_w=L.ln1)
+            self._attention(L, 1, Sq=S)
+            self._gemv(L.o, self.attn_buf[:S], h1, residual=h0)
+            self._gemv(L.gate_up, h1, self.act_buf[:S], norm_w=L.ln2, act=1)
+            self._gemv(L.down, self.act_buf[:S], h0, residual=h1)
+        self._gemv(self.lm_head, h0, self.logits[:S], norm_w=self.final_norm)
+        rc = lib.ipex_argmax(ptr(self.logits), ptr(self.vout), S, self.vocab, self.logits.stride(0), dtc, pdl,
+                             current_stream())
+        api.check(rc, "argmax")
+
+    def verify_step(self, S: int, use_graph: bool = True):
+        """Score ``vtokens[:S]`` (1 <= S <= min(8, max_batch)) as the next ``S`` tokens of sequence 0 in one pass:
+        their K/V go to cache rows ``past_len[0] ..``, ``logits[:S]`` hold the scores after each of them and
+        ``vout[:S]`` the arg-max tokens.  ``past_len`` is left as it was: the caller advances it by the number of
+        tokens it keeps, which is all the cropping a rejected draft needs (rows past ``past_len`` are dead).
+        The reference verifies drafts with a full module-tree forward and crops the cache tensors afterwards
+        (python/llm/src/ipex_llm/transformers/speculative.py:1071-1113, 540-608)."""
+        if S < 1 or S > min(8, self.max_batch):
+            raise ValueError(f"verify_step scores 1..{min(8, self.max_batch)} tokens, got {S}")
+        if self.layers[0].o.tp is not None:
+            raise NotImplementedError("verify_step runs on a single GPU")
+        if self._nsplit is None:
+            self._nsplit = cuda_ops.pick_nsplit(1,self.n_kv, self.max_len, rows=self.n_heads // self.n_kv)
+        if not use_graph or os.environ.get("IPEX_LLM_ENGINE_GRAPH", "1") == "0":
+            self._verify_kernels(S)
+            return
+        key = ("verify", S)
+        entry = self._graphs.get(key)
+        if entry is None:
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._verify_kernels(S)       # warm-up: writes only rows past past_len and scratch buffers
+            torch.cuda.current_stream().wait_stream(s)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._verify_kernels(S)
+            entry = (g, self.cache, 0)
+            self._graphs[key] = entry
+        entry[0].replay()
 
     def _step_kernels(self, B: int):
         """Issue one decode step for ``B`` sequences on the current stream: tokens[:B] -> tokens[:B]."""

@@ -447,29 +447,92 @@ __global__ void __launch_bounds__(kThreads) gemv_dense_kernel(GemvArgs a) {
   {
     const T* x = reinterpret_cast<const T*>(a.x);
     const T* nw = reinterpret_cast<const T*>(a.norm_w);
-    for (int m = 0; m < a.M; m++) {
-      float rstd = 1.f;
+    // K is a multiple of 16, so 8-element vectors never straddle the end of a row
+    const bool vec = (a.ldx & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                     (nw == nullptr || (reinterpret_cast<uintptr_t>(nw) & 15) == 0);
+    if (vec) {
+      // all rows at once: one pass for the sums of squares with ONE block reduction (through `red`, free until
+      // the epilogue), one pass that normalises and stores 16 bytes per row and thread
+      float rstd[8];
+#pragma unroll
+      for (int m = 0; m < 8; m++) rstd[m] = 1.f;
       if (nw != nullptr) {
-        float ss = 0.f;
-        for (int k = tid; k < a.K; k += kThreads) {
-          float v = DT<T>::to_f(x[(size_t)m * a.ldx + k]);
-          ss += v * v;
+        float ss[8];
+#pragma unroll
+        for (int m = 0; m < 8; m++) ss[m] = 0.f;
+        for (int k = tid * 8; k < a.K; k += kThreads * 8) {
+#pragma unroll
+          for (int m = 0; m < 8; m++) {
+            if (m < a.M) {
+              const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)m * a.ldx + k);
+              const T* pv = reinterpret_cast<const T*>(&v);
+#pragma unroll
+              for (int j = 0; j < 8; j++) {
+                const float f = DT<T>::to_f(pv[j]);
+                ss[m] += f * f;
+              }
+            }
+          }
         }
-        ss = warp_sum(ss);
-        if (lane == 0) scratch[warp] = ss;
+#pragma unroll
+        for (int m = 0; m < 8; m++) {
+          ss[m] = warp_sum(ss[m]);
+          if (lane == 0) red[warp * 8 + m] = ss[m];
+        }
         __syncthreads();
-        float tot = 0.f;
-        for (int w = 0; w < kWarps; w++) tot += scratch[w];
-        rstd = rsqrtf(tot / (float)a.K + a.eps);
-        __syncthreads();
+#pragma unroll
+        for (int m = 0; m < 8; m++) {
+          float tot = 0.f;
+          for (int w = 0; w < kWarps; w++) tot += red[w * 8 + m];
+          rstd[m] = rsqrtf(tot / (float)a.K + a.eps);
+        }
       }
-      for (int k = tid; k < Kp; k += kThreads) {
-        float v = 0.f;
-        if (k < a.K) {
-          v = DT<T>::to_f(x[(size_t)m * a.ldx + k]);
-          if (nw != nullptr) v = v * rstd * (DT<T>::to_f(nw[k]) + a.norm_offset);
+      for (int k = tid * 8; k < Kp; k += kThreads * 8) {
+        uint4 nv = make_uint4(0, 0, 0, 0);
+        if (nw != nullptr && k < a.K) nv = *reinterpret_cast<const uint4*>(nw + k);
+        const T* pn = reinterpret_cast<const T*>(&nv);
+#pragma unroll
+        for (int m = 0; m < 8; m++) {
+          if (m < a.M) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (k < a.K) {
+              v = *reinterpret_cast<const uint4*>(x + (size_t)m * a.ldx + k);
+              if (nw != nullptr) {
+                T* pv = reinterpret_cast<T*>(&v);
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                  pv[j] = DT<T>::from_f(DT<T>::to_f(pv[j]) * rstd[m] * (DT<T>::to_f(pn[j]) + a.norm_offset));
+              }
+            }
+            *reinterpret_cast<uint4*>(xs + m * xs_stride + k) = v;
+          }
         }
-        xs[m * xs_stride + k] = DT<T>::from_f(v);
+      }
+    } else {
+      for (int m = 0; m < a.M; m++) {
+        float rstd = 1.f;
+        if (nw != nullptr) {
+          float ss = 0.f;
+          for (int k = tid; k < a.K; k += kThreads) {
+            float v = DT<T>::to_f(x[(size_t)m * a.ldx + k]);
+            ss += v * v;
+          }
+          ss = warp_sum(ss);
+          if (lane == 0) scratch[warp] = ss;
+          __syncthreads();
+          float tot = 0.f;
+          for (int w = 0; w < kWarps; w++) tot += scratch[w];
+          rstd = rsqrtf(tot / (float)a.K + a.eps);
+          __syncthreads();
+        }
+        for (int k = tid; k < Kp; k += kThreads) {
+          float v = 0.f;
+          if (k < a.K) {
+            v = DT<T>::to_f(x[(size_t)m * a.ldx + k]);
+            if (nw != nullptr) v = v * rstd * (DT<T>::to_f(nw[k]) + a.norm_offset);
+          }
+          xs[m * xs_stride + k] = DT<T>::from_f(v);
+        }
       }
     }
   }
@@ -526,6 +589,27 @@ __global__ void __launch_bounds__(kThreads) gemv_dense_kernel(GemvArgs a) {
   }
   __syncthreads();
   T* y = reinterpret_cast<T*>(a.y);
+  if (RT == 2 && a.act != 0) {
+    // rows [row0, row0+16) hold a gate tile, the next 16 its up tile (16-row interleaved weight)
+    for (int i = tid; i < 128; i += kThreads) {
+      const int col = i / 16, row = i % 16;
+      float gsum = 0.f, usum = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; w++) {
+        gsum += red[((size_t)(w * RT) * 16 + row) * 8 + col];
+        usum += red[((size_t)(w * RT + 1) * 16 + row) * 8 + col];
+      }
+      const int n = blockIdx.x * 16 + row;
+      if (n < a.N / 2 && col < a.M) {
+        if (a.bias != nullptr) {
+          gsum += load_as_float<T>(a.bias, (size_t)row0 + row);
+          usum += load_as_float<T>(a.bias, (size_t)row0 + 16 + row);
+        }
+        y[(size_t)col * a.ldy + n] = DT<T>::from_f(act_apply(gsum, a.act) * usum);
+      }
+    }
+    return;
+  }
   for (int i = tid; i < RT * 128; i += kThreads) {
     const int r = i / 128, col = (i % 128) / 16, row = i % 16;
     float s = 0.f;
@@ -592,8 +676,24 @@ IPEX_API int ipex_gemv_lowbit(const void* w, int wf, const void* x, void* y, int
   a.w_list = nullptr; a.expert_ids = nullptr; a.x_div = 1; a.x_div_slots = 1;
   cudaStream_t s = (cudaStream_t)stream;
   if (wf == WF_F16 || wf == WF_BF16) {
-    if (act != 0) return (int)cudaErrorInvalidValue;
     const int Kp = (int)ceil_to_i64(K, 64);
+    if (act != 0) {
+      // gate/up interleaved in 16-row tiles: one CTA per (gate tile, up tile) pair, N/2 output columns
+      if ((N % 32) != 0) return (int)cudaErrorInvalidValue;
+      size_t smem2 = (((size_t)M * (Kp + 8) * 2 + 15) & ~(size_t)15) + (size_t)kWarps * 2 * 128 * 4 + 64;
+      dim3 grid2(N / 32);
+      if (wf == WF_F16 && dtype == DT_F16) {
+        auto kern = gemv_dense_kernel<__half, 2>;
+        if (smem2 > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+        return (int)launch_kernel(kern, grid2, dim3(kThreads), smem2, s, pdl != 0, a);
+      }
+      if (wf == WF_BF16 && dtype == DT_BF16) {
+        auto kern = gemv_dense_kernel<__nv_bfloat16, 2>;
+        if (smem2 > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+        return (int)launch_kernel(kern, grid2, dim3(kThreads), smem2, s, pdl != 0, a);
+      }
+      return (int)cudaErrorInvalidValue;
+    }
     size_t smem = (((size_t)M * (Kp + 8) * 2 + 15) & ~(size_t)15) + (size_t)kWarps * 128 * 4 + 64;
     dim3 grid((N + 15) / 16);
     if (wf == WF_F16) {

@@ -79,6 +79,180 @@ def _crop(cache, length: int):
     cache.crop(length)
 
 
+def _engine_pair(target, draft, need_len: int):
+    """Flattened graph engines of target and draft with equal geometry (they share one cache), or None when
+    either model is outside the engine's coverage."""
+    import os
+    if os.environ.get("IPEX_LLM_SPEC_ENGINE", "1") == "0":
+        return None
+    dev = next(target.parameters()).device
+    if dev.type != "cuda" or next(draft.parameters()).device != dev:
+        return None
+    try:
+        from ..engine import DecoderEngine, supports
+        if not supports(target, {}) or not supports(draft, {}):
+            return None
+        max_len = (max(need_len, 2048) + 255) // 256 * 256
+        pair = []
+        for m, mb in ((target, 8), (draft, 1)):
+            eng = getattr(m, "_ipex_engine", None)
+            if eng is None or eng.max_batch < mb or eng.max_len != max_len:
+                eng = DecoderEngine(m, max_batch=mb, max_len=max_len)
+                m._ipex_engine = eng
+            pair.append(eng)
+        t, d = pair
+        if t.kv_fp8 != d.kv_fp8 or t.dtype != d.dtype or t.n_kv != d.n_kv or t.hd != d.hd or \
+                len(t.layers) != len(d.layers) or t.layers[0].o.tp is not None:
+            return None
+        return t, d
+    except NotImplementedError:
+        return None
+
+
+def _speculative_generate_engine(self, t, d, input_ids, max_new_tokens, max_step_draft, th_stop_draft,
+                                 auto_th_stop_draft, auto_parameters, hf_adjust, min_step_draft, do_sample,
+                                 temperature, top_k, top_p, eos_ids, streamer):
+    """The same algorithm on the two graph engines: every draft token is one graph replay of the int4 engine, the
+    verification is ONE graph replay of the target engine scoring up to 8 tokens (multi-row GEMVs, the split-KV
+    attention kernel with the new rows causal among themselves), and rejecting drafts is just not advancing the
+    device-side length.  Host work per iteration: one read of the draft's confidence per proposal (the early
+    stop needs it) and one read of the target's tokens."""
+    device = input_ids.device
+    clear_benchmarks(self)
+    max_step_draft = max(1, min(max_step_draft, 7))       # current token + drafts are scored as <= 8 GEMV rows
+    min_step_draft = min(min_step_draft, max_step_draft)
+    out_ids = []
+    tmp_matchness = 0.0
+    step_verify = 0
+
+    _sync(device)
+    tic = time.time()
+    logits = t.prefill(input_ids)                          # [1, V]; K/V of the prompt in t.cache
+    d.bind_cache(t.cache, 1)
+    if do_sample:
+        probs = torch.softmax(_warp_logits(logits[0], temperature, top_k, top_p), dim=-1)
+        current = int(torch.multinomial(probs, 1))
+    else:
+        current = int(torch.argmax(logits[0]))
+    out_ids.append(current)
+    n_past = input_ids.shape[1]
+    _sync(device)
+    self.first_token_time = time.time() - tic
+    e2e_tic = time.time()
+    if streamer is not None:
+        streamer.put(input_ids.cpu())
+        streamer.put(torch.tensor([[current]]))
+    finished = bool(eos_ids) and current in eos_ids
+
+    while len(out_ids) < max_new_tokens and not finished:
+        _sync(device)
+        t0 = time.time()
+        # ---- 1. draft: graph replays of the int4 engine on the shared cache ----
+        d.past_len[:1].fill_(n_past)
+        d.tokens[:1].fill_(current)
+        drafts, draft_probs = [], []
+        for _ in range(max_step_draft):
+            d.decode_step(1)
+            row = d.logits[0]
+            if do_sample:
+                probs = torch.softmax(_warp_logits(row, temperature, top_k, top_p), dim=-1)
+                nt = torch.multinomial(probs, 1).view(-1)
+                d.tokens[:1].copy_(nt)
+                conf = float(probs[nt[0]])
+                tok = int(nt[0])
+                draft_probs.append(probs)
+            else:
+                # confidence of the arg-max token = 1 / sum(exp(l - l_max))
+                lf = row.float()
+                conf, tok = float(1.0 / torch.exp(lf - lf.max()).sum()), int(d.tokens[0])
+            drafts.append(tok)
+            if len(out_ids) + len(drafts) >= max_new_tokens:
+                break
+            if conf < th_stop_draft and len(drafts) >= min_step_draft:
+                break
+        drafted_n = len(drafts)
+        _sync(device)
+        t1 = time.time()
+        self.draft_time.append(t1 - t0)
+
+        # ---- 2. verify: one pass of the target over [current, drafts] ----
+        S = drafted_n + 1
+        t.vtokens[:S].copy_(torch.tensor([current] + drafts, dtype=torch.int64), non_blocking=False)
+        t.past_len[:1].fill_(n_past)
+        t.verify_step(S)
+        if not do_sample:
+            target_tokens = t.vout[:S].tolist()
+            n_match = 0
+            while n_match < drafted_n and target_tokens[n_match] == drafts[n_match]:
+                n_match += 1
+            accepted = target_tokens[: n_match + 1]
+        else:
+            v_logits = t.logits[:S]
+            n_match, accepted = 0, []
+            for i in range(drafted_n):
+                p_t = torch.softmax(_warp_logits(v_logits[i], temperature, top_k, top_p), dim=-1)
+                p_d = draft_probs[i]
+                ratio = float((p_t[drafts[i]] / p_d[drafts[i]].clamp_min(1e-20)).clamp(max=1.0))
+                if float(torch.rand(())) <= ratio:
+                    accepted.append(drafts[i])
+                    n_match += 1
+                else:
+                    resid = (p_t - p_d).clamp_min(0)
+                    resid = resid / resid.sum().clamp_min(1e-20)
+                    accepted.append(int(torch.multinomial(resid, 1)))
+                    break
+            if n_match == drafted_n:
+                p_t = torch.softmax(_warp_logits(v_logits[drafted_n], temperature, top_k, top_p), dim=-1)
+                accepted.append(int(torch.multinomial(p_t, 1)))
+        _sync(device)
+        t2 = time.time()
+        self.verify_time.append(t2 - t1)
+        self.generate_time.append(t2 - t0)
+
+        # ---- 3. commit: rows of [current, matched drafts] stay, the rest is dead storage past the length ----
+        n_past += n_match + 1
+        room = max_new_tokens - len(out_ids)
+        accepted = accepted[:room]
+        out_ids.extend(accepted)
+        if streamer is not None:
+            streamer.put(torch.tensor([accepted]))
+        current = accepted[-1]
+        self.draft_num.append(drafted_n)
+        self.accept_num.append(n_match)
+        self.n_drafted += drafted_n
+        self.n_matched += n_match
+        step_verify += 1
+
+        # ---- 4. adapt the early-stop threshold to the observed acceptance ----
+        if auto_th_stop_draft and step_verify % auto_parameters[0] == 0:
+            tmp_matchness = auto_parameters[1] * tmp_matchness + (1 - auto_parameters[1]) * (n_match / drafted_n)
+            if tmp_matchness < auto_parameters[2]:
+                new_th = th_stop_draft + auto_parameters[3]
+            elif drafted_n == max_step_draft:
+                new_th = th_stop_draft
+            else:
+                new_th = th_stop_draft - auto_parameters[3]
+            th_stop_draft = auto_parameters[4] * th_stop_draft + (1 - auto_parameters[4]) * new_th
+        if hf_adjust:
+            max_step_draft = min(7, max_step_draft + 1) if n_match == max_step_draft else max(1, max_step_draft - 1)
+        for e in eos_ids:
+            if e in out_ids:
+                out_ids = out_ids[: out_ids.index(e) + 1]
+                finished = True
+                break
+
+    if streamer is not None:
+        streamer.end()
+    t.past_len[:1].fill_(n_past)
+    t.sync_cache_length(n_past)
+    _sync(device)
+    self.n_token_generated = len(out_ids)
+    self.e2e_time_without_first = time.time() - e2e_tic
+    self.th_stop_draft = th_stop_draft
+    new = torch.tensor([out_ids], dtype=input_ids.dtype, device=device)
+    return torch.cat([input_ids, new], dim=-1)
+
+
 @torch.no_grad()
 def speculative_generate(self, inputs: Optional[torch.Tensor] = None, draft_model=None, max_new_tokens=10,
                          max_step_draft=8, th_stop_draft=0.8, auto_th_stop_draft=True,
@@ -88,6 +262,19 @@ def speculative_generate(self, inputs: Optional[torch.Tensor] = None, draft_mode
     invalidInputError(inputs is not None and inputs.dim() == 2, "inputs must be a [batch, seq] tensor of token ids")
     invalidInputError(inputs.shape[0] == 1, "speculative decoding supports batch size 1")
     min_step_draft = max(1, min_step_draft)
+    if inputs.device.type == "cuda" and (attention_mask is None or bool(attention_mask.all())):
+        pair = _engine_pair(self, draft_model, inputs.shape[1] + max_new_tokens + 16)
+        if pair is not None:
+            gc_ = generation_config or self.generation_config
+            sample_ = sampling_kwargs.get("do_sample", getattr(gc_, "do_sample", False))
+            eos_ = sampling_kwargs.get("eos_token_id", getattr(gc_, "eos_token_id", None))
+            return _speculative_generate_engine(
+                self, pair[0], pair[1], inputs, max_new_tokens, max_step_draft, th_stop_draft, auto_th_stop_draft,
+                auto_parameters, hf_adjust, min_step_draft, sample_,
+                sampling_kwargs.get("temperature", getattr(gc_, "temperature", 1.0)),
+                (sampling_kwargs.get("top_k", getattr(gc_, "top_k", None)) if sample_ else None),
+                (sampling_kwargs.get("top_p", getattr(gc_, "top_p", None)) if sample_ else None),
+                [] if eos_ is None else ([eos_] if isinstance(eos_, int) else list(eos_)), streamer)
     gc = generation_config or self.generation_config
     do_sample = sampling_kwargs.get("do_sample", getattr(gc, "do_sample", False))
     temperature = sampling_kwargs.get("temperature", getattr(gc, "temperature", 1.0))

@@ -132,6 +132,36 @@ def test_gemv_dense(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M", [1, 7])
+def test_gemv_dense_norm_residual_act(dtype, M):
+    """Dense half weights with the fused RMSNorm prologue (vector and scalar staging), residual and SwiGLU."""
+    from ipex_llm_b200.engine.decoder_engine import _W, _interleave_row_tiles
+    from ipex_llm_b200.native import cuda_api as api
+    from ipex_llm_b200.ops.cuda_ops import gemv_lowbit
+    torch.manual_seed(8)
+    K, I = 1040, 608
+    wf = api.WF_F16 if dtype == torch.float16 else api.WF_BF16
+    xb = torch.randn(M, K + 3).to(dtype).cuda()
+    gamma = (1.0 + 0.1 * torch.randn(K)).to(dtype).cuda()
+    wg = (torch.randn(I, K) * 0.03).to(dtype).cuda()
+    wu = (torch.randn(I, K) * 0.03).to(dtype).cuda()
+    res = torch.randn(M, I).to(dtype).cuda()
+    tol = 6e-3 if dtype == torch.float16 else 3e-2
+    for x in (xb[:, :K].contiguous(), xb[:, :K]):          # aligned rows, then a row stride of K + 3 elements
+        xf = x.float()
+        xn = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * gamma.float()
+        xn = xn.to(dtype).float()
+        ref = xn @ wg.float().t() + res.float()
+        y = gemv_lowbit(x, wg, None, I, K, norm_weight=gamma, eps=1e-5, residual=res, wf=wf).float()
+        assert (y - ref).abs().max().item() < tol * ref.abs().max().item()
+        gu = _interleave_row_tiles(_W(wg, wf, None, I, K), _W(wu, wf, None, I, K))
+        ref2 = torch.nn.functional.silu(xn @ wg.float().t()) * (xn @ wu.float().t())
+        y2 = gemv_lowbit(x, gu.data, None, 2 * I, K, norm_weight=gamma, eps=1e-5, act=1, wf=wf).float()
+        assert y2.shape == (M, I)
+        assert (y2 - ref2).abs().max().item() < tol * ref2.abs().max().item() + 1e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_norms_act_softmax(dtype):
     from ipex_llm_b200.ops import cuda_ops
     torch.manual_seed(6)
