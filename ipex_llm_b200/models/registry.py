@@ -11,6 +11,7 @@ from typing import Callable, List, Optional, Tuple
 
 from . import common as C
 from . import decoder as D
+from . import rwkv as R
 
 
 @dataclass
@@ -106,6 +107,17 @@ FAMILIES = {
     "aquila": Family(post=[("AquilaRMSNorm", C.rms_norm_forward)]),
     "deepseek_v3": Family(post=[("DeepseekV3RMSNorm", C.rms_norm_forward), ("DeepseekV3MLP", C.mlp_silu_forward)]),
     "mllama": Family(post=[("MllamaTextRMSNorm", C.rms_norm_forward), ("MllamaTextMLP", C.mlp_silu_forward)]),
+    "rwkv": Family(pre=[R.rescale_before_quantization],
+                   post=[("RwkvSelfAttention", R.rwkv4_attention_forward), ("RwkvFeedForward", R.rwkv4_ffn_forward)]),
+    # LayerNorm families without a dedicated forward file: low-bit linears + the fused LayerNorm kernel
+    "gpt_neox": Family(post=[("LayerNorm", C.layer_norm_forward)]),
+    "bloom": Family(post=[("LayerNorm", C.layer_norm_forward)]),
+    "gpt2": Family(post=[("LayerNorm", C.layer_norm_forward)]),
+    "gpt_bigcode": Family(post=[("LayerNorm", C.layer_norm_forward)]),
+    "falcon": Family(post=[("LayerNorm", C.layer_norm_forward)]),
+    "mpt": Family(post=[("LayerNorm", C.layer_norm_forward)]),
+    "phi": Family(post=[("LayerNorm", C.layer_norm_forward)]),
+    "opt": Family(post=[("LayerNorm", C.layer_norm_forward)]),
 }
 
 
