@@ -58,6 +58,21 @@ struct GemmArgs {
   int tp_rank, tp_world;
   void* const* tp_stage;
   int* const* tp_flags;
+  // all-gather in front of the GEMM (ag_flags != null): x is this rank's copy of the gathered activation, rows
+  // [r * ag_rows, (r + 1) * ag_rows) are pushed into it by rank r, which then sets ag_flags[r] to ag_epoch.  The
+  // loader waits for the ranks a token tile covers before it issues the tile's first load.
+  const int* ag_flags;
+  int ag_rows, ag_epoch;
+  // ... and the push of this rank's own rows, done by the epilogue warps of every CTA before their first tile:
+  // ag_src [rows of this rank, K] (row stride ag_ld_src) goes to rows tp_rank * ag_rows .. of ag_dst[p] for every
+  // rank p (ag_dst[p] = rank p's gathered buffer, row stride K); the CTA that draws the last ticket of ag_ticket
+  // publishes ag_epoch in slot tp_rank of every rank's flag array ag_peer_flags[p].
+  const void* ag_src;
+  int64_t ag_ld_src;
+  void* const* ag_dst;
+  int* const* ag_peer_flags;
+  int* ag_ticket;
+  int ag_world;
 };
 
 __device__ __forceinline__ int pair_row(int r) { return (r & 7) * 2 + (r >> 3); }
@@ -319,6 +334,9 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
 __device__ __forceinline__ void red_release_sys_add(int* p, int v) {
   asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 template <typename T, int BT>
 __device__ bool tp_finalize(const GemmArgs& a, int t, int qd, int lane, int ntiles, volatile int* abort_flag) {
@@ -434,8 +452,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
+      uint32_t ag_ready = 0;  // ranks whose rows are known to have landed
       for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
         const int nb = t / a.m_tiles, mb = t % a.m_tiles;
+        if (a.ag_flags != nullptr) {
+          const int row_hi = (mb * BT + BT < a.M ? mb * BT + BT : a.M) - 1;
+          for (int r = (mb * BT) / a.ag_rows; r <= row_hi / a.ag_rows && ok; ++r) {
+            if (ag_ready & (1u << r)) continue;
+            bool got = false;
+            for (uint32_t it = 0; it < kSpinLimit; ++it) {
+              if (ld_acquire_sys(a.ag_flags + r) - a.ag_epoch >= 0) { got = true; break; }
+              if (it >= 64) {
+                __nanosleep(it >= 4096 ? 256 : 32);
+                if (*abort_flag) break;
+              }
+            }
+            if (got) {
+              ag_ready |= 1u << r;
+              // the rows were written by a peer's generic stores; the TMA engine reads through the async proxy
+              asm volatile("fence.proxy.async;" ::: "memory");
+            } else {
+              *abort_flag = 1;
+              report(a.err, 15);
+              ok = false;
+            }
+          }
+          if (!ok) break;
+        }
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) { ok = false; report(a.err, 8); break; }
           mbar_expect_tx(&full[s], kDense ? C::kStageBytes : C::kBBytes);
@@ -487,6 +530,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     T* out = reinterpret_cast<T*>(a.out);
     const T* res = reinterpret_cast<const T*>(a.residual);
     const T* bias = reinterpret_cast<const T*>(a.bias);
+    if (a.ag_src != nullptr) {
+      // ---- all-gather half of the fused op: push this rank's rows to every rank, then publish the epoch ----
+      const int te = threadIdx.x - 64;                          // 0..127 over the four epilogue warps
+      const int vec_per_row = a.K / 8;                          // 16-byte vectors per row
+      int my_rows = a.M - a.tp_rank * a.ag_rows;
+      my_rows = my_rows < 0 ? 0 : (my_rows > a.ag_rows ? a.ag_rows : my_rows);
+      const int64_t total = (int64_t)my_rows * vec_per_row;
+      const T* src = reinterpret_cast<const T*>(a.ag_src);
+      for (int64_t v = (int64_t)blockIdx.x * 128 + te; v < total; v += (int64_t)gridDim.x * 128) {
+        const int64_t row = v / vec_per_row, c = v % vec_per_row;
+        const uint4 val = *reinterpret_cast<const uint4*>(src + row * a.ag_ld_src + c * 8);
+        for (int p = 0; p < a.ag_world; ++p) {
+          T* dst = reinterpret_cast<T*>(a.ag_dst[p]) + ((int64_t)a.tp_rank * a.ag_rows + row) * a.K + c * 8;
+          *reinterpret_cast<uint4*>(dst) = val;
+        }
+      }
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");           // the four epilogue warps only
+      if (te == 0) {
+        const int ticket = atomicAdd(a.ag_ticket, 1);
+        if (ticket == (int)gridDim.x - 1) {
+          *a.ag_ticket = 0;                                     // ready for the next launch
+          __threadfence_system();
+          for (int p = 0; p < a.ag_world; ++p) st_release_sys(a.ag_peer_flags[p] + a.tp_rank, a.ag_epoch);
+        }
+      }
+    }
     int it = 0;
     int prev_t = -1;      // tensor-parallel mode: tile whose partials are pushed but not yet reduced
     bool ok_tp = true;
@@ -722,6 +792,56 @@ IPEX_API int ipex_gemm_lowbit_tcgen05_ar(const void* x, const void* w, void* out
   a.tp_rank = tp_rank; a.tp_world = tp_world;
   a.tp_stage = reinterpret_cast<void* const*>(tp_stage);
   a.tp_flags = reinterpret_cast<int* const*>(tp_flags);
+  cudaStream_t st = (cudaStream_t)stream;
+  return (int)(dtype == DT_F16 ? dispatch_wf<__half>(wf, bt, tx, tx, a, sm_count(), st)
+                               : dispatch_wf<__nv_bfloat16>(wf, bt, tx, tx, a, sm_count(), st));
+}
+
+// Column-parallel layer behind an all-gather, as ONE kernel: every rank holds `ag_rows` consecutive token rows of
+// the activation (x_local, row stride ld_local; rank r owns rows [r * ag_rows, ...) of the M gathered rows).  The
+// kernel's epilogue warps push those rows into every rank's gathered buffer (plain peer stores over NVLink) and
+// publish `epoch` in the ranks' flag arrays; its loader waits, per token tile, for the flags of the ranks whose rows
+// the tile covers and then reads the tile from THIS rank's copy with TMA, so tiles of rows that have arrived are
+// multiplied while later rows are still in flight.  out = gathered_x . W^T (+ bias), optional act(gate) * up.
+//   xg          this rank's gathered buffer [M, K] (row stride K), 16-byte aligned, in symmetric memory
+//   ag_dst      device array of `world` pointers: every rank's gathered buffer (same parity)
+//   ag_flags    device array of `world` pointers: every rank's flag array [world] ints (same parity)
+//   my_flags    this rank's flag array (= ag_flags[rank]);  ticket: one zeroed int on this device, left zero
+// Flags only grow (epochs increase from call to call); waits are bounded: *err = 15 when a peer never arrives.
+IPEX_API int ipex_gemm_lowbit_tcgen05_ag(const void* x_local, int64_t ld_local, const void* xg, const void* w,
+                                         void* out, const void* bias, const float* lut, int M, int N, int K,
+                                         int64_t ldo, int wf, int act, int dtype, int* err, void* stream, int rank,
+                                         int world, int ag_rows, const void* ag_dst, const void* ag_flags,
+                                         const int* my_flags, int* ticket, int epoch) {
+  if (M < 1 || N < 1 || K < 1 || (K % 8) != 0 || (ld_local % 8) != 0) return (int)cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(xg) & 15) || (reinterpret_cast<uintptr_t>(x_local) & 15))
+    return (int)cudaErrorInvalidValue;
+  if (dtype != DT_F16 && dtype != DT_BF16) return (int)cudaErrorInvalidValue;
+  if (world < 2 || world > 8 || rank < 0 || rank >= world || ag_rows < 1 || (int64_t)ag_rows * world < M ||
+      ag_dst == nullptr || ag_flags == nullptr || my_flags == nullptr || ticket == nullptr)
+    return (int)cudaErrorInvalidValue;
+  if (act != 0 && (N % 32) != 0) return (int)cudaErrorInvalidValue;
+  if (wf == WF_LUT4 && lut == nullptr) return (int)cudaErrorInvalidValue;
+  if (wf == WF_F16 || wf == WF_BF16) return (int)cudaErrorInvalidValue;
+  const int bt = ipex_gemm_tcgen05_token_tile(M);
+  const CUtensorMapDataType tdt = dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap tx;
+  if (!tc5::encode_2d_sw128(&tx, tdt, xg, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, kBK, bt)) return -1;
+  GemmArgs a = {};
+  a.w = reinterpret_cast<const uint8_t*>(w); a.lut = lut;
+  a.out = out; a.bias = bias; a.residual = nullptr; a.ldo = ldo; a.ldr = 0;
+  a.Np = ceil_to_i64(N, 16); a.Kp = ceil_to_i64(K, 128);
+  a.M = M; a.N = N; a.K = K;
+  a.m_tiles = (M + bt - 1) / bt;
+  a.n_tiles = (N + kBM - 1) / kBM;
+  a.act = act;
+  a.err = err;
+  a.tp_rank = rank; a.tp_world = 1;    // no reduction of the output: every rank owns its own columns
+  a.ag_flags = my_flags; a.ag_rows = ag_rows; a.ag_epoch = epoch;
+  a.ag_src = x_local; a.ag_ld_src = ld_local;
+  a.ag_dst = reinterpret_cast<void* const*>(ag_dst);
+  a.ag_peer_flags = reinterpret_cast<int* const*>(ag_flags);
+  a.ag_ticket = ticket; a.ag_world = world;
   cudaStream_t st = (cudaStream_t)stream;
   return (int)(dtype == DT_F16 ? dispatch_wf<__half>(wf, bt, tx, tx, a, sm_count(), st)
                                : dispatch_wf<__nv_bfloat16>(wf, bt, tx, tx, a, sm_count(), st));

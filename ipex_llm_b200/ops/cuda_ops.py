@@ -499,6 +499,49 @@ def _is_causal_mask(mask, q_len, kv_len) -> bool:
     return bool((allowed == (ki <= qi)).all())
 
 
+def _token_major(t: torch.Tensor) -> bool:
+    """``t [B, H, S, D]`` is a view of a token-major activation: element (b, h, s, d) at
+    ``(b * S + s) * ld + h * D + d`` (what slicing the fused qkv output and transposing gives)."""
+    B, H, S, D = t.shape
+    ld = t.stride(2)
+    return t.stride(3) == 1 and t.stride(1) == D and (B == 1 or t.stride(0) == S * ld) and ld % 8 == 0 and \
+        t.data_ptr() % 16 == 0
+
+
+def attn_prefill_tcgen05_ok(q, k, v) -> bool:
+    """Shapes and layouts the tcgen05 prompt-attention kernel takes; ``IPEX_LLM_TCGEN05_ATTN=0`` switches it off."""
+    if os.environ.get("IPEX_LLM_TCGEN05_ATTN", "0") == "0" or not q.is_cuda or q.requires_grad:
+        return False
+    if q.dtype not in (torch.float16, torch.bfloat16) or k.dtype != q.dtype or v.dtype != q.dtype:
+        return False
+    B, Hq, S, D = q.shape
+    if D not in (64, 128) or k.shape[2] != S or S < 64 or Hq % k.shape[1] != 0 or B > 65535:
+        return False
+    if not hasattr(cuda_lib(), "ipex_attn_prefill_tcgen05"):
+        return False
+    return _token_major(q) and _token_major(k)
+
+
+def attn_prefill_tcgen05(q, k, v, scale: float, causal: bool = True) -> torch.Tensor:
+    """Prompt attention (Sq == Skv) on the tcgen05 kernel.  ``q [B, Hq, S, D]`` and ``k [B, Hkv, S, D]`` are
+    token-major views (see ``_token_major``), already rotated; ``v`` any layout.  Returns ``[B, Hq, S, D]`` as a
+    view of a ``[B, S, Hq, D]`` buffer, so the ``transpose(1, 2).reshape(T, Hq * D)`` that feeds the output
+    projection is free."""
+    lib = cuda_lib()
+    B, Hq, S, D = q.shape
+    Hkv = k.shape[1]
+    s_pad = (S + 7) // 8 * 8
+    vt = torch.zeros(B, Hkv, D, s_pad, dtype=q.dtype, device=q.device) if s_pad != S else \
+        torch.empty(B, Hkv, D, S, dtype=q.dtype, device=q.device)
+    vt[..., :S].copy_(v.transpose(-1, -2))
+    out = torch.empty(B, S, Hq, D, dtype=q.dtype, device=q.device)
+    rc = lib.ipex_attn_prefill_tcgen05(ptr(q), ptr(k), ptr(vt), ptr(out), B, S, Hq, Hkv, D, q.stride(2), k.stride(2),
+                                       s_pad, Hq * D, float(scale), int(bool(causal)), _dt(q),
+                                       ptr(error_flag(q.device)), current_stream())
+    api.check(rc, "attn_prefill_tcgen05")
+    return out.transpose(1, 2)
+
+
 def sdpa_prefill(q, k, v, mask, scale, softcap, sliding_window, causal=True):
     """Prefill attention.  Uses the package's tcgen05 flash kernel when built and applicable; otherwise the
     library SDPA (flash) on repeated KV heads — the same fallback the reference takes off its own device
@@ -528,6 +571,8 @@ def sdpa_prefill(q, k, v, mask, scale, softcap, sliding_window, causal=True):
             m = m.to(q.dtype)
         return torch.nn.functional.scaled_dot_product_attention(q, k, v, attn_mask=m, scale=scale,
                                                                 enable_gqa=n_rep > 1)
+    if attn_prefill_tcgen05_ok(q, k, v):
+        return attn_prefill_tcgen05(q, k, v, scale, causal)
     return torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=causal and q.shape[2] > 1,
                                                             scale=scale, enable_gqa=n_rep > 1)
 

@@ -124,3 +124,36 @@ def gemm_lowbit_ar(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K:
         raise RuntimeError("ipex_llm_b200: the driver's tensor-map encoder rejected the GEMM operands")
     api.check(rc, "gemm_lowbit_tcgen05_ar")
     return out
+
+
+def gemm_lowbit_ag(x_local: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K: int, M_total: int, comm,
+                   out: torch.Tensor = None, bias: torch.Tensor = None, act: int = 0, wf: int = None) -> torch.Tensor:
+    """Column-parallel projection behind an all-gather, fused: ``x_local`` holds this rank's
+    ``ceil(M_total / world)`` consecutive token rows (fewer on the last ranks); the kernel pushes them to every
+    rank over NVLink, and multiplies each token tile of the gathered activation as soon as the ranks it covers have
+    arrived.  Returns ``gathered_x @ dequant(W).T (+ bias)`` (or ``act(gate) * up``) for all ``M_total`` tokens.
+    ``comm`` is the group's ``SymmComm``; every rank issues the same calls in the same order."""
+    from .cuda_ops import QTYPE_TO_WF, lut_for
+    lib = cuda_lib()
+    world = comm.world
+    ag_rows = (M_total + world - 1) // world
+    if x_local.stride(1) != 1 or x_local.stride(0) % 8 != 0 or x_local.data_ptr() % 16 != 0:
+        x_local = x_local.contiguous()
+    n_out = N // 2 if act else N
+    if out is None:
+        out = torch.empty((M_total, n_out), dtype=x_local.dtype, device=x_local.device)
+    if wf is None:
+        wf = QTYPE_TO_WF[qtype]
+    lut = lut_for(qtype, x_local.device) if qtype is not None else None
+    rank, world, xg, dst, flags, my_flags, ticket, epoch = comm.gemm_ag_args(M_total * K * 2)
+    fn = lib.ipex_gemm_lowbit_tcgen05_ag
+    vp, ci, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
+    fn.argtypes = [vp, i64, vp, vp, vp, vp, vp, ci, ci, ci, i64, ci, ci, ci, vp, vp, ci, ci, ci, vp, vp, vp, vp, ci]
+    fn.restype = ci
+    rc = fn(ptr(x_local), x_local.stride(0), xg, ptr(w_data), ptr(out), ptr(bias), ptr(lut), M_total, N, K,
+            out.stride(0), wf, act, api.dtype_code(x_local.dtype), ptr(_err(x_local.device)), current_stream(), rank,
+            world, ag_rows, ptr(dst), ptr(flags), my_flags, ticket, epoch)
+    if rc == -1:
+        raise RuntimeError("ipex_llm_b200: the driver's tensor-map encoder rejected the GEMM operands")
+    api.check(rc, "gemm_lowbit_tcgen05_ag")
+    return out

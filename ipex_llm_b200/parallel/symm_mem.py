@@ -117,7 +117,7 @@ class SymmComm:
         with the same sizes in the same order (they do: the ranks run the same layers on the same token count)."""
         import torch.distributed._symmetric_memory as symm_mem
         need_stage = (stage_bytes + 255) // 256 * 256
-        need_flags = (n_counters * 4 + 255) // 256 * 256
+        need_flags = (n_counters * 4 + 255) // 256 * 256 + 256      # last 256 bytes: epoch flags of the all-gather
         cur = getattr(self, "_gemm_cap", (0, 0))
         if need_stage > cur[0] or need_flags > cur[1]:
             cap_stage = max(need_stage, cur[0], 32 << 20)
@@ -135,13 +135,33 @@ class SymmComm:
             bases = [int(p) for p in handle.buffer_ptrs]
             dist.barrier(group=self.group)
             self._gemm_buf, self._gemm_handle, self._gemm_cap = buf, handle, (cap_stage, cap_flags)
-            self._gemm_stage, self._gemm_flags = [], []
+            self._gemm_stage, self._gemm_flags, self._gemm_ag_flags = [], [], []
             for par in range(2):
                 o = par * per
                 self._gemm_stage.append(torch.tensor([b + o for b in bases], dtype=torch.int64, device=self.device))
                 self._gemm_flags.append(torch.tensor([b + o + cap_stage for b in bases], dtype=torch.int64,
                                                      device=self.device))
+                self._gemm_ag_flags.append(torch.tensor([b + o + per - 256 for b in bases], dtype=torch.int64,
+                                                        device=self.device))
+            self._gemm_local = [(bases[self.rank] + par * per, bases[self.rank] + par * per + per - 256)
+                                for par in range(2)]
             self._gemm_parity = 0
+            self._ag_epoch = 0          # the fresh buffer holds zeros: epochs restart (same on every rank)
         par = self._gemm_parity
         self._gemm_parity ^= 1
         return self.rank, self.world, self._gemm_stage[par], self._gemm_flags[par]
+
+    def gemm_ag_args(self, gather_bytes: int):
+        """Buffers for the next GEMM whose activation is all-gathered inside the kernel
+        (``ipex_gemm_lowbit_tcgen05_ag``): returns ``(rank, world, local_gather_ptr, gather_ptr_array,
+        flag_ptr_array, local_flags_ptr, ticket_ptr, epoch)``.  Shares the two-parity symmetric buffer (and the
+        parity alternation) with the fused all-reduce GEMM, so consecutive fused ops never write the region a peer
+        may still be reading.  Collective: same sizes, same order on every rank."""
+        rank, world, stage, _ = self.gemm_ar_args(gather_bytes, 0)
+        par = self._gemm_parity ^ 1                      # the parity gemm_ar_args just handed out
+        self._ag_epoch += 1
+        if getattr(self, "_ag_ticket", None) is None:
+            self._ag_ticket = torch.zeros(1, dtype=torch.int32, device=self.device)
+        local_gather, local_flags = self._gemm_local[par]
+        return (rank, world, local_gather, stage, self._gemm_ag_flags[par], local_flags,
+                self._ag_ticket.data_ptr(), self._ag_epoch)

@@ -118,6 +118,31 @@ def bench_attn(a):
             "us": us, "kv_bytes": kvbytes, "gbs": kvbytes / us / 1e3}
 
 
+def bench_attn_prefill(a):
+    """Causal prompt attention, ``--kv-len`` tokens: the tcgen05 kernel (``--impl tcgen05``, default) or the library
+    SDPA (``--impl sdpa``) on the same token-major views of a fused qkv activation."""
+    from ..ops import cuda_ops
+    dt = torch.float16 if a.dtype == "fp16" else torch.bfloat16
+    B, Hq, Hkv, S, D = a.batch, a.heads, a.kv_heads, a.kv_len, a.head_dim
+    n_sets = min(16, max(2, int(300e6 // (B * S * (Hq + 2 * Hkv) * D * 2)) + 1))
+    sets = []
+    for _ in range(n_sets):
+        qkv = torch.randn(B, S, Hq + 2 * Hkv, D, device="cuda", dtype=dt)
+        sets.append((qkv[:, :, :Hq].transpose(1, 2), qkv[:, :, Hq:Hq + Hkv].transpose(1, 2),
+                     qkv[:, :, Hq + Hkv:].transpose(1, 2)))
+    scale = D ** -0.5
+    if a.impl == "sdpa":
+        fn = lambda i: torch.nn.functional.scaled_dot_product_attention(*sets[i % n_sets], is_causal=True,
+                                                                        scale=scale, enable_gqa=Hq != Hkv)
+    else:
+        fn = lambda i: cuda_ops.attn_prefill_tcgen05(*sets[i % n_sets], scale, True)
+    us = _time(fn, a.iters, a.warmup)
+    cuda_ops.check_error_flag(sets[0][0].device)
+    flops = 4.0 * B * Hq * S * S * D / 2          # causal: half of the score matrix
+    return {"op": "attn_prefill", "impl": a.impl or "tcgen05", "batch": B, "heads": Hq, "kv_heads": Hkv, "seq": S,
+            "head_dim": D, "us": us, "tflops": flops / us / 1e6}
+
+
 def bench_rmsnorm(a):
     from ..ops import cuda_ops
     dt = torch.float16 if a.dtype == "fp16" else torch.bfloat16
@@ -132,7 +157,7 @@ def bench_rmsnorm(a):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("--op", default="gemv", choices=["gemv", "gemm", "attn", "rmsnorm"])
+    ap.add_argument("--op", default="gemv", choices=["gemv", "gemm", "attn", "attn_prefill", "rmsnorm"])
     ap.add_argument("--qtype", default="sym_int4")
     ap.add_argument("--dtype", default="fp16", choices=["fp16", "bf16"])
     ap.add_argument("--impl", default="", help="GEMV implementation override: v1 | tma | direct")
@@ -154,7 +179,8 @@ def main(argv=None):
     _GRAPH = a.graph
     if not torch.cuda.is_available():
         raise SystemExit("kernel_bench needs a CUDA device")
-    res = {"gemv": bench_gemv, "gemm": bench_gemm, "attn": bench_attn, "rmsnorm": bench_rmsnorm}[a.op](a)
+    res = {"gemv": bench_gemv, "gemm": bench_gemm, "attn": bench_attn, "attn_prefill": bench_attn_prefill,
+           "rmsnorm": bench_rmsnorm}[a.op](a)
     pk = _peaks()
     if "gbs" in res and pk.get("hbm_gbs"):
         res["frac_of_measured_hbm"] = res["gbs"] / pk["hbm_gbs"]

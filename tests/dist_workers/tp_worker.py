@@ -100,6 +100,35 @@ def main():
                 err = (out.float() - ref).abs().max().item() / ref.abs().max().item()
                 assert err < 1e-2, ("gemm_ar", name, Mtok, err)
         cuda_ops.check_error_flag(dev)
+        # 2c. column-parallel GEMM with the all-gather of its activation fused in front (each rank owns a slice of
+        #     the token rows and its own output columns)
+        if hasattr(cuda_ops.cuda_lib(), "ipex_gemm_lowbit_tcgen05_ag"):
+            for Mtot, Nout, act in ((70, 384, 0), (301, 1024, 0), (520, 512, 1)):
+                torch.manual_seed(11)                      # same activation on every rank, sliced by rows
+                xfull = torch.randn(Mtot, K, device=dev).half()
+                rows = (Mtot + world - 1) // world
+                x_loc = xfull[rank * rows:(rank + 1) * rows].contiguous()
+                torch.manual_seed(50 + rank)               # rank-specific weights: its own output columns
+                wcol = torch.randn(Nout, K, device=dev) * 0.05
+                bcol = torch.randn(Nout, device=dev).half()
+                for name in ("sym_int4", "fp8_e4m3"):
+                    q = qt.qtype_from_name(name)
+                    packed = quantize_to_device_layout(wcol.half(), q)
+                    deq = cuda_ops.dequantize_device(packed, (Nout, K), q, torch.float32)
+                    full = xfull.float() @ deq.t()
+                    if act:
+                        # gate / up alternate in 16-row tiles of the weight
+                        t16 = full.view(Mtot, Nout // 32, 2, 16)
+                        ref = (torch.nn.functional.silu(t16[:, :, 0]) * t16[:, :, 1]).reshape(Mtot, Nout // 2)
+                    else:
+                        ref = full + bcol.float()
+                    for _ in range(3):
+                        out = tcgen05_gemm.gemm_lowbit_ag(x_loc, packed, q, Nout, K, Mtot, comm,
+                                                          bias=None if act else bcol, act=act)
+                    torch.cuda.synchronize()
+                    err = (out.float() - ref).abs().max().item() / ref.abs().max().item()
+                    assert err < 1e-2, ("gemm_ag", name, Mtot, act, err)
+            cuda_ops.check_error_flag(dev)
 
     # 3. tiny llama, tensor parallel
     torch.manual_seed(0)
