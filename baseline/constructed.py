@@ -19,6 +19,7 @@ import argparse
 import json
 import math
 import os
+import sys
 
 import torch
 import torch.distributed as dist
@@ -134,6 +135,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--graph", action="store_true", help="capture the decode step in a CUDA graph on multi-rank runs too")
     a = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -160,7 +162,13 @@ def main():
             first_ms = e0.elapsed_time(e1)
         m.pos.fill_(spec["prompt"])
         step = m.decode_step
-        if not a.no_graph:
+        # Multi-rank runs issue eager launches unless --graph is given: capturing the NCCL all-reduces of the
+        # 70B model did not return within ten minutes on two GPUs, and eager launches are what the reference's
+        # own stack issues.  The JSON line records which mode ran.
+        use_graph = not a.no_graph and (world == 1 or a.graph)
+        print(f"[constructed] rank {rank}: prompt pass done ({first_ms:.1f} ms), cuda_graph={use_graph}",
+              file=sys.stderr, flush=True)
+        if use_graph:
             s = torch.cuda.Stream()
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
@@ -193,7 +201,7 @@ def main():
                           "tokens_per_s": round(a.batch * 1000.0 / float(t[0]), 2),
                           "first_token_ms": round(float(t[1]), 2), "steps": a.steps, "warmup": a.warmup,
                           "weights": str(spec["dtype"]).replace("torch.", "") + " (dequantized once)",
-                          "cuda_graph": not a.no_graph}))
+                          "cuda_graph": use_graph}))
     if world > 1:
         dist.destroy_process_group()
 

@@ -209,8 +209,22 @@ class DecoderEngine:
                                         residual=residual[s:e] if residual is not None else None,
                                         pdl=self.use_pdl, wf=w.wf)
                 continue
+            if w.tp is not None and norm_w is None and act == 0 and out[s:e].is_contiguous() and \
+                    (residual is None or residual[s:e].is_contiguous()) and w.tp.symm() is not None and \
+                    (e - s) * w.N * out.element_size() <= w.tp.symm().ar_bytes and \
+                    os.environ.get("IPEX_LLM_TP_STAGED_AR", "1") != "0":
+                # row-parallel layer, default: the GEMV writes its partial product straight into this rank's
+                # symmetric staging buffer and ONE kernel does the peer-memory all-reduce + bias + residual
+                # (two launches per layer half instead of GEMV, copy, all-reduce, bias add, residual add)
+                comm = w.tp.symm()
+                stage, token = comm.ar_stage((e - s) * w.N, out.dtype)
+                cuda_ops.gemv_lowbit(x[s:e], w.data, w.qtype, w.N, w.K, out=stage.view(e - s, w.N),
+                                     pdl=self.use_pdl, wf=w.wf)
+                comm.all_reduce_staged(token, out[s:e], residual=residual[s:e] if residual is not None else None,
+                                       bias=bias if bias is not None else w.bias)
+                continue
             if w.tp is not None:
-                # dense (unquantized) row-parallel layer: plain GEMV, stand-alone all-reduce, then the residual
+                # row-parallel layer, stand-alone steps: plain GEMV, all-reduce, then bias and residual
                 cuda_ops.gemv_lowbit(x[s:e], w.data, w.qtype, w.N, w.K, out=out[s:e], pdl=False, wf=w.wf)
                 w.tp.all_reduce(out[s:e])
                 b_ = bias if bias is not None else w.bias
@@ -291,15 +305,29 @@ class DecoderEngine:
         rc = lib.ipex_embedding(ptr(self.vtokens), ptr(self.embed), ptr(h0), S, self.H, 1.0, dtc, 0, current_stream())
         api.check(rc, "embedding")
         for L in self.layers:
-            self._gemv(L.qkv, h0, self.qkv_buf[:S], norm_w=L.ln1)
+            self._vproj(L.qkv, h0, self.qkv_buf[:S], norm_w=L.ln1)
             self._attention(L, 1, Sq=S)
-            self._gemv(L.o, self.attn_buf[:S], h1, residual=h0)
-            self._gemv(L.gate_up, h1, self.act_buf[:S], norm_w=L.ln2, act=1)
-            self._gemv(L.down, self.act_buf[:S], h0, residual=h1)
-        self._gemv(self.lm_head, h0, self.logits[:S], norm_w=self.final_norm)
+            self._vproj(L.o, self.attn_buf[:S], h1, residual=h0)
+            self._vproj(L.gate_up, h1, self.act_buf[:S], norm_w=L.ln2, act=1)
+            self._vproj(L.down, self.act_buf[:S], h0, residual=h1)
+        self._vproj(self.lm_head, h0, self.logits[:S], norm_w=self.final_norm)
         rc = lib.ipex_argmax(ptr(self.logits), ptr(self.vout), S, self.vocab, self.logits.stride(0), dtc, pdl,
                              current_stream())
         api.check(rc, "argmax")
+
+    def _vproj(self, w: _W, x, out, norm_w=None, residual=None, act=0):
+        """Projection of the multi-token verification pass.  Dense half weights (the speculative target) with more
+        than two rows go through the tcgen05 GEMM: its 128-row weight tiles arrive by TMA and amortise the staging
+        of the token rows, which the 16-row GEMV CTAs pay per CTA (8 rows measured 2.25x a single-row step there).
+        Everything else takes the multi-row GEMV."""
+        S = x.shape[0]
+        if w.wf in (api.WF_F16, api.WF_BF16) and S > 2 and w.tp is None and w.K % 8 == 0 and \
+                (act == 0 or w.N % 32 == 0) and os.environ.get("IPEX_LLM_VERIFY_GEMM", "1") != "0":
+            from ..ops import tcgen05_gemm
+            xin = cuda_ops.rms_norm(x, norm_w, self.eps) if norm_w is not None else x
+            tcgen05_gemm.gemm_dense(xin, w.data, bias=w.bias, residual=residual, out=out, act=act)
+            return
+        self._gemv(w, x, out, norm_w=norm_w, residual=residual, act=act)
 
     def verify_step(self, S: int, use_graph: bool = True):
         """Score ``vtokens[:S]`` (1 <= S <= min(8, max_batch)) as the next ``S`` tokens of sequence 0 in one pass:

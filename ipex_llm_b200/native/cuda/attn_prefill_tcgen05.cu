@@ -11,10 +11,12 @@
 // through TMA, V is read from a transposed copy ([B, Hkv, D, S]) so that its tile is K-major too, and P is written
 // by the softmax threads in the same swizzle.  One CTA owns 128 queries of one head and walks the key blocks:
 //
-//   warp 4 (one lane): TMA loads, K / V^T double buffered
-//   warp 5 (one lane): issues the MMAs, S(j+1) is issued before the softmax threads have folded PV(j) into O
-//   warps 0-3        : thread r owns query row r: row max / exp2 / row sum on S read from TMEM, P to shared
-//                      memory, running output O[D] in registers rescaled by exp2(m_old - m_new) per block
+//   warp 8 (one lane): TMA loads, K / V^T double buffered
+//   warp 9 (one lane): issues the MMAs, S(j+1) is issued before the softmax threads have folded PV(j) into O
+//   warps 0-7        : two threads per query row (warps w and w + 4 read the same TMEM lanes), each owning 64 of
+//                      the block's 128 score columns and half of the output columns: row max (exchanged through
+//                      shared memory), exp2, row sum, P to shared memory, running output O[D/2] in registers
+//                      rescaled by exp2(m_old - m_new) per block
 //
 // No cluster multicast.  Every mbarrier wait is bounded; a wait that runs out raises the CTA's abort flag, the
 // error word gets a code (31 loader, 32 MMA issuer, 33 softmax) and all roles leave, after which TMEM is freed.
@@ -27,7 +29,13 @@ using namespace tc5;
 
 constexpr int kBQ = 128;   // queries per CTA (MMA M)
 constexpr int kBKV = 128;  // keys per block
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;  // 8 softmax warps, loader warp, MMA warp
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 struct PrefillArgs {
   void* out;          // [B, S, Hq, D] with row stride ldo (elements) between tokens
@@ -62,8 +70,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   uint64_t* p_full = bars + 6;
   uint64_t* o_full = bars + 7;
   uint64_t* o_free = bars + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* x_full = bars + 9;                      // row-maximum exchange inside a thread pair
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* xch = reinterpret_cast<float*>(bars + 32);  // [2][128]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nqb = (a.S + kBQ - 1) / kBQ;
@@ -79,19 +89,20 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       mbar_init(&kv_empty[i], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 256);
     mbar_init(o_full, 1);
-    mbar_init(o_free, 128);
+    mbar_init(o_free, 256);
+    mbar_init(x_full, 256);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 5) tmem_alloc(tmem_slot, kTmemCols);
+  if (warp == 9) tmem_alloc(tmem_slot, kTmemCols);
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ---------------- loader ----------------
     if (lane == 0) {
       prefetch_tmap(&tm_q);
@@ -122,7 +133,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_f16<T>(kBQ, kBKV);
@@ -163,56 +174,64 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
     __syncwarp();
   } else {
-    // ---------------- softmax + output: thread = query row ----------------
-    const int r = threadIdx.x;                       // 0..127, TMEM lane
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    // ---------------- softmax + output: two threads per query row, each owns half of the columns ----------------
+    const int r = threadIdx.x & 127, hf = threadIdx.x >> 7;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const int qpos = qb * kBQ + r;
-    float o[D];
+    constexpr int kOH = D / 2;                        // output columns of this thread: [hf * kOH, (hf + 1) * kOH)
+    float o[kOH];
 #pragma unroll
-    for (int d = 0; d < D; ++d) o[d] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    for (int d = 0; d < kOH; ++d) o[d] = 0.f;
+    float m = -INFINITY, l = 0.f;                     // m: row maximum (shared by the pair), l: this thread's part
     bool ok = true;
     for (int j = 0; j < nkv; ++j) {
       const uint32_t jp = j & 1;
       if (!mbar_wait(s_full, jp, abort_flag)) { ok = false; if (lane == 0) report(a.err, 33); break; }
       tcgen05_fence_after();
       const int k0 = j * kBKV;
-      // keys this row may see in the block: [k0, klim)
+      // keys this row may see in the block: [k0, k0 + klim); this thread looks at block columns [hf*64, hf*64+64)
       int klim = a.S - k0;
       if (a.causal) klim = min(klim, qpos - k0 + 1);
-      klim = min(klim, kBKV);
-      // pass 1: row maximum (raw scores; the scale is positive)
-      float mx = m;
-#pragma unroll 1
-      for (int c = 0; c < kBKV / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_base + lane_addr + c * 32, v);
+      const int lim = min(klim, kBKV) - hf * 64;      // local columns below `lim` are visible
+      uint32_t v0[32], v1[32];
+      tmem_ld_32x32(tmem_base + lane_addr + hf * 64, v0);
+      tmem_ld_32x32(tmem_base + lane_addr + hf * 64 + 32, v1);
+      float mx = -INFINITY;
+      if (lim >= 64) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c * 32 + i < klim) mx = fmaxf(mx, __uint_as_float(v[i]) * a.scale_log2);
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (i < lim) mx = fmaxf(mx, __uint_as_float(v0[i]));
+          if (32 + i < lim) mx = fmaxf(mx, __uint_as_float(v1[i]));
+        }
       }
+      mx *= a.scale_log2;                             // the scale is positive: max commutes with it
+      xch[hf * 128 + r] = mx;
+      mbar_arrive(x_full);
+      if (!mbar_wait(x_full, jp, abort_flag)) { ok = false; if (lane == 0) report(a.err, 33); break; }
+      mx = fmaxf(fmaxf(mx, xch[(hf ^ 1) * 128 + r]), m);
       // a row that sees nothing yet keeps m = -inf; use 0 as the reference so that exp2 stays finite
       const float mref = mx == -INFINITY ? 0.f : mx;
-      const float corr = exp2f(m - mref);            // m = -inf -> 0
+      const float corr = ex2(m - mref);               // m = -inf -> 0
       float psum = 0.f;
-      // pass 2: probabilities -> P tile (K-major, 128-byte swizzle), row sum
-#pragma unroll 1
-      for (int c = 0; c < kBKV / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_base + lane_addr + c * 32, v);
+      uint8_t* prow = sP + hf * (kBQ * 128) + r * 128;  // P k-block `hf` holds block columns [hf*64, hf*64+64)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
         __align__(16) T pk[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float p = 0.f;
-          if (c * 32 + i < klim) p = exp2f(__uint_as_float(v[i]) * a.scale_log2 - mref);
+          const float sv = __uint_as_float(half == 0 ? v0[i] : v1[i]);
+          float p = ex2(fmaf(sv, a.scale_log2, -mref));
+          if (lim < 64 && half * 32 + i >= lim) p = 0.f;
           const T pt = from_float<T>(p);
           pk[i] = pt;
           psum += to_float<T>(pt);                   // the sum the tensor cores will see
         }
-        uint8_t* prow = sP + (c >> 1) * (kBQ * 128) + r * 128;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const int chunk = (c & 1) * 4 + q;
+          const int chunk = half * 4 + q;
           *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = reinterpret_cast<const uint4*>(pk)[q];
         }
       }
@@ -221,24 +240,32 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       fence_proxy_async_smem();
       tcgen05_fence_before();
       mbar_arrive(p_full);
-      // fold PV(j) into the running output
+      // fold this thread's half of PV(j) into the running output
       if (!mbar_wait(o_full, jp, abort_flag)) { ok = false; if (lane == 0) report(a.err, 33); break; }
       tcgen05_fence_after();
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < kOH / 32; ++c) {
         uint32_t v[32];
-        tmem_ld_32x32(tmem_base + lane_addr + kBKV + c * 32, v);
+        tmem_ld_32x32(tmem_base + lane_addr + kBKV + hf * kOH + c * 32, v);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * corr + __uint_as_float(v[i]);
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], corr, __uint_as_float(v[i]));
       }
       tcgen05_fence_before();
       mbar_arrive(o_free);
     }
+    if (ok) {
+      // the pair's row sum: one more exchange through the same slots
+      xch[hf * 128 + r] = l;
+      mbar_arrive(x_full);
+      ok = mbar_wait(x_full, nkv & 1, abort_flag);
+      if (!ok && lane == 0) report(a.err, 33);
+      l += xch[(hf ^ 1) * 128 + r];
+    }
     if (ok && qpos < a.S) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      T* op = reinterpret_cast<T*>(a.out) + ((int64_t)b * a.S + qpos) * a.ldo + (int64_t)h * D;
+      T* op = reinterpret_cast<T*>(a.out) + ((int64_t)b * a.S + qpos) * a.ldo + (int64_t)h * D + hf * kOH;
 #pragma unroll
-      for (int c = 0; c < D / 8; ++c) {
+      for (int c = 0; c < kOH / 8; ++c) {
         __align__(16) T ov[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) ov[i] = from_float<T>(o[c * 8 + i] * inv);
@@ -248,7 +275,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   }
   tcgen05_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == 9) tmem_dealloc(tmem_base, kTmemCols);
 }
 
 template <typename T, int D>
@@ -264,7 +291,7 @@ int launch(const void* q, const void* k, const void* vt, void* out, int B, int S
   PrefillArgs a;
   a.out = out; a.err = err; a.ldo = ldo; a.B = B; a.S = S; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal;
   a.scale_log2 = scale * 1.4426950408889634f;
-  const size_t smem = 1024 + (size_t)kBQ * D * 2 + (size_t)kBQ * kBKV * 2 + 2 * ((size_t)kBKV * D * 2 * 2) + 256;
+  const size_t smem = 1024 + (size_t)kBQ * D * 2 + (size_t)kBQ * kBKV * 2 + 2 * ((size_t)kBKV * D * 2 * 2) + 256 + 1024;
   auto kern = attn_prefill_kernel<T, D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;

@@ -56,7 +56,7 @@ __device__ bool block_rendezvous(int* const* flags, int rank, int world, int b, 
 
 template <typename T>
 __global__ void allreduce_oneshot_kernel(const T* const* bufs, int* const* flags, T* out, int64_t n, int rank, int world,
-                                         int* err) {
+                                         int* err, const T* residual, const T* bias, int ncols) {
   pdl_launch_dependents();
   pdl_wait();
   // this rank's contribution is already in bufs[rank] (written by the previous kernel on this stream)
@@ -74,6 +74,15 @@ __global__ void allreduce_oneshot_kernel(const T* const* bufs, int* const* flags
 #pragma unroll
       for (int j = 0; j < VEC; j++) acc[j] += DT<T>::to_f(e[j]);
     }
+    // epilogue of a row-parallel layer: + residual (same shape as out) + bias (per column, ncols columns per row)
+    if (residual != nullptr) {
+#pragma unroll
+      for (int j = 0; j < VEC; j++) acc[j] += DT<T>::to_f(residual[v * VEC + j]);
+    }
+    if (bias != nullptr) {
+#pragma unroll
+      for (int j = 0; j < VEC; j++) acc[j] += DT<T>::to_f(bias[(v * VEC + j) % ncols]);
+    }
     __align__(16) T o[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; j++) o[j] = DT<T>::from_f(acc[j]);
@@ -84,6 +93,8 @@ __global__ void allreduce_oneshot_kernel(const T* const* bufs, int* const* flags
        i += (int64_t)gridDim.x * blockDim.x) {
     float acc = 0.f;
     for (int r = 0; r < world; r++) acc += DT<T>::to_f(*reinterpret_cast<const volatile T*>(bufs[r] + i));
+    if (residual != nullptr) acc += DT<T>::to_f(residual[i]);
+    if (bias != nullptr) acc += DT<T>::to_f(bias[i % ncols]);
     out[i] = DT<T>::from_f(acc);
   }
 }
@@ -110,21 +121,33 @@ __global__ void wait_timeout_probe_kernel(int* counter, int expect, int spins, i
 
 // bufs / flags: device arrays of `world` pointers (every rank's input buffer and arrival counters for this
 // call's parity).  n elements of `dtype`; out is local.  blocks <= number of counters per parity (64).
-IPEX_API int ipex_allreduce_oneshot(const void* bufs, const void* flags, void* out, int64_t n, int dtype, int rank,
-                                    int world, int* err, int blocks, int pdl, void* stream) {
-  if (world < 1 || world > 8 || blocks < 1 || blocks > 64) return (int)cudaErrorInvalidValue;
+// Same with the epilogue of a row-parallel layer: out = sum over ranks + residual (n elements, or null) + bias
+// (ncols values repeated along the rows, or null).  out may alias residual.
+IPEX_API int ipex_allreduce_oneshot_epi(const void* bufs, const void* flags, void* out, int64_t n, int dtype, int rank,
+                                        int world, int* err, int blocks, int pdl, const void* residual,
+                                        const void* bias, int ncols, void* stream) {
+  if (world < 1 || world > 8 || blocks < 1 || blocks > 64 || (bias != nullptr && ncols < 1))
+    return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == DT_F16)
     return (int)launch_kernel(allreduce_oneshot_kernel<__half>, dim3(blocks), dim3(512), 0, s, pdl != 0,
-                              (const __half* const*)bufs, (int* const*)flags, (__half*)out, n, rank, world, err);
+                              (const __half* const*)bufs, (int* const*)flags, (__half*)out, n, rank, world, err,
+                              (const __half*)residual, (const __half*)bias, ncols);
   if (dtype == DT_BF16)
     return (int)launch_kernel(allreduce_oneshot_kernel<__nv_bfloat16>, dim3(blocks), dim3(512), 0, s, pdl != 0,
                               (const __nv_bfloat16* const*)bufs, (int* const*)flags, (__nv_bfloat16*)out, n, rank,
-                              world, err);
+                              world, err, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)bias, ncols);
   if (dtype == DT_F32)
     return (int)launch_kernel(allreduce_oneshot_kernel<float>, dim3(blocks), dim3(512), 0, s, pdl != 0,
-                              (const float* const*)bufs, (int* const*)flags, (float*)out, n, rank, world, err);
+                              (const float* const*)bufs, (int* const*)flags, (float*)out, n, rank, world, err,
+                              (const float*)residual, (const float*)bias, ncols);
   return (int)cudaErrorInvalidValue;
+}
+
+IPEX_API int ipex_allreduce_oneshot(const void* bufs, const void* flags, void* out, int64_t n, int dtype, int rank,
+                                    int world, int* err, int blocks, int pdl, void* stream) {
+  return ipex_allreduce_oneshot_epi(bufs, flags, out, n, dtype, rank, world, err, blocks, pdl, nullptr, nullptr, 0,
+                                    stream);
 }
 
 IPEX_API int ipex_symm_barrier(const void* flags, int rank, int world, int* err, void* stream) {

@@ -700,10 +700,23 @@ IPEX_API int ipex_gemm_tcgen05_token_tile(int M) { return M <= 32 ? 32 : (M <= 6
 // out[M,N] = x[M,K] . w[N,K]^T (+ bias[N]) (+ residual[M,N]).  x, w, out, bias, residual share one 16-bit dtype.
 // Row strides (elements): ldx, ldw multiples of 8 (TMA wants 16-byte strides); x and w 16-byte aligned.
 // Returns a cudaError_t, or -1 when the driver's tensor-map encoder is unavailable / rejects the arguments.
+IPEX_API int ipex_gemm_tcgen05_act(const void* x, const void* w, void* out, const void* bias, const void* residual,
+                                   int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int64_t ldr, int dtype,
+                                   int act, int* err, void* stream);
+
 IPEX_API int ipex_gemm_tcgen05(const void* x, const void* w, void* out, const void* bias, const void* residual, int M,
                                int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int64_t ldr, int dtype, int* err,
                                void* stream) {
+  return ipex_gemm_tcgen05_act(x, w, out, bias, residual, M, N, K, ldx, ldw, ldo, ldr, dtype, 0, err, stream);
+}
+
+// Dense GEMM with the gate/up activation epilogue: act != 0 expects w rows as 16-row tiles gate, up, gate, up, ...
+// and writes act(gate) * up into N/2 columns (no residual then).
+IPEX_API int ipex_gemm_tcgen05_act(const void* x, const void* w, void* out, const void* bias, const void* residual,
+                                   int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int64_t ldr, int dtype,
+                                   int act, int* err, void* stream) {
   if (M < 1 || N < 1 || K < 1 || (ldx % 8) != 0 || (ldw % 8) != 0) return (int)cudaErrorInvalidValue;
+  if (act != 0 && (residual != nullptr || (N % 32) != 0)) return (int)cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return (int)cudaErrorInvalidValue;
   if (dtype != DT_F16 && dtype != DT_BF16) return (int)cudaErrorInvalidValue;
   const int bt = ipex_gemm_tcgen05_token_tile(M);
@@ -716,6 +729,7 @@ IPEX_API int ipex_gemm_tcgen05(const void* x, const void* w, void* out, const vo
   a.M = M; a.N = N; a.K = K;
   a.m_tiles = (M + bt - 1) / bt;
   a.n_tiles = (N + kBM - 1) / kBM;
+  a.act = act;
   a.err = err;
   cudaStream_t st = (cudaStream_t)stream;
   return (int)(dtype == DT_F16 ? dispatch_bt<__half, WF_F16>(bt, tw, tx, a, sm_count(), st)

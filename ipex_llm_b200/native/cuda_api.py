@@ -20,6 +20,7 @@ _SIGS = {
     "ipex_gemv_lowbit_tma_ar": [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp, cf, cf, vp, vp, ci, vp, ci, ci, vp, vp,
                                 ci, ci, ci, vp, vp],
     "ipex_allreduce_oneshot": [vp, vp, vp, i64, ci, ci, ci, vp, ci, ci, vp],
+    "ipex_allreduce_oneshot_epi": [vp, vp, vp, i64, ci, ci, ci, vp, ci, ci, vp, vp, ci, vp],
     "ipex_symm_barrier": [vp, ci, ci, vp, vp],
     "ipex_wait_timeout_probe": [vp, ci, ci, vp, vp],
     "ipex_gemv_int4_direct": [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp, cf, cf, vp, vp, ci, ci, vp, ci, ci, vp],

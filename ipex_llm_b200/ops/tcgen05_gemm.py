@@ -27,8 +27,10 @@ def dense_supported(M: int, N: int, K: int, dtype) -> bool:
 
 
 def gemm_dense(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor = None, residual: torch.Tensor = None,
-               out: torch.Tensor = None) -> torch.Tensor:
-    """``x [M, K] @ w[N, K].T (+ bias) (+ residual)``; ``x``/``w`` row strides must be multiples of 8 elements."""
+               out: torch.Tensor = None, act: int = 0) -> torch.Tensor:
+    """``x [M, K] @ w[N, K].T (+ bias) (+ residual)``; ``x``/``w`` row strides must be multiples of 8 elements.
+    ``act`` != 0: ``w`` holds gate / up rows interleaved in 16-row tiles and the result is ``act(gate) * up`` with
+    ``N / 2`` columns (1 = SiLU, 2 = GELU-tanh)."""
     lib = cuda_lib()
     M, K = x.shape
     N = w.shape[0]
@@ -37,12 +39,15 @@ def gemm_dense(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor = None, resi
     if w.stride(1) != 1 or w.stride(0) % 8 != 0 or w.data_ptr() % 16 != 0:
         w = w.contiguous()
     if out is None:
-        out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+        out = torch.empty((M, N // 2 if act else N), dtype=x.dtype, device=x.device)
     if residual is not None and residual.stride(1) != 1:
         residual = residual.contiguous()
-    rc = lib.ipex_gemm_tcgen05(ptr(x), ptr(w), ptr(out), ptr(bias), ptr(residual), M, N, K, x.stride(0), w.stride(0),
-                               out.stride(0), residual.stride(0) if residual is not None else 0,
-                               api.dtype_code(x.dtype), ptr(_err(x.device)), current_stream())
+    fn = lib.ipex_gemm_tcgen05_act
+    vp, ci, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
+    fn.argtypes, fn.restype = [vp, vp, vp, vp, vp, ci, ci, ci, i64, i64, i64, i64, ci, ci, vp, vp], ci
+    rc = fn(ptr(x), ptr(w), ptr(out), ptr(bias), ptr(residual), M, N, K, x.stride(0), w.stride(0), out.stride(0),
+            residual.stride(0) if residual is not None else 0, api.dtype_code(x.dtype), int(act), ptr(_err(x.device)),
+            current_stream())
     if rc == -1:
         raise RuntimeError("ipex_llm_b200: the driver's tensor-map encoder rejected the GEMM operands")
     api.check(rc, "gemm_tcgen05")

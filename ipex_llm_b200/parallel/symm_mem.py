@@ -97,6 +97,28 @@ class SymmComm:
         api.check(rc, "allreduce_oneshot")
         return t
 
+    def ar_stage(self, numel: int, dtype):
+        """Staging view for the NEXT all-reduce: a producer kernel (the row-parallel GEMV) writes this rank's
+        contribution straight into symmetric memory, which saves the copy ``all_reduce`` starts with.  Returns
+        ``(view, token)``; pass the token to ``all_reduce_staged``.  Takes this call's parity, so the pair counts as
+        one collective in the per-rank call order."""
+        par = self.next_parity()
+        nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+        return self._local_ar[par][:nbytes].view(dtype), par
+
+    def all_reduce_staged(self, token: int, out: torch.Tensor, residual: torch.Tensor = None,
+                          bias: torch.Tensor = None, pdl: bool = False) -> torch.Tensor:
+        """Second half of ``ar_stage``: ``out = sum over ranks of the staged vectors (+ residual) (+ bias per
+        column)``, in one kernel.  ``out`` and ``residual`` are contiguous and may be the same tensor."""
+        lib = cuda_lib()
+        n = out.numel()
+        blocks = max(1, min(_N_BLOCK_FLAGS, (n + 4095) // 4096))
+        rc = lib.ipex_allreduce_oneshot_epi(ptr(self.ar_bufs[token]), ptr(self.block_flags[token]), ptr(out), n,
+                                            api.dtype_code(out.dtype), self.rank, self.world, ptr(self.err), blocks,
+                                            int(pdl), ptr(residual), ptr(bias), out.shape[-1], current_stream())
+        api.check(rc, "allreduce_oneshot_epi")
+        return out
+
     def barrier(self):
         lib = cuda_lib()
         par = self.next_parity()

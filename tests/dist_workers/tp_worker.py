@@ -55,6 +55,24 @@ def main():
                 out = comm.all_reduce(t.clone())
                 tol = 1e-5 if dtype == torch.float32 else 3e-2
                 assert (out.float() - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item()), (dtype, n)
+        # 1b. staged all-reduce with the row-parallel epilogue (+ residual + per-column bias) in the same kernel
+        for dtype in (torch.float16, torch.bfloat16):
+            for rows, cols in ((1, 4096), (3, 1000)):
+                torch.manual_seed(200 + rank)
+                part = torch.randn(rows, cols, device=dev).to(dtype)
+                torch.manual_seed(300)
+                res = torch.randn(rows, cols, device=dev).to(dtype)
+                bias = torch.randn(cols, device=dev).to(dtype)
+                ref = part.clone().float()
+                dist.all_reduce(ref)
+                ref = ref + res.float() + bias.float()
+                for _ in range(2):
+                    stage, token = comm.ar_stage(rows * cols, dtype)
+                    stage.view(rows, cols).copy_(part)
+                    out = res.clone()
+                    comm.all_reduce_staged(token, out, residual=out, bias=bias)
+                torch.cuda.synchronize()
+                assert (out.float() - ref).abs().max().item() <= 3e-2 * max(1.0, ref.abs().max().item()), (dtype, rows)
         # 2. fused row-parallel GEMV + all-reduce, every tiled family
         torch.manual_seed(7)
         N, K, M = 1024, 512 * world, 3
