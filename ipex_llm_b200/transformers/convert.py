@@ -85,6 +85,9 @@ def is_linear_module(module):
     elif isinstance(module, (ColumnParallelLinear, RowParallelLinear)):
         in_features, out_features = module.in_features, module.out_features
         mp_group = module.mp_group if isinstance(module, RowParallelLinear) else None
+    elif module.__class__.__name__ == "Conv1D" and hasattr(module, "nf") and module.weight.dim() == 2:
+        # GPT-2 style "Conv1D": y = x @ W + b with W stored [in, out]; converted through its transpose
+        in_features, out_features = module.weight.shape[0], module.weight.shape[1]
     elif module.__class__.__name__ in ("LinearLayer", "LinearAllreduce"):
         # DeepSpeed AutoTP containers: weight [out, in]; LinearAllreduce carries the process group
         in_features, out_features = module.weight.shape[1], module.weight.shape[0]
@@ -107,6 +110,14 @@ def is_linear_module(module):
     else:
         result = False
     return result, (in_features, out_features, mp_group)
+
+
+def _linear_weight(module) -> torch.Tensor:
+    """The ``[out, in]`` weight of a module ``is_linear_module`` accepted (Conv1D stores the transpose)."""
+    w = module.weight.data
+    if module.__class__.__name__ == "Conv1D":
+        w = w.t().contiguous()
+    return w
 
 
 def convert_gptq(module, awq=False, llm_awq=False, act_order=False):
@@ -160,7 +171,7 @@ def _make_low_bit(module, name, in_features, out_features, mp_group, cur_qtype, 
                                                      _shape=torch.Size((out_features, in_features)),
                                                      qtype=cur_qtype).to(device)
     else:
-        w = module.weight.data
+        w = _linear_weight(module)
         param = FP4Params(w, requires_grad=False, quantized=False, _shape=None,
                           convert_shape_only=convert_shape_only, qtype=cur_qtype, imatrix=cur_imatrix,
                           in_features=in_features, enable_scale_search=enable_scale_search)
@@ -217,7 +228,7 @@ def _replace_with_low_bit_linear(model, qtype, modules_to_not_convert=None, conv
                 new_linear = cls(in_features, out_features, has_bias, mp_group=mp_group,
                                  optimize_lm_head=optimize_lm_head)
                 dt = torch.float16 if qtype == qt.FP16 else torch.bfloat16
-                new_linear.weight = nn.Parameter(module.weight.data.to(dt), requires_grad=False)
+                new_linear.weight = nn.Parameter(_linear_weight(module).to(dt), requires_grad=False)
                 if has_bias:
                     new_linear.bias = nn.Parameter(module.bias.data.to(dt), requires_grad=False)
                 if str(device) not in ("cpu", "meta"):
