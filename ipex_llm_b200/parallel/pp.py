@@ -214,6 +214,15 @@ def pipeline_parallel_generate(self, inputs: Optional[torch.Tensor] = None, max_
             else:
                 send(res.to(dtype), rank + 1)
             drain(keep=2 * n_mb)
+        # token-level streaming from the first stage: the ring has just delivered every sequence's token of the
+        # previous step (on a single stage, of this step)
+        if streamer is not None and first:
+            if step == 0:
+                streamer.put(input_ids.cpu())
+            if world == 1:
+                streamer.put(out_new[:, step].cpu())
+            elif step > 0:
+                streamer.put(out_new[:, step - 1].cpu())
         if step == 0:
             sync()
             self.first_token_time = time.perf_counter() - t_start
@@ -229,7 +238,8 @@ def pipeline_parallel_generate(self, inputs: Optional[torch.Tensor] = None, max_
         dist.broadcast(out_new, src=world - 1)
     self.rest_cost_mean = sum(self.next_token_time) / max(1, len(self.next_token_time))
     result = torch.cat([input_ids, out_new], dim=1)
-    if streamer is not None and rank == 0:
-        streamer.put(result.cpu())
+    if streamer is not None and first:
+        if world > 1:
+            streamer.put(out_new[:, max_new_tokens - 1].cpu())     # the last step's tokens came with the broadcast
         streamer.end()
     return result

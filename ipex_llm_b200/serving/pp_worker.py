@@ -32,6 +32,60 @@ class BatchTask:
     input_ids: Optional[List[List[int]]] = None
 
 
+class _TokenEmitter:
+    """Streamer of the pipeline loop on the first stage: one ``put`` per decoding step with every sequence's
+    token; each request gets the text its tokens add, as they arrive (the reference streams per token through
+    its ring as well, pipeline_parallel.py:837-927).  Text that may still change is held back: an incomplete
+    UTF-8 sequence, and a tail that is the beginning of one of the request's stop strings."""
+
+    def __init__(self, tokenizer, requests):
+        self.tok = tokenizer
+        self.reqs = list(requests)
+        n = len(self.reqs)
+        self.tokens = [[] for _ in range(n)]
+        self.done = [False] * n
+        self.sent = [0] * n          # characters already emitted per request
+        self.prefix = [""] * n       # the emitted text itself (to check it is a prefix of the final text)
+        self._first = True
+
+    def put(self, value):
+        if self._first and value.dim() == 2:
+            self._first = False      # the prompt
+            return
+        self._first = False
+        ids = value.reshape(-1).tolist()
+        eos = self.tok.eos_token_id
+        for i, r in enumerate(self.reqs):
+            if self.done[i] or i >= len(ids):
+                continue
+            t = ids[i]
+            if (eos is not None and t == eos) or len(self.tokens[i]) >= r.params.max_new_tokens:
+                self.done[i] = True
+                continue
+            self.tokens[i].append(t)
+            text = self.tok.decode(self.tokens[i], skip_special_tokens=True)
+            cut = _first_stop(text, r.params.stop)
+            if cut >= 0:
+                text, self.done[i] = text[:cut], True
+            else:
+                if text.endswith("�"):
+                    continue
+                hold = 0
+                for s in r.params.stop or []:
+                    for k in range(min(len(s) - 1, len(text)), 0, -1):
+                        if text.endswith(s[:k]):
+                            hold = max(hold, k)
+                            break
+                text = text[: len(text) - hold] if hold else text
+            if len(text) > self.sent[i]:
+                r.emit(text[self.sent[i]:])
+                self.prefix[i] = text
+                self.sent[i] = len(text)
+
+    def end(self):
+        pass
+
+
 class PPModelWorker(ModelWorker):
     def __init__(self, checkpoint=None, rank=None, world_size=None, low_bit="sym_int4", max_num_seqs=4,
                  max_prefilled_seqs=0, torch_dtype=torch.float16, model=None, tokenizer=None):
@@ -84,7 +138,8 @@ class PPModelWorker(ModelWorker):
             return False
         ids = torch.tensor(task.input_ids, dtype=torch.long)
         t0 = time.perf_counter()
-        out = self.model.generate(ids, max_new_tokens=task.max_tokens, do_sample=False,
+        emitter = _TokenEmitter(self.tokenizer, batch) if self.rank == 0 else None
+        out = self.model.generate(ids, max_new_tokens=task.max_tokens, do_sample=False, streamer=emitter,
                                   eos_token_id=self.tokenizer.eos_token_id, pad_token_id=self.tokenizer.pad_token_id)
         if self.rank == 0:
             self.stats["first_token_s"].append(getattr(self.model, "first_token_time", 0.0))
@@ -102,8 +157,11 @@ class PPModelWorker(ModelWorker):
                 cut = _first_stop(r.text, r.params.stop)
                 if cut >= 0:
                     r.text, reason = r.text[:cut], "stop"
-                if r.text:
-                    r.emit(r.text)
+                # whatever the per-token stream has not delivered yet (held-back partial characters, or everything
+                # when the model's generate did not stream)
+                rest = r.text[emitter.sent[i]:] if r.text.startswith(emitter.prefix[i]) else ""
+                if rest:
+                    r.emit(rest)
                 self._finish(r, reason)
             self.stats["requests"] += len(batch)
             self.stats["batches"] += 1

@@ -45,6 +45,27 @@ def main():
     # fp16 stage hand-offs on the GPU can flip a near-tie late in a sequence; the CPU path is fp32 and exact
     assert match == 1.0 if not cuda else match > 0.9, (match, out, ref)
     assert staged.first_token_time > 0 and len(staged.next_token_time) == 7
+
+    # token-level streaming from the first stage: the prompt, then one put per step with every sequence's token
+    class _Collect:
+        def __init__(self):
+            self.prompt, self.steps, self.ended = None, [], False
+
+        def put(self, t):
+            if self.prompt is None:
+                self.prompt = t.clone()
+            else:
+                self.steps.append(t.clone())
+
+        def end(self):
+            self.ended = True
+
+    st = _Collect() if rank == 0 else None
+    out2 = staged.generate(ids.to(dev), max_new_tokens=8, do_sample=False, streamer=st)
+    if rank == 0:
+        assert st.ended and st.prompt.shape == (3, 17) and len(st.steps) == 8, (len(st.steps), st.ended)
+        streamed = torch.stack([s.reshape(-1) for s in st.steps], dim=1)
+        assert torch.equal(streamed, out2[:, 17:].cpu()), (streamed, out2[:, 17:])
     dist.barrier()
     dist.destroy_process_group()
     print(f"rank {rank}: ok")

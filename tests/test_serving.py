@@ -25,6 +25,40 @@ def worker():
     w.shutdown()
 
 
+def test_pipeline_token_emitter():
+    """The first stage's per-step streamer: deltas per request, stop strings held back and cut, eos, token limits."""
+    from ipex_llm_b200.serving.model_worker import SamplingParams
+    from ipex_llm_b200.serving.pp_worker import _TokenEmitter
+
+    class Tok:
+        eos_token_id = 2
+
+        def decode(self, ids, **kw):
+            return "".join(chr(ord("a") + (i % 26)) for i in ids)
+
+    class Req:
+        def __init__(self, max_new_tokens, stop):
+            self.params = SamplingParams(max_new_tokens=max_new_tokens, stop=stop)
+            self.pieces = []
+
+        def emit(self, s):
+            self.pieces.append(s)
+
+    reqs = [Req(10, []), Req(3, []), Req(10, ["hi"]), Req(10, [])]
+    em = _TokenEmitter(Tok(), reqs)
+    em.put(torch.zeros(4, 5, dtype=torch.long))                 # prompt
+    # per step: request 0 spells "defg...", 1 is cut by its limit, 2 runs into the stop string "hi", 3 ends with eos
+    steps = [[3, 3, 6, 3], [4, 4, 7, 2], [5, 5, 8, 9], [6, 6, 9, 9], [7, 7, 10, 9]]
+    for s in steps:
+        em.put(torch.tensor(s))
+    em.end()
+    assert "".join(reqs[0].pieces) == "defgh" and len(reqs[0].pieces) == 5      # one delta per token
+    assert "".join(reqs[1].pieces) == "def"                                      # max_new_tokens = 3
+    assert "".join(reqs[2].pieces) == "g" and em.done[2]                         # "h" held back, then "hi" cut
+    assert "".join(reqs[3].pieces) == "d" and em.done[3]                         # eos at the second step
+    assert em.sent[0] == 5 and em.prefix[2] == "g"
+
+
 def test_batch_streamer_incremental_text():
     from ipex_llm.transformers.streamer import BatchTextIteratorStreamer
 
