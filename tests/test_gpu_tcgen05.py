@@ -121,9 +121,12 @@ def test_dense_linear_routes_to_tcgen05():
     assert _rel_err(out, x.float() @ w.float().t()) < 2e-3
 
 
+@pytest.mark.parametrize("dequant_min_tokens", ["100000", "1"])
 @pytest.mark.parametrize("low_bit", ["sym_int4", "fp8_e4m3"])
-def test_flat_prefill_matches_module_path(low_bit, monkeypatch):
-    """The engine's flattened prompt pass (tcgen05 GEMMs with fused residual / act) against the module-tree pass."""
+def test_flat_prefill_matches_module_path(low_bit, dequant_min_tokens, monkeypatch):
+    """The engine's flattened prompt pass (tcgen05 GEMMs with fused residual / act) against the module-tree pass,
+    with the dequantizer warps in the GEMM and with the weight expanded once in front of the dense kernel."""
+    monkeypatch.setenv("IPEX_LLM_PREFILL_DEQUANT_MIN_TOKENS", dequant_min_tokens)
     from transformers import LlamaConfig
     from ipex_llm.transformers import AutoModelForCausalLM
     from ipex_llm_b200.engine import get_engine
