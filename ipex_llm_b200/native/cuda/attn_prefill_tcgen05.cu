@@ -77,8 +77,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nqb = (a.S + kBQ - 1) / kBQ;
-  const int qb = nqb - 1 - (int)blockIdx.x;         // the longest rows first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // Blocks are dispatched x-fastest: heads run along x and query blocks, longest first, along y, so every head's
+  // longest rows start before any shorter ones (longest-processing-time-first over the SMs).
+  const int qb = nqb - 1 - (int)blockIdx.y;
+  const int h = blockIdx.x, b = blockIdx.z;
   const int kvh = h / (a.Hq / a.Hkv);
   const int nkv = a.causal ? qb + 1 : (a.S + kBKV - 1) / kBKV;
 
@@ -278,6 +280,32 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   if (warp == 9) tmem_dealloc(tmem_base, kTmemCols);
 }
 
+// V (token-major, element (b, s, h, d) at v[(b*S + s) * ldv + h*D + d]) -> V^T [B, Hkv, D, s_pad], zeros for
+// s in [S, s_pad).  64 x 64 tiles through shared memory: 128-byte contiguous reads along d and writes along s.
+template <typename T>
+__global__ void __launch_bounds__(256) transpose_v_kernel(const T* __restrict__ v, T* __restrict__ vt, int S, int Hkv,
+                                                          int D, int64_t ldv, int64_t s_pad) {
+  __shared__ T tile[64][66];
+  const int s0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
+  const int bh = blockIdx.z, b = bh / Hkv, h = bh % Hkv;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int sl = ty + 4 * i, s = s0 + sl;
+    T val = DT<T>::from_f(0.f);
+    if (s < S) val = v[((int64_t)b * S + s) * ldv + (int64_t)h * D + d0 + tx];
+    tile[sl][tx] = val;
+  }
+  __syncthreads();
+  if (s0 + tx < s_pad) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int dl = ty + 4 * i;
+      vt[((int64_t)bh * D + d0 + dl) * s_pad + s0 + tx] = tile[tx][dl];
+    }
+  }
+}
+
 template <typename T, int D>
 int launch(const void* q, const void* k, const void* vt, void* out, int B, int S, int Hq, int Hkv, int64_t ldq,
            int64_t ldk, int64_t s_pad, int64_t ldo, float scale, int causal, int* err, cudaStream_t stream) {
@@ -295,7 +323,7 @@ int launch(const void* q, const void* k, const void* vt, void* out, int B, int S
   auto kern = attn_prefill_kernel<T, D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  dim3 grid((S + kBQ - 1) / kBQ, Hq, B);
+  dim3 grid(Hq, (S + kBQ - 1) / kBQ, B);
   kern<<<grid, kThreads, smem, stream>>>(tm_q, tm_k, tm_vt, a);
   return (int)cudaGetLastError();
 }
@@ -325,4 +353,22 @@ IPEX_API int ipex_attn_prefill_tcgen05(const void* q, const void* k, const void*
       return launch<__nv_bfloat16, 64>(q, k, vt, out, B, S, Hq, Hkv, ldq, ldk, s_pad, ldo, scale, causal, err, s);
   }
   return (int)cudaErrorInvalidValue;
+}
+
+// The transposed V the kernel above reads: v is token-major (row stride ldv elements), vt [B, Hkv, D, s_pad] gets
+// zeros past S.  D a multiple of 64, 16-bit dtype.
+IPEX_API int ipex_attn_transpose_v(const void* v, void* vt, int B, int S, int Hkv, int D, int64_t ldv, int64_t s_pad,
+                                   int dtype, void* stream) {
+  if (B < 1 || S < 1 || Hkv < 1 || (D % 64) != 0 || s_pad < S || (int64_t)B * Hkv > 65535)
+    return (int)cudaErrorInvalidValue;
+  dim3 grid((unsigned)((s_pad + 63) / 64), D / 64, B * Hkv);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == DT_F16)
+    transpose_v_kernel<__half><<<grid, 256, 0, s>>>((const __half*)v, (__half*)vt, S, Hkv, D, ldv, s_pad);
+  else if (dtype == DT_BF16)
+    transpose_v_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)v, (__nv_bfloat16*)vt, S, Hkv, D, ldv,
+                                                          s_pad);
+  else
+    return (int)cudaErrorInvalidValue;
+  return (int)cudaGetLastError();
 }

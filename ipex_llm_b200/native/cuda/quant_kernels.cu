@@ -252,8 +252,19 @@ __global__ void dequant_tiled_kernel(const uint8_t* __restrict__ w, T* __restric
         vals[k] = c * d;
       }
     }
+    T* dst = out + r * ld + k0;
+    if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+      // the thread's 8 outputs as 16-byte stores (one for 16-bit outputs, two for fp32)
+      __align__(16) T o8[8];
 #pragma unroll
-    for (int k = 0; k < 8; k++) out[r * ld + k0 + k] = DT<T>::from_f(vals[k]);
+      for (int k = 0; k < 8; k++) o8[k] = DT<T>::from_f(vals[k]);
+#pragma unroll
+      for (int v = 0; v < (int)(sizeof(T) * 8 / 16); v++)
+        reinterpret_cast<uint4*>(dst)[v] = reinterpret_cast<const uint4*>(o8)[v];
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; k++) dst[k] = DT<T>::from_f(vals[k]);
+    }
   }
 }
 

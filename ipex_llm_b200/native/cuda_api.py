@@ -29,6 +29,7 @@ _SIGS = {
     "ipex_act_mul": [vp, vp, vp, i64, ci, ci, ci, vp],
     "ipex_softmax_inplace": [vp, i64, ci, ci, vp],
     "ipex_attn_prefill_tcgen05": [vp, vp, vp, vp, ci, ci, ci, ci, ci, i64, i64, i64, i64, cf, ci, ci, vp, vp],
+    "ipex_attn_transpose_v": [vp, vp, ci, ci, ci, ci, i64, i64, ci, vp],
     "ipex_rwkv_wkv_v4": [vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp],
     "ipex_rwkv_linear_attention_v5": [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp],
     "ipex_rwkv_time_shift": [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp],

@@ -531,9 +531,16 @@ def attn_prefill_tcgen05(q, k, v, scale: float, causal: bool = True) -> torch.Te
     B, Hq, S, D = q.shape
     Hkv = k.shape[1]
     s_pad = (S + 7) // 8 * 8
-    vt = torch.zeros(B, Hkv, D, s_pad, dtype=q.dtype, device=q.device) if s_pad != S else \
-        torch.empty(B, Hkv, D, S, dtype=q.dtype, device=q.device)
-    vt[..., :S].copy_(v.transpose(-1, -2))
+    if _token_major(v) and B * Hkv <= 65535 and hasattr(lib, "ipex_attn_transpose_v"):
+        # tiled transpose kernel (a strided torch copy of this shape runs at a fraction of the memory rate and
+        # cost as much as the attention itself)
+        vt = torch.empty(B, Hkv, D, s_pad, dtype=q.dtype, device=q.device)
+        rc = lib.ipex_attn_transpose_v(ptr(v), ptr(vt), B, S, Hkv, D, v.stride(2), s_pad, _dt(q), current_stream())
+        api.check(rc, "attn_transpose_v")
+    else:
+        vt = torch.zeros(B, Hkv, D, s_pad, dtype=q.dtype, device=q.device) if s_pad != S else \
+            torch.empty(B, Hkv, D, S, dtype=q.dtype, device=q.device)
+        vt[..., :S].copy_(v.transpose(-1, -2))
     out = torch.empty(B, S, Hq, D, dtype=q.dtype, device=q.device)
     rc = lib.ipex_attn_prefill_tcgen05(ptr(q), ptr(k), ptr(vt), ptr(out), B, S, Hq, Hkv, D, q.stride(2), k.stride(2),
                                        s_pad, Hq * D, float(scale), int(bool(causal)), _dt(q),

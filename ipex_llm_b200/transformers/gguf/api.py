@@ -89,6 +89,87 @@ def _hf_config(cfg: dict, arch: str, vocab: int):
     return transformers.LlamaConfig(**common), "llama"
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# LayerNorm / fused-qkv families (reference gguf/models/bloom.py, falcon.py, mpt.py)
+# ---------------------------------------------------------------------------------------------------------------
+_GPT_LIKE = ("bloom", "falcon", "mpt")
+
+_GPT_TOP = {
+    "bloom": {"token_embd": "transformer.word_embeddings", "token_embd_norm": "transformer.word_embeddings_layernorm",
+              "output_norm": "transformer.ln_f", "output": "lm_head"},
+    "falcon": {"token_embd": "transformer.word_embeddings", "output_norm": "transformer.ln_f", "output": "lm_head"},
+    "mpt": {"token_embd": "transformer.wte", "output_norm": "transformer.norm_f", "output": "lm_head"},
+}
+_GPT_BLOCK = {
+    "bloom": ("transformer.h", {"attn_norm": "input_layernorm", "attn_qkv": "self_attention.query_key_value",
+                                "attn_output": "self_attention.dense", "ffn_norm": "post_attention_layernorm",
+                                "ffn_up": "mlp.dense_h_to_4h", "ffn_down": "mlp.dense_4h_to_h"}),
+    # new_decoder_architecture (40B-style) files carry two norms: attn_norm is ln_mlp there and attn_norm_2 ln_attn
+    "falcon": ("transformer.h", {"attn_norm": "input_layernorm", "attn_norm_2": "ln_attn",
+                                 "attn_qkv": "self_attention.query_key_value", "attn_output": "self_attention.dense",
+                                 "ffn_up": "mlp.dense_h_to_4h", "ffn_down": "mlp.dense_4h_to_h"}),
+    "mpt": ("transformer.blocks", {"attn_norm": "norm_1", "attn_qkv": "attn.Wqkv", "attn_output": "attn.out_proj",
+                                   "ffn_norm": "norm_2", "ffn_up": "ffn.up_proj", "ffn_down": "ffn.down_proj"}),
+}
+
+
+def get_gpt_module_name(arch: str, name: str, new_decoder_architecture: bool = False) -> Optional[str]:
+    """GGUF tensor name -> Hugging Face parameter name for bloom / falcon / mpt."""
+    stem, _, kind = name.rpartition(".")           # "...weight" / "...bias"
+    if stem in _GPT_TOP[arch]:
+        return f"{_GPT_TOP[arch][stem]}.{kind}"
+    m = re.match(r"blk\.(\d+)\.(.+)", stem)
+    if not m:
+        return None
+    prefix, table = _GPT_BLOCK[arch]
+    sub = table.get(m.group(2))
+    if sub is None:
+        return None
+    if arch == "falcon" and new_decoder_architecture and m.group(2) == "attn_norm":
+        sub = "ln_mlp"
+    return f"{prefix}.{m.group(1)}.{sub}.{kind}"
+
+
+def _qkv_to_hf(arch: str, t: torch.Tensor, n_head: int, n_kv: int) -> torch.Tensor:
+    """llama.cpp stores fused qkv as ``[all Q; all K; all V]``; bloom and falcon checkpoints interleave them per
+    (kv) head: ``[n_kv, q heads of the group + k + v, head_dim, ...]``.  MPT already is ``[Q; K; V]``."""
+    if arch == "mpt":
+        return t
+    rest = t.shape[1:]
+    hd = t.shape[0] // (n_head + 2 * n_kv)
+    q, k, v = t.split([n_head * hd, n_kv * hd, n_kv * hd], dim=0)
+    q = q.reshape(n_kv, n_head // n_kv, hd, *rest)
+    k = k.reshape(n_kv, 1, hd, *rest)
+    v = v.reshape(n_kv, 1, hd, *rest)
+    return torch.cat([q, k, v], dim=1).reshape(t.shape)
+
+
+def _gpt_like_config(cfg: dict, arch: str, vocab: int):
+    import transformers
+    g = lambda k, d=None: cfg.get(f"{arch}.{k}", d)  # noqa: E731
+    E, L, Hn = g("embedding_length"), g("block_count"), g("attention.head_count")
+    eps = g("attention.layer_norm_epsilon", 1e-5)
+    tok = dict(bos_token_id=cfg.get("tokenizer.ggml.bos_token_id"), eos_token_id=cfg.get("tokenizer.ggml.eos_token_id"))
+    if arch == "bloom":
+        return transformers.BloomConfig(vocab_size=vocab, hidden_size=E, n_layer=L, n_head=Hn,
+                                        layer_norm_epsilon=eps, **tok), Hn, Hn
+    if arch == "falcon":
+        n_kv = g("attention.head_count_kv", 1) or 1
+        new_arch = 1 < n_kv < Hn
+        return transformers.FalconConfig(vocab_size=vocab, hidden_size=E, num_hidden_layers=L, num_attention_heads=Hn,
+                                         num_kv_heads=n_kv, new_decoder_architecture=new_arch,
+                                         multi_query=n_kv == 1, parallel_attn=True, bias=False, alibi=False,
+                                         layer_norm_epsilon=eps, **tok), Hn, n_kv
+    ffn = g("feed_forward_length", 4 * E)
+    attn_cfg = {"alibi": True, "alibi_bias_max": int(g("attention.max_alibi_bias", 8) or 8)}
+    clip = g("attention.clamp_kqv")
+    if clip:
+        attn_cfg["clip_qkv"] = float(clip)
+    return transformers.MptConfig(vocab_size=vocab, d_model=E, n_layers=L, n_heads=Hn, expansion_ratio=ffn // E,
+                                  max_seq_len=g("context_length", 2048), no_bias=True, layer_norm_epsilon=eps,
+                                  attn_config=attn_cfg, **tok), Hn, Hn
+
+
 class GGUFTokenizer:
     """Minimal tokenizer over the vocabulary stored in the file (sentencepiece pieces rebuilt into a processor)."""
 
@@ -140,15 +221,18 @@ def load_gguf_model(fpath: str, dtype: torch.dtype = torch.float, low_bit: str =
     cfg = loader.config
     arch = cfg.get("general.architecture")
     print("model_family:" + str(arch))
-    invalidInputError(arch in _LLAMA_LIKE, f"Unsupported model family: {arch}")
+    invalidInputError(arch in _LLAMA_LIKE or arch in _GPT_LIKE, f"Unsupported model family: {arch}")
     vocab = len(cfg["tokenizer.ggml.tokens"]) if "tokenizer.ggml.tokens" in cfg else None
     names = loader.tensor_loader.names()
     if vocab is None:
         vocab = loader.tensor_loader.infos[names.index("token_embd.weight")][1][1]
-    hf_cfg, family = _hf_config(cfg, arch, vocab)
-    n_head, n_kv = hf_cfg.num_attention_heads, hf_cfg.num_key_value_heads
-    if "output.weight" not in names:
-        hf_cfg.tie_word_embeddings = True
+    gpt_like = arch in _GPT_LIKE
+    if gpt_like:
+        hf_cfg, n_head, n_kv = _gpt_like_config(cfg, arch, vocab)
+    else:
+        hf_cfg, family = _hf_config(cfg, arch, vocab)
+        n_head, n_kv = hf_cfg.num_attention_heads, hf_cfg.num_key_value_heads
+    hf_cfg.tie_word_embeddings = "output.weight" not in names
 
     try:
         from transformers.initialization import no_init_weights
@@ -160,7 +244,19 @@ def load_gguf_model(fpath: str, dtype: torch.dtype = torch.float, low_bit: str =
     params = dict(model.named_parameters())
     loaded = set()
 
+    new_arch = bool(getattr(hf_cfg, "new_decoder_architecture", False))
+
     def process(name, tensor):
+        if gpt_like:
+            target = get_gpt_module_name(arch, name, new_arch)
+            if target is None or target not in params:
+                return
+            if ".attn_qkv." in name:
+                tensor = _qkv_to_hf(arch, tensor, n_head, n_kv)
+            with torch.no_grad():
+                params[target].copy_(tensor.to(params[target].dtype).reshape(params[target].shape))
+            loaded.add(target)
+            return
         target = get_llama_module_name(name)
         if target is None or target not in params:
             return

@@ -71,3 +71,100 @@ def test_load_gguf_llama(tmp_path):
     assert cos > 0.995, cos
     out = model.generate(ids, max_new_tokens=4, do_sample=False)
     assert out.shape == (2, 14)
+
+
+def _qkv_to_gguf(t, n_head, n_kv):
+    """Checkpoint layout [n_kv, q heads of the group + k + v, head_dim, ...] -> llama.cpp's [all Q; all K; all V]."""
+    rest = t.shape[1:]
+    hd = t.shape[0] // (n_head + 2 * n_kv)
+    g = t.reshape(n_kv, n_head // n_kv + 2, hd, *rest)
+    q = g[:, :-2].reshape(n_head * hd, *rest)
+    k = g[:, -2].reshape(n_kv * hd, *rest)
+    v = g[:, -1].reshape(n_kv * hd, *rest)
+    return torch.cat([q, k, v], dim=0)
+
+
+def _export_gpt_like(model, arch, path, n_head, n_kv, meta_extra):
+    from ipex_llm_b200.transformers.gguf.api import _GPT_BLOCK, _GPT_TOP
+    from ipex_llm_b200.transformers.gguf.gguf import write_gguf
+    sd = model.state_dict()
+    tensors = {}
+    for gg, hf in _GPT_TOP[arch].items():
+        for kind in ("weight", "bias"):
+            key = f"{hf}.{kind}"
+            if key in sd and not (gg == "output" and getattr(model.config, "tie_word_embeddings", False)):
+                tensors[f"{gg}.{kind}"] = (sd[key], "f16" if sd[key].dim() > 1 else "f32")
+    prefix, table = _GPT_BLOCK[arch]
+    n_layers = len([k for k in sd if k.startswith(prefix + ".") and k.endswith(table["attn_qkv"] + ".weight")])
+    for i in range(n_layers):
+        for gg, hf in table.items():
+            for kind in ("weight", "bias"):
+                key = f"{prefix}.{i}.{hf}.{kind}"
+                if key not in sd and arch == "falcon" and gg == "attn_norm":
+                    key = f"{prefix}.{i}.ln_mlp.{kind}"          # two-norm (40B-style) blocks: attn_norm is ln_mlp
+                if key not in sd:
+                    continue
+                t = sd[key]
+                if gg == "attn_qkv" and arch != "mpt":
+                    t = _qkv_to_gguf(t, n_head, n_kv)
+                tensors[f"blk.{i}.{gg}.{kind}"] = (t, "q8_0" if t.dim() > 1 else "f32")
+    meta = {"general.architecture": arch, "general.name": "tiny-" + arch, "general.file_type": 7,
+            "tokenizer.ggml.bos_token_id": 1, "tokenizer.ggml.eos_token_id": 2}
+    meta.update(meta_extra)
+    write_gguf(path, meta, tensors)
+
+
+def _randomize(model):
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() > 1:
+                p.normal_(0, 0.05)
+            else:
+                p.add_(torch.randn_like(p) * 0.05)
+
+
+import pytest
+
+
+@pytest.mark.parametrize("arch", ["bloom", "falcon", "falcon-gqa", "mpt"])
+def test_load_gguf_layernorm_families(tmp_path, arch):
+    """bloom / falcon / mpt files: tensor-name maps, fused-qkv re-interleaving, configs rebuilt from the metadata."""
+    import transformers as tf
+    from ipex_llm.transformers import AutoModelForCausalLM
+    torch.manual_seed(0)
+    if arch == "bloom":
+        cfg = tf.BloomConfig(hidden_size=128, n_layer=2, n_head=4, vocab_size=320, tie_word_embeddings=False)
+        n_head = n_kv = 4
+        meta = {"bloom.embedding_length": 128, "bloom.block_count": 2, "bloom.attention.head_count": 4,
+                "bloom.attention.layer_norm_epsilon": float(cfg.layer_norm_epsilon), "bloom.context_length": 256}
+    elif arch.startswith("falcon"):
+        gqa = arch.endswith("gqa")
+        n_head, n_kv = 4, (2 if gqa else 1)
+        cfg = tf.FalconConfig(hidden_size=128, num_hidden_layers=2, num_attention_heads=4, vocab_size=320,
+                              num_kv_heads=n_kv, new_decoder_architecture=gqa, multi_query=not gqa,
+                              parallel_attn=True, bias=False, alibi=False, tie_word_embeddings=False)
+        meta = {"falcon.embedding_length": 128, "falcon.block_count": 2, "falcon.attention.head_count": 4,
+                "falcon.attention.head_count_kv": n_kv, "falcon.context_length": 256,
+                "falcon.attention.layer_norm_epsilon": float(cfg.layer_norm_epsilon)}
+    else:
+        cfg = tf.MptConfig(d_model=128, n_layers=2, n_heads=4, vocab_size=320, max_seq_len=256, no_bias=True)
+        n_head = n_kv = 4
+        meta = {"mpt.embedding_length": 128, "mpt.block_count": 2, "mpt.attention.head_count": 4,
+                "mpt.feed_forward_length": 512, "mpt.context_length": 256, "mpt.attention.max_alibi_bias": 8.0,
+                "mpt.attention.layer_norm_epsilon": float(cfg.layer_norm_epsilon)}
+    src = tf.AutoModelForCausalLM.from_config(cfg).eval()
+    _randomize(src)
+    file_arch = "falcon" if arch.startswith("falcon") else arch
+    path = str(tmp_path / f"{arch}.gguf")
+    _export_gpt_like(src, file_arch, path, n_head, n_kv, meta)
+    model, tok = AutoModelForCausalLM.from_gguf(path, low_bit="sym_int8")
+    assert tok is None
+    assert model.config.model_type == file_arch
+    ids = torch.randint(0, 320, (2, 10))
+    with torch.no_grad():
+        a = src(ids).logits[:, -1].float()
+        b = model(ids).logits[:, -1].float()
+    cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item()
+    assert cos > 0.995, (arch, cos)
+    out = model.generate(ids, max_new_tokens=3, do_sample=False)
+    assert out.shape == (2, 13)
