@@ -480,12 +480,10 @@ class DecoderEngine:
                 out += residual
             return out
         M = x.shape[0]
-        if M >= int(os.environ.get("IPEX_LLM_PREFILL_DEQUANT_MIN_TOKENS", "768")) and w.qtype is not None and \
-                (act == 0 or w.N % 32 == 0):
-            # long prompts: expand the packed weight once into a transient half-precision matrix and run the dense
-            # TMA-fed kernel.  Measured at 1024 tokens: dense 1012-1143 TFLOP/s against 744 with the dequantizer
-            # warps in the loop, and the expansion (one pass over the weight) costs less than the difference; the
-            # transient is one layer's weight and is recycled by the allocator.
+        if M >= cuda_ops.dequant_once_min_tokens() and w.qtype is not None and (act == 0 or w.N % 32 == 0):
+            # opt-in for very long prompts (see cuda_ops.dequant_once_min_tokens): expand the packed weight once
+            # into a transient half-precision matrix and run the dense TMA-fed kernel; the transient is one layer's
+            # weight and is recycled by the allocator.
             wd = cuda_ops.dequantize_device(w.data, (w.N, w.K), w.qtype, x.dtype)
             return tcgen05_gemm.gemm_dense(x, wd, bias=w.bias, residual=residual, act=act)
         return tcgen05_gemm.gemm_lowbit(x, w.data, w.qtype, w.N, w.K, bias=w.bias, residual=residual, act=act,

@@ -213,6 +213,19 @@ def lowbit_linear(x: torch.Tensor, weight: FP4Params) -> torch.Tensor:
     return dense_linear(x, w)
 
 
+_DEQUANT_ONCE_MIN_TOKENS = 1 << 30
+
+
+def dequant_once_min_tokens() -> int:
+    """From this many tokens on, a low-bit GEMM expands its weight once into a transient half-precision matrix and
+    runs the dense tcgen05 kernel instead of dequantizing inside the GEMM's producer warps.  Off by default: in
+    isolation the dense kernel is faster at 1024 tokens (1012-1143 TFLOP/s against 744), but with the expansion
+    pass in front the 1024-token prompt pass of a 7B int4 model measured 32.0 ms against 30.5 ms with the
+    dequantizers in the loop.  ``IPEX_LLM_PREFILL_DEQUANT_MIN_TOKENS`` sets the threshold (e.g. 4096 for very long
+    prompts, where the expansion is amortised over four times the math)."""
+    return int(os.environ.get("IPEX_LLM_PREFILL_DEQUANT_MIN_TOKENS", str(_DEQUANT_ONCE_MIN_TOKENS)))
+
+
 def gemm_lowbit(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K: int, out: torch.Tensor = None,
                 bias: torch.Tensor = None, residual: torch.Tensor = None) -> torch.Tensor:
     """M > 8: tcgen05 GEMM with in-kernel dequantization when the kernel is built; otherwise dequantize to the
@@ -222,6 +235,10 @@ def gemm_lowbit(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K: in
     fn = getattr(lib, "ipex_gemm_lowbit_tcgen05", None)
     if fn is not None and os.environ.get("IPEX_LLM_TCGEN05", "1") != "0" and x.dtype in (torch.float16, torch.bfloat16):
         from . import tcgen05_gemm
+        if M >= dequant_once_min_tokens() and is_tiled(qtype) and K % 8 == 0:
+            # many tokens: expand the weight once and use the dense TMA-fed kernel (see dequant_once_min_tokens)
+            wd = dequantize_device(w_data, (N, K), qtype, x.dtype)
+            return tcgen05_gemm.gemm_dense(x, wd, bias=bias, residual=residual, out=out)
         if tcgen05_gemm.supported(M, N, K, qtype):
             return tcgen05_gemm.gemm_lowbit(x, w_data, qtype, N, K, out=out, bias=bias, residual=residual)
     w = dequantize_device(w_data, (N, K), qtype, x.dtype)
@@ -510,7 +527,7 @@ def _token_major(t: torch.Tensor) -> bool:
 
 def attn_prefill_tcgen05_ok(q, k, v) -> bool:
     """Shapes and layouts the tcgen05 prompt-attention kernel takes; ``IPEX_LLM_TCGEN05_ATTN=0`` switches it off."""
-    if os.environ.get("IPEX_LLM_TCGEN05_ATTN", "0") == "0" or not q.is_cuda or q.requires_grad:
+    if os.environ.get("IPEX_LLM_TCGEN05_ATTN", "1") == "0" or not q.is_cuda or q.requires_grad:
         return False
     if q.dtype not in (torch.float16, torch.bfloat16) or k.dtype != q.dtype or v.dtype != q.dtype:
         return False
