@@ -15,6 +15,7 @@ import torch
 from ..models.registry import family_for
 from ..ops import cuda_ops
 from ..ops.linear import LowBitLinear
+from ..utils.tracing import nvtx_range
 from .decoder_engine import DecoderEngine
 
 _UNSUPPORTED_KW = ("num_beams", "penalty_alpha", "num_return_sequences", "constraints", "force_words_ids",
@@ -109,7 +110,8 @@ def engine_generate(model, input_ids, generation_config=None, streamer=None, att
 
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    logits = eng.prefill(input_ids)
+    with nvtx_range("ipex_llm.prefill"):
+        logits = eng.prefill(input_ids)
     if rep_pen and rep_pen != 1.0:
         cuda_ops.repetition_penalty_inplace(logits, input_ids, rep_pen)
     nxt = _sample(logits, do_sample, temperature, top_k, top_p)
@@ -134,7 +136,8 @@ def engine_generate(model, input_ids, generation_config=None, streamer=None, att
     check_every = 16 if streamer is None else 1
     while n_gen < max_new:
         ts = time.perf_counter()
-        eng.decode_step(B)
+        with nvtx_range("ipex_llm.decode_step"):
+            eng.decode_step(B)
         if graph_greedy:
             nxt = eng.tokens[:B]
         else:
