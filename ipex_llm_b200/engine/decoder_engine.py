@@ -221,7 +221,7 @@ class DecoderEngine:
                 cuda_ops.gemv_lowbit(x[s:e], w.data, w.qtype, w.N, w.K, out=stage.view(e - s, w.N),
                                      pdl=self.use_pdl, wf=w.wf)
                 comm.all_reduce_staged(token, out[s:e], residual=residual[s:e] if residual is not None else None,
-                                       bias=bias if bias is not None else w.bias)
+                                       bias=bias if bias is not None else w.bias, pdl=self.use_pdl)
                 continue
             if w.tp is not None:
                 # row-parallel layer, stand-alone steps: plain GEMV, all-reduce, then bias and residual
@@ -468,7 +468,14 @@ class DecoderEngine:
         from ..ops import tcgen05_gemm
         if w.tp is not None:
             comm = w.tp.symm()
-            if comm is not None and os.environ.get("IPEX_LLM_TP_FUSED_GEMM_AR", "1") != "0":
+            # The fused epilogue is a one-shot all-reduce: every rank stores its partial tile into EVERY rank's
+            # staging buffer, (world - 1) x the output per rank over NVLink.  At two ranks that equals the traffic
+            # of reduce-scatter + all-gather; beyond that it only pays for small outputs (a 2048-token prompt of
+            # the 70B model at 8 ranks moved 235 MB per layer half and the prompt pass did not scale: 385 ms
+            # against 287 ms at 2 ranks), so larger outputs go through the bandwidth-optimal library all-reduce.
+            fused_ok = comm is not None and (comm.world <= 2 or x.shape[0] * w.N * x.element_size() <= (2 << 20))
+            fused_env = os.environ.get("IPEX_LLM_TP_FUSED_GEMM_AR", "auto")
+            if comm is not None and (fused_env == "1" or (fused_env != "0" and fused_ok)):
                 # the all-reduce runs inside the GEMM's epilogue (peer stores + arrival counters over NVLink)
                 return tcgen05_gemm.gemm_lowbit_ar(x, w.data, w.qtype, w.N, w.K, comm, bias=w.bias,
                                                    residual=residual, wf=w.wf)
