@@ -10,8 +10,9 @@ and ``value`` the whole-job decode throughput in tokens/s.
 * N = 1, default model: Llama-2-7B architecture, random N(0, 0.02) weights, sym_int4 (group 64, fp16 scales),
   fp16 activations, fp8 e5m2 KV cache, batch 1, 1024 prompt tokens.
 * N > 1: Llama-3-70B architecture in block-scaled fp8_e4m3 (128-blocks, fp32 scales), bf16 activations,
-  tensor parallel over the N GPUs with the fused GEMV+all-reduce kernels (strong scaling: the same model and
-  batch on more GPUs).  ``--model llama3-70b`` runs the same model on one GPU.
+  tensor parallel over the N GPUs (row-parallel GEMVs write into symmetric staging memory and one peer-memory
+  kernel does all-reduce + bias + residual; strong scaling: the same model and batch on more GPUs).
+  ``--model llama3-70b`` runs the same model on one GPU.
 
 Timing: W untimed steps, then K steps between CUDA events on the launching stream, barrier + synchronize on
 both sides, max over ranks.  Weights (3.6 GB and up) are far larger than the 126 MB L2, so every step streams

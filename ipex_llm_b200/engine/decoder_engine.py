@@ -243,6 +243,8 @@ class DecoderEngine:
         n = len(self.layers)
         if self._use_chain(getattr(self, "batch", 1) or 1):
             return 1 + 1 + 2 * n + 1          # embedding, first qkv, (attention + chained GEMVs) per layer, argmax
+        if self.layers[0].o.tp is not None:
+            return 1 + 7 * n + 2              # tensor parallel: + one all-reduce kernel after o_proj and down_proj
         return 1 + 5 * n + 2
 
     def _use_chain(self, B: int) -> bool:

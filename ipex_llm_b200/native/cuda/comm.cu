@@ -68,11 +68,18 @@ __global__ void allreduce_oneshot_kernel(const T* const* bufs, int* const* flags
     float acc[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; j++) acc[j] = 0.f;
-    for (int r = 0; r < world; r++) {
-      const uint4 raw = ld_relaxed_sys_v4(bufs[r] + v * VEC);
-      const T* e = reinterpret_cast<const T*>(&raw);
+    // issue every rank's load before the first use: the remote round trips overlap instead of adding up
+    uint4 raw[8];
 #pragma unroll
-      for (int j = 0; j < VEC; j++) acc[j] += DT<T>::to_f(e[j]);
+    for (int r = 0; r < 8; r++)
+      if (r < world) raw[r] = ld_relaxed_sys_v4(bufs[r] + v * VEC);
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+      if (r < world) {
+        const T* e = reinterpret_cast<const T*>(&raw[r]);
+#pragma unroll
+        for (int j = 0; j < VEC; j++) acc[j] += DT<T>::to_f(e[j]);
+      }
     }
     // epilogue of a row-parallel layer: + residual (same shape as out) + bias (per column, ncols columns per row)
     if (residual != nullptr) {
