@@ -221,7 +221,8 @@ class DecoderEngine:
                 cuda_ops.gemv_lowbit(x[s:e], w.data, w.qtype, w.N, w.K, out=stage.view(e - s, w.N),
                                      pdl=self.use_pdl, wf=w.wf)
                 comm.all_reduce_staged(token, out[s:e], residual=residual[s:e] if residual is not None else None,
-                                       bias=bias if bias is not None else w.bias, pdl=self.use_pdl)
+                                       bias=bias if bias is not None else w.bias,
+                                       pdl=self.use_pdl and os.environ.get("IPEX_LLM_TP_AR_PDL", "1") != "0")
                 continue
             if w.tp is not None:
                 # row-parallel layer, stand-alone steps: plain GEMV, all-reduce, then bias and residual
