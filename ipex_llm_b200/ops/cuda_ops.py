@@ -450,10 +450,11 @@ def pick_nsplit(B: int, Hkv: int, kv_len: int, n_sm: int = 148, rows: int = 1) -
     ts = 4 // rg_p2                      # warps sharing a row group split the tokens
     tokens_per_split = 4 * ts * steps
     by_len = max(1, -(-kv_len // tokens_per_split))
-    # few kv heads per GPU (tensor parallel over many ranks): the rule above would leave most SMs idle (18 CTAs for
-    # one kv head of the 70B model at 8 ranks, each walking 32 steps); split further, down to 8 steps per walk,
-    # until about 64 CTAs exist
-    min_ctas = int(os.environ.get("IPEX_LLM_ATTN_MIN_CTAS", "64"))
+    # few kv heads per GPU (tensor parallel over many ranks) leave most SMs idle under the rule above (18 CTAs for
+    # one kv head of the 70B model at 8 ranks).  Splitting further, down to 8 steps per walk, is available through
+    # IPEX_LLM_ATTN_MIN_CTAS but off: measured on that shape, 64 splits took 54 us against 44 us for 18 (the merge
+    # by the last CTA grows with the split count), and the 8-rank decode step went from 12.8 to 15.8 ms with it
+    min_ctas = int(os.environ.get("IPEX_LLM_ATTN_MIN_CTAS", "0"))
     if B * Hkv * by_len < min_ctas:
         finest = max(1, kv_len // (4 * ts * 8))
         by_len = max(by_len, min(-(-min_ctas // max(1, B * Hkv)), finest))
