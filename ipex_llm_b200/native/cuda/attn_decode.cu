@@ -15,6 +15,8 @@
 // mode A (engine): new K/V rows come from the qkv GEMV output, are rotated, written to the cache by row block 0
 //                  of the last split, and attended to from shared memory (causal among themselves).
 // mode B (module path): the cache already holds every token; q is already rotated.
+#include <cstdlib>
+
 #include "common/utils.cuh"
 
 namespace {
@@ -449,6 +451,16 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
   }
 }
 
+// IPEX_LLM_ATTN_RW4=1: 5..8 query rows per kv head use four rows per warp (two row groups, the warps of a group
+// split the tokens) instead of two rows per warp with every warp walking all tokens of the split.
+static bool wide_rows() {
+  static const bool on = [] {
+    const char* v = getenv("IPEX_LLM_ATTN_RW4");
+    return v != nullptr && v[0] == '1';
+  }();
+  return on;
+}
+
 template <typename T, bool FP8, int D>
 cudaError_t launch_rw(const AttnArgs& a, cudaStream_t s, bool pdl) {
   const int G = a.Hq / a.Hkv;
@@ -464,7 +476,7 @@ cudaError_t launch_rw(const AttnArgs& a, cudaStream_t s, bool pdl) {
     size_t sm = smem_for(1);
     if (sm > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     return launch_kernel(k, grid, dim3(kAttnThreads), sm, s, pdl, a);
-  } else if (rows <= 8) {
+  } else if (rows <= 8 && !(rows > 4 && wide_rows())) {
     auto k = attn_decode_kernel<T, FP8, D, 2>;
     size_t sm = smem_for(2);
     if (sm > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
