@@ -52,7 +52,7 @@ def reference_arm(args):
     (libllama-api.so, bigdl-core-xe) from the network at build time, and it has no CUDA code path."""
     print(json.dumps({
         "impl": "reference",
-        "unavailable": "pip install of /root/reference/python/llm fails offline (setup.py downloads its prebuilt "
+        "unavailable": "pip install of the reference's python/llm fails offline (setup.py downloads its prebuilt "
                        "Intel-only native libraries at build time: URLError name resolution); no CUDA path exists"}))
     return 0
 
