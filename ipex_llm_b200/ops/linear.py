@@ -154,7 +154,14 @@ class LowBitLinear(nn.Linear):
                 result = MatMulLowBit.apply(x_2d, w, self.out_len)
             else:
                 from . import cuda_ops
+                # IPEX_LLM_LOW_MEM=1: give cached blocks back around the large products of a long prompt
+                # (reference low_bit_linear.py:648-671)
+                low_mem = x_2d.shape[0] >= 1024 and os.environ.get("IPEX_LLM_LOW_MEM", "0") == "1"
+                if low_mem:
+                    torch.cuda.empty_cache()
                 result = cuda_ops.lowbit_linear(x_2d, w)
+                if low_mem:
+                    torch.cuda.empty_cache()
             result = result.view(new_shape)
             result = _all_reduce(result, self.mp_group)
             if self.bias is not None:
