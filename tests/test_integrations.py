@@ -102,3 +102,15 @@ def test_native_style_classes_and_legacy_names(tiny):
     assert pieces[-1]["choices"][0]["finish_reason"] in ("length", "stop")
     emb = llm.create_embedding("w3 w4")
     assert len(emb["data"][0]["embedding"]) == 64
+
+
+def test_ggml_quantize_module(tiny_llama_dir, tmp_path):
+    """The reference's ``ipex_llm.ggml.quantize`` import path: qtype table and in-process ``quantize``."""
+    import torch
+    from ipex_llm.ggml.quantize import ggml_tensor_qtype, quantize
+    from ipex_llm.transformers import AutoModelForCausalLM
+    assert ggml_tensor_qtype["sym_int4"] == 2 and ggml_tensor_qtype["nf4"] == 10
+    out = quantize(tiny_llama_dir, str(tmp_path / "q"), model_family="llama", dtype="q8_0")
+    model = AutoModelForCausalLM.load_low_bit(out)
+    ids = torch.randint(0, 32000, (1, 8))
+    assert model.generate(ids, max_new_tokens=2, do_sample=False).shape == (1, 10)
