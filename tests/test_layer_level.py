@@ -1,0 +1,75 @@
+"""Layer-level numerics the way the reference checks them (python/llm/test/inference_gpu/
+test_transformers_api_attention.py:37-183, _mlp.py, _RMSNorm.py): capture the input of one layer's attention / MLP /
+norm in the unoptimized model with a forward pre-hook, feed it to the same layer of the optimized model, compare."""
+import copy
+
+import pytest
+import torch
+
+
+def _tiny():
+    from transformers import LlamaConfig, LlamaForCausalLM
+    torch.manual_seed(0)
+    cfg = LlamaConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=3, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=1000, max_position_embeddings=256, tie_word_embeddings=False)
+    m = LlamaForCausalLM(cfg).eval()
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() > 1:
+                p.normal_(0, 0.05)
+    return m
+
+
+@pytest.mark.parametrize("layer_attr,bound", [("self_attn", 5e-2), ("mlp", 5e-2), ("input_layernorm", 1e-4)])
+def test_layer_output_matches_unoptimized(layer_attr, bound):
+    from ipex_llm import optimize_model
+    ref = _tiny()
+    opt = optimize_model(copy.deepcopy(ref), low_bit="sym_int8")
+    ids = torch.randint(0, 1000, (1, 24))
+    captured = {}
+
+    def pre_hook(module, args, kwargs):
+        captured["args"], captured["kwargs"] = args, kwargs
+
+    def post_hook(module, args, kwargs, output):
+        captured["out"] = output[0] if isinstance(output, tuple) else output
+
+    layer = getattr(ref.model.layers[-1], layer_attr)
+    h1 = layer.register_forward_pre_hook(pre_hook, with_kwargs=True)
+    h2 = layer.register_forward_hook(post_hook, with_kwargs=True)
+    with torch.no_grad():
+        ref(ids)
+    h1.remove()
+    h2.remove()
+    opt_layer = getattr(opt.model.layers[-1], layer_attr)
+    kwargs = dict(captured["kwargs"])
+    kwargs.pop("past_key_values", None)
+    kwargs.pop("past_key_value", None)
+    with torch.no_grad():
+        out = opt_layer(*captured["args"], **kwargs)
+    out = out[0] if isinstance(out, tuple) else out
+    diff = (out.float() - captured["out"].float()).abs().max().item()
+    assert diff <= bound * max(1.0, captured["out"].abs().max().item()), (layer_attr, diff)
+
+
+def test_whisper_tiny_converts():
+    """optimize_model on an encoder-decoder speech model (reference test_optimize_model_api.py:23-40)."""
+    from transformers import WhisperConfig, WhisperForConditionalGeneration
+    from ipex_llm import optimize_model
+    from ipex_llm.transformers.low_bit_linear import LowBitLinear
+    torch.manual_seed(0)
+    cfg = WhisperConfig(d_model=128, encoder_layers=2, decoder_layers=2, encoder_attention_heads=4,
+                        decoder_attention_heads=4, encoder_ffn_dim=256, decoder_ffn_dim=256, vocab_size=600,
+                        num_mel_bins=16, max_source_positions=50, max_target_positions=32,
+                        decoder_start_token_id=1, pad_token_id=0, bos_token_id=1, eos_token_id=2)
+    model = WhisperForConditionalGeneration(cfg).eval()
+    feats = torch.randn(1, 16, 100)
+    dec = torch.tensor([[1, 5, 7]])
+    with torch.no_grad():
+        ref = model(input_features=feats, decoder_input_ids=dec).logits
+    opt = optimize_model(model, low_bit="sym_int8")
+    assert sum(isinstance(m, LowBitLinear) for m in opt.modules()) >= 16
+    with torch.no_grad():
+        out = opt(input_features=feats, decoder_input_ids=dec).logits
+    cos = torch.nn.functional.cosine_similarity(out.flatten().float(), ref.flatten(), dim=0).item()
+    assert cos > 0.99, cos
