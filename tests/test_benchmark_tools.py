@@ -44,3 +44,22 @@ def test_perplexity_windows(tiny_llama_dir):
     # strided windows score every token exactly once and stay in the same range
     strided = ppl.perplexity_hf(ids, seq_len=48, stride=24)
     assert 0.3 * 32000 < strided < 3 * 32000
+
+
+def test_check_results_and_stress(tmp_path, monkeypatch):
+    import yaml
+    from ipex_llm_b200.benchmark import all_in_one, check_results, stress_test
+    monkeypatch.chdir(tmp_path)
+    conf = {"repo_id": ["synthetic:tiny"], "warm_up": 0, "num_trials": 1, "low_bit": "sym_int8", "batch_size": 1,
+            "in_out_pairs": ["8-2"], "test_api": ["transformer_int4"]}
+    with open("config.yaml", "w") as f:
+        yaml.safe_dump(conf, f)
+    all_in_one.main(["config.yaml"])
+    assert check_results.main(["-c", "transformer_int4-results-", "-y", "config.yaml"]) == 0
+    conf["in_out_pairs"].append("16-2")                 # a configured case without a row
+    with open("config2.yaml", "w") as f:
+        yaml.safe_dump(conf, f)
+    assert check_results.main(["-c", "transformer_int4-results-", "-y", "config2.yaml"]) == 1
+    rc = stress_test.main(["--repo-id", "synthetic:tiny", "--test-api", "transformer_int4", "--low-bit", "sym_int8",
+                           "--in-out", "8-3", "--rounds", "3", "--max-latency-drift", "100"])
+    assert rc == 0
