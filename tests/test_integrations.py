@@ -114,3 +114,14 @@ def test_ggml_quantize_module(tiny_llama_dir, tmp_path):
     model = AutoModelForCausalLM.load_low_bit(out)
     ids = torch.randint(0, 32000, (1, 8))
     assert model.generate(ids, max_new_tokens=2, do_sample=False).shape == (1, 10)
+
+
+def test_ipex_llm_init_settings(capsys):
+    from ipex_llm_b200.cli import ipex_llm_init
+    env = ipex_llm_init.settings(gpu=True, tcmalloc=False, jemalloc=False, threads=6)
+    assert env["OMP_NUM_THREADS"] == "6" and env["CUDA_DEVICE_MAX_CONNECTIONS"] == "1"
+    assert env["MASTER_ADDR"] == "127.0.0.1" and "LD_PRELOAD" not in env
+    assert "CUDA_DEVICE_MAX_CONNECTIONS" not in ipex_llm_init.settings(False, False, False)
+    assert ipex_llm_init.main(["--gpu", "--threads", "3"]) == 0
+    out = capsys.readouterr().out
+    assert "export OMP_NUM_THREADS=3" in out and "export NCCL_NVLS_ENABLE=1" in out
