@@ -438,8 +438,10 @@ class DecoderEngine:
     # ------------------------------------------------------------------------------------------------
     @torch.no_grad()
     def prefill(self, input_ids: torch.Tensor, attention_mask=None):
-        """Prompt pass through the module path (tensor-core GEMMs + prefill attention), writing K/V into the
-        engine's cache; returns the logits of the last position ``[B, V]``."""
+        """Prompt pass, writing K/V into the engine's cache; returns the logits of the last position ``[B, V]``.
+        Unmasked prompts of quantized models take the flattened pass (``_prefill_flat``: tcgen05 GEMMs with fused
+        residual / SwiGLU epilogues and the tcgen05 attention, about nine kernels per layer); masked batches, tiny
+        prompts and dense-weight models go through the module tree."""
         B, S = input_ids.shape
         if S + 1 > self.max_len:
             raise ValueError(f"prompt of {S} tokens does not fit max_len={self.max_len}")
