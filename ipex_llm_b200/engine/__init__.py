@@ -1,7 +1,8 @@
 """Native decode engine: selection and the ``generate`` loop built on it.
 
-``engine_generate`` is what ``model.generate`` runs for a converted CUDA model of a supported family: prompt pass
-through the module path, then one CUDA-graph replay per token.  Per-token timing follows the reference's
+``engine_generate`` is what ``model.generate`` runs for a converted CUDA model of a supported family: the engine's
+prompt pass (flattened tcgen05 pass for unmasked prompts, module tree otherwise), then one CUDA-graph replay per
+token.  Per-token timing follows the reference's
 ``BenchmarkWrapper`` definitions (first token = prompt pass + first sampling, rest = mean of the remaining steps;
 python/llm/src/ipex_llm/utils/benchmark_util_4_47.py:3376-3393) and is left on the model as
 ``first_token_time`` / ``rest_cost_mean`` / ``last_token_time``.
