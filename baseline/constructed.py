@@ -135,7 +135,6 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--graph", action="store_true", help="capture the decode step in a CUDA graph on multi-rank runs too")
     a = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -162,10 +161,10 @@ def main():
             first_ms = e0.elapsed_time(e1)
         m.pos.fill_(spec["prompt"])
         step = m.decode_step
-        # Multi-rank runs issue eager launches unless --graph is given: capturing the NCCL all-reduces of the
-        # 70B model did not return within ten minutes on two GPUs, and eager launches are what the reference's
-        # own stack issues.  The JSON line records which mode ran.
-        use_graph = not a.no_graph and (world == 1 or a.graph)
+        # Only single-rank runs capture the decode step in a CUDA graph.  Multi-rank runs issue eager launches,
+        # which is what the reference's own stack does; a captured step that contains the library all-reduces is
+        # not offered (an earlier form of it did not return on two GPUs).  The JSON line records which mode ran.
+        use_graph = not a.no_graph and world == 1
         print(f"[constructed] rank {rank}: prompt pass done ({first_ms:.1f} ms), cuda_graph={use_graph}",
               file=sys.stderr, flush=True)
         if use_graph:

@@ -83,10 +83,14 @@ IPEX_API int ipex_attn_decode_noalloc(const void* q, const void* knew, const voi
                                       int fp8_kv, int dtype, int pdl, void* stream) {
   if (Hkv < 1 || Hq < 1 || Hq % Hkv != 0 || Sq < 1 || nsplit < 1 || B < 1) return (int)cudaErrorInvalidValue;
   const int G = Hq / Hkv;
-  const int64_t need_f = ipex_attn_decode_scratch_floats(B, Hkv, G, Sq, D, nsplit);
-  const int64_t need_c = ipex_attn_decode_counter_ints(B, Hkv, G, Sq);
-  if (need_f > kMaxFloats) return IPEX_NOALLOC_E_SCRATCH;
+  // With a single split every CTA writes its result straight to `out` and never reads or writes the partials or
+  // the tickets, so such a launch needs nothing from the array and no limit applies to it.
+  const int64_t need_f = nsplit == 1 ? 0 : ipex_attn_decode_scratch_floats(B, Hkv, G, Sq, D, nsplit);
+  const int64_t need_c = nsplit == 1 ? 0 : ipex_attn_decode_counter_ints(B, Hkv, G, Sq);
+  // Tickets first: one ticket stands for at least 16 * 2 * (D + 2) floats of partials, so a launch that is over
+  // the ticket limit is over the float limit as well, and the more specific code is the useful one.
   if (need_c > kMaxCounters) return IPEX_NOALLOC_E_COUNTERS;
+  if (need_f > kMaxFloats) return IPEX_NOALLOC_E_SCRATCH;
   unsigned char* base = nullptr;
   int rc = scratch_for_current_device(&base);
   if (rc != 0) return rc;
@@ -95,8 +99,10 @@ IPEX_API int ipex_attn_decode_noalloc(const void* q, const void* knew, const voi
   // Tickets must be zero when the kernel starts.  A completed launch leaves them zero, but the array is shared with
   // every other caller on the device, so clear the part this launch uses on the caller's stream instead of relying
   // on what an earlier call left behind.
-  cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)need_c * sizeof(int), (cudaStream_t)stream);
-  if (e != cudaSuccess) return (int)e;
+  if (need_c > 0) {
+    cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)need_c * sizeof(int), (cudaStream_t)stream);
+    if (e != cudaSuccess) return (int)e;
+  }
   return ipex_attn_decode(q, knew, vnew, kcache, vcache, out, past_len, past_scalar, cosp, sinp, partials, counters,
                           strides, B, Sq, Hq, Hkv, D, nsplit, rope, R, causal, window, scale, softcap, fp8_kv, dtype,
                           pdl, stream);

@@ -15,7 +15,9 @@
 // Limits (fixed at build time, also returned by the two *_max_* functions):
 //   partials : ipex_attn_decode_scratch_floats(...) <= 2 * 1024 * 1024 floats (8 MiB)
 //   tickets  : ipex_attn_decode_counter_ints(...)   <= 4096 ints
-// A launch that needs more is refused with IPEX_NOALLOC_E_SCRATCH / IPEX_NOALLOC_E_COUNTERS and nothing is launched.
+// A launch that needs more is refused with IPEX_NOALLOC_E_COUNTERS (checked first) or IPEX_NOALLOC_E_SCRATCH and
+// nothing is launched.  A single-split launch (nsplit == 1) writes its result directly, uses neither area and is
+// therefore never refused for size.
 //
 // Set-up: the first call on each device looks up the device address of the array (cudaGetSymbolAddress with that
 // device current).  Make that first call (or call ipex_attn_decode_noalloc_setup()) during start-up, before any

@@ -461,11 +461,20 @@ def pick_nsplit(B: int, Hkv: int, kv_len: int, n_sm: int = 148, rows: int = 1) -
     return int(max(1, min(by_len, 128)))
 
 
+_attn_ws_retired = []
+
+
 def attn_workspace(device, floats: int, ints: int):
-    """Per-device scratch of the split-KV kernel (grown on demand, tickets zeroed once)."""
+    """Per-device scratch of the split-KV kernel (grown on demand, tickets zeroed once).
+
+    A captured CUDA graph bakes in the addresses it was given, so a workspace that has been handed out is never
+    returned to the allocator: when a larger request arrives the old pair is parked in ``_attn_ws_retired`` and
+    stays valid for every graph that references it."""
     key = str(device)
     ws = _attn_ws.get(key)
     if ws is None or ws[0].numel() < floats or ws[1].numel() < ints:
+        if ws is not None:
+            _attn_ws_retired.append(ws)
         ws = (torch.empty(max(floats, 1 << 16), dtype=torch.float32, device=device),
               torch.zeros(max(ints, 4096), dtype=torch.int32, device=device))
         _attn_ws[key] = ws

@@ -123,12 +123,22 @@ class LowBitLinear(nn.Linear):
             data = state_dict[key]
             w = self.weight
             shape = w._shape if w._shape is not None else torch.Size(self.weight_shape)
+            from ..quant.params import packed_nbytes
+            want = packed_nbytes(int(shape[0]) * int(shape[1]), w.qtype)
+            got = data.numel() * data.element_size()
+            if got != want:   # a truncated or foreign tensor must fail at load time, not at the first forward
+                error_msgs.append(f"size mismatch for {key}: packed {qt.qtype_name(w.qtype)} weight of shape "
+                                  f"{tuple(shape)} needs {want} bytes, the checkpoint holds {got}")
+                return
             self._parameters["weight"] = FP4Params(data.detach(), requires_grad=False, quantized=True,
                                                    _shape=torch.Size(shape), qtype=w.qtype, layout="canonical")
             state_dict = {k: v for k, v in state_dict.items() if k != key}
-        super()._load_from_state_dict(state_dict, prefix, local_metadata, False, missing_keys, unexpected_keys,
+        # `strict` is forwarded as given: Module.load_state_dict passes True at this level even for a non-strict
+        # load, and that is what fills missing_keys, so a packed weight or bias that is absent from the checkpoint
+        # is reported instead of leaving an empty parameter behind.
+        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys,
                                       error_msgs)
-        if found and key in missing_keys:     # a packed weight that is absent from the checkpoint stays "missing"
+        if found and key in missing_keys:     # the packed weight was installed above from the original dict
             missing_keys.remove(key)
 
     def forward(self, x: torch.Tensor):

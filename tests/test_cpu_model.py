@@ -235,3 +235,26 @@ def test_env_flags(monkeypatch):
     assert cfg.quantize_kv_cache_flag() is None
     monkeypatch.setenv("IPEX_LLM_LOW_MEM", "1")
     assert cfg.low_mem()
+
+
+@pytest.mark.parametrize("with_keys_file", [True, False])
+@pytest.mark.parametrize("victim", ["model.layers.1.self_attn.o_proj.weight", "truncate"])
+def test_load_low_bit_rejects_absent_or_truncated_tensor(int4_model, tmp_path, with_keys_file, victim):
+    """A packed weight that is missing from the checkpoint, or shorter than its shape needs, fails at load time
+    whether or not load_keys.json is there to list it (reference model.py:593-739 errors at load as well)."""
+    from ipex_llm.transformers import AutoModelForCausalLM
+    d = str(tmp_path / "ckpt")
+    int4_model.save_low_bit(d)
+    f = os.path.join(d, "pytorch_model.bin")
+    sd = torch.load(f, map_location="cpu", weights_only=True)
+    if victim == "truncate":
+        k = "model.layers.0.mlp.gate_proj.weight"
+        sd[k] = sd[k][: sd[k].numel() // 2].clone()
+    else:
+        assert victim in sd
+        del sd[victim]
+    torch.save(sd, f)
+    if not with_keys_file:
+        os.remove(os.path.join(d, "load_keys.json"))
+    with pytest.raises(RuntimeError):
+        AutoModelForCausalLM.load_low_bit(d)

@@ -123,10 +123,25 @@ def test_noalloc_rejects_oversized_requests():
                                       B, Sq, Hq, Hkv, D, nsplit, 0, 0, 1, 0, 1.0, 0.0, 0, 0, 0, current_stream())
     assert rc == -1
     assert b"exceed" in lib.ipex_attn_decode_noalloc_strerror(rc)
-    # too many tickets: batch x kv heads beyond 4096, one split so the partials would still fit
+    # too many tickets: batch x kv heads beyond 4096 with two splits.  The ticket limit is checked first, so the
+    # code is the ticket one although the partials of such a launch do not fit either.
     B2 = 128
     assert lib.ipex_attn_decode_counter_ints(B2, 64, 1, 1) > max_c
     rc = lib.ipex_attn_decode_noalloc(ptr(q), None, None, ptr(k), ptr(k), ptr(out), None, 64, None, None, strides,
-                                      B2, 1, 64, 64, 64, 1, 0, 0, 1, 0, 1.0, 0.0, 0, 0, 0, current_stream())
-    assert rc in (-1, -2)
+                                      B2, 1, 64, 64, 64, 2, 0, 0, 1, 0, 1.0, 0.0, 0, 0, 0, current_stream())
+    assert rc == -2
+    assert b"tickets" in lib.ipex_attn_decode_noalloc_strerror(rc)
     torch.cuda.synchronize()
+
+
+def test_noalloc_single_split_needs_no_work_buffer():
+    """One split writes straight to the output: the array is not used, so a batch whose split partials would be
+    far over the limit is accepted and matches the regular entry point."""
+    lib = _lib()
+    torch.cuda.set_device(0)
+    B, Hq, Hkv, Sq, Skv, D = 32, 32, 32, 1, 96, 128
+    assert lib.ipex_attn_decode_scratch_floats(B, Hkv, 1, Sq, D, 1) > lib.ipex_attn_decode_noalloc_max_floats()
+    q, k, v, kf, vf = _case(B, Hq, Hkv, Sq, Skv, D, False, torch.float16, seed=7)
+    out_a, out_b = _run_both(lib, q, k, v, 1, D ** -0.5)
+    assert torch.isfinite(out_b.float()).all()
+    assert torch.equal(out_a, out_b) or (out_a.float() - out_b.float()).abs().max().item() < 2e-3
