@@ -170,6 +170,7 @@ class DecoderEngine:
         self._graphs = {}
         self._lib = cuda_lib()
         self._nsplit = None
+        self._mega = None          # whole-step kernel launcher, created on first use (False = not applicable)
 
     # ------------------------------------------------------------------------------------------------
     def new_cache(self, batch: int):
@@ -239,9 +240,22 @@ class DecoderEngine:
                                  residual=residual[s:e] if residual is not None else None, act=act,
                                  pdl=self.use_pdl, wf=w.wf)
 
+    def mega_step(self, B: int):
+        """The whole-step kernel launcher when the model and batch fit it (see engine/mega.py), else None."""
+        if self._mega is None:
+            from .mega import MegaStep
+            why = MegaStep.supported(self)
+            self._mega = MegaStep(self) if why is None else False
+            self.mega_reason = why
+        if self._mega is False or B > self._mega.max_batch:
+            return None
+        return self._mega
+
     @property
     def kernel_launches_per_step(self) -> int:
         n = len(self.layers)
+        if self.mega_step(getattr(self, "batch", 1) or 1) is not None:
+            return 1                          # embedding ... arg-max in one persistent kernel
         if self._use_chain(getattr(self, "batch", 1) or 1):
             return 1 + 1 + 2 * n + 1          # embedding, first qkv, (attention + chained GEMVs) per layer, argmax
         if self.layers[0].o.tp is not None:
@@ -365,6 +379,10 @@ class DecoderEngine:
 
     def _step_kernels(self, B: int):
         """Issue one decode step for ``B`` sequences on the current stream: tokens[:B] -> tokens[:B]."""
+        mega = self.mega_step(B)
+        if mega is not None:
+            mega.step(B)                      # embedding -> layers -> lm_head -> arg-max -> past_len + 1
+            return
         lib = self._lib
         dtc = api.dtype_code(self.dtype)
         pdl = int(self.use_pdl)

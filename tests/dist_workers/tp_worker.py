@@ -4,7 +4,8 @@ Checks, on every rank:
   1. (cuda) the peer-memory all-reduce against ``dist.all_reduce``;
   2. (cuda) the row-parallel GEMV fused with its all-reduce against the unsharded matmul;
   3. ``auto_tp`` + conversion of a tiny Llama: logits equal to the single-process low-bit model of the same
-     checkpoint, identical on all ranks; (cuda) greedy decode through the graph engine agrees across ranks.
+     checkpoint, identical on all ranks; (cuda) greedy decode through the graph engine agrees across ranks;
+  4. (cuda) the whole-step decode kernel with the all-reduce inside against the per-kernel path.
 Exit code 0 = all passed.
 """
 import argparse
@@ -175,6 +176,60 @@ def main():
         assert getattr(shard, "_ipex_engine", None) is not None
         from ipex_llm_b200.ops import cuda_ops
         cuda_ops.check_error_flag(dev)
+        # 4. whole-step decode kernel with the all-reduce inside (fp8 weights, grouped-query heads): logits and tokens
+        #    against the per-kernel path of the same sharded model, identical on every rank
+        from transformers import LlamaConfig
+        from ipex_llm_b200.engine import get_engine
+        from ipex_llm_b200.engine.mega import MegaStep
+        for low_bit, dt in (("fp8_e4m3", torch.bfloat16), ("sym_int4", torch.float16)):
+            cfg = LlamaConfig(hidden_size=1024, intermediate_size=2816, num_hidden_layers=3, num_attention_heads=16,
+                              num_key_value_heads=2, vocab_size=32000, max_position_embeddings=1024,
+                              tie_word_embeddings=False)
+            m = AutoModelForCausalLM.from_config(cfg, load_in_low_bit=low_bit, device=str(dev), torch_dtype=dt,
+                                                 seed=0, tp_group=tp)
+            eng = get_engine(m, 2, 512)
+            assert MegaStep.supported(eng) is None, MegaStep.supported(eng)
+            g = torch.Generator(device="cpu").manual_seed(5)
+            pids = torch.randint(0, 32000, (2, 90), generator=g).to(dev)
+            recs = {}
+            for mega in (False, True):
+                lg = eng.prefill(pids)
+                eng.tokens[:2] = lg.argmax(-1)
+                eng._mega = None if mega else False
+                eng._graphs = {}
+                rec = []
+                for _ in range(4):
+                    eng.decode_step(2, use_graph=False)
+                    rec.append((eng.logits[:2].float().clone(), eng.tokens[:2].clone()))
+                torch.cuda.synchronize()
+                cuda_ops.check_error_flag(dev)
+                recs[mega] = rec
+            assert eng._mega not in (None, False)
+            l0, l1 = recs[False][0][0], recs[True][0][0]
+            cos = torch.nn.functional.cosine_similarity(l0.flatten(), l1.flatten(), dim=0).item()
+            assert cos > 0.999, (low_bit, cos)
+            toks = torch.stack([t for _, t in recs[True]])
+            allt = [torch.empty_like(toks) for _ in range(world)]
+            dist.all_gather(allt, toks)
+            for t in allt:
+                assert torch.equal(t, allt[0]), "ranks chose different tokens in the fused step"
+            lgs = recs[True][-1][0].contiguous()
+            alll = [torch.empty_like(lgs) for _ in range(world)]
+            dist.all_gather(alll, lgs)
+            for t in alll:
+                # replicated projections are summed in a timing-dependent order on each rank: equal up to rounding
+                assert torch.allclose(t, alll[0], atol=0.06 if dt == torch.bfloat16 else 0.01), \
+                    "ranks disagree on the fused step's logits"
+            # graph replay of the fused step
+            lg = eng.prefill(pids)
+            eng.tokens[:2] = lg.argmax(-1)
+            for i in range(4):
+                eng.decode_step(2, use_graph=True)
+                assert torch.equal(eng.tokens[:2], recs[True][i][1]), (low_bit, i)
+            torch.cuda.synchronize()
+            cuda_ops.check_error_flag(dev)
+            if rank == 0:
+                print(f"fused step, tensor parallel {world} ranks, {low_bit}: cos {cos:.6f}", flush=True)
     dist.barrier()
     dist.destroy_process_group()
     print(f"rank {rank}: ok")
