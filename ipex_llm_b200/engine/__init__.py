@@ -142,7 +142,7 @@ def engine_generate(model, input_ids, generation_config=None, streamer=None, att
         if graph_greedy:
             nxt = eng.tokens[:B]
         else:
-            lg = eng.logits[:B].clone()
+            lg = eng.gather_logits(B).clone()      # a no-op unless the lm_head is vocabulary-parallel
             if rep_pen and rep_pen != 1.0:
                 cuda_ops.repetition_penalty_inplace(lg, out[:, :S + n_gen], rep_pen)
             nxt = _sample(lg, do_sample, temperature, top_k, top_p)

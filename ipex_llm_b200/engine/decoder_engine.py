@@ -123,6 +123,11 @@ class DecoderEngine:
             self.embed = self.embed.to(dt)
         self.final_norm = base.norm.weight.data.to(dt)
         self.lm_head = _W.from_module(model.lm_head, dt)
+        # vocabulary-parallel lm_head: this rank scores rows [vocab_offset, vocab_offset + lm_head.N) of the vocabulary
+        self.lm_gather = getattr(model.lm_head, "tp_gather", None)
+        if self.lm_gather is not None and getattr(self.lm_gather, "world_size", 1) <= 1:
+            self.lm_gather = None
+        self.vocab_offset = self.lm_gather.rank * self.lm_head.N if self.lm_gather is not None else 0
         self.layers: List[_Layer] = []
         for blk in base.layers:
             L = _Layer()
@@ -240,6 +245,25 @@ class DecoderEngine:
                                  residual=residual[s:e] if residual is not None else None, act=act,
                                  pdl=self.use_pdl, wf=w.wf)
 
+    def _lm_head(self, x, B: int):
+        """Final norm + lm_head for ``B`` rows into ``logits[:B]`` (the full vocabulary on every rank)."""
+        if self.lm_gather is None:
+            self._gemv(self.lm_head, x, self.logits[:B], norm_w=self.final_norm)
+            return
+        off, n = self.vocab_offset, self.lm_head.N
+        self._gemv(self.lm_head, x, self.logits[:B, off:off + n], norm_w=self.final_norm)
+        self.gather_logits(B)
+
+    def gather_logits(self, B: int):
+        """Vocabulary-parallel lm_head: every rank holds its slice of ``logits[:B]``; exchange the slices (a library
+        all-gather, issued outside graph capture)."""
+        if self.lm_gather is None:
+            return self.logits[:B]
+        off, n = self.vocab_offset, self.lm_head.N
+        full = self.lm_gather.all_gather_last_dim(self.logits[:B, off:off + n].contiguous())
+        self.logits[:B].copy_(full)
+        return self.logits[:B]
+
     def mega_step(self, B: int):
         """The whole-step kernel launcher when the model and batch fit it (see engine/mega.py), else None."""
         if self._mega is None:
@@ -327,7 +351,10 @@ class DecoderEngine:
             self._vproj(L.o, self.attn_buf[:S], h1, residual=h0)
             self._vproj(L.gate_up, h1, self.act_buf[:S], norm_w=L.ln2, act=1)
             self._vproj(L.down, self.act_buf[:S], h0, residual=h1)
-        self._vproj(self.lm_head, h0, self.logits[:S], norm_w=self.final_norm)
+        if self.lm_gather is None:
+            self._vproj(self.lm_head, h0, self.logits[:S], norm_w=self.final_norm)
+        else:
+            self._lm_head(h0, S)
         rc = lib.ipex_argmax(ptr(self.logits), ptr(self.vout), S, self.vocab, self.logits.stride(0), dtc, pdl,
                              current_stream())
         api.check(rc, "argmax")
@@ -411,7 +438,7 @@ class DecoderEngine:
                 self._gemv(L.o, self.attn_buf[:B], h1, residual=h0)
                 self._gemv(L.gate_up, h1, self.act_buf[:B], norm_w=L.ln2, act=1)
                 self._gemv(L.down, self.act_buf[:B], h0, residual=h1)
-            self._gemv(self.lm_head, h0, self.logits[:B], norm_w=self.final_norm)
+            self._lm_head(h0, B)
         rc = lib.ipex_argmax(ptr(self.logits), ptr(self.tokens), B, self.vocab, self.logits.stride(0), dtc, pdl,
                              current_stream())
         api.check(rc, "argmax")
@@ -421,6 +448,8 @@ class DecoderEngine:
         """One token for every sequence.  The step is captured once per (batch, cache) and replayed."""
         if self._nsplit is None:
             self._nsplit = cuda_ops.pick_nsplit(B, self.n_kv, self.max_len, rows=self.n_heads // self.n_kv)
+        if self.lm_gather is not None and self.mega_step(B) is None:
+            use_graph = False      # the logits exchange of the per-kernel path is a library collective: not captured
         if not use_graph or os.environ.get("IPEX_LLM_ENGINE_GRAPH", "1") == "0":
             self._step_kernels(B)
             return
@@ -542,7 +571,7 @@ class DecoderEngine:
             act = self._gemm(L.gate_up, x, act=1)                                        # [T, I]
             h = self._gemm(L.down, act, residual=h1)
         last = h.view(B, S, H)[:, -1].contiguous()
-        self._gemv(self.lm_head, last, self.logits[:B], norm_w=self.final_norm)
+        self._lm_head(last, B)
         self.past_len[:B] = S
         return self.logits[:B].clone()
 

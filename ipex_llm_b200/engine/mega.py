@@ -117,7 +117,9 @@ class MegaStep:
             if (L.o.tp is None) != (L.down.tp is None):
                 return "inconsistent tensor-parallel layers"
         if eng.lm_head.bias is not None or eng.lm_head.tp is not None:
-            return "lm_head bias / sharding"
+            return "lm_head bias / row sharding"
+        if eng.lm_head.N % 16 != 0:
+            return "lm_head rows"
         return None
 
     def __init__(self, eng):
@@ -207,8 +209,9 @@ class MegaStep:
         a.cosp, a.sinp = eng.cos.data_ptr(), eng.sin.data_ptr()
         a.tokens, a.past_len = eng.tokens.data_ptr(), eng.past_len.data_ptr()
         a.h0, a.h1 = eng.h[0].data_ptr(), eng.h[1].data_ptr()
+        # a vocabulary-parallel lm_head writes this rank's slice of the full-width logits rows
         a.qkv, a.attn, a.act, a.logits = (eng.qkv_buf.data_ptr(), eng.attn_buf.data_ptr(), eng.act_buf.data_ptr(),
-                                          eng.logits.data_ptr())
+                                          eng.logits.data_ptr() + eng.vocab_offset * eng.logits.element_size())
         a.attn_scratch, a.attn_counters, a.amax = scratch.data_ptr(), self.counters.data_ptr(), self.amax.data_ptr()
         a.barrier, a.abort_word, a.err = self.sync.data_ptr(), self.sync.data_ptr() + 8, self.err.data_ptr()
         a.c_b, a.c_h, a.c_s = k0.stride(0), k0.stride(1), k0.stride(2)
@@ -220,6 +223,7 @@ class MegaStep:
         a.tp_rank, a.tp_world, a.tp_npad, a.vocab_offset = 0, 1, 0, 0
         if self.tp is not None:
             a.tp_rank, a.tp_world, a.tp_npad = self.tp_rank, self.tp_world, self.tp.npad
+            a.vocab_offset = eng.vocab_offset
             a.tp_bufs, a.tp_flags, a.tp_keys, a.tp_kflags = (p.data_ptr() for p in self.tp.ptrs)
             a.tp_epoch = self.tp.epoch.data_ptr()
         if self.prof is not None:

@@ -33,6 +33,15 @@ def reshape_lm_head_input(x: torch.Tensor) -> torch.Tensor:
     return x
 
 
+def _gather_last_dim(t: torch.Tensor, module):
+    """Vocabulary-parallel layers (``tp_gather`` set by the converter) return their slice of the output features;
+    the full tensor is the concatenation over the group."""
+    grp = getattr(module, "tp_gather", None)
+    if grp is None or getattr(grp, "world_size", 1) <= 1:
+        return t
+    return grp.all_gather_last_dim(t)
+
+
 def _all_reduce(t: torch.Tensor, mp_group):
     """Row-parallel output reduction.  ``mp_group`` may be a torch ProcessGroup, an object with an
     ``all_reduce`` method (vLLM GroupCoordinator style) or a ``TPGroup`` of this package."""
@@ -176,7 +185,7 @@ class LowBitLinear(nn.Linear):
             result = _all_reduce(result, self.mp_group)
             if self.bias is not None:
                 result = result + self.bias
-            return result
+            return _gather_last_dim(result, self)
         # CPU
         if not w.quantized:
             w = w.quantize("cpu")
@@ -192,7 +201,7 @@ class LowBitLinear(nn.Linear):
         result = _all_reduce(result, self.mp_group)
         if self.bias is not None:
             result = result + self.bias
-        return result
+        return _gather_last_dim(result, self)
 
     def extra_repr(self):
         return (f"in_features={self.in_len}, out_features={self.out_len}, qtype={qt.qtype_name(self.qtype)}, "
@@ -235,7 +244,7 @@ class FP16Linear(nn.Linear):
         result = _all_reduce(result, self.mp_group)
         if self.bias is not None:
             result = result + self.bias
-        return result.to(x.dtype)
+        return _gather_last_dim(result, self).to(x.dtype)
 
 
 class BF16Linear(FP16Linear):

@@ -6,14 +6,20 @@ keeps the ``mp_group`` on the row-parallel linears to all-reduce their outputs
 python/llm/src/ipex_llm/transformers/convert.py:215-226, low_bit_linear.py:675-682).  DeepSpeed is not a
 dependency here: ``auto_tp`` does the injection itself —
 
-* column-parallel (output rows split): q/k/v (by heads, GQA aware), gate/up, fused ``qkv_proj`` / ``gate_up_proj``;
+* column-parallel (output rows split): q/k/v (by heads, GQA aware), gate/up;
 * row-parallel (input columns split, output all-reduced): ``o_proj``, ``down_proj``;
-* everything else (norms, embeddings, lm_head) replicated.
+* ``lm_head`` vocabulary-parallel (rows split, logits gathered; the reference does the same under vLLM,
+  python/llm/src/ipex_llm/vllm/xpu/model_convert.py:52-54) unless ``IPEX_LLM_TP_VOCAB_PARALLEL=0`` or the vocabulary
+  does not split into multiples of 16 rows;
+* everything else (norms, embeddings) replicated.  Models that keep q/k/v or gate/up fused in one ``nn.Linear``
+  (phi3-style ``qkv_proj`` / ``gate_up_proj``) are refused: their rows interleave heads and would need a re-layout.
 
 ``TPGroup.all_reduce`` uses the fused NVLink kernels of ``parallel.symm_mem`` on CUDA and falls back to the
 process group's all-reduce elsewhere (gloo ranks in the CPU tests).
 """
 from __future__ import annotations
+
+import os
 
 import torch
 import torch.distributed as dist
@@ -155,6 +161,10 @@ def auto_tp(model: nn.Module, group: TPGroup = None, rank=None, world_size=None)
         for name, child in list(mod.named_children()):
             if not isinstance(child, nn.Linear) or isinstance(child, (ColumnParallelLinear, RowParallelLinear)):
                 continue
+            if name in ("qkv_proj", "gate_up_proj", "query_key_value", "dense_h_to_4h"):
+                raise NotImplementedError(
+                    f"auto_tp: '{name}' holds several projections in one matrix; tensor parallelism needs them "
+                    "split (q/k/v, gate/up) before sharding")
             if name in COLUMN_NAMES:
                 unit = head_dim if name in ("q_proj", "k_proj", "v_proj") else 1
                 mod._modules[name] = _column(child, rank, world, group, unit)
@@ -174,6 +184,13 @@ def auto_tp(model: nn.Module, group: TPGroup = None, rank=None, world_size=None)
             mod.down_proj = nn.Parameter(dn.data[:, :, rank * per:(rank + 1) * per].contiguous(), requires_grad=False)
             mod.intermediate_dim = per
             mod._tp_group = group
+    head = getattr(model, "lm_head", None)
+    if isinstance(head, nn.Linear) and not isinstance(head, ColumnParallelLinear) and \
+            os.environ.get("IPEX_LLM_TP_VOCAB_PARALLEL", "1") != "0" and \
+            not getattr(cfg, "tie_word_embeddings", False) and head.out_features % (16 * world) == 0:
+        new = _column(head, rank, world, group)
+        new.gather_output = True          # the converted module gathers its logits over the group
+        model.lm_head = new
     model._tp_group = group
     model.config.tp_size = world
     return model

@@ -234,6 +234,8 @@ def _replace_with_low_bit_linear(model, qtype, modules_to_not_convert=None, conv
                 if str(device) not in ("cpu", "meta"):
                     new_linear = new_linear.to(device)
             new_linear.requires_grad_(False)
+            if getattr(module, "gather_output", False):
+                new_linear.tp_gather = getattr(module, "tp_group", None)     # vocabulary-parallel lm_head
             model._modules[name] = new_linear
             has_been_replaced = True
             continue

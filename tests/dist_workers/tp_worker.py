@@ -200,7 +200,7 @@ def main():
                 rec = []
                 for _ in range(4):
                     eng.decode_step(2, use_graph=False)
-                    rec.append((eng.logits[:2].float().clone(), eng.tokens[:2].clone()))
+                    rec.append((eng.gather_logits(2).float().clone(), eng.tokens[:2].clone()))
                 torch.cuda.synchronize()
                 cuda_ops.check_error_flag(dev)
                 recs[mega] = rec
