@@ -1,7 +1,13 @@
 #!/usr/bin/env python
 """Headline benchmark: decode latency / throughput of low-bit Llama models on B200.
 
-    python bench.py --gpus N --steps K --warmup W [--model llama2-7b|llama3-70b] [--batch B] [--impl ours|reference]
+    python bench.py --gpus N --steps K --warmup W [--config 7b|70b-tp|7b-spec|mixtral-pp|qlora-dp] [--batch B]
+                    [--model llama2-7b|llama3-70b] [--impl ours|reference|constructed]
+
+``--config`` picks one of the benchmark set-ups (default: ``7b`` on one GPU, ``70b-tp`` on several):
+``7b`` / ``70b-tp`` decode latency (below); ``7b-spec`` self-speculative decoding (fp16 target + int4 draft);
+``mixtral-pp`` Mixtral-8x7B sym_int4 pipeline-parallel generation, batch 8, 1024 in / 128 out; ``qlora-dp`` QLoRA
+fine-tuning of Llama-2-13B nf4, data parallel, sequence 512, micro-batch 4 per GPU.
 
 One "step" is one decode step (one new token for every sequence of the batch) after a prompt pass of
 ``--prompt`` random tokens.  ``ms_per_step`` is therefore the reference harness's "2+ avg latency (ms/token)"
@@ -10,13 +16,16 @@ and ``value`` the whole-job decode throughput in tokens/s.
 * N = 1, default model: Llama-2-7B architecture, random N(0, 0.02) weights, sym_int4 (group 64, fp16 scales),
   fp16 activations, fp8 e5m2 KV cache, batch 1, 1024 prompt tokens.
 * N > 1: Llama-3-70B architecture in block-scaled fp8_e4m3 (128-blocks, fp32 scales), bf16 activations,
-  tensor parallel over the N GPUs (row-parallel GEMVs write into symmetric staging memory and one peer-memory
-  kernel does all-reduce + bias + residual; strong scaling: the same model and batch on more GPUs).
+  tensor parallel over the N GPUs (one persistent kernel per token and rank: the row-parallel projections push
+  their partial tiles into the peers' symmetric memory and reduce them in the same kernel, the lm_head is
+  vocabulary-parallel; strong scaling: the same model and batch on more GPUs).
   ``--model llama3-70b`` runs the same model on one GPU.
 
 Timing: W untimed steps, then K steps between CUDA events on the launching stream, barrier + synchronize on
-both sides, max over ranks.  Weights (3.6 GB and up) are far larger than the 126 MB L2, so every step streams
-them from HBM again.  SM clocks and throttle reasons are sampled with nvidia-smi during the timed region.
+both sides, max over ranks.  When K steps last less than a second, further blocks of K steps are timed the same way
+until a second has passed; ``ms_per_step`` is the mean over all of them and ``steps_timed`` says how many ran
+(``steps`` stays the K that was asked for).  Weights (3.6 GB and up) are far larger than the 126 MB L2, so every
+step streams them from HBM again.  SM clocks and throttle reasons are sampled with nvidia-smi during the timed region.
 The ``e2e`` figure drives the same decode through the public ``model.decode_step`` API with the step's input
 token copied from pinned host memory and the sampled token read back to the host every step.
 """
@@ -45,6 +54,12 @@ MODELS = {
                  num_key_value_heads=4, vocab_size=32000, rms_norm_eps=1e-6, rope_theta=10000.0,
                  max_position_embeddings=2048, low_bit="sym_int4", dtype="float16", prompt=64, batch=1),
 }
+
+
+# Decode throughput of the cuBLAS + NCCL stand-in recorded in BASELINE.md (tokens/s at batch 1), by (model, GPUs):
+# the denominator of ``vs_baseline``.  Set-ups without a recorded number report null.
+BASELINE_TOK_S = {("llama2-7b", 1): 171.0, ("llama3-70b", 2): 23.0, ("llama3-70b", 8): 22.1}
+BASELINE_SAMPLES_S = {("llama2-13b", 1): 10.17}
 
 
 def reference_arm(args):
@@ -107,6 +122,49 @@ class ClockSampler:
         return out
 
 
+def other_config(args):
+    """The set-ups that are not a decode-latency run: their own drivers measure them (CUDA events or the generate
+    loop's per-token timers, max over ranks) and this wrapper prints the result in the common JSON shape."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    if args.config == "mixtral-pp":
+        from ipex_llm_b200.parallel import bench_pp
+        argv = ["--model", args.model if args.model != "auto" else "mixtral-8x7b", "--batch", str(args.batch or 8),
+                "--prompt", str(args.prompt or 1024), "--new-tokens", str(max(8, args.steps))]
+        res = bench_pp.run(argv)
+        extra = {"metric": "pipeline-parallel decode tokens/s (first_token_ms = prompt pass)", "scaling": "strong",
+                 "dtype": "fp16", "parallelism": f"pp{world}"}
+    elif args.config == "qlora-dp":
+        from ipex_llm_b200.train import bench_qlora
+        argv = ["--model", args.model if args.model != "auto" else "llama2-13b", "--steps", str(args.steps),
+                "--warmup", str(args.warmup)]
+        res = bench_qlora.run(argv)
+        extra = {"metric": "QLoRA finetune samples/s", "scaling": "weak", "dtype": "bf16", "parallelism": f"dp{world}"}
+    else:
+        from ipex_llm_b200.utils import bench_speculative
+        res = bench_speculative.run(["--new-tokens", str(max(32, args.steps))])
+        extra = {"metric": "self-speculative decode tokens/s", "scaling": "strong", "dtype": "fp16",
+                 "parallelism": "single"}
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0 and res is not None:
+        base = BASELINE_SAMPLES_S.get((res.get("model"), world)) if args.config == "qlora-dp" else None
+        line = {"metric": extra["metric"], "value": res.get("value"), "unit": res.get("unit"), "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": res.get("ms_per_step"),
+                "higher_is_better": True, "scaling": extra["scaling"],
+                "vs_baseline": round(res["value"] / base, 3) if base and res.get("value") else None,
+                "dtype": extra["dtype"], "impl": "ours",
+                "data": "synthetic random token ids, random-init weights of the named architecture",
+                "config": {"model": res.get("model"), "parallelism": extra["parallelism"],
+                           **{k: v for k, v in res.items() if k not in ("metric", "value", "unit", "ms_per_step")}},
+                "clocks": clocks}
+        print(json.dumps(line))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -115,6 +173,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "constructed"],
                     help="reference: the unmodified reference (unavailable offline); constructed: its semantics on "
                          "stock cuBLAS + NCCL (baseline/constructed.py)")
+    ap.add_argument("--config", default="auto", choices=["auto", "7b", "70b-tp", "7b-spec", "mixtral-pp", "qlora-dp"])
     ap.add_argument("--model", default="auto")
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--prompt", type=int, default=None)
@@ -135,6 +194,12 @@ def main():
         runpy.run_path(sys.argv[0], run_name="__main__")
         return 0
     args.warmup = max(args.warmup, 3)
+    if args.config in ("mixtral-pp", "qlora-dp", "7b-spec"):
+        return other_config(args)
+    if args.config == "7b" and args.model == "auto":
+        args.model = "llama2-7b"
+    if args.config == "70b-tp" and args.model == "auto":
+        args.model = "llama3-70b"
 
     import torch
     import torch.distributed as dist
@@ -185,7 +250,9 @@ def main():
     dev = torch.device("cuda", local_rank)
     g = torch.Generator(device="cpu").manual_seed(1234)
     ids_host = torch.randint(0, cfg.vocab_size, (batch, prompt), generator=g)
-    total_len = prompt + args.warmup * 2 + args.steps * 2 + 16
+    # room for the warm-ups, the timed blocks (padded to a second, at most 4096 steps) and the end-to-end loop
+    max_steps = max(args.steps, min(4096, 1536 // max(1, batch)))
+    total_len = prompt + args.warmup * 2 + max_steps + args.steps + 48
     eng = get_engine(model, batch, total_len)
 
     # ---- prompt pass (1st token), timed on the device ----
@@ -216,13 +283,23 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        eng.decode_step(batch)
-    e1.record()
-    barrier()
-    dev_ms = e0.elapsed_time(e1)
+    dev_ms, steps_timed = 0.0, 0
+    while True:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            eng.decode_step(batch)
+        e1.record()
+        barrier()
+        block_ms = e0.elapsed_time(e1)
+        if world > 1:       # every rank must take the same decision: use the slowest rank's time
+            tb = torch.tensor([block_ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(tb, op=dist.ReduceOp.MAX)
+            block_ms = float(tb[0])
+        dev_ms += block_ms
+        steps_timed += args.steps
+        if dev_ms >= 1000.0 or steps_timed + args.steps > max_steps:
+            break
 
     # ---- end to end through the public per-step API: pinned host token in, sampled token out, every step ----
     e2e = None
@@ -241,21 +318,31 @@ def main():
         e2e = e2e_s
     clocks = sampler.stop() if rank == 0 else None
 
+    # ---- the reference harness's own metric: per-token cost of model.generate (first token / mean of the rest) ----
+    gen_stats = None
+    if not args.no_e2e:
+        n_new = min(32, max(4, args.steps))
+        model.generate(ids, max_new_tokens=n_new, do_sample=False)
+        gen_stats = {"first_cost_ms": round(1e3 * float(model.first_token_time), 3),
+                     "rest_cost_mean_ms": round(1e3 * float(model.rest_cost_mean), 4), "new_tokens": n_new}
+
     if world > 1:
-        t = torch.tensor([dev_ms, e2e if e2e is not None else 0.0, first_ms], device=dev, dtype=torch.float64)
+        t = torch.tensor([e2e if e2e is not None else 0.0, first_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_ms, e2e_m, first_ms = t.tolist()
+        e2e_m, first_ms = t.tolist()
         e2e = e2e_m if e2e is not None else None
 
     if rank == 0:
-        ms_per_step = dev_ms / args.steps
+        ms_per_step = dev_ms / steps_timed
         value = batch * 1000.0 / ms_per_step
+        base = BASELINE_TOK_S.get((name, n_gpus)) if batch == 1 else None
         line = {
             "metric": "decode tokens/s (2nd+ token latency in ms_per_step): Llama-2-7B int4 on 1 GPU, "
                       "Llama-3-70B fp8 tensor-parallel on N GPUs",
             "value": round(value, 3), "unit": "tokens/s", "n_gpus": n_gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "fp16" if dtype == torch.float16 else "bf16",
+            "warmup": args.warmup, "steps_timed": steps_timed, "ms_per_step": round(ms_per_step, 5),
+            "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": round(value / base, 3) if base else None, "dtype": "fp16" if dtype == torch.float16 else "bf16",
             "data": "synthetic random token ids, random-init N(0,0.02) weights of the named architecture",
             "impl": "ours",
             "config": {"model": name, "low_bit": low_bit, "global_batch": batch, "seq_len": prompt,
@@ -263,11 +350,13 @@ def main():
                        "parallelism": f"tp{n_gpus}" if n_gpus > 1 else "single",
                        "l2_policy": "inputs larger than L2: every step streams the full packed weights "
                                     f"({sum(p.numel() * p.element_size() for p in model.parameters()) / 1e9:.2f} GB)",
-                       "decode_engine": "cuda-graph + programmatic dependent launch"},
+                       "decode_engine": "one persistent kernel per token (cuda-graph replay)"
+                       if eng.kernel_launches_per_step == 1 else "cuda-graph + programmatic dependent launch"},
             "first_token_ms": round(first_ms, 3),
             "first_token_cold_ms": round(first_cold_ms, 3),
             "model_build_s": round(load_s, 2),
-            "gpu_launches": int(args.steps * eng.kernel_launches_per_step),
+            "gpu_launches": int(steps_timed * eng.kernel_launches_per_step),
+            "generate": gen_stats,
             "clocks": clocks,
         }
         if e2e is not None:

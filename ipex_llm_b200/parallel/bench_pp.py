@@ -27,7 +27,8 @@ ARCH = {
 }
 
 
-def main(argv=None):
+def run(argv=None):
+    """Run the benchmark; returns the result dictionary on rank 0 (None elsewhere)."""
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="mixtral-8x7b", choices=list(ARCH))
     ap.add_argument("--batch", type=int, default=8)
@@ -52,14 +53,21 @@ def main(argv=None):
     first, rest = model.first_token_time, model.rest_cost_mean
     t = torch.tensor([first, rest], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    res = None
     if rank == 0:
-        print(json.dumps({"metric": "pipeline-parallel decode", "model": a.model, "n_gpus": world, "stages": world,
-                          "batch": a.batch, "prompt": a.prompt, "new_tokens": a.new_tokens, "low_bit": a.low_bit,
-                          "first_token_ms": round(float(t[0]) * 1e3, 2), "ms_per_step": round(float(t[1]) * 1e3, 3),
-                          "value": round(a.batch / float(t[1]), 2), "unit": "tokens/s",
-                          "out_shape": list(out.shape)}))
+        res = {"metric": "pipeline-parallel decode", "model": a.model, "n_gpus": world, "stages": world,
+               "batch": a.batch, "prompt": a.prompt, "new_tokens": a.new_tokens, "low_bit": a.low_bit,
+               "first_token_ms": round(float(t[0]) * 1e3, 2), "ms_per_step": round(float(t[1]) * 1e3, 3),
+               "value": round(a.batch / float(t[1]), 2), "unit": "tokens/s", "out_shape": list(out.shape)}
     dist.barrier()
     dist.destroy_process_group()
+    return res
+
+
+def main(argv=None):
+    res = run(argv)
+    if res is not None:
+        print(json.dumps(res))
 
 
 if __name__ == "__main__":

@@ -29,7 +29,8 @@ ARCH = {
 }
 
 
-def main(argv=None):
+def run(argv=None):
+    """Run the benchmark; returns the result dictionary on rank 0 (None elsewhere)."""
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="llama2-13b", choices=list(ARCH))
     ap.add_argument("--steps", type=int, default=8)
@@ -105,9 +106,10 @@ def main(argv=None):
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    res = None
     if rank == 0:
         ms = float(t[0])
-        print(json.dumps({"metric": "QLoRA finetune throughput", "model": a.model, "n_gpus": world,
+        res = ({"metric": "QLoRA finetune throughput", "model": a.model, "n_gpus": world,
                           "value": round(world * a.micro_batch * 1000.0 / ms, 3), "unit": "samples/s",
                           "tokens_per_s": round(world * a.micro_batch * a.seq * 1000.0 / ms, 1),
                           "ms_per_step": round(ms, 3), "steps": a.steps, "warmup": a.warmup, "seq_len": a.seq,
@@ -115,9 +117,16 @@ def main(argv=None):
                           "optimizer": "fused reduce-scatter + AdamW + all-gather kernel" if a.optimizer == "fused"
                           else "NCCL all_reduce + torch.optim.AdamW", "base": "nf4", "compute": "bf16",
                           "gradient_checkpointing": not a.no_checkpointing, "last_loss": round(last, 4),
-                          "h2d_bytes_per_step": a.micro_batch * a.seq * 8, "d2h_bytes_per_step": 4}))
+                          "h2d_bytes_per_step": a.micro_batch * a.seq * 8, "d2h_bytes_per_step": 4})
     if world > 1:
         dist.destroy_process_group()
+    return res
+
+
+def main(argv=None):
+    res = run(argv)
+    if res is not None:
+        print(json.dumps(res))
 
 
 if __name__ == "__main__":

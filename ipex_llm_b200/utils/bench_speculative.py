@@ -35,7 +35,8 @@ def _snap_target_to_draft(target, draft):
             mods[name].weight.data.copy_(deq)
 
 
-def main(argv=None):
+def run(argv=None):
+    """Run the benchmark and return the result dictionary."""
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="llama2-7b", choices=list(ARCH))
     ap.add_argument("--prompt", type=int, default=1024)
@@ -92,7 +93,13 @@ def main(argv=None):
         line["speedup_vs_target_alone"] = round(line["e2e_tokens_per_s"] / line["target_alone_e2e_tokens_per_s"], 3)
     finally:
         model.draft_model = draft
-    print(json.dumps(line))
+    line["value"], line["unit"] = line["e2e_tokens_per_s"], "tokens/s"
+    line["ms_per_step"] = round(1e3 * res["seconds"] / max(1, res["new_tokens"]), 4)
+    return line
+
+
+def main(argv=None):
+    print(json.dumps(run(argv)))
 
 
 if __name__ == "__main__":
