@@ -137,6 +137,13 @@ class FusedLoraAdamW(torch.optim.Optimizer):
         g = self.param_groups[0]
         lr, (b1, b2), eps, wd = g["lr"], g["betas"], g["eps"], g["weight_decay"]
         if self.max_grad_norm and self.max_grad_norm > 0:
+            # Clip by the global norm of the AVERAGED gradient, as DDP + clip_grad_norm_ does.  The fused kernel
+            # reduces and updates in one pass, so the average is formed first (one extra all-reduce, only when
+            # clipping is on); every rank then holds the same clipped gradient and the kernel's own averaging of
+            # the world's copies leaves it unchanged.
+            if self.world > 1:
+                dist.all_reduce(self.flat_grads, group=self.group)
+                self.flat_grads.div_(self.world)
             norm = torch.linalg.vector_norm(self.flat_grads.float())
             self.flat_grads.mul_(torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0).to(self.dtype))
         if self.device.type == "cuda":
@@ -198,11 +205,14 @@ class FusedLoraAdamW(torch.optim.Optimizer):
 
 
 class PagedAdamW(torch.optim.Optimizer):
-    """AdamW whose moments live in pinned host pages and stream through the device chunk by chunk.
+    """AdamW whose moments live in pinned host pages and stream through the device page by page.
 
-    For models whose optimizer state does not fit beside the weights.  Each step walks the parameters in pages of
-    ``page_elems`` values: H2D of the page's moments on a side stream (double buffered), fused update on the device,
-    D2H of the new moments.
+    For models whose optimizer state does not fit beside the weights (the reference leaves this to DeepSpeed's
+    optimizer offload, python/llm/example/GPU/LLM-Finetuning/QLoRA/alpaca-qlora/deepspeed_zero2.json).  A step
+    walks the parameters in pages of at most ``page_elems`` values.  On CUDA the pages are double buffered: a copy
+    stream brings the moments of page i + 1 to the device and takes the new moments of page i - 1 back to the host
+    while the current stream updates page i; events order the two streams per buffer.  On CPU tensors the same
+    arithmetic runs in place.
     """
 
     def __init__(self, params, lr=2e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, page_elems: int = 1 << 22):
@@ -215,31 +225,71 @@ class PagedAdamW(torch.optim.Optimizer):
         for p in plist:
             self._host[p] = (torch.zeros(p.numel(), dtype=torch.float32, pin_memory=pin),
                              torch.zeros(p.numel(), dtype=torch.float32, pin_memory=pin))
+        self._bufs = None
+        self._copy = None
+
+    @staticmethod
+    def _update(flat_p, flat_g, m, v, lo, hi, lr, b1, b2, eps, wd, bc1, bc2):
+        gr = flat_g[lo:hi].float()
+        m.mul_(b1).add_(gr, alpha=1 - b1)
+        v.mul_(b2).addcmul_(gr, gr, value=1 - b2)
+        w = flat_p[lo:hi].float()
+        w.mul_(1 - lr * wd).addcdiv_(m, (v / bc2).sqrt_().add_(eps), value=-lr / bc1)
+        flat_p[lo:hi].copy_(w)
 
     @torch.no_grad()
     def step(self, closure=None):
         loss = closure() if closure is not None else None
         self._step += 1
+        items = []          # (param, lo, hi, hyper-parameters)
         for g in self.param_groups:
             lr, (b1, b2), eps, wd = g["lr"], g["betas"], g["eps"], g["weight_decay"]
             bc1, bc2 = 1 - b1 ** self._step, 1 - b2 ** self._step
             for p in g["params"]:
                 if p.grad is None:
                     continue
+                for lo in range(0, p.numel(), self.page_elems):
+                    items.append((p, lo, min(lo + self.page_elems, p.numel()), (lr, b1, b2, eps, wd, bc1, bc2)))
+        if not items:
+            return loss
+        dev = items[0][0].device
+        if dev.type != "cuda":
+            for p, lo, hi, hp in items:
                 hm, hv = self._host[p]
-                flat_p, flat_g = p.data.view(-1), p.grad.view(-1)
-                for lo in range(0, flat_p.numel(), self.page_elems):
-                    hi = min(lo + self.page_elems, flat_p.numel())
-                    m = hm[lo:hi].to(p.device, non_blocking=True)
-                    v = hv[lo:hi].to(p.device, non_blocking=True)
-                    gr = flat_g[lo:hi].float()
-                    m.mul_(b1).add_(gr, alpha=1 - b1)
-                    v.mul_(b2).addcmul_(gr, gr, value=1 - b2)
-                    w = flat_p[lo:hi].float()
-                    w.mul_(1 - lr * wd).addcdiv_(m, (v / bc2).sqrt_().add_(eps), value=-lr / bc1)
-                    flat_p[lo:hi].copy_(w)
-                    hm[lo:hi].copy_(m, non_blocking=True)
-                    hv[lo:hi].copy_(v, non_blocking=True)
-        if torch.cuda.is_available():
-            torch.cuda.current_stream().synchronize()
+                self._update(p.data.view(-1), p.grad.view(-1), hm[lo:hi], hv[lo:hi], lo, hi, *hp)
+            return loss
+        if self._bufs is None or self._bufs[0][0].device != dev:
+            self._bufs = [tuple(torch.empty(self.page_elems, dtype=torch.float32, device=dev) for _ in range(2))
+                          for _ in range(2)]
+            self._copy = torch.cuda.Stream(device=dev)
+            self._ready = [torch.cuda.Event() for _ in range(2)]
+            self._done = [torch.cuda.Event() for _ in range(2)]
+        cur, cp = torch.cuda.current_stream(dev), self._copy
+        cp.wait_stream(cur)                      # the gradients and the previous step's use of the buffers
+
+        def load(i):
+            p, lo, hi, _ = items[i]
+            hm, hv = self._host[p]
+            m, v = self._bufs[i % 2]
+            with torch.cuda.stream(cp):
+                m[: hi - lo].copy_(hm[lo:hi], non_blocking=True)
+                v[: hi - lo].copy_(hv[lo:hi], non_blocking=True)
+                self._ready[i % 2].record(cp)
+
+        load(0)
+        for i, (p, lo, hi, hp) in enumerate(items):
+            slot = i % 2
+            if i + 1 < len(items):
+                load(i + 1)                      # queued behind the write-back that frees that buffer (same stream)
+            cur.wait_event(self._ready[slot])
+            m, v = self._bufs[slot]
+            self._update(p.data.view(-1), p.grad.view(-1), m[: hi - lo], v[: hi - lo], lo, hi, *hp)
+            self._done[slot].record(cur)
+            hm, hv = self._host[p]
+            with torch.cuda.stream(cp):
+                cp.wait_event(self._done[slot])
+                hm[lo:hi].copy_(m[: hi - lo], non_blocking=True)
+                hv[lo:hi].copy_(v[: hi - lo], non_blocking=True)
+        cur.wait_stream(cp)
+        cp.synchronize()                         # host pages are complete when step() returns
         return loss

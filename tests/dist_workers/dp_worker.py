@@ -32,7 +32,9 @@ def main():
     shapes = [(8, 4096), (4096, 8), (8, 11008), (11008, 8), (3, 5)]
     params = [torch.nn.Parameter((torch.randn(s) * 0.1).to(dtype).to(dev)) for s in shapes]
     ref = [torch.nn.Parameter(p.detach().float().clone()) for p in params]
-    opt = FusedLoraAdamW(params, lr=1e-2, weight_decay=0.05)
+    # clipping by the global norm of the averaged gradient, as torch's clip_grad_norm_ on the reference copy
+    clip = 0.5
+    opt = FusedLoraAdamW(params, lr=1e-2, weight_decay=0.05, max_grad_norm=clip)
     ropt = torch.optim.AdamW(ref, lr=1e-2, weight_decay=0.05)
     for step in range(4):
         for p, r in zip(params, ref):
@@ -45,6 +47,7 @@ def main():
                 gg = torch.Generator().manual_seed(1000 * step + 10 * rr + p.numel() % 7)
                 acc += (torch.randn(p.shape, generator=gg) * 0.5).to(dtype).float()
             r.grad = (acc / world).to(r.device)
+        torch.nn.utils.clip_grad_norm_(ref, clip)
         opt.step()
         ropt.step()
         opt.zero_grad()

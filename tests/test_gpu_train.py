@@ -53,3 +53,25 @@ def test_qlora_forward_backward_gpu():
     grads = [p.grad for n, p in pm.named_parameters() if "lora_B" in n]
     assert len(grads) == 6 and all(g is not None and torch.isfinite(g).all() for g in grads)
     assert any(float(g.abs().sum()) > 0 for g in grads)
+
+
+def test_paged_adamw_double_buffered_matches_torch_adamw():
+    """Moments in pinned host pages, two device buffers, copy stream + events: same numbers as torch.optim.AdamW."""
+    from ipex_llm_b200.parallel.dp import PagedAdamW
+    torch.manual_seed(0)
+    ws = [torch.randn(300, 70, device="cuda"), torch.randn(5000, device="cuda"), torch.randn(8, 64, device="cuda")]
+    a = [torch.nn.Parameter(w.clone()) for w in ws]
+    b = [torch.nn.Parameter(w.clone()) for w in ws]
+    oa = PagedAdamW(a, lr=1e-2, weight_decay=0.01, page_elems=4096)      # several pages per tensor
+    ob = torch.optim.AdamW(b, lr=1e-2, weight_decay=0.01)
+    for step in range(5):
+        for pa, pb in zip(a, b):
+            g = torch.randn_like(pa)
+            pa.grad, pb.grad = g.clone(), g.clone()
+        oa.step()
+        ob.step()
+    torch.cuda.synchronize()
+    for pa, pb in zip(a, b):
+        assert torch.allclose(pa, pb, atol=1e-5, rtol=1e-4)
+    hm, hv = oa._host[a[0]]
+    assert hm.is_pinned() and float(hm.abs().sum()) > 0 and float(hv.sum()) > 0

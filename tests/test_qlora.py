@@ -165,3 +165,21 @@ def test_relora_merge_and_lisa_switching(tmp_path):
         assert act == list(cb.active_layers_indices)
         assert not any(p.requires_grad for l in cb.layers for p in l.parameters() if hasattr(p, "qtype"))
     assert len(seen) >= 1
+
+
+def test_paged_adamw_matches_torch_adamw_cpu():
+    from ipex_llm_b200.parallel.dp import PagedAdamW
+    torch.manual_seed(0)
+    ws = [torch.randn(37, 5), torch.randn(130)]
+    a = [torch.nn.Parameter(w.clone()) for w in ws]
+    b = [torch.nn.Parameter(w.clone()) for w in ws]
+    oa = PagedAdamW(a, lr=1e-2, weight_decay=0.01, page_elems=64)
+    ob = torch.optim.AdamW(b, lr=1e-2, weight_decay=0.01)
+    for step in range(4):
+        for pa, pb in zip(a, b):
+            g = torch.randn_like(pa)
+            pa.grad, pb.grad = g.clone(), g.clone()
+        oa.step()
+        ob.step()
+    for pa, pb in zip(a, b):
+        assert torch.allclose(pa, pb, atol=1e-6, rtol=1e-5)
