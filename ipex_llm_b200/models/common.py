@@ -188,30 +188,32 @@ def repeat_kv(hidden_states: torch.Tensor, n_rep: int) -> torch.Tensor:
 
 def scaled_dot_product_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
                                  mask: torch.Tensor = None, is_causal: bool = False, scale: float = None,
-                                 softcap: float = None, sliding_window: int = None) -> torch.Tensor:
+                                 softcap: float = None, sliding_window: int = None,
+                                 infer_causal: bool = True) -> torch.Tensor:
     """softmax(q k^T * scale + mask) v with GQA handled inside.
 
     ``query`` is ``[B, Hq, Sq, D]``; ``key``/``value`` are ``[B, Hkv, Skv, D]`` in the activation dtype or packed
     e5m2 bytes (uint8).  Routing (reference models/common.py:249-305): short queries against a long cache
     (decode, speculative verification, lookup: Sq <= 32) go to the split-KV decode kernel, which reads fp8 KV
-    directly; everything else goes to the prefill path."""
+    directly; everything else goes to the prefill path.  With ``infer_causal`` (the decoder forwards of this
+    package) a missing mask on a multi-token query means causal; encoders and cross-attention pass False and get
+    exactly ``is_causal``."""
     bsz, n_heads, q_len, head_dim = query.shape
     kv_len = key.shape[2]
     n_kv = key.shape[1]
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
     fp8 = key.dtype == torch.uint8
+    causal = bool(is_causal) or (infer_causal and mask is None and q_len > 1)
 
     if query.is_cuda and not query.requires_grad and query.dtype in (torch.float16, torch.bfloat16):
         from ..ops import cuda_ops
         if q_len <= 32 and cuda_ops.sdpa_decode_supported(head_dim, value.shape[-1]):
-            return cuda_ops.sdpa_decode(query, key, value, mask, scale, softcap, sliding_window,
-                                        causal=is_causal or (mask is None and q_len > 1))
+            return cuda_ops.sdpa_decode(query, key, value, mask, scale, softcap, sliding_window, causal=causal)
         if fp8:
             key = fp8_e5m2_dequantize(key, query.dtype)
             value = fp8_e5m2_dequantize(value, query.dtype)
-        return cuda_ops.sdpa_prefill(query, key, value, mask, scale, softcap, sliding_window,
-                                     causal=is_causal or (mask is None and q_len > 1))
+        return cuda_ops.sdpa_prefill(query, key, value, mask, scale, softcap, sliding_window, causal=causal)
 
     if fp8:
         key = fp8_e5m2_dequantize(key, query.dtype)
@@ -223,8 +225,12 @@ def scaled_dot_product_attention(query: torch.Tensor, key: torch.Tensor, value: 
             mask = mask[..., :kv_len]
             if mask.dtype != torch.bool and mask.dtype != query.dtype:
                 mask = mask.to(query.dtype)
+        if mask is None and causal and q_len != kv_len:
+            # a causal query block at the end of a longer cache (chunked prompt, verification of several tokens)
+            qi = torch.arange(kv_len - q_len, kv_len, device=query.device).view(-1, 1)
+            mask = torch.arange(kv_len, device=query.device).view(1, -1) <= qi
         return F.scaled_dot_product_attention(query, key, value, attn_mask=mask, scale=scale,
-                                              is_causal=(mask is None and q_len > 1 and q_len == kv_len))
+                                              is_causal=(mask is None and causal))
     # eager path (soft-capped logits, sliding window)
     w = torch.matmul(query.float(), key.float().transpose(2, 3)) * scale
     if softcap is not None:
@@ -232,12 +238,95 @@ def scaled_dot_product_attention(query: torch.Tensor, key: torch.Tensor, value: 
     if mask is not None:
         m = mask[..., :kv_len]
         w = w.masked_fill(~m, float("-inf")) if m.dtype == torch.bool else w + m.float()
-    else:
+    elif causal or sliding_window is not None:
         qi = torch.arange(kv_len - q_len, kv_len, device=w.device).view(-1, 1)
         ki = torch.arange(kv_len, device=w.device).view(1, -1)
-        allowed = ki <= qi
+        allowed = ki <= qi if causal else torch.ones(q_len, kv_len, dtype=torch.bool, device=w.device)
         if sliding_window is not None:
             allowed = allowed & (ki > qi - sliding_window)
         w = w.masked_fill(~allowed, float("-inf"))
     w = torch.softmax(w, dim=-1)
     return torch.matmul(w, value.float()).to(query.dtype)
+
+
+# ------------------------------------------------------------------------------------------------
+# attention interface of transformers 5: every model whose attention goes through ALL_ATTENTION_FUNCTIONS
+# ------------------------------------------------------------------------------------------------
+ATTN_INTERFACE_NAME = "ipex_llm"
+
+
+def attention_interface(module, query, key, value, attention_mask=None, dropout: float = 0.0, scaling=None,
+                        is_causal=None, softcap=None, sliding_window=None, **kwargs):
+    """The package's SDPA behind the transformers attention-interface contract: ``query [B, Hq, Sq, D]``,
+    ``key`` / ``value [B, Hkv, Skv, D]`` (already read back from the cache), returns ``([B, Sq, Hq, Dv], None)``.
+
+    This is how the families that the reference patches file by file (whisper, bert, mllama, qwen2_vl, deepseek,
+    starcoder2, stablelm, gpt_neox, bloom, ... python/llm/src/ipex_llm/transformers/convert.py:1303-2040) reach the
+    native attention kernels here without a forward of their own."""
+    if is_causal is None:
+        is_causal = query.shape[2] > 1 and attention_mask is None and getattr(module, "is_causal", True)
+    mask = attention_mask
+    if mask is not None and mask.dim() == 4 and mask.shape[-1] > key.shape[2]:
+        mask = mask[..., : key.shape[2]]
+    if dropout and module.training:
+        # training with attention dropout keeps the library path
+        import torch.nn.functional as F_
+        k2, v2 = repeat_kv(key, query.shape[1] // key.shape[1]), repeat_kv(value, query.shape[1] // key.shape[1])
+        out = F_.scaled_dot_product_attention(query, k2, v2, attn_mask=mask, dropout_p=dropout, scale=scaling,
+                                              is_causal=bool(is_causal) and mask is None)
+        return out.transpose(1, 2).contiguous(), None
+    out = scaled_dot_product_attention(query, key, value, mask, is_causal=bool(is_causal), scale=scaling,
+                                       softcap=softcap, sliding_window=sliding_window, infer_causal=False)
+    return out.transpose(1, 2).contiguous(), None
+
+
+def register_attention_interface() -> bool:
+    """Register ``attention_interface`` under the name ``ipex_llm``; False when transformers has no such registry."""
+    try:
+        from transformers import AttentionInterface
+    except ImportError:
+        return False
+    try:
+        AttentionInterface.register(ATTN_INTERFACE_NAME, attention_interface)
+        try:   # masks are built as for the sdpa path
+            from transformers import AttentionMaskInterface
+            from transformers.masking_utils import sdpa_mask
+            AttentionMaskInterface.register(ATTN_INTERFACE_NAME, sdpa_mask)
+        except Exception:  # noqa: BLE001
+            pass
+        return True
+    except Exception:  # noqa: BLE001
+        return False
+
+
+def use_attention_interface(model) -> bool:
+    """Point the model (and its sub-configs) at the registered interface.  Models whose attention classes do not go
+    through the registry simply ignore the setting."""
+    if not register_attention_interface():
+        return False
+    done = False
+    seen = set()
+    stack = [getattr(model, "config", None)]
+    while stack:
+        cfg = stack.pop()
+        if cfg is None or id(cfg) in seen:
+            continue
+        seen.add(id(cfg))
+        try:
+            cfg._attn_implementation = ATTN_INTERFACE_NAME
+            done = True
+        except Exception:  # noqa: BLE001
+            pass
+        for name in ("text_config", "vision_config", "audio_config", "decoder", "encoder", "llm_config"):
+            sub = getattr(cfg, name, None)
+            if sub is not None and hasattr(sub, "to_dict"):
+                stack.append(sub)
+    for mod in model.modules():
+        cfg = getattr(mod, "config", None)
+        if cfg is not None and id(cfg) not in seen and hasattr(cfg, "to_dict"):
+            seen.add(id(cfg))
+            try:
+                cfg._attn_implementation = ATTN_INTERFACE_NAME
+            except Exception:  # noqa: BLE001
+                pass
+    return done

@@ -93,7 +93,10 @@ FAMILIES = {
     "gemma2": _llama_like("Gemma2", mlp_forward=C.mlp_gelu_forward, norm_forward=C.gemma_rms_norm_forward,
                           spec=D.AttnSpec(softcap_attr="attn_logit_softcapping", sliding=True)),
     "phi3": _llama_like("Phi3", merge=False),
-    "glm": Family(post=[("GlmRMSNorm", C.rms_norm_forward)]),
+    # GLM: GPT-J style ("two") rotary on half of the head dims, fused gate_up_proj (reference models/glm.py,
+    # chatglm2.py:225-262 for the rotary pairing)
+    "glm": _llama_like("Glm", spec=D.AttnSpec(interleaved_rope=True)),
+    "glm4": _llama_like("Glm4", spec=D.AttnSpec(interleaved_rope=True)),
     "starcoder2": Family(pre=[_merge_qkv("Starcoder2Attention")],
                          post=[("Starcoder2Attention", D.decoder_attention_forward),
                                ("Starcoder2Model", D.decoder_model_forward)]),

