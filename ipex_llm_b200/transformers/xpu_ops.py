@@ -1,8 +1,13 @@
 """Reference module path ``ipex_llm.transformers.xpu_ops`` (python/llm/src/ipex_llm/transformers/xpu_ops.py:23-162):
-the reference registers fake tensors for the ops of its closed ``xe_linear`` / ``xe_addons`` extensions.  Here the
-same op names are plain Python functions over this package's CUDA kernels, for code that called the extensions
-directly."""
+the reference registers fake tensors for the ops of its closed ``xe_linear`` / ``xe_addons`` extensions.  Importing
+this module registers the same op names as ``torch.ops.ipex_llm.*`` custom ops with fake-tensor kernels
+(``ops/library.py``), so graphs traced by ``torch.compile`` can carry them; the functions below are the eager
+conveniences for code that called the extensions directly."""
 import torch
+
+from ..ops import library as _library
+
+_library.register()
 
 from ..ops import cuda_ops as _ops
 from ..ops.rwkv import rwkv_linear_attention_v4, rwkv_linear_attention_v5, rwkv_time_shift  # noqa: F401

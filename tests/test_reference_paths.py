@@ -44,3 +44,36 @@ def test_names_behind_the_paths():
     assert lin.weight.device.type == "meta"
     import bigdl.llm.transformers.low_bit_linear as legacy
     assert legacy.LowBitLinear is impl
+
+
+def test_torch_library_ops_have_fake_kernels_and_match_eager():
+    """``torch.ops.ipex_llm.*`` exist with the reference's op names, trace with fake tensors (meta device) and
+    compute the same numbers as the module path on CPU."""
+    import torch
+    import ipex_llm.transformers.xpu_ops  # noqa: F401  (registers the ops)
+    from ipex_llm_b200.ops.linear import LowBitLinear
+    from ipex_llm_b200.quant import qtypes as qt
+    from ipex_llm_b200.quant.params import FP4Params
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(128, 48, bias=False)
+    w = FP4Params(lin.weight.data, quantized=False, qtype=qt.SYM_INT8).quantize("cpu")
+    x = torch.randn(3, 128)
+    y = torch.ops.ipex_llm.forward_new(x, w.data, qt.SYM_INT8, 48)
+    ref = torch.nn.functional.linear(x, w.dequantize(torch.float32))
+    assert torch.allclose(y, ref, atol=1e-4)
+    g = torch.randn(3, 48)
+    n = torch.ops.ipex_llm.rms_norm(torch.ones(48), g, 1e-6)
+    assert torch.allclose(n, g * torch.rsqrt(g.pow(2).mean(-1, keepdim=True) + 1e-6), atol=1e-5)
+    # fake kernels: shapes without data
+    with torch.device("meta"):
+        xm, wm = torch.empty(5, 128), torch.empty(w.data.numel(), dtype=torch.uint8)
+    ym = torch.ops.ipex_llm.forward_new(xm, wm, qt.SYM_INT8, 48)
+    assert ym.shape == (5, 48) and ym.device.type == "meta"
+    q = torch.empty(2, 4, 1, 64, device="meta")
+    kv = torch.empty(2, 4, 9, 64, device="meta")
+    assert torch.ops.ipex_llm.sdp(q, kv, kv).shape == (2, 4, 1, 64)
+    # ... and through torch.compile's tracer (fake tensors), eager backend
+    def f(a):
+        return torch.ops.ipex_llm.rms_norm(torch.ones(48), a, 1e-6) * 2
+    out = torch.compile(f, backend="eager")(g)
+    assert torch.allclose(out, n * 2, atol=1e-5)
