@@ -3,6 +3,7 @@
 Endpoints (same set as python/llm/src/ipex_llm/serving/fastapi/api_server.py:103-437):
   POST /generate, /generate_stream      TGI-style
   POST /v1/chat/completions, /v1/completions   OpenAI-compatible (streaming with server-sent events)
+  POST /v1/audio/transcriptions                OpenAI-compatible speech-to-text (workers started with model_type "audio")
   GET  /v1/models, /health, /metrics
 ``IPEX_LLM_FASTAPI_TIMEOUT`` bounds the time a request may wait for its next piece.
 """
@@ -14,7 +15,7 @@ import os
 import time
 from typing import AsyncIterator, List, Optional
 
-from fastapi import FastAPI, HTTPException
+from fastapi import FastAPI, HTTPException, Request
 from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
 from .model_worker import ModelWorker, SamplingParams
@@ -183,6 +184,31 @@ class FastApp:
             pt, ct = sum(f["prompt_tokens"] for f in fins), sum(f["generated_tokens"] for f in fins)
             return CompletionResponse(model=self.name, choices=choices,
                                       usage=UsageInfo(prompt_tokens=pt, completion_tokens=ct, total_tokens=pt + ct))
+
+        @app.post("/v1/audio/transcriptions")
+        async def transcriptions(request: Request):
+            """multipart/form-data with ``file`` (PCM WAV) and optional ``model``, ``language``, ``prompt``,
+            ``response_format`` (json | text), as the reference's endpoint (api_server.py:403-425)."""
+            from .audio import decode_wav, parse_multipart, resample
+            form = parse_multipart(await request.body(), request.headers.get("content-type", ""))
+            if not isinstance(form.get("file"), tuple):
+                raise HTTPException(status_code=400, detail="multipart field 'file' with a WAV file is required")
+            if not hasattr(w, "transcribe"):
+                raise HTTPException(status_code=400, detail="this worker serves no speech model")
+            try:
+                samples, rate = decode_wav(form["file"][1])
+            except Exception as e:  # noqa: BLE001
+                raise HTTPException(status_code=400, detail=f"cannot decode the audio file: {e}")
+            loop = asyncio.get_running_loop()
+            try:
+                text = await asyncio.wait_for(
+                    loop.run_in_executor(None, w.transcribe, resample(samples, rate), form.get("language") or None),
+                    timeout=_timeout())
+            except asyncio.TimeoutError:
+                raise HTTPException(status_code=504, detail="transcription timed out")
+            if (form.get("response_format") or "json") == "text":
+                return PlainTextResponse(text)
+            return JSONResponse({"text": text})
 
 def _reason(item) -> Optional[str]:
     r = item.get("finish_reason")

@@ -84,6 +84,12 @@ class ModelWorker:
                   use_cache=True)
         if model_type == "audio":
             model = AutoModelForSpeechSeq2Seq.from_pretrained(model_path, **kw)
+            try:
+                from transformers import AutoProcessor
+                self.processor = AutoProcessor.from_pretrained(model_path)
+            except Exception:  # noqa: BLE001 - the feature extractor alone is enough
+                from transformers import AutoFeatureExtractor
+                self.processor = AutoFeatureExtractor.from_pretrained(model_path)
         else:
             try:
                 model = AutoModelForCausalLM.from_pretrained(model_path, **kw)
@@ -94,6 +100,28 @@ class ModelWorker:
         model = model.eval().to(device)
         tok = AutoTokenizer.from_pretrained(model_path, trust_remote_code=True, padding_side="left")
         return model, tok
+
+    # ------------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def transcribe(self, samples, language: Optional[str] = None, max_new_tokens: int = 128) -> str:
+        """Speech-to-text for one 16 kHz mono waveform (numpy float32) with a speech sequence-to-sequence model
+        (reference model_worker.py:100-118)."""
+        proc = getattr(self, "processor", None)
+        fe = getattr(proc, "feature_extractor", proc)
+        if fe is None:
+            raise RuntimeError("transcribe needs a worker created with model_type='audio'")
+        feats = fe(samples, sampling_rate=16000, return_tensors="pt").input_features
+        dev = next(self.model.parameters()).device
+        feats = feats.to(dev, self.dtype if dev.type == "cuda" else torch.float32)
+        kw = {}
+        if language and hasattr(proc, "get_decoder_prompt_ids"):
+            try:
+                kw["forced_decoder_ids"] = proc.get_decoder_prompt_ids(language=language, task="transcribe")
+            except Exception:  # noqa: BLE001 - tokenizers without language tokens
+                pass
+        ids = self.model.generate(input_features=feats, max_new_tokens=max_new_tokens, do_sample=False, **kw)
+        tok = getattr(proc, "tokenizer", None) or self.tokenizer
+        return tok.batch_decode(ids, skip_special_tokens=True)[0].strip()
 
     # ------------------------------------------------------------------------------------------------
     def start(self):

@@ -140,3 +140,53 @@ def test_fastchat_protocol_worker(worker):
                                                               "temperature": 0.0, "echo": False}) as resp:
             chunks = [json.loads(x) for x in resp.read().split(b"\0") if x]
         assert chunks[-1]["text"] == r["text"] and chunks[-1]["finish_reason"] in ("length", "stop")
+
+
+def test_audio_transcription_endpoint(monkeypatch):
+    """multipart upload of a WAV file -> decoded, resampled to 16 kHz, handed to the worker's speech model."""
+    import io
+    import wave
+
+    import numpy as np
+    from fastapi.testclient import TestClient
+    from ipex_llm_b200.serving.api_server import FastApp
+    from ipex_llm_b200.serving.audio import decode_wav, parse_multipart, resample
+
+    rate = 8000
+    t = np.arange(rate // 2) / rate
+    pcm = (np.sin(2 * np.pi * 440 * t) * 20000).astype("<i2")
+    buf = io.BytesIO()
+    with wave.open(buf, "wb") as w:
+        w.setnchannels(1)
+        w.setsampwidth(2)
+        w.setframerate(rate)
+        w.writeframes(pcm.tobytes())
+    wav = buf.getvalue()
+    x, r = decode_wav(wav)
+    assert r == rate and abs(float(np.abs(x).max()) - 20000 / 32768) < 1e-3
+    assert len(resample(x, r)) == len(x) * 2
+
+    seen = {}
+
+    class Worker:
+        model_name = "fake-whisper"
+        tokenizer = None
+        stats = {"requests": 0, "batches": 0, "generated_tokens": 0, "first_token_s": [], "next_token_s": []}
+
+        def transcribe(self, samples, language=None):
+            seen["n"], seen["language"] = len(samples), language
+            return "hello world"
+
+    client = TestClient(FastApp(Worker()).app)
+    boundary = "----ipexllmtest"
+    body = (f"--{boundary}\r\nContent-Disposition: form-data; name=\"language\"\r\n\r\nen\r\n"
+            f"--{boundary}\r\nContent-Disposition: form-data; name=\"file\"; filename=\"a.wav\"\r\n"
+            f"Content-Type: audio/wav\r\n\r\n").encode() + wav + f"\r\n--{boundary}--\r\n".encode()
+    form = parse_multipart(body, f"multipart/form-data; boundary={boundary}")
+    assert form["language"] == "en" and form["file"][0] == "a.wav" and form["file"][1] == wav
+    resp = client.post("/v1/audio/transcriptions", content=body,
+                       headers={"content-type": f"multipart/form-data; boundary={boundary}"})
+    assert resp.status_code == 200 and resp.json() == {"text": "hello world"}
+    assert seen == {"n": len(x) * 2, "language": "en"}
+    bad = client.post("/v1/audio/transcriptions", content=b"x", headers={"content-type": "text/plain"})
+    assert bad.status_code == 400
