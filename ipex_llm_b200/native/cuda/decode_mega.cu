@@ -741,7 +741,7 @@ __device__ __forceinline__ void finalize_tile(const MegaArgs& a, const OpInfo& o
 
 template <typename T, int WFK>
 __device__ bool consume_op(const MegaArgs& a, const OpInfo& op, const Ctx& c, int start, int& it0, int& g0,
-                           TpState& tp) {
+                           TpState& tp, const void* next_norm_w, int next_norm_k) {
   constexpr int CPS = Geo<WFK>::CPS;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -762,6 +762,13 @@ __device__ bool consume_op(const MegaArgs& a, const OpInfo& op, const Ctx& c, in
   const bool prof = c.prof != nullptr && tid == 0;
   long long tp0 = 0;
   if (prof) tp0 = clock64();
+  // The NEXT op's norm weight is first touched one op from now, by every CTA at once, right after a grid barrier:
+  // ask L2 for it now (a few lines per CTA) so that its staging pass does not open with an HBM miss.
+  if (next_norm_w != nullptr) {
+    const int lines = (next_norm_k * (int)sizeof(T) + 127) / 128;
+    for (int i = blockIdx.x * kCThreads + tid; i < lines; i += gridDim.x * kCThreads)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint8_t*>(next_norm_w) + (size_t)i * 128));
+  }
   if constexpr (WFK == WFK_I8) {
     if (Kp <= 8 * kCThreads * kNVMax) stage_x_fast<T, true>(a, op, c, Kp);
     else stage_x_i8<T>(a, op, c, Kp);
@@ -1404,7 +1411,14 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
 
   for (int q = 0; q <= 4 * L && ok; q++) {
     const OpInfo op = get_op(a, q);
-    ok = consume_op<T, WFK>(a, op, c, start, it0, g0, tp);
+    const void* next_nw = nullptr;
+    int next_nk = 0;
+    if (q < 4 * L) {
+      const OpInfo nx = get_op(a, q + 1);
+      next_nw = nx.norm_w;
+      next_nk = nx.K;
+    }
+    ok = consume_op<T, WFK>(a, op, c, start, it0, g0, tp, next_nw, next_nk);
     if (!ok) break;
     {
       const int Np = (int)ceil_to_i64(op.N, 16);

@@ -251,8 +251,8 @@ class _BaseAutoModelClass:
                 warnings.warn("bnb_4bit_quant_type is None, use default int4", FutureWarning)
                 load_in_low_bit = "sym_int4"
             if getattr(qc, "bnb_4bit_use_double_quant", False):
-                warnings.warn("BitsAndBytesConfig's double quantization is applied to the device layout of nf4 "
-                              "scales only", FutureWarning)
+                # same behaviour as the reference (model.py:215-218): nf4 keeps one fp16 scale per 64-group
+                warnings.warn("double quantization of the nf4 scales is not supported, set to False", FutureWarning)
             if qc.bnb_4bit_compute_dtype is not None:
                 bnb_dtype = qc.bnb_4bit_compute_dtype
                 invalidInputError(bnb_dtype in (torch.float32, torch.bfloat16),
