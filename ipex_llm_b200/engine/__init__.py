@@ -26,7 +26,7 @@ _UNSUPPORTED_KW = ("num_beams", "penalty_alpha", "num_return_sequences", "constr
 
 def supports(model, kwargs) -> bool:
     fam = family_for(model)
-    if fam is None or fam.engine != "llama":
+    if fam is None or fam.engine not in ("llama", "mixtral"):
         return False
     if getattr(model, "_ipex_engine_disabled", False):
         return False
@@ -38,9 +38,20 @@ def supports(model, kwargs) -> bool:
         blk = model.model.layers[0]
     except Exception:  # noqa: BLE001
         return False
-    if not hasattr(blk.self_attn, "qkv_proj") or not hasattr(blk.mlp, "gate_proj"):
+    if not hasattr(blk.self_attn, "qkv_proj"):
         return False
-    for mod in (blk.self_attn.qkv_proj, blk.self_attn.o_proj, blk.mlp.gate_proj, blk.mlp.down_proj):
+    mlp_mods = ()
+    if hasattr(blk.mlp, "experts"):
+        # sparse mixture-of-experts layers: the expert bank must be the packed one the MoE kernels read
+        ex = blk.mlp.experts
+        if not (hasattr(ex, "intermediate_dim") and hasattr(blk.mlp, "gate") and cuda_ops.moe_supported(ex)) or \
+                getattr(ex, "_tp_group", None) is not None or getattr(blk.mlp, "shared_expert", None) is not None:
+            return False
+    elif hasattr(blk.mlp, "gate_proj"):
+        mlp_mods = (blk.mlp.gate_proj, blk.mlp.down_proj)
+    else:
+        return False
+    for mod in (blk.self_attn.qkv_proj, blk.self_attn.o_proj) + mlp_mods:
         if isinstance(mod, LowBitLinear) and not cuda_ops.is_tiled(mod.weight.qtype):
             return False
     hd = getattr(model.config, "head_dim", None) or model.config.hidden_size // model.config.num_attention_heads

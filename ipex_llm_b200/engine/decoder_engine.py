@@ -136,9 +136,21 @@ class DecoderEngine:
                 raise NotImplementedError("decode engine expects merged qkv_proj (optimize_model=True)")
             L.qkv = _W.from_module(attn.qkv_proj, dt)
             L.o = _W.from_module(attn.o_proj, dt)
-            g, u = _W.from_module(mlp.gate_proj, dt), _W.from_module(mlp.up_proj, dt)
-            L.gate_up = _interleave_row_tiles(g, u)
-            L.down = _W.from_module(mlp.down_proj, dt)
+            L.moe = None
+            if hasattr(mlp, "experts"):
+                # sparse mixture-of-experts block: router matrix + expert bank (kernels of ops/cuda_ops.moe_forward)
+                if not cuda_ops.moe_supported(mlp.experts) or getattr(mlp.experts, "_tp_group", None) is not None \
+                        or getattr(mlp, "shared_expert", None) is not None:
+                    raise NotImplementedError("decode engine: this mixture-of-experts block needs the module tree")
+                L.moe = mlp.experts
+                L.router = mlp.gate.weight.data.to(dt).contiguous()
+                L.top_k = int(getattr(mlp.gate, "top_k", None) or getattr(mlp, "top_k", 2))
+                L.renorm = bool(getattr(mlp.gate, "norm_topk_prob", True))
+                L.gate_up = L.down = None
+            else:
+                g, u = _W.from_module(mlp.gate_proj, dt), _W.from_module(mlp.up_proj, dt)
+                L.gate_up = _interleave_row_tiles(g, u)
+                L.down = _W.from_module(mlp.down_proj, dt)
             L.ln1 = blk.input_layernorm.weight.data.to(dt)
             L.ln2 = blk.post_attention_layernorm.weight.data.to(dt)
             L.layer_idx = attn.layer_idx
@@ -148,7 +160,9 @@ class DecoderEngine:
         total_heads = self.layers[0].qkv.N // self.hd
         self.n_kv = total_heads // (groups + 2)
         self.n_heads = total_heads - 2 * self.n_kv
-        self.inter = self.layers[0].gate_up.N // 2
+        self.has_moe = any(L.moe is not None for L in self.layers)
+        dense = [L for L in self.layers if L.moe is None]
+        self.inter = dense[0].gate_up.N // 2 if dense else self.layers[0].moe.intermediate_dim
         self.tp_group = getattr(self.layers[0], "tp", None)
 
         # rotary table (fp32) from the model's own rotary module, so every rope-scaling flavour is honoured
@@ -282,6 +296,10 @@ class DecoderEngine:
             return 1                          # embedding ... arg-max in one persistent kernel
         if self._use_chain(getattr(self, "batch", 1) or 1):
             return 1 + 1 + 2 * n + 1          # embedding, first qkv, (attention + chained GEMVs) per layer, argmax
+        if self.has_moe:
+            # per layer: qkv, attention, o_proj, norm, router GEMM, softmax/top-k, two expert GEMVs, combine, residual
+            n_moe = sum(1 for L in self.layers if L.moe is not None)
+            return 1 + 5 * (n - n_moe) + 10 * n_moe + 2
         if self.layers[0].o.tp is not None:
             return 1 + 7 * n + 2              # tensor parallel: + one all-reduce kernel after o_proj and down_proj
         return 1 + 5 * n + 2
@@ -289,6 +307,8 @@ class DecoderEngine:
     def _use_chain(self, B: int) -> bool:
         """The chained-GEMV kernel covers single-GPU models whose projections are all symmetric int4."""
         cached = self.__dict__.get("_chain_ok")
+        if cached is None and self.has_moe:
+            cached = self._chain_ok = False
         if cached is None:
             ws = [w for L in self.layers for w in (L.qkv, L.o, L.gate_up, L.down)] + [self.lm_head]
             # opt-in: at batch 1 on a 7B model the chained kernel measured 2.59 ms/token against 2.20 ms for the
@@ -306,6 +326,17 @@ class DecoderEngine:
     def _op(self, w: _W, x, y, norm_w=None, residual=None, act=0):
         return {"w": w.data, "x": x, "y": y, "N": w.N, "K": w.K, "norm_w": norm_w, "bias": w.bias,
                 "residual": residual, "act": act, "eps": self.eps}
+
+    def _moe_mlp(self, L: _Layer, h1, out):
+        """``out = h1 + experts(norm(h1))`` of a sparse mixture-of-experts layer: router scores, fused softmax /
+        top-k, per-slot expert GEMVs through a device pointer table (few rows) or expert-sorted tcgen05 GEMMs that
+        read their row ranges on the device (prompts).  Nothing synchronises with the host, so the sequence is
+        captured into the decode graph like the dense layers."""
+        x = cuda_ops.rms_norm(h1, L.ln2, self.eps)
+        scores = torch.matmul(x, L.router.t())
+        _, w, idx = cuda_ops.moe_softmax_topk(scores, L.top_k, L.renorm)
+        y = cuda_ops.moe_forward(L.moe, x, idx, w)
+        return torch.add(y, h1, out=out)
 
     def _attention(self, L: _Layer, B: int, Sq: int = 1):
         """Rope + cache append + attention for ``B`` sequences of ``Sq`` new tokens each; rows of the activation
@@ -349,6 +380,9 @@ class DecoderEngine:
             self._vproj(L.qkv, h0, self.qkv_buf[:S], norm_w=L.ln1)
             self._attention(L, 1, Sq=S)
             self._vproj(L.o, self.attn_buf[:S], h1, residual=h0)
+            if L.moe is not None:
+                self._moe_mlp(L, h1, h0)
+                continue
             self._vproj(L.gate_up, h1, self.act_buf[:S], norm_w=L.ln2, act=1)
             self._vproj(L.down, self.act_buf[:S], h0, residual=h1)
         if self.lm_gather is None:
@@ -436,6 +470,9 @@ class DecoderEngine:
                 self._gemv(L.qkv, h0, self.qkv_buf[:B], norm_w=L.ln1)
                 self._attention(L, B)
                 self._gemv(L.o, self.attn_buf[:B], h1, residual=h0)
+                if L.moe is not None:
+                    self._moe_mlp(L, h1, h0)
+                    continue
                 self._gemv(L.gate_up, h1, self.act_buf[:B], norm_w=L.ln2, act=1)
                 self._gemv(L.down, self.act_buf[:B], h0, residual=h1)
             self._lm_head(h0, B)
@@ -507,7 +544,7 @@ class DecoderEngine:
     def _flat_prefill_ok(self) -> bool:
         ok = self.__dict__.get("_flat_ok")
         if ok is None:
-            ws = [w for L in self.layers for w in (L.qkv, L.o, L.gate_up, L.down)]
+            ws = [w for L in self.layers for w in (L.qkv, L.o, L.gate_up, L.down) if w is not None]
             ok = os.environ.get("IPEX_LLM_FLAT_PREFILL", "1") != "0" and \
                 hasattr(self._lib, "ipex_gemm_lowbit_tcgen05") and \
                 all(w.K % 128 == 0 and w.N % 16 == 0 and w.wf not in (api.WF_F16, api.WF_BF16) for w in ws)
@@ -567,6 +604,9 @@ class DecoderEngine:
             a = cuda_ops.sdpa_prefill(q, k, v, None, scale, None, None, causal=True)    # [B, Hq, S, D]
             a = a.transpose(1, 2).reshape(T, Hq * D)
             h1 = self._gemm(L.o, a, residual=h)
+            if L.moe is not None:
+                h = self._moe_mlp(L, h1, torch.empty_like(h1))
+                continue
             x = cuda_ops.rms_norm(h1, L.ln2, self.eps)
             act = self._gemm(L.gate_up, x, act=1)                                        # [T, I]
             h = self._gemm(L.down, act, residual=h1)

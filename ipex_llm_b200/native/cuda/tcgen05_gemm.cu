@@ -73,6 +73,10 @@ struct GemmArgs {
   int* const* ag_peer_flags;
   int* ag_ticket;
   int ag_world;
+  // grouped use (mixture-of-experts prompts): the launch covers rows [m_range[0], m_range[0] + m_range[1]) of x and
+  // out, read from DEVICE memory when the kernel starts, so the host never learns how many tokens an expert got.
+  // M / m_tiles given at launch are the upper bound that sized the grid.
+  const int* m_range;
 };
 
 __device__ __forceinline__ int pair_row(int r) { return (r & 7) * 2 + (r >> 3); }
@@ -402,6 +406,13 @@ __global__ void __launch_bounds__(Fam<WF>::threads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, GemmArgs a) {
   using C = Cfg<BT>;
   constexpr bool kDense = Fam<WF>::dense;
+  int row0 = 0;
+  if (a.m_range != nullptr) {
+    row0 = a.m_range[0];
+    a.M = a.m_range[1];
+    a.m_tiles = (a.M + BT - 1) / BT;
+    a.out = reinterpret_cast<T*>(a.out) + (int64_t)row0 * a.ldo;
+  }
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -483,7 +494,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) { ok = false; report(a.err, 8); break; }
           mbar_expect_tx(&full[s], kDense ? C::kStageBytes : C::kBBytes);
           if constexpr (kDense) tma_load_2d(sA + s * C::kABytes, &tm_w, kb * kBK, nb * kBM, &full[s]);
-          tma_load_2d(sB + s * C::kBBytes, &tm_x, kb * kBK, mb * BT, &full[s]);
+          tma_load_2d(sB + s * C::kBBytes, &tm_x, kb * kBK, row0 + mb * BT, &full[s]);
           if (++s == C::kStages) { s = 0; ph ^= 1; }
         }
       }
@@ -759,6 +770,38 @@ IPEX_API int ipex_gemm_lowbit_tcgen05(const void* x, const void* w, void* out, c
   a.n_tiles = (N + kBM - 1) / kBM;
   a.act = act;
   a.err = err;
+  cudaStream_t st = (cudaStream_t)stream;
+  return (int)(dtype == DT_F16 ? dispatch_wf<__half>(wf, bt, tx, tx, a, sm_count(), st)
+                               : dispatch_wf<__nv_bfloat16>(wf, bt, tx, tx, a, sm_count(), st));
+}
+
+// Grouped form for mixture-of-experts prompts: rows [m_range[0], m_range[0] + m_range[1]) of x [M_total, K] times
+// one expert's packed weight into the same rows of out [M_total, N (or N / 2 with act)].  m_range is a DEVICE pointer
+// to (first row, row count): the host launches every expert without knowing its token count.  `bt` is the token
+// tile (32 / 64 / 128 / 256); the grid is sized for m_upper rows, CTAs beyond the real tile count leave at once.
+IPEX_API int ipex_gemm_lowbit_tcgen05_grouped(const void* x, const void* w, void* out, const float* lut,
+                                              const int* m_range, int M_total, int m_upper, int N, int K, int64_t ldx,
+                                              int64_t ldo, int wf, int act, int dtype, int bt, int* err, void* stream) {
+  if (M_total < 1 || m_upper < 1 || N < 1 || K < 1 || (ldx % 8) != 0 || m_range == nullptr)
+    return (int)cudaErrorInvalidValue;
+  if (reinterpret_cast<uintptr_t>(x) & 15) return (int)cudaErrorInvalidValue;
+  if (dtype != DT_F16 && dtype != DT_BF16) return (int)cudaErrorInvalidValue;
+  if (act != 0 && (N % 32) != 0) return (int)cudaErrorInvalidValue;
+  if (wf == WF_LUT4 && lut == nullptr) return (int)cudaErrorInvalidValue;
+  if (bt != 32 && bt != 64 && bt != 128 && bt != 256) return (int)cudaErrorInvalidValue;
+  const CUtensorMapDataType tdt = dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap tx;
+  if (!tc5::encode_2d_sw128(&tx, tdt, x, (uint64_t)K, (uint64_t)M_total, (uint64_t)ldx * 2, kBK, bt)) return -1;
+  GemmArgs a = {};
+  a.w = reinterpret_cast<const uint8_t*>(w); a.lut = lut;
+  a.out = out; a.bias = nullptr; a.residual = nullptr; a.ldo = ldo; a.ldr = 0;
+  a.Np = ceil_to_i64(N, 16); a.Kp = ceil_to_i64(K, 128);
+  a.M = m_upper; a.N = N; a.K = K;
+  a.m_tiles = (m_upper + bt - 1) / bt;
+  a.n_tiles = (N + kBM - 1) / kBM;
+  a.act = act;
+  a.err = err;
+  a.m_range = m_range;
   cudaStream_t st = (cudaStream_t)stream;
   return (int)(dtype == DT_F16 ? dispatch_wf<__half>(wf, bt, tx, tx, a, sm_count(), st)
                                : dispatch_wf<__nv_bfloat16>(wf, bt, tx, tx, a, sm_count(), st));

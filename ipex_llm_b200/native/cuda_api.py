@@ -57,6 +57,7 @@ _OPTIONAL = {
     "ipex_gemm_tcgen05": [vp, vp, vp, vp, vp, ci, ci, ci, i64, i64, i64, i64, ci, vp, vp],
     "ipex_gemm_tcgen05_token_tile": [ci],
     "ipex_gemm_lowbit_tcgen05": [vp, vp, vp, vp, vp, vp, ci, ci, ci, i64, i64, i64, ci, ci, ci, vp, vp],
+    "ipex_gemm_lowbit_tcgen05_grouped": [vp, vp, vp, vp, vp, ci, ci, ci, ci, i64, i64, ci, ci, ci, ci, vp, vp],
     "ipex_lora_rs_adamw": [vp, vp, vp, vp, vp, vp, vp, vp, i64, ci, ci, cf, cf, cf, cf, cf, ci, ci, ci, vp, vp],
     "ipex_moe_softmax_topk": [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp],
 }

@@ -641,6 +641,7 @@ class _MoeBank:
             gu_ptrs.append(merged.data.data_ptr())
             dn_ptrs.append(e.w2.weight.data.data_ptr())
         dev = experts[0].w1.weight.data.device
+        self.gu_ptrs_host, self.dn_ptrs_host = gu_ptrs, dn_ptrs
         self.gu_ptrs = torch.tensor(gu_ptrs, dtype=torch.int64, device=dev)
         self.dn_ptrs = torch.tensor(dn_ptrs, dtype=torch.int64, device=dev)
         self.wf, self.qtype, self.H, self.I = wf, q, H, I
@@ -664,14 +665,10 @@ def moe_forward(experts, hidden_states, top_k_index, top_k_weights):
     slots = T * k
     if slots > _MOE_MAX_SLOTS:
         return _moe_forward_grouped(experts, hidden_states, top_k_index, top_k_weights)
-    bank = experts.__dict__.get("_cuda_bank")
-    if bank is None:
-        bank = _MoeBank(experts)
-        experts.__dict__["_cuda_bank"] = bank
+    bank = _moe_bank(experts)
     x = hidden_states.contiguous()
     dt = x.dtype
-    act_code = 1 if getattr(experts.act_fn, "__name__", "silu") in ("silu", "SiLU") or \
-        type(experts.act_fn).__name__ in ("SiLU", "SiLUActivation") else 2
+    act_code = _moe_act_code(experts)
     ids = top_k_index.reshape(-1).to(torch.int64).contiguous()
     act = torch.empty((slots, bank.I), dtype=dt, device=x.device)
     y = torch.empty((slots, bank.H), dtype=dt, device=x.device)
@@ -697,8 +694,71 @@ def moe_forward(experts, hidden_states, top_k_index, top_k_weights):
     return out
 
 
+def _moe_bank(experts):
+    bank = experts.__dict__.get("_cuda_bank")
+    if bank is None:
+        bank = _MoeBank(experts)
+        experts.__dict__["_cuda_bank"] = bank
+    return bank
+
+
+def _moe_act_code(experts) -> int:
+    return 1 if getattr(experts.act_fn, "__name__", "silu") in ("silu", "SiLU") or \
+        type(experts.act_fn).__name__ in ("SiLU", "SiLUActivation") else 2
+
+
 def _moe_forward_grouped(experts, hidden_states, top_k_index, top_k_weights):
-    """Prompt-sized inputs: tokens grouped per expert, each group through the low-bit tensor-core GEMM."""
+    """Prompt-sized inputs.  The (token, choice) slots are sorted by expert on the device; every expert's rows then
+    go through the low-bit tcgen05 GEMM, which reads its row range (first row, row count) from device memory, so the
+    host launches 2 x num_experts GEMMs without ever learning the routing (no synchronisation, graph-capturable).
+    gate/up is one GEMM with ``act(gate) * up`` in its epilogue."""
+    from . import tcgen05_gemm
+    lib = cuda_lib()
+    fn = getattr(lib, "ipex_gemm_lowbit_tcgen05_grouped", None)
+    H, I = experts.hidden_dim, experts.intermediate_dim
+    if fn is None or not tcgen05_gemm.supported(1, 2 * I, H, experts.qtype) or \
+            not tcgen05_gemm.supported(1, H, I, experts.qtype) or (2 * I) % 32 != 0 or \
+            hidden_states.dtype not in (torch.float16, torch.bfloat16):
+        return _moe_forward_per_expert(experts, hidden_states, top_k_index, top_k_weights)
+    bank = _moe_bank(experts)
+    E = experts.num_experts
+    T, k = top_k_index.shape
+    slots = T * k
+    x = hidden_states.contiguous()
+    flat = top_k_index.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=E)
+    ranges = torch.stack([torch.cumsum(counts, 0) - counts, counts], dim=1).to(torch.int32).contiguous()   # [E, 2]
+    xs = x[order // k]                                         # [slots, H], rows grouped by expert
+    act = torch.empty((slots, I), dtype=x.dtype, device=x.device)
+    ys = torch.empty((slots, H), dtype=x.dtype, device=x.device)
+    lut = lut_for(bank.qtype, x.device)
+    vp, ci, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
+    fn.argtypes, fn.restype = [vp, vp, vp, vp, vp, ci, ci, ci, ci, i64, i64, ci, ci, ci, ci, vp, vp], ci
+    bt = tcgen05_gemm.token_tile(max(1, (slots + E - 1) // E))
+    err, st, dt, code = ptr(error_flag(x.device)), current_stream(), _dt(x), _moe_act_code(experts)
+    for e in range(E):
+        rc = fn(ptr(xs), bank.gu_ptrs_host[e], ptr(act), ptr(lut), ranges[e].data_ptr(), slots, slots, 2 * I, H,
+                xs.stride(0), act.stride(0), bank.wf, code, dt, bt, err, st)
+        api.check(rc, "gemm_lowbit_tcgen05_grouped(gate_up)")
+    for e in range(E):
+        rc = fn(ptr(act), bank.dn_ptrs_host[e], ptr(ys), ptr(lut), ranges[e].data_ptr(), slots, slots, H, I,
+                act.stride(0), ys.stride(0), bank.wf, 0, dt, bt, err, st)
+        api.check(rc, "gemm_lowbit_tcgen05_grouped(down)")
+    y = torch.empty_like(ys)
+    y[order] = ys                                              # back to (token, choice) order
+    out = torch.empty_like(x)
+    w = top_k_weights.to(torch.float32).contiguous()
+    cfn = lib.ipex_moe_combine
+    cfn.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 4 + [ctypes.c_void_p]
+    cfn.restype = ctypes.c_int
+    rc = cfn(ptr(y), ptr(w), ptr(out), T, k, H, dt, st)
+    api.check(rc, "moe_combine")
+    return out
+
+
+def _moe_forward_per_expert(experts, hidden_states, top_k_index, top_k_weights):
+    """Expert-by-expert form with one host synchronisation (kept for weight formats the grouped GEMM lacks)."""
     from ..models.common import SILU, _act_mul
     final = torch.zeros_like(hidden_states)
     E = experts.num_experts

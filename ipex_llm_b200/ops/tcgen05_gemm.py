@@ -54,6 +54,11 @@ def gemm_dense(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor = None, resi
     return out
 
 
+def token_tile(M: int) -> int:
+    """Token tile (32 / 64 / 128 / 256) the kernels use for ``M`` rows."""
+    return 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
+
+
 # weight families the in-kernel dequantizer handles (codes of native/cuda/common/utils.cuh)
 _LOWBIT_FAMILIES = ("WF_SYM_INT4", "WF_ASYM_INT4", "WF_LUT4", "WF_FP8_E4M3", "WF_FP8_E5M2", "WF_INT8")
 

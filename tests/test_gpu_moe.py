@@ -65,6 +65,29 @@ def test_moe_forward_matches_expert_loop(qname, T):
     assert err < 1e-2, err
 
 
+@pytest.mark.parametrize("qname", ["sym_int4", "fp8_e4m3"])
+@pytest.mark.parametrize("T", [300, 1100])
+def test_moe_grouped_prompt_device_ranges(qname, T):
+    """Prompt-sized routing with a skew (one expert gets most tokens, one gets none): the grouped GEMMs read their
+    row ranges on the device and must agree with the per-expert loop that synchronises with the host."""
+    from ipex_llm_b200.ops import cuda_ops
+    E, H, I, k = 8, 256, 512, 2
+    bank = _bank(E, H, I, qname, torch.float16)
+    torch.manual_seed(T)
+    x = (torch.randn(T, H, device="cuda") * 0.5).half()
+    logits = torch.randn(T, E, device="cuda")
+    logits[:, 3] += 3.0            # most tokens pick expert 3
+    logits[:, 5] = -1e4            # nobody picks expert 5
+    _, w, idx = cuda_ops.moe_softmax_topk(logits, k, True)
+    assert hasattr(cuda_ops.cuda_lib(), "ipex_gemm_lowbit_tcgen05_grouped")
+    out = cuda_ops._moe_forward_grouped(bank, x, idx, w)
+    ref = cuda_ops._moe_forward_per_expert(bank, x, idx, w)
+    torch.cuda.synchronize()
+    cuda_ops.check_error_flag(x.device)
+    err = (out.float() - ref.float()).abs().max().item() / ref.float().abs().max().item()
+    assert err < 1e-2, err
+
+
 def test_tiny_mixtral_decode_gpu():
     from transformers import MixtralConfig
     from ipex_llm.transformers import AutoModelForCausalLM
@@ -79,3 +102,40 @@ def test_tiny_mixtral_decode_gpu():
     with torch.no_grad():
         full = m(out[:, :-1]).logits[:, -1].argmax(-1)
     assert torch.equal(full, out[:, -1])
+
+
+def test_mixtral_runs_on_the_graph_engine():
+    """Mixtral's sparse layers are part of the flattened engine: graph-captured decode steps (router, expert GEMVs
+    through the device pointer table) and the flat prompt pass (expert-sorted grouped GEMMs) agree with the module
+    tree, for batch 1 and for a batch of 8."""
+    from transformers import MixtralConfig
+    from ipex_llm.transformers import AutoModelForCausalLM
+    from ipex_llm_b200 import engine
+    cfg = MixtralConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, vocab_size=1000, max_position_embeddings=512, num_local_experts=8,
+                        num_experts_per_tok=2, tie_word_embeddings=False, sliding_window=None)
+    m = AutoModelForCausalLM.from_config(cfg, load_in_low_bit="sym_int4", torch_dtype=torch.float16, device="cuda")
+    assert engine.supports(m, {})
+    for B, S in ((1, 12), (8, 40)):
+        ids = torch.randint(0, 1000, (B, S), device="cuda", generator=torch.Generator("cuda").manual_seed(B))
+        eng = engine.get_engine(m, B, S + 8)
+        assert eng.has_moe
+        logits = eng.prefill(ids).float()
+        with torch.no_grad():
+            ref = m(ids).logits[:, -1].float()
+        assert (logits - ref).abs().max() < 2e-2 * ref.abs().max(), (logits - ref).abs().max()
+        # two graph-captured decode steps against full forwards over the extended sequences
+        seq = ids
+        for _ in range(2):
+            nxt = ref.argmax(-1)
+            seq = torch.cat([seq, nxt[:, None]], dim=1)
+            eng.tokens[:B] = nxt
+            eng.decode_step(B, use_graph=True)
+            torch.cuda.synchronize()
+            step = eng.logits[:B].float()
+            with torch.no_grad():
+                ref = m(seq).logits[:, -1].float()
+            assert (step - ref).abs().max() < 2e-2 * ref.abs().max(), (step - ref).abs().max()
+        assert len(eng._graphs) > 0, "decode steps were not graph-captured"
+    out = m.generate(ids, max_new_tokens=6, do_sample=False)
+    assert out.shape == (8, 46)
