@@ -335,8 +335,10 @@ class DecoderEngine:
         x = cuda_ops.rms_norm(h1, L.ln2, self.eps)
         scores = torch.matmul(x, L.router.t())
         _, w, idx = cuda_ops.moe_softmax_topk(scores, L.top_k, L.renorm)
-        y = cuda_ops.moe_forward(L.moe, x, idx, w)
-        return torch.add(y, h1, out=out)
+        y = cuda_ops.moe_forward(L.moe, x, idx, w, residual=h1, out=out)
+        if y.data_ptr() != out.data_ptr():
+            out.copy_(y)
+        return out
 
     def _attention(self, L: _Layer, B: int, Sq: int = 1):
         """Rope + cache append + attention for ``B`` sequences of ``Sq`` new tokens each; rows of the activation

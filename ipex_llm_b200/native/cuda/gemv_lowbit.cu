@@ -44,6 +44,13 @@ struct GemvArgs {
   const int64_t* expert_ids;
   int x_div;
   int x_div_slots;  // number of slots (grid.y)
+  // expert-grouped mode (moe_ranges != null): blockIdx.y is an EXPERT, blockIdx.z a group of eight of its slots.
+  // moe_ranges[e] = (first position, count) in the expert-sorted slot list moe_order; the expert's weights are read
+  // once for up to eight tokens.  x row = moe_order[pos] / x_div (moe_gather) or pos; y row = moe_order[pos]
+  // (moe_scatter) or pos.
+  const int* moe_ranges = nullptr;
+  const int* moe_order = nullptr;
+  int moe_gather = 0, moe_scatter = 0, moe_experts = 0, moe_zchunks = 1, moe_rows = 8;
 };
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -101,10 +108,13 @@ __device__ __forceinline__ float load_as_float(const void* p, size_t i) {
 
 // Stage x (optionally RMS-normalised) into shared memory as fp16 rows of stride xs_stride, zero padded to Kp.
 template <typename T>
-__device__ void stage_x(const GemvArgs& a, __half* xs, int xs_stride, int Kp, float* scratch) {
+__device__ void stage_x(const GemvArgs& a, __half* xs, int xs_stride, int Kp, float* scratch,
+                        const int* xrow = nullptr) {
   const int tid = threadIdx.x;
-  const T* x = reinterpret_cast<const T*>(a.x);
+  const T* x0 = reinterpret_cast<const T*>(a.x);
   for (int m = 0; m < a.M; m++) {
+    // rows of x are consecutive, or picked through xrow (expert-grouped mode); x[m * ldx + k] below is row m's k
+    const T* x = xrow != nullptr ? x0 + ((ptrdiff_t)xrow[m] - (ptrdiff_t)m) * (ptrdiff_t)a.ldx : x0;
     float rstd = 1.0f;
     if (a.norm_w != nullptr) {
       float ss = 0.f;
@@ -145,7 +155,22 @@ __global__ void __launch_bounds__(kThreads) gemv_tiled_kernel(GemvArgs a) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int tile_row0 = blockIdx.x * RT;
-  if (a.w_list != nullptr) {
+  __shared__ int s_xrow[8], s_yrow[8];
+  const bool grouped = a.moe_ranges != nullptr;
+  if (grouped) {
+    pdl_wait();                      // the ranges and the order come from the kernel before this one
+    const int e = blockIdx.y, first = a.moe_ranges[2 * e], cnt = a.moe_ranges[2 * e + 1];
+    const int base = blockIdx.z * a.moe_rows;
+    if (base >= cnt) return;
+    a.M = cnt - base < a.moe_rows ? cnt - base : a.moe_rows;
+    a.w = a.w_list[e];
+    if (tid < a.M) {
+      const int pos = first + base + tid, slot = a.moe_order[pos];
+      s_xrow[tid] = a.moe_gather ? slot / a.x_div : pos;
+      s_yrow[tid] = a.moe_scatter ? slot : pos;
+    }
+    __syncthreads();
+  } else if (a.w_list != nullptr) {
     const int slot = blockIdx.y;
     a.w = a.w_list[a.expert_ids[slot]];
     a.x = reinterpret_cast<const T*>(a.x) + (size_t)(slot / a.x_div) * a.ldx;
@@ -187,7 +212,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tiled_kernel(GemvArgs a) {
     __half2 v = __floats2half2_rn(a.lut[tid & 15], a.lut[tid >> 4]);
     lut256[tid] = *reinterpret_cast<uint32_t*>(&v);
   }
-  stage_x<T>(a, xs, xs_stride, Kp, scratch);
+  stage_x<T>(a, xs, xs_stride, Kp, scratch, grouped ? s_xrow : nullptr);
   __syncthreads();
   if (WF == WF_ASYM_INT4) {
     const int groups = Kp / 64;
@@ -388,7 +413,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tiled_kernel(GemvArgs a) {
       if (n < a.N && col < a.M) {
         if (a.bias != nullptr) s += load_as_float<T>(a.bias, n);
         if (a.residual != nullptr) s += load_as_float<T>(a.residual, (size_t)col * a.ldr + n);
-        y[(size_t)col * a.ldy + n] = DT<T>::from_f(s);
+        y[(size_t)(grouped ? s_yrow[col] : col) * a.ldy + n] = DT<T>::from_f(s);
       }
     }
   } else if (RT == 2) {
@@ -407,7 +432,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tiled_kernel(GemvArgs a) {
           gsum += load_as_float<T>(a.bias, (size_t)blockIdx.x * 32 + row);
           usum += load_as_float<T>(a.bias, (size_t)blockIdx.x * 32 + 16 + row);
         }
-        y[(size_t)col * a.ldy + n] = DT<T>::from_f(act_apply(gsum, a.act) * usum);
+        y[(size_t)(grouped ? s_yrow[col] : col) * a.ldy + n] = DT<T>::from_f(act_apply(gsum, a.act) * usum);
       }
     }
   }
@@ -637,6 +662,7 @@ cudaError_t launch_tiled(const GemvArgs& a, cudaStream_t stream, bool pdl) {
     if (e != cudaSuccess) return e;
   }
   dim3 grid((Np / 16 + RT - 1) / RT, a.w_list != nullptr ? a.x_div_slots : 1);
+  if (a.moe_ranges != nullptr) grid = dim3(grid.x, a.moe_experts, a.moe_zchunks);
   return launch_kernel(kern, grid, dim3(kThreads), smem, stream, pdl, a);
 }
 
@@ -732,5 +758,40 @@ IPEX_API int ipex_moe_gemv(const void* w_list, int wf, const void* expert_ids, i
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == DT_F16) return (int)dispatch_wf<__half>(wf, a, s, pdl != 0);
   if (dtype == DT_BF16) return (int)dispatch_wf<__nv_bfloat16>(wf, a, s, pdl != 0);
+  return (int)cudaErrorInvalidValue;
+}
+
+// Tokens of one expert that one CTA of ipex_moe_gemv_grouped multiplies at a time: eight when their staged rows
+// leave room for three CTAs per SM, else as many as keep two CTAs per SM (long contractions).
+IPEX_API int ipex_moe_gemv_group_rows(int K) {
+  const size_t row = ((size_t)ceil_to_i64(K, 128) + 8) * 2;
+  if (8 * row <= 68 * 1024) return 8;
+  int r = (int)((104 * 1024) / row);
+  return r < 1 ? 1 : (r > 8 ? 8 : r);
+}
+
+// Expert-grouped form for small batches: the slots are sorted by expert (ipex_moe_sort_slots) and CTA (tile, e, z)
+// multiplies up to R = ipex_moe_gemv_group_rows(K) of expert e's tokens with one read of its weights.  gather: x row =
+// order[pos] / x_div, else pos; scatter: y row = order[pos], else pos.  zchunks >= ceil(max tokens of one expert / R).
+IPEX_API int ipex_moe_gemv_grouped(const void* w_list, int wf, const void* ranges, const void* order, int experts,
+                                   int zchunks, const void* x, int x_div, int gather, int scatter, void* y, int N,
+                                   int K, int ldx, int ldy, int act, const float* lut, int dtype, void* stream) {
+  if (experts < 1 || experts > 65535 || zchunks < 1 || zchunks > 65535 || x_div < 1 || (K % 64) != 0 ||
+      wf == WF_F16 || wf == WF_BF16 || ranges == nullptr || order == nullptr)
+    return (int)cudaErrorInvalidValue;
+  GemvArgs a;
+  a.w = nullptr; a.x = x; a.y = y; a.norm_w = nullptr; a.bias = nullptr; a.residual = nullptr; a.lut = lut;
+  a.moe_rows = ipex_moe_gemv_group_rows(K);
+  a.M = a.moe_rows; a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy; a.ldr = 0; a.eps = 0.f; a.norm_offset = 0.f;
+  a.act = act;
+  a.w_list = reinterpret_cast<const uint8_t* const*>(w_list);
+  a.expert_ids = nullptr;
+  a.x_div = x_div; a.x_div_slots = 1;
+  a.moe_ranges = reinterpret_cast<const int*>(ranges);
+  a.moe_order = reinterpret_cast<const int*>(order);
+  a.moe_gather = gather; a.moe_scatter = scatter; a.moe_experts = experts; a.moe_zchunks = zchunks;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == DT_F16) return (int)dispatch_wf<__half>(wf, a, s, false);
+  if (dtype == DT_BF16) return (int)dispatch_wf<__nv_bfloat16>(wf, a, s, false);
   return (int)cudaErrorInvalidValue;
 }

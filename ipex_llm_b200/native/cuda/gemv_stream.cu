@@ -1,0 +1,638 @@
+// Low-bit GEMV / skinny GEMM for decode (M <= 8), warp-private streaming version, sm_100a.
+//
+//   y[M, N] = epilogue( prologue(x)[M, K] * dequant(W)[N, K]^T )      W: symmetric int4 or fp8 e4m3 device tiles
+//
+// Same contract and tile layout as gemv_tma.cu.  That kernel splits every 16-row tile over sixteen warps, so at
+// K = 4096 a warp multiplies two 1 KB chunks and then takes part in a sixteen-way reduction through shared-memory
+// atomics and tickets: ~220 warp instructions per chunk, of which fewer than half are the contraction, and a marginal
+// streaming rate of ~2.75 TB/s.  Here the bookkeeping is taken out of the K loop:
+//   * every warp owns a ring of stages and its own mbarriers; lane 0 refills a stage right after the warp has read
+//     it (cp.async.bulk, global -> shared), so the K loop has no cross-warp synchronisation at all and the first
+//     stages are requested before griddepcontrol.wait (weights never depend on the previous kernel);
+//   * a tile is shared by `wpt` warps (1, 2, 4, 8 or 16, chosen on the host so that all warps of the GPU have work):
+//     each takes a contiguous range of the tile's K chunks, accumulates it in registers, and the partial tiles meet
+//     once per tile in a double-buffered shared buffer behind a named barrier of just those warps;
+//   * activations are staged once per CTA as 15-bit integers (int8 hi / lo rows) or e4m3 hi / lo rows, and hi / lo of
+//     a token are two B columns of the same tensor-core instruction (mma.sync m16n8k32 s8 / e4m3), so one MMA per 512
+//     weights serves up to four tokens; five to eight tokens use a second MMA on the same weight operands.
+// Every mbarrier wait is bounded; on expiry the warp records an error code in *err, stops multiplying and keeps
+// attending the barriers of its group so that nobody waits for it.
+#include "common/utils.cuh"
+#include <cuda_fp8.h>
+
+namespace {
+
+constexpr int kW = 16;              // warps per CTA (all of them stream and multiply)
+constexpr int kThreads = kW * 32;
+constexpr int kSpin = 1 << 22;
+constexpr int kPad = 64;            // extra bytes per staged activation row (bank spread)
+constexpr int WFK_I8 = 0, WFK_FP8 = 1;
+
+struct StreamArgs {
+  const uint8_t* w;
+  const void* x;
+  void* y;
+  const void* norm_w;
+  const void* bias;
+  const void* residual;
+  int* err;
+  int M, N, K;
+  int ldx, ldy, ldr;
+  float eps, norm_offset;
+  int act;      // 0 none, 1 silu(gate)*up, 2 gelu_tanh(gate)*up  (row tiles interleaved gate, up)
+  int stages;   // ring depth of a warp
+  int cpw;      // 128-k chunks per stage
+  int wpt;      // warps per tile
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  uint32_t done = 0;
+  for (int i = 0; i < kSpin; i++) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (i >= 8) __nanosleep(i < 64 ? 20 : 100);
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void group_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// D = A * B + {c0, c1, c0, c1}: a token's accumulator seeds (hi, lo) start rows g and g + 8 alike
+__device__ __forceinline__ void mma_s8_seed(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                            uint32_t b0, uint32_t b1, int c0, int c1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1));
+}
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float act_apply(float g, int act) {
+  if (act == 1) return g / (1.0f + __expf(-g));
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  return 0.5f * g * (1.0f + tanhf(k0 * (g + k1 * g * g * g)));
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Activation staging, all 512 threads.  Token m becomes two byte rows of xq (2m: hi, 2m + 1: lo), a scale dxs[m], and
+// (int8 path) per-(64-group, token) accumulator seeds (-8 sum hi, -8 sum lo) that apply the "- 8" of the codes.
+//   int8 : xi = round(x / dx) in [-16383, 16383], hi = xi >> 7, lo = xi & 127, bytes in the octet order
+//          (k0,k4,k1,k5 | k2,k6,k3,k7) of the masked weight words;
+//   fp8  : hi = e4m3(x / dx), lo = e4m3(x / dx - hi), natural k order.
+// RMS norm fused (norm_w != null); rows zero padded to Kp.  scratch: [M][2][kW] floats.
+// ------------------------------------------------------------------------------------------------------------------
+template <typename T, int WFK>
+__device__ void stage_x(const StreamArgs& a, uint8_t* xq, int2* seeds, int NT, float* dxs, float* scratch, int Kp) {
+  const int tid = threadIdx.x;
+  const int M = a.M;
+  const T* x = reinterpret_cast<const T*>(a.x);
+  const T* nw = reinterpret_cast<const T*>(a.norm_w);
+  const int nvec = a.K / 8;   // K % 64 == 0
+  const int stride = Kp + kPad;
+  const int groups = Kp / 64;
+  if (WFK == WFK_I8)
+    for (int i = tid; i < groups * NT; i += kThreads)
+      if ((i % NT) >= M) seeds[i] = make_int2(0, 0);
+  // The sixteen warps split into one team per row (sixteen, eight, four or two warps each), so the rows are
+  // staged side by side: every global load of a row is in flight at once instead of row after row.
+  const int warp = tid >> 5;
+  const int wpr = M <= 1 ? 16 : (M <= 2 ? 8 : (M <= 4 ? 4 : 2));   // warps per row
+  const int m = warp / wpr;                                         // this thread's row (>= M: none)
+  const int tr = (warp % wpr) * 32 + (tid & 31), team = wpr * 32;
+  const T* xr = x + (size_t)(m < M ? m : 0) * a.ldx;
+  // pass 1: sum of squares and largest |x * w| of the row
+  if (m < M) {
+    float ss = 0.f, mx = 0.f;
+    for (int v = tr; v < nvec; v += team) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(xr + v * 8);
+      const T* e = reinterpret_cast<const T*>(&raw);
+      uint4 wraw = make_uint4(0, 0, 0, 0);
+      if (nw != nullptr) wraw = *reinterpret_cast<const uint4*>(nw + v * 8);
+      const T* we = reinterpret_cast<const T*>(&wraw);
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        float f = DT<T>::to_f(e[j]);
+        ss += f * f;
+        if (nw != nullptr) f *= DT<T>::to_f(we[j]) + a.norm_offset;
+        mx = fmaxf(mx, fabsf(f));
+      }
+    }
+    ss = warp_sum(ss);
+    mx = warp_max(mx);
+    if ((tid & 31) == 0) {
+      scratch[(m * 2) * kW + (warp % wpr)] = ss;
+      scratch[(m * 2 + 1) * kW + (warp % wpr)] = mx;
+    }
+  }
+  __syncthreads();
+  // pass 2: quantize
+  if (m < M) {
+    float tot = 0.f, amax = 0.f;
+    for (int w = 0; w < wpr; w++) {
+      tot += scratch[(m * 2) * kW + w];
+      amax = fmaxf(amax, scratch[(m * 2 + 1) * kW + w]);
+    }
+    const float rstd = nw != nullptr ? rsqrtf(tot / (float)a.K + a.eps) : 1.0f;
+    amax *= rstd;
+    const float top = WFK == WFK_I8 ? 16383.f : 448.f;
+    const float dx = amax > 0.f ? amax / top : 1.0f;
+    const float inv = rstd / dx;
+    if (tr == 0) dxs[m] = dx;
+    uint8_t* xh = xq + (size_t)(2 * m) * stride;
+    uint8_t* xl = xq + (size_t)(2 * m + 1) * stride;
+    for (int v0 = 0; v0 < Kp / 8; v0 += team) {
+      const int v = v0 + tr;
+      int sh = 0, sl = 0;
+      if (v < Kp / 8) {
+        uint32_t ph[2] = {0, 0}, pl[2] = {0, 0};
+        if (v < nvec) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(xr + v * 8);
+          const T* e = reinterpret_cast<const T*>(&raw);
+          uint4 wraw = make_uint4(0, 0, 0, 0);
+          if (nw != nullptr) wraw = *reinterpret_cast<const uint4*>(nw + v * 8);
+          const T* we = reinterpret_cast<const T*>(&wraw);
+          if constexpr (WFK == WFK_I8) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+              float f = DT<T>::to_f(e[j]);
+              if (nw != nullptr) f *= DT<T>::to_f(we[j]) + a.norm_offset;
+              int xi = __float2int_rn(f * inv);
+              xi = max(-16383, min(16383, xi));
+              const int hi = xi >> 7, lo = xi & 127;
+              sh += hi;
+              sl += lo;
+              const int pos = ((j & 2) ? 4 : 0) + ((j & 1) ? 2 : 0) + ((j & 4) ? 1 : 0);
+              ph[pos >> 2] |= (uint32_t)(hi & 0xFF) << (8 * (pos & 3));
+              pl[pos >> 2] |= (uint32_t)lo << (8 * (pos & 3));
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+              float f0 = DT<T>::to_f(e[j]), f1 = DT<T>::to_f(e[j + 1]);
+              if (nw != nullptr) {
+                f0 *= DT<T>::to_f(we[j]) + a.norm_offset;
+                f1 *= DT<T>::to_f(we[j + 1]) + a.norm_offset;
+              }
+              f0 *= inv;
+              f1 *= inv;
+              const __nv_fp8x2_storage_t h = __nv_cvt_float2_to_fp8x2(make_float2(f0, f1), __NV_SATFINITE, __NV_E4M3);
+              const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(h, __NV_E4M3);
+              const float r0 = f0 - __half2float(__ushort_as_half(hr.x));
+              const float r1 = f1 - __half2float(__ushort_as_half(hr.y));
+              const __nv_fp8x2_storage_t l = __nv_cvt_float2_to_fp8x2(make_float2(r0, r1), __NV_SATFINITE, __NV_E4M3);
+              ph[j >> 2] |= (uint32_t)h << (16 * ((j >> 1) & 1));
+              pl[j >> 2] |= (uint32_t)l << (16 * ((j >> 1) & 1));
+            }
+          }
+        }
+        *reinterpret_cast<uint2*>(xh + v * 8) = make_uint2(ph[0], ph[1]);
+        *reinterpret_cast<uint2*>(xl + v * 8) = make_uint2(pl[0], pl[1]);
+      }
+      if constexpr (WFK == WFK_I8) {
+        // 8 consecutive octets (= 8 consecutive lanes) form a 64-group
+        sh += __shfl_xor_sync(0xffffffffu, sh, 1); sl += __shfl_xor_sync(0xffffffffu, sl, 1);
+        sh += __shfl_xor_sync(0xffffffffu, sh, 2); sl += __shfl_xor_sync(0xffffffffu, sl, 2);
+        sh += __shfl_xor_sync(0xffffffffu, sh, 4); sl += __shfl_xor_sync(0xffffffffu, sl, 4);
+        if ((tid & 7) == 0 && v < Kp / 8) seeds[(v >> 3) * NT + m] = make_int2(-8 * sh, -8 * sl);
+      }
+    }
+  }
+  __syncthreads();
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// One stage (nch chunks of one 16-row tile, starting at chunk c0 of the row) by one warp.
+// acc[h][0] += row g, acc[h][1] += row g + 8 of token t + 4h (unscaled by the token's dx).
+// ------------------------------------------------------------------------------------------------------------------
+template <int MH>
+__device__ __forceinline__ void stage_mma_i8(const uint8_t* st, int cpw, int nch, int c0, const uint8_t* xq,
+                                             const int2* seeds, int M, int stride, float (&acc)[MH][2]) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  constexpr uint32_t kM = 0x0F0F0F0Fu;
+  constexpr int NT = 4 * MH;
+  const uint8_t* sc = st + cpw * 1024;
+  const bool has_x0 = g < 2 * (M < 4 ? M : 4);
+  const bool has_x1 = MH > 1 && g < 2 * (M - 4);
+  const uint8_t* xrow0 = xq + (size_t)g * stride + 16 * t;
+  const uint8_t* xrow1 = xq + (size_t)(g + 8) * stride + 16 * t;
+#pragma unroll 2
+  for (int ch = 0; ch < nch; ch++) {
+    const int cg = c0 + ch;
+    const uint8_t* tp = st + ch * 1024;
+    const uint4 qa = *reinterpret_cast<const uint4*>(tp + g * 64 + t * 16);
+    const uint4 qb = *reinterpret_cast<const uint4*>(tp + (g + 8) * 64 + t * 16);
+    const uint32_t s0 = *reinterpret_cast<const uint32_t*>(sc + ch * 64 + (0 * 16 + 2 * g) * 2);
+    const uint32_t s1 = *reinterpret_cast<const uint32_t*>(sc + ch * 64 + (1 * 16 + 2 * g) * 2);
+    const float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&s0));
+    const float2 d1 = __half22float2(*reinterpret_cast<const __half2*>(&s1));
+    const uint32_t a00 = qa.x & kM, a01 = qb.x & kM, a02 = (qa.x >> 4) & kM, a03 = (qb.x >> 4) & kM;
+    const uint32_t a10 = qa.z & kM, a11 = qb.z & kM, a12 = (qa.z >> 4) & kM, a13 = (qb.z >> 4) & kM;
+    const uint32_t a20 = qa.y & kM, a21 = qb.y & kM, a22 = (qa.y >> 4) & kM, a23 = (qb.y >> 4) & kM;
+    const uint32_t a30 = qa.w & kM, a31 = qb.w & kM, a32 = (qa.w >> 4) & kM, a33 = (qb.w >> 4) & kM;
+#pragma unroll
+    for (int h = 0; h < MH; h++) {
+      uint4 xa = make_uint4(0, 0, 0, 0), xb = xa;
+      if (h == 0 ? has_x0 : has_x1) {
+        const uint8_t* xr = h == 0 ? xrow0 : xrow1;
+        xa = *reinterpret_cast<const uint4*>(xr + cg * 128);
+        xb = *reinterpret_cast<const uint4*>(xr + cg * 128 + 64);
+      }
+      const int2 sd0 = seeds[(2 * cg) * NT + 4 * h + t];
+      const int2 sd1 = seeds[(2 * cg + 1) * NT + 4 * h + t];
+      int c0v[4], c1v[4];
+      mma_s8_seed(c0v, a00, a01, a02, a03, xa.x, xa.y, sd0.x, sd0.y);
+      mma_s8_seed(c1v, a10, a11, a12, a13, xb.x, xb.y, sd1.x, sd1.y);
+      mma_s8(c0v, a20, a21, a22, a23, xa.z, xa.w);
+      mma_s8(c1v, a30, a31, a32, a33, xb.z, xb.w);
+      acc[h][0] += d0.x * (float)(c0v[0] * 128 + c0v[1]) + d1.x * (float)(c1v[0] * 128 + c1v[1]);
+      acc[h][1] += d0.y * (float)(c0v[2] * 128 + c0v[3]) + d1.y * (float)(c1v[2] * 128 + c1v[3]);
+    }
+  }
+}
+
+// fp8 e4m3 weights against the e4m3 (hi, lo) activation rows: no conversion of the codes at all.  A 128-k chunk is
+// two [16 rows][64 B] tiles in natural k order; a lane's 16 bytes of a weight row and the same 16 bytes of an
+// activation row are the operands of two m16n8k32 MMAs (the contraction order of the instruction is permuted the
+// same way on both sides, which leaves the sum unchanged).  One fp32 scale per (row, 128 k).
+template <int MH>
+__device__ __forceinline__ void stage_mma_fp8(const uint8_t* st, int cpw, int nch, int c0, const uint8_t* xq, int M,
+                                              int stride, float (&acc)[MH][2]) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const uint8_t* sc = st + cpw * 2048;
+  const bool has_x0 = g < 2 * (M < 4 ? M : 4);
+  const bool has_x1 = MH > 1 && g < 2 * (M - 4);
+  const uint8_t* xrow0 = xq + (size_t)g * stride + 16 * t;
+  const uint8_t* xrow1 = xq + (size_t)(g + 8) * stride + 16 * t;
+#pragma unroll 2
+  for (int ch = 0; ch < nch; ch++) {
+    const int cg = c0 + ch;
+    const uint8_t* tp = st + ch * 2048 + g * 64 + t * 16;
+    const uint4 qa0 = *reinterpret_cast<const uint4*>(tp);
+    const uint4 qb0 = *reinterpret_cast<const uint4*>(tp + 512);
+    const uint4 qa1 = *reinterpret_cast<const uint4*>(tp + 1024);
+    const uint4 qb1 = *reinterpret_cast<const uint4*>(tp + 1536);
+    const float2 d = *reinterpret_cast<const float2*>(sc + ch * 64 + 2 * g * 4);
+#pragma unroll
+    for (int h = 0; h < MH; h++) {
+      uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
+      if (h == 0 ? has_x0 : has_x1) {
+        const uint8_t* xr = h == 0 ? xrow0 : xrow1;
+        x0 = *reinterpret_cast<const uint4*>(xr + cg * 128);
+        x1 = *reinterpret_cast<const uint4*>(xr + cg * 128 + 64);
+      }
+      float c0v[4] = {0.f, 0.f, 0.f, 0.f}, c1v[4] = {0.f, 0.f, 0.f, 0.f};
+      mma_e4m3(c0v, qa0.x, qb0.x, qa0.y, qb0.y, x0.x, x0.y);
+      mma_e4m3(c1v, qa1.x, qb1.x, qa1.y, qb1.y, x1.x, x1.y);
+      mma_e4m3(c0v, qa0.z, qb0.z, qa0.w, qb0.w, x0.z, x0.w);
+      mma_e4m3(c1v, qa1.z, qb1.z, qa1.w, qb1.w, x1.z, x1.w);
+      acc[h][0] += d.x * ((c0v[0] + c0v[1]) + (c1v[0] + c1v[1]));
+      acc[h][1] += d.y * ((c0v[2] + c0v[3]) + (c1v[2] + c1v[3]));
+    }
+  }
+}
+
+// Position of a warp in its sequence of stages: unit (RT consecutive row tiles), tile of the unit, stage of the tile.
+struct Walk {
+  int unit, r, sp;
+};
+
+template <typename T, int WFK, int RT, int MH>
+__global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const StreamArgs a) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  constexpr int CB = WFK == WFK_I8 ? 1024 : 2048;   // code bytes per 128-k chunk of a row tile
+  constexpr int SB = 64;                            // scale bytes per chunk
+  constexpr int NT = 4 * MH;
+  const int Kp = (int)ceil_to_i64(a.K, 128);
+  const int Np = (int)ceil_to_i64(a.N, 16);
+  const int chunks = Kp / 128;
+  const int stride = Kp + kPad;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int S = a.stages, CPW = a.cpw, wpt = a.wpt;
+  const int stage_bytes = CPW * (CB + SB);
+  const int ntiles = Np / 16;
+  const int nunits = (ntiles + RT - 1) / RT;
+  const int G = kW / wpt, grp = warp / wpt, wi = warp % wpt;
+  // this warp's chunks of every tile, and how many stages they make
+  const int cper = (chunks + wpt - 1) / wpt;
+  const int cbeg = wi * cper < chunks ? wi * cper : chunks;
+  const int cend = cbeg + cper < chunks ? cbeg + cper : chunks;
+  const int spt = (cend - cbeg + CPW - 1) / CPW;
+  const int ustep = gridDim.x * G;
+  const int unit0 = blockIdx.x + gridDim.x * grp;
+
+  // shared memory: rings | barriers | xq | seeds | dxs | scratch | reduction buffers
+  uint8_t* ring = smem_raw + (size_t)warp * S * stage_bytes;
+  size_t off = (size_t)kW * S * stage_bytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw + off) + warp * S;
+  off += (size_t)kW * S * sizeof(uint64_t);
+  off = (off + 15) & ~(size_t)15;
+  uint8_t* xq = smem_raw + off;
+  off += ((size_t)2 * a.M * stride + 15) & ~(size_t)15;
+  int2* seeds = reinterpret_cast<int2*>(smem_raw + off);
+  if (WFK == WFK_I8) off += (size_t)(Kp / 64) * NT * sizeof(int2);
+  float* dxs = reinterpret_cast<float*>(smem_raw + off);
+  off += 32;
+  float* scratch = reinterpret_cast<float*>(smem_raw + off);
+  off += (size_t)8 * 2 * kW * sizeof(float);
+  float* red = reinterpret_cast<float*>(smem_raw + off);   // [G][2][wpt][RT * MH * 2][32] when wpt > 1
+
+  const uint8_t* codes = a.w;
+  const size_t code_bytes = (size_t)Np * chunks * CB / 16;
+  const uint8_t* scales = a.w + code_bytes;
+
+  // lane 0 requests stage `w` of this warp into ring slot `slot`
+  auto issue = [&](const Walk& w, int slot) {
+    const int tile = w.unit * RT + w.r;
+    const int c0 = cbeg + w.sp * CPW;
+    const int nch = cend - c0 < CPW ? cend - c0 : CPW;
+    uint8_t* dst = ring + (size_t)slot * stage_bytes;
+    mbar_expect_tx(&full[slot], (uint32_t)(nch * (CB + SB)));
+    const size_t chunk_index = (size_t)tile * chunks + c0;
+    bulk_g2s(dst, codes + chunk_index * CB, (uint32_t)(nch * CB), &full[slot]);
+    bulk_g2s(dst + CPW * CB, scales + chunk_index * SB, (uint32_t)(nch * SB), &full[slot]);
+  };
+  // next stage of the warp's sequence; false when the sequence has ended
+  auto advance = [&](Walk& w) {
+    if (++w.sp < spt) return true;
+    w.sp = 0;
+    if (++w.r < RT && w.unit * RT + w.r < ntiles) return true;
+    w.r = 0;
+    w.unit += ustep;
+    return w.unit < nunits;
+  };
+
+  Walk iw = {unit0, 0, 0};
+  bool more = unit0 < nunits && spt > 0;   // stages left to request
+  if (lane == 0) {
+    for (int s = 0; s < S; s++) mbar_init(&full[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // fill the ring before waiting for the previous kernel: the weights do not depend on it
+    for (int s = 0; s < S && more; s++) {
+      issue(iw, s);
+      more = advance(iw);
+    }
+  }
+  __syncwarp();
+  pdl_launch_dependents();
+  pdl_wait();
+  stage_x<T, WFK>(a, xq, seeds, NT, dxs, scratch, Kp);
+
+  T* y = reinterpret_cast<T*>(a.y);
+  bool ok = true;
+  int slot = 0;
+  uint32_t phase = 0;
+  int nu = 0;   // units done (parity of the reduction buffer)
+  for (int unit = unit0; unit < nunits; unit += ustep, nu++) {
+    float acc[RT][MH][2];
+#pragma unroll
+    for (int r = 0; r < RT; r++)
+#pragma unroll
+      for (int h = 0; h < MH; h++) acc[r][h][0] = acc[r][h][1] = 0.f;
+#pragma unroll
+    for (int r = 0; r < RT; r++) {
+      if (unit * RT + r >= ntiles) break;
+      for (int sp = 0; sp < spt; sp++) {
+        if (ok && !mbar_wait(&full[slot], phase)) {
+          if (lane == 0) atomicExch(a.err, 2);
+          ok = false;
+        }
+        if (ok) {
+          const int c0 = cbeg + sp * CPW;
+          const int nch = cend - c0 < CPW ? cend - c0 : CPW;
+          const uint8_t* st = ring + (size_t)slot * stage_bytes;
+          if constexpr (WFK == WFK_I8) stage_mma_i8<MH>(st, CPW, nch, c0, xq, seeds, a.M, stride, acc[r]);
+          else stage_mma_fp8<MH>(st, CPW, nch, c0, xq, a.M, stride, acc[r]);
+        }
+        __syncwarp();
+        if (lane == 0 && ok && more) {
+          // the warp's reads of this slot (generic proxy) are ordered before the refill (async proxy)
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          issue(iw, slot);
+          more = advance(iw);
+        }
+        if (++slot == S) { slot = 0; phase ^= 1; }
+      }
+    }
+    // ---- the wpt partial tiles meet in shared memory; warp 0 of the group finishes the unit ----
+    if (wpt > 1) {
+      float* buf = red + ((size_t)(grp * 2 + (nu & 1)) * wpt) * (RT * MH * 2 * 32);
+      if (wi != 0) {
+#pragma unroll
+        for (int r = 0; r < RT; r++)
+#pragma unroll
+          for (int h = 0; h < MH; h++) {
+            buf[((size_t)wi * RT * MH * 2 + (r * MH + h) * 2 + 0) * 32 + lane] = acc[r][h][0];
+            buf[((size_t)wi * RT * MH * 2 + (r * MH + h) * 2 + 1) * 32 + lane] = acc[r][h][1];
+          }
+      }
+      group_sync(1 + grp, wpt * 32);
+      if (wi != 0) continue;
+      for (int w = 1; w < wpt; w++) {
+#pragma unroll
+        for (int r = 0; r < RT; r++)
+#pragma unroll
+          for (int h = 0; h < MH; h++) {
+            acc[r][h][0] += buf[((size_t)w * RT * MH * 2 + (r * MH + h) * 2 + 0) * 32 + lane];
+            acc[r][h][1] += buf[((size_t)w * RT * MH * 2 + (r * MH + h) * 2 + 1) * 32 + lane];
+          }
+      }
+    }
+    if (!ok) continue;
+    // ---- epilogue: lane (g, t) holds rows g and g + 8 of the unit's tiles for tokens t and t + 4 ----
+#pragma unroll
+    for (int h = 0; h < MH; h++) {
+      const int m = t + 4 * h;
+      if (m >= a.M) continue;
+      const float dx = dxs[m];
+      if (RT == 2 && a.act != 0) {
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+          const int row = g + 8 * half;
+          const int n = unit * 16 + row;
+          if (n >= a.N / 2) continue;
+          float gsum = acc[0][h][half] * dx, usum = acc[RT - 1][h][half] * dx;
+          if (a.bias != nullptr) {
+            gsum += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[(size_t)unit * 32 + row]);
+            usum += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[(size_t)unit * 32 + 16 + row]);
+          }
+          y[(size_t)m * a.ldy + n] = DT<T>::from_f(act_apply(gsum, a.act) * usum);
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < RT; r++)
+#pragma unroll
+          for (int half = 0; half < 2; half++) {
+            const int n = (unit * RT + r) * 16 + g + 8 * half;
+            if (n >= a.N) continue;
+            float sv = acc[r][h][half] * dx;
+            if (a.bias != nullptr) sv += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[n]);
+            if (a.residual != nullptr)
+              sv += DT<T>::to_f(reinterpret_cast<const T*>(a.residual)[(size_t)m * a.ldr + n]);
+            y[(size_t)m * a.ldy + n] = DT<T>::from_f(sv);
+          }
+      }
+    }
+  }
+}
+
+struct Plan {
+  int stages, cpw, wpt, grid;
+  size_t smem;
+};
+
+int g_ring_kb = 168;   // shared memory of one CTA given to the sixteen rings (ipex_gemv_stream_tune)
+int g_cpw = 0;         // chunks per stage, 0 = automatic
+int g_wpt = 0;         // warps per tile, 0 = automatic
+
+template <int WFK, int RT, int MH>
+bool make_plan(const StreamArgs& a, Plan& p) {
+  constexpr int CB = WFK == WFK_I8 ? 1024 : 2048;
+  const int Kp = (int)ceil_to_i64(a.K, 128), Np = (int)ceil_to_i64(a.N, 16);
+  const int chunks = Kp / 128;
+  const int nunits = (Np / 16 + RT - 1) / RT;
+  const int sms = 148;
+  p.grid = nunits < sms ? nunits : sms;
+  // warps per tile: as few as keep every warp of the GPU busy (a warp needs at least two chunks of the tile).
+  // Wider splits balance the groups of an SM better on paper but did not measure faster (more reductions, shorter
+  // uninterrupted runs per warp).
+  int wpt = g_wpt;
+  if (wpt <= 0) {
+    wpt = 1;
+    while (wpt < kW && (int64_t)nunits * wpt < (int64_t)p.grid * kW && 2 * wpt <= chunks) wpt *= 2;
+  }
+  while (wpt > 1 && 2 * wpt > chunks) wpt /= 2;
+  p.wpt = wpt;
+  const int cper = (chunks + wpt - 1) / wpt;
+  size_t fixed = (size_t)kW * 16 * 8 + 16 + (((size_t)2 * a.M * (Kp + kPad) + 15) & ~(size_t)15) + 32 +
+                 (size_t)8 * 2 * kW * 4 + 128;
+  if (WFK == WFK_I8) fixed += (size_t)(Kp / 64) * 4 * MH * 8;
+  if (wpt > 1) fixed += (size_t)kW * 2 * RT * MH * 2 * 32 * 4;
+  const size_t cap = 227 * 1024;
+  if (fixed + (size_t)kW * 2 * (CB + 64) > cap) return false;
+  size_t ring = (size_t)g_ring_kb * 1024;
+  if (fixed + ring > cap) ring = cap - fixed;
+  const size_t per_warp = ring / kW;
+  // stage size: at most the warp's share of a tile, about a third of its ring, at least one chunk
+  int cpw = g_cpw > 0 ? g_cpw : (int)(per_warp / 3 / (CB + 64));
+  if (cpw > cper) cpw = cper;
+  if (cpw > 8) cpw = 8;
+  if (cpw < 1) cpw = 1;
+  int stages = (int)(per_warp / ((size_t)cpw * (CB + 64)));
+  if (stages > 16) stages = 16;
+  if (stages < 2) return false;
+  p.cpw = cpw;
+  p.stages = stages;
+  p.smem = fixed + (size_t)kW * stages * cpw * (CB + 64);
+  return p.smem <= cap;
+}
+
+template <typename T, int WFK, int RT, int MH>
+cudaError_t launch_stream(StreamArgs a, cudaStream_t stream, bool pdl) {
+  Plan p;
+  if (!make_plan<WFK, RT, MH>(a, p)) return cudaErrorInvalidValue;
+  a.stages = p.stages;
+  a.cpw = p.cpw;
+  a.wpt = p.wpt;
+  auto kern = gemv_stream_kernel<T, WFK, RT, MH>;
+  if (p.smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
+    if (e != cudaSuccess) return e;
+  }
+  return launch_kernel(kern, dim3(p.grid), dim3(kThreads), p.smem, stream, pdl, a);
+}
+
+template <typename T, int WFK>
+cudaError_t dispatch(const StreamArgs& a, cudaStream_t s, bool pdl) {
+  if (a.act != 0) {
+    return a.M <= 4 ? launch_stream<T, WFK, 2, 1>(a, s, pdl) : launch_stream<T, WFK, 2, 2>(a, s, pdl);
+  }
+  return a.M <= 4 ? launch_stream<T, WFK, 1, 1>(a, s, pdl) : launch_stream<T, WFK, 1, 2>(a, s, pdl);
+}
+
+}  // namespace
+
+// Process-wide tuning: shared memory given to the rings (<= 0 keeps it), chunks per stage and warps per tile
+// (0 = automatic, negative keeps the setting).
+IPEX_API void ipex_gemv_stream_tune(int ring_kb, int chunks_per_stage, int warps_per_tile) {
+  if (ring_kb > 0) g_ring_kb = ring_kb > 200 ? 200 : ring_kb;
+  if (chunks_per_stage >= 0) g_cpw = chunks_per_stage > 8 ? 8 : chunks_per_stage;
+  if (warps_per_tile >= 0 && (warps_per_tile & (warps_per_tile - 1)) == 0 && warps_per_tile <= kW)
+    g_wpt = warps_per_tile;
+}
+
+// Same arguments as ipex_gemv_lowbit_tma; weight families: symmetric int4 and fp8 e4m3.  Returns
+// cudaErrorInvalidValue for anything else or when the staged activations leave no room for the rings (the caller
+// then uses the other GEMV kernels).  *err: 2 = a bounded wait for weight data expired.
+IPEX_API int ipex_gemv_lowbit_stream(const void* w, int wf, const void* x, void* y, int M, int N, int K, int ldx,
+                                     int ldy, const void* norm_w, float eps, float norm_offset, const void* bias,
+                                     const void* residual, int ldr, int act, const float* lut, int dtype, int pdl,
+                                     int* err, void* stream) {
+  (void)lut;
+  if (M < 1 || M > 8 || N < 1 || (K % 64) != 0 || err == nullptr) return (int)cudaErrorInvalidValue;
+  if ((ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0) return (int)cudaErrorInvalidValue;
+  if (wf != WF_SYM_INT4 && wf != WF_FP8_E4M3) return (int)cudaErrorInvalidValue;
+  if (wf == WF_FP8_E4M3 && (K % 128) != 0) return (int)cudaErrorInvalidValue;
+  if (act != 0 && (N % 32) != 0) return (int)cudaErrorInvalidValue;
+  StreamArgs a;
+  a.w = (const uint8_t*)w; a.x = x; a.y = y; a.norm_w = norm_w; a.bias = bias; a.residual = residual;
+  a.err = err;
+  a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy; a.ldr = ldr; a.eps = eps; a.norm_offset = norm_offset;
+  a.act = act; a.stages = 0; a.cpw = 0; a.wpt = 1;
+  cudaStream_t s = (cudaStream_t)stream;
+  auto run = [&](const StreamArgs& b, bool dep) -> int {
+    if (dtype == DT_F16) {
+      return wf == WF_SYM_INT4 ? (int)dispatch<__half, WFK_I8>(b, s, dep) : (int)dispatch<__half, WFK_FP8>(b, s, dep);
+    }
+    if (dtype == DT_BF16) {
+      return wf == WF_SYM_INT4 ? (int)dispatch<__nv_bfloat16, WFK_I8>(b, s, dep)
+                               : (int)dispatch<__nv_bfloat16, WFK_FP8>(b, s, dep);
+    }
+    return (int)cudaErrorInvalidValue;
+  };
+  int rc = run(a, pdl != 0);
+  if (rc != (int)cudaErrorInvalidValue || M <= 4) return rc;
+  // five to eight rows of a long contraction do not fit beside the rings: two launches of up to four rows each
+  // (the weights are streamed twice, still far cheaper than leaving the pipelined kernels)
+  const size_t es = 2;   // fp16 / bf16
+  StreamArgs lo = a, hi = a;
+  lo.M = 4;
+  hi.M = M - 4;
+  hi.x = reinterpret_cast<const uint8_t*>(x) + (size_t)4 * ldx * es;
+  hi.y = reinterpret_cast<uint8_t*>(y) + (size_t)4 * ldy * es;
+  if (residual != nullptr) hi.residual = reinterpret_cast<const uint8_t*>(residual) + (size_t)4 * ldr * es;
+  rc = run(lo, pdl != 0);
+  if (rc != 0) return rc;
+  return run(hi, pdl != 0);
+}

@@ -45,6 +45,62 @@ struct TmaArgs {
   int tp_rank, tp_world, tp_npad;
   float* const* tp_bufs;   // [tp_world] device pointers: rank r's partial buffer [tp_world][8][tp_npad] fp32
   int* const* tp_flags;    // [tp_world] device pointers: rank r's per-tile arrival counters
+  // mixture-of-experts mode (moe_ranges != null): ONE launch walks every expert that received tokens.  The
+  // (token, choice) slots are sorted by expert: moe_ranges[e] = (first position, count) in moe_order.  For each
+  // expert (and each group of at most M of its tokens) the CTA stages those rows of x again and streams its share
+  // of the expert's row tiles; the weight ring keeps flowing across experts.  x row = moe_order[pos] / moe_xdiv
+  // (moe_gather) or pos; y row = moe_order[pos] (moe_scatter) or pos.
+  const uint8_t* const* moe_w = nullptr;
+  const int* moe_ranges = nullptr;
+  const int* moe_order = nullptr;
+  int moe_experts = 0, moe_slots = 0, moe_gather = 0, moe_scatter = 0, moe_xdiv = 1;
+};
+
+// Barrier of the kCW consumer warps with a bounded wait: sync[0] counts arrivals (monotonic, `target` = warps x
+// passes so far), sync[1] != 0 means a warp gave up.  Returns false if the others did not arrive.
+__device__ __forceinline__ bool pass_barrier(int* sync, int target) {
+  __syncwarp();
+  int good = 1;
+  if ((threadIdx.x & 31) == 0) {
+    __threadfence_block();
+    atomicAdd(sync, 1);
+    good = 0;
+    for (int i = 0; i < (1 << 22); i++) {
+      if (*(volatile int*)(sync + 1) != 0) break;
+      if (*(volatile int*)sync >= target) { good = 1; break; }
+      __nanosleep(32);
+    }
+    __threadfence_block();
+  }
+  good = __shfl_sync(0xffffffffu, good, 0);
+  return good != 0;
+}
+
+// Enumerates the passes of a launch: one for a plain GEMV; in mixture-of-experts mode one per (expert that received
+// tokens, group of at most `mcap` of them).  Producer and consumers walk the same sequence.
+struct PassWalk {
+  int e = -1, base = 0, cnt = 0, first = 0;
+  __device__ bool next(const TmaArgs& a, int mcap) {
+    if (a.moe_ranges == nullptr) {
+      if (e >= 0) return false;
+      e = 0;
+      return true;
+    }
+    if (e >= 0) {
+      base += mcap;
+      if (base < cnt) return true;
+    }
+    for (++e; e < a.moe_experts; ++e) {
+      cnt = a.moe_ranges[2 * e + 1];
+      cnt = cnt < a.moe_slots ? cnt : a.moe_slots;
+      if (cnt > 0) {
+        first = a.moe_ranges[2 * e];
+        base = 0;
+        return true;
+      }
+    }
+    return false;
+  }
 };
 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
@@ -142,13 +198,14 @@ __device__ __forceinline__ float act_apply(float g, int act) {
 
 // x -> fp16 rows in shared memory (optionally RMS-normalised), zero padded to Kp; consumer threads only
 template <typename T, bool PRESCALE>
-__device__ void stage_x(const TmaArgs& a, __half* xs, int xs_stride, int Kp, float* scratch) {
+__device__ void stage_x(const TmaArgs& a, __half* xs, int xs_stride, int Kp, float* scratch,
+                        const int* xrow = nullptr) {
   const int tid = threadIdx.x;
   const T* x = reinterpret_cast<const T*>(a.x);
   const T* nw = reinterpret_cast<const T*>(a.norm_w);
   const int nvec = a.K / 8;  // K % 64 == 0
   for (int m = 0; m < a.M; m++) {
-    const T* xr = x + (size_t)m * a.ldx;
+    const T* xr = x + (size_t)(xrow != nullptr ? xrow[m] : m) * a.ldx;
     float rstd = 1.0f;
     if (nw != nullptr) {
       float ss = 0.f;
@@ -216,7 +273,7 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
 //   xh / xl : [M][Kp + kI8Pad] bytes      dxs : [8] floats      seeds : [Kp/64][8 tokens] int2 = (-8 sum hi, -8 sum lo)
 template <typename T>
 __device__ void stage_x_i8(const TmaArgs& a, int8_t* xh, int8_t* xl, int stride, int Kp, float* dxs, int2* seeds,
-                           float* scratch) {
+                           float* scratch, const int* xrow = nullptr) {
   const int tid = threadIdx.x;
   const T* x = reinterpret_cast<const T*>(a.x);
   const T* nw = reinterpret_cast<const T*>(a.norm_w);
@@ -226,7 +283,7 @@ __device__ void stage_x_i8(const TmaArgs& a, int8_t* xh, int8_t* xl, int stride,
     if ((i & 7) >= a.M) seeds[i] = make_int2(0, 0);
   if (tid < 8) dxs[tid] = 0.f;
   for (int m = 0; m < a.M; m++) {
-    const T* xr = x + (size_t)m * a.ldx;
+    const T* xr = x + (size_t)(xrow != nullptr ? xrow[m] : m) * a.ldx;
     float ss = 0.f, mx = 0.f;
     for (int v = tid; v < nvec; v += kCThreads) {
       const uint4 raw = *reinterpret_cast<const uint4*>(xr + v * 8);
@@ -311,6 +368,8 @@ __global__ void __launch_bounds__(kThreadsTma, IPEX_GEMV_MIN_BLOCKS) gemv_tma_ke
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int STAGES = a.stages, CPS = a.cps;
+  const int Mcap = a.M;                  // rows the shared-memory layout holds; a.M becomes the rows of the pass
+  const bool moe = a.moe_ranges != nullptr;
   const int stage_bytes = CPS * (CB + SB + MB);
   const int stages_per_tile = (chunks + CPS - 1) / CPS;
   const int ntiles = Np / 16;
@@ -324,7 +383,7 @@ __global__ void __launch_bounds__(kThreadsTma, IPEX_GEMV_MIN_BLOCKS) gemv_tma_ke
   off += (size_t)2 * STAGES * sizeof(uint64_t);
   off = (off + 15) & ~(size_t)15;
   __half* xs = reinterpret_cast<__half*>(smem_raw + off);
-  off += ((size_t)a.M * xs_stride * sizeof(__half) + 15) & ~(size_t)15;
+  off += ((size_t)Mcap * xs_stride * sizeof(__half) + 15) & ~(size_t)15;
   float* red = reinterpret_cast<float*>(smem_raw + off);      // [kNB][RT][16][8], zero between uses
   off += (size_t)kNB * RT * 128 * sizeof(float);
   int* red_cnt = reinterpret_cast<int*>(smem_raw + off);      // [kNB] tickets
@@ -332,20 +391,21 @@ __global__ void __launch_bounds__(kThreadsTma, IPEX_GEMV_MIN_BLOCKS) gemv_tma_ke
   off += 2 * kNB * sizeof(int);
   float* scratch = reinterpret_cast<float*>(smem_raw + off);
   off += 128;
+  int* xrow = reinterpret_cast<int*>(smem_raw + off);          // expert mode: rows of x / y of the pass [2][8]
+  int* yrow = xrow + 8;
+  int* pass_sync = yrow + 8;                                   // [0] arrivals at the pass barrier, [1] abort flag
+  off += 96;
   float* dxs = reinterpret_cast<float*>(smem_raw + off);       // integer path: per-token activation scale
   off += 32;
   int2* seeds = reinterpret_cast<int2*>(smem_raw + off);       // integer path: [Kp/64][8] accumulator seeds
   if (kI8) off += (size_t)(Kp / 64) * 8 * sizeof(int2);
   float* xcorr = reinterpret_cast<float*>(smem_raw + off);     // int4: [M][Kp/64]
-  if (WF == WF_SYM_INT4 || WF == WF_ASYM_INT4) off += (size_t)a.M * (Kp / 64) * sizeof(float);
+  if (WF == WF_SYM_INT4 || WF == WF_ASYM_INT4) off += (size_t)Mcap * (Kp / 64) * sizeof(float);
   float* xsum = reinterpret_cast<float*>(smem_raw + off);      // asym: [M][Kp/64]
-  if (WF == WF_ASYM_INT4) off += (size_t)a.M * (Kp / 64) * sizeof(float);
+  if (WF == WF_ASYM_INT4) off += (size_t)Mcap * (Kp / 64) * sizeof(float);
   uint32_t* lut256 = reinterpret_cast<uint32_t*>(smem_raw + off);
 
-  const uint8_t* codes = a.w;
   const size_t code_bytes = k4bit ? (size_t)Np * Kp / 2 : (size_t)Np * Kp;
-  const uint8_t* scales = a.w + code_bytes;
-  const uint8_t* mins = scales + (size_t)Np * (Kp / 64) * 2;
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; s++) {
@@ -360,31 +420,41 @@ __global__ void __launch_bounds__(kThreadsTma, IPEX_GEMV_MIN_BLOCKS) gemv_tma_ke
   if (warp == kCW) {
     // ---------------- producer: independent of the previous kernel, starts immediately ----------------
     if (lane == 0) {
-      int it = 0;
+      int it = 0, goff = 0;
       bool ok = true;
-      for (int grp = blockIdx.x; grp < ngroups && ok; grp += gridDim.x) {
-        for (int r = 0; r < RT && ok; r++) {
-          const int tile = grp * RT + r;
-          if (tile >= ntiles) break;
-          for (int sp = 0; sp < stages_per_tile; sp++, it++) {
-            const int slot = it % STAGES;
-            if (it >= STAGES) {
-              if (!mbar_wait(&empty_bar[slot], ((it / STAGES) - 1) & 1)) {
-                atomicExch(a.err, 1);
-                ok = false;
-                break;
+      PassWalk walk;
+      if (moe) pdl_wait();               // the expert ranges come from the kernel before this one
+      while (ok && walk.next(a, Mcap)) {
+        const uint8_t* codes = moe ? a.moe_w[walk.e] : a.w;
+        const uint8_t* scales = codes + code_bytes;
+        const uint8_t* mins = scales + (size_t)Np * (Kp / 64) * 2;
+        // row-tile groups are dealt round-robin over the CTAs, continuing where the previous pass stopped
+        for (int grp = (blockIdx.x + gridDim.x - goff) % gridDim.x; grp < ngroups && ok; grp += gridDim.x) {
+          for (int r = 0; r < RT && ok; r++) {
+            const int tile = grp * RT + r;
+            if (tile >= ntiles) break;
+            for (int sp = 0; sp < stages_per_tile; sp++, it++) {
+              const int slot = it % STAGES;
+              if (it >= STAGES) {
+                if (!mbar_wait(&empty_bar[slot], ((it / STAGES) - 1) & 1)) {
+                  atomicExch(a.err, 1);
+                  ok = false;
+                  break;
+                }
               }
+              const int c0 = sp * CPS;
+              const int nch = min(CPS, chunks - c0);
+              uint8_t* dst = ring + (size_t)slot * stage_bytes;
+              mbar_expect_tx(&full_bar[slot], (uint32_t)(nch * (CB + SB + MB)));
+              const size_t chunk_index = (size_t)tile * chunks + c0;
+              bulk_g2s(dst, codes + chunk_index * CB, (uint32_t)(nch * CB), &full_bar[slot]);
+              bulk_g2s(dst + CPS * CB, scales + chunk_index * SB, (uint32_t)(nch * SB), &full_bar[slot]);
+              if (MB)
+                bulk_g2s(dst + CPS * (CB + SB), mins + chunk_index * MB, (uint32_t)(nch * MB), &full_bar[slot]);
             }
-            const int c0 = sp * CPS;
-            const int nch = min(CPS, chunks - c0);
-            uint8_t* dst = ring + (size_t)slot * stage_bytes;
-            mbar_expect_tx(&full_bar[slot], (uint32_t)(nch * (CB + SB + MB)));
-            const size_t chunk_index = (size_t)tile * chunks + c0;
-            bulk_g2s(dst, codes + chunk_index * CB, (uint32_t)(nch * CB), &full_bar[slot]);
-            bulk_g2s(dst + CPS * CB, scales + chunk_index * SB, (uint32_t)(nch * SB), &full_bar[slot]);
-            if (MB) bulk_g2s(dst + CPS * (CB + SB), mins + chunk_index * MB, (uint32_t)(nch * MB), &full_bar[slot]);
           }
         }
+        goff = (goff + ngroups) % gridDim.x;
       }
     }
     return;
@@ -400,378 +470,406 @@ __global__ void __launch_bounds__(kThreadsTma, IPEX_GEMV_MIN_BLOCKS) gemv_tma_ke
     lut256[tid] = *reinterpret_cast<uint32_t*>(&v);
   }
   int8_t* xh = reinterpret_cast<int8_t*>(xs);
-  int8_t* xl = xh + (size_t)a.M * xs_stride;
-  if constexpr (kI8) stage_x_i8<T>(a, xh, xl, xs_stride, Kp, dxs, seeds, scratch);
-  else stage_x<T, kInt4>(a, xs, xs_stride, Kp, scratch);
-  consumer_sync();
-  if (kInt4) {
-    // per (row of x, 64-group): the constant part of sum_k A_k x'_k to take out of the accumulator, and for the
-    // asymmetric format the plain sum of x (for the "+ min" term)
-    const int groups = Kp / 64;
-    const float zlo = WF == WF_SYM_INT4 ? 1032.f : 1024.f;
-    const float zhi = WF == WF_SYM_INT4 ? 1152.f : 1024.f;
-    for (int i = tid; i < a.M * groups; i += kCThreads) {
-      const int m = i / groups, gi = i % groups;
-      float slo = 0.f, shi = 0.f;
-      for (int k = 0; k < 64; k++) {
-        const float v = __half2float(xs[m * xs_stride + gi * 64 + k]);
-        if (k & 2) shi += v; else slo += v;
-      }
-      xcorr[i] = zlo * slo + zhi * shi;
-      if (WF == WF_ASYM_INT4) xsum[i] = slo + 16.f * shi;
-    }
+  int8_t* xl = xh + (size_t)Mcap * xs_stride;
+  T* y = reinterpret_cast<T*>(a.y);
+  int it = 0, giter = 0, goff = 0, npass = 0;
+  bool ok = true;
+  PassWalk walk;
+  if (moe) {
+    if (tid == 0) { pass_sync[0] = 0; pass_sync[1] = 0; }
     consumer_sync();
   }
+  while (ok && walk.next(a, Mcap)) {
+    if (moe) {
+      // Every warp must be done with the previous pass's rows before they are replaced.  A warp that gave up on a
+      // bounded wait never arrives, so this barrier is bounded too (and watches the abort flag).
+      if (!pass_barrier(pass_sync, ++npass * kCW)) {
+        if (lane == 0) atomicExch(a.err, 5);
+        break;
+      }
+      a.M = walk.cnt - walk.base < Mcap ? walk.cnt - walk.base : Mcap;
+      if (tid < a.M) {
+        const int pos = walk.first + walk.base + tid;
+        int slot = a.moe_order[pos];
+        slot = slot < 0 ? 0 : (slot >= a.moe_slots ? a.moe_slots - 1 : slot);
+        xrow[tid] = a.moe_gather ? slot / a.moe_xdiv : pos;
+        yrow[tid] = a.moe_scatter ? slot : pos;
+      }
+      consumer_sync();
+    }
+    if constexpr (kI8) stage_x_i8<T>(a, xh, xl, xs_stride, Kp, dxs, seeds, scratch, moe ? xrow : nullptr);
+    else stage_x<T, kInt4>(a, xs, xs_stride, Kp, scratch, moe ? xrow : nullptr);
+    consumer_sync();
+    if (kInt4) {
+      // per (row of x, 64-group): the constant part of sum_k A_k x'_k to take out of the accumulator, and for the
+      // asymmetric format the plain sum of x (for the "+ min" term)
+      const int groups = Kp / 64;
+      const float zlo = WF == WF_SYM_INT4 ? 1032.f : 1024.f;
+      const float zhi = WF == WF_SYM_INT4 ? 1152.f : 1024.f;
+      for (int i = tid; i < a.M * groups; i += kCThreads) {
+        const int m = i / groups, gi = i % groups;
+        float slo = 0.f, shi = 0.f;
+        for (int k = 0; k < 64; k++) {
+          const float v = __half2float(xs[m * xs_stride + gi * 64 + k]);
+          if (k & 2) shi += v; else slo += v;
+        }
+        xcorr[i] = zlo * slo + zhi * shi;
+        if (WF == WF_ASYM_INT4) xsum[i] = slo + 16.f * shi;
+      }
+      consumer_sync();
+    }
 
-  const bool has_x = g < a.M;
-  T* y = reinterpret_cast<T*>(a.y);
-  int it = 0, giter = 0;
-  bool ok = true;
-  for (int grp = blockIdx.x; grp < ngroups && ok; grp += gridDim.x, giter++) {
-    float acc[RT][4];
+    const bool has_x = g < a.M;
+    // row-tile groups are dealt round-robin over the CTAs, continuing where the previous pass stopped
+    for (int grp = (blockIdx.x + gridDim.x - goff) % gridDim.x; grp < ngroups && ok; grp += gridDim.x, giter++) {
+      float acc[RT][4];
 #pragma unroll
-    for (int r = 0; r < RT; r++)
+      for (int r = 0; r < RT; r++)
 #pragma unroll
-      for (int i = 0; i < 4; i++) acc[r][i] = 0.f;
+        for (int i = 0; i < 4; i++) acc[r][i] = 0.f;
 #pragma unroll
-    for (int r = 0; r < RT; r++) {
-      const int tile = grp * RT + r;
-      if (tile >= ntiles) break;
-      for (int sp = 0; sp < stages_per_tile; sp++, it++) {
-        const int slot = it % STAGES;
-        if (!mbar_wait(&full_bar[slot], (it / STAGES) & 1)) {
-          atomicExch(a.err, 2);
+      for (int r = 0; r < RT; r++) {
+        const int tile = grp * RT + r;
+        if (tile >= ntiles) break;
+        for (int sp = 0; sp < stages_per_tile; sp++, it++) {
+          const int slot = it % STAGES;
+          if (!mbar_wait(&full_bar[slot], (it / STAGES) & 1)) {
+            atomicExch(a.err, 2);
+            ok = false;
+            break;
+          }
+          const int c0 = sp * CPS;
+          const int nch = min(CPS, chunks - c0);
+          const uint8_t* st = ring + (size_t)slot * stage_bytes;
+          const uint8_t* st_scales = st + CPS * CB;
+          const uint8_t* st_mins = st + CPS * (CB + SB);
+          for (int c = warp; c < nch; c += kCW) {
+            const int cg = c0 + c;
+            if constexpr (kI8) {
+              const uint8_t* tp = st + c * CB;
+              const uint4 qa = *reinterpret_cast<const uint4*>(tp + g * 64 + t * 16);
+              const uint4 qb = *reinterpret_cast<const uint4*>(tp + (g + 8) * 64 + t * 16);
+              const uint32_t s0 = *reinterpret_cast<const uint32_t*>(st_scales + c * SB + (0 * 16 + 2 * g) * 2);
+              const uint32_t s1 = *reinterpret_cast<const uint32_t*>(st_scales + c * SB + (1 * 16 + 2 * g) * 2);
+              uint4 h0 = make_uint4(0, 0, 0, 0), h1 = h0, l0 = h0, l1 = h0;
+              if (has_x) {
+                const int8_t* ph = xh + (size_t)g * xs_stride + cg * 128 + 16 * t;
+                const int8_t* pl = xl + (size_t)g * xs_stride + cg * 128 + 16 * t;
+                h0 = *reinterpret_cast<const uint4*>(ph);
+                h1 = *reinterpret_cast<const uint4*>(ph + 64);
+                l0 = *reinterpret_cast<const uint4*>(pl);
+                l1 = *reinterpret_cast<const uint4*>(pl + 64);
+              }
+              const int4 sd0 = *reinterpret_cast<const int4*>(seeds + (2 * cg) * 8 + 2 * t);
+              const int4 sd1 = *reinterpret_cast<const int4*>(seeds + (2 * cg + 1) * 8 + 2 * t);
+              constexpr uint32_t kM = 0x0F0F0F0Fu;
+              // group 0 (words x, y), group 1 (words z, w)
+              int ah0[4] = {sd0.x, sd0.z, sd0.x, sd0.z}, al0[4] = {sd0.y, sd0.w, sd0.y, sd0.w};
+              int ah1[4] = {sd1.x, sd1.z, sd1.x, sd1.z}, al1[4] = {sd1.y, sd1.w, sd1.y, sd1.w};
+              {
+                const uint32_t a0 = qa.x & kM, a1 = qb.x & kM, a2 = (qa.x >> 4) & kM, a3 = (qb.x >> 4) & kM;
+                mma_s8(ah0, a0, a1, a2, a3, h0.x, h0.y);
+                mma_s8(al0, a0, a1, a2, a3, l0.x, l0.y);
+              }
+              {
+                const uint32_t a0 = qa.z & kM, a1 = qb.z & kM, a2 = (qa.z >> 4) & kM, a3 = (qb.z >> 4) & kM;
+                mma_s8(ah1, a0, a1, a2, a3, h1.x, h1.y);
+                mma_s8(al1, a0, a1, a2, a3, l1.x, l1.y);
+              }
+              {
+                const uint32_t a0 = qa.y & kM, a1 = qb.y & kM, a2 = (qa.y >> 4) & kM, a3 = (qb.y >> 4) & kM;
+                mma_s8(ah0, a0, a1, a2, a3, h0.z, h0.w);
+                mma_s8(al0, a0, a1, a2, a3, l0.z, l0.w);
+              }
+              {
+                const uint32_t a0 = qa.w & kM, a1 = qb.w & kM, a2 = (qa.w >> 4) & kM, a3 = (qb.w >> 4) & kM;
+                mma_s8(ah1, a0, a1, a2, a3, h1.z, h1.w);
+                mma_s8(al1, a0, a1, a2, a3, l1.z, l1.w);
+              }
+              const float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&s0));
+              const float2 d1 = __half22float2(*reinterpret_cast<const __half2*>(&s1));
+              acc[r][0] += d0.x * (float)(ah0[0] * 128 + al0[0]) + d1.x * (float)(ah1[0] * 128 + al1[0]);
+              acc[r][1] += d0.x * (float)(ah0[1] * 128 + al0[1]) + d1.x * (float)(ah1[1] * 128 + al1[1]);
+              acc[r][2] += d0.y * (float)(ah0[2] * 128 + al0[2]) + d1.y * (float)(ah1[2] * 128 + al1[2]);
+              acc[r][3] += d0.y * (float)(ah0[3] * 128 + al0[3]) + d1.y * (float)(ah1[3] * 128 + al1[3]);
+              continue;
+            }
+            uint4 xa0 = make_uint4(0, 0, 0, 0), xa1 = xa0, xb0 = xa0, xb1 = xa0;
+            if (has_x) {
+              const __half* xp = xs + g * xs_stride + cg * 128 + 16 * t;
+              xa0 = *reinterpret_cast<const uint4*>(xp);
+              xa1 = *reinterpret_cast<const uint4*>(xp + 8);
+              xb0 = *reinterpret_cast<const uint4*>(xp + 64);
+              xb1 = *reinterpret_cast<const uint4*>(xp + 72);
+            }
+            if constexpr (k4bit) {
+              const uint8_t* tp = st + c * CB;
+              const uint4 qa = *reinterpret_cast<const uint4*>(tp + g * 64 + t * 16);
+              const uint4 qb = *reinterpret_cast<const uint4*>(tp + (g + 8) * 64 + t * 16);
+              const uint32_t s0 = *reinterpret_cast<const uint32_t*>(st_scales + c * SB + (0 * 16 + 2 * g) * 2);
+              const uint32_t s1 = *reinterpret_cast<const uint32_t*>(st_scales + c * SB + (1 * 16 + 2 * g) * 2);
+              const float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&s0));
+              const float2 d1 = __half22float2(*reinterpret_cast<const __half2*>(&s1));
+              float c0v[4] = {0.f, 0.f, 0.f, 0.f}, c1v[4] = {0.f, 0.f, 0.f, 0.f};
+              if constexpr (WF == WF_LUT4) {
+                auto lp = [&](uint32_t word, int byte) { return lut256[(word >> (8 * byte)) & 0xFF]; };
+                mma_f16(c0v, lp(qa.x, 0), lp(qb.x, 0), lp(qa.x, 1), lp(qb.x, 1), xa0.x, xa0.y);
+                mma_f16(c0v, lp(qa.x, 2), lp(qb.x, 2), lp(qa.x, 3), lp(qb.x, 3), xa0.z, xa0.w);
+                mma_f16(c0v, lp(qa.y, 0), lp(qb.y, 0), lp(qa.y, 1), lp(qb.y, 1), xa1.x, xa1.y);
+                mma_f16(c0v, lp(qa.y, 2), lp(qb.y, 2), lp(qa.y, 3), lp(qb.y, 3), xa1.z, xa1.w);
+                mma_f16(c1v, lp(qa.z, 0), lp(qb.z, 0), lp(qa.z, 1), lp(qb.z, 1), xb0.x, xb0.y);
+                mma_f16(c1v, lp(qa.z, 2), lp(qb.z, 2), lp(qa.z, 3), lp(qb.z, 3), xb0.z, xb0.w);
+                mma_f16(c1v, lp(qa.w, 0), lp(qb.w, 0), lp(qa.w, 1), lp(qb.w, 1), xb1.x, xb1.y);
+                mma_f16(c1v, lp(qa.w, 2), lp(qb.w, 2), lp(qa.w, 3), lp(qb.w, 3), xb1.z, xb1.w);
+              } else {
+                // two independent accumulation chains per 64-group keep the tensor pipe busy
+                float c0w[4] = {0.f, 0.f, 0.f, 0.f}, c1w[4] = {0.f, 0.f, 0.f, 0.f};
+                {
+                  Int4Raw A(qa.x), B(qb.x);
+                  mma_f16(c0v, A.p[0], B.p[0], A.p[1], B.p[1], xa0.x, xa0.y);
+                  mma_f16(c0w, A.p[2], B.p[2], A.p[3], B.p[3], xa0.z, xa0.w);
+                }
+                {
+                  Int4Raw A(qa.z), B(qb.z);
+                  mma_f16(c1v, A.p[0], B.p[0], A.p[1], B.p[1], xb0.x, xb0.y);
+                  mma_f16(c1w, A.p[2], B.p[2], A.p[3], B.p[3], xb0.z, xb0.w);
+                }
+                {
+                  Int4Raw A(qa.y), B(qb.y);
+                  mma_f16(c0v, A.p[0], B.p[0], A.p[1], B.p[1], xa1.x, xa1.y);
+                  mma_f16(c0w, A.p[2], B.p[2], A.p[3], B.p[3], xa1.z, xa1.w);
+                }
+                {
+                  Int4Raw A(qa.w), B(qb.w);
+                  mma_f16(c1v, A.p[0], B.p[0], A.p[1], B.p[1], xb1.x, xb1.y);
+                  mma_f16(c1w, A.p[2], B.p[2], A.p[3], B.p[3], xb1.z, xb1.w);
+                }
+                const int groups = Kp / 64;
+                const int n0 = 2 * t, n1 = 2 * t + 1;
+                const float k00 = n0 < a.M ? xcorr[n0 * groups + 2 * cg] : 0.f;
+                const float k01 = n0 < a.M ? xcorr[n0 * groups + 2 * cg + 1] : 0.f;
+                const float k10 = n1 < a.M ? xcorr[n1 * groups + 2 * cg] : 0.f;
+                const float k11 = n1 < a.M ? xcorr[n1 * groups + 2 * cg + 1] : 0.f;
+                c0v[0] += c0w[0] - k00; c0v[1] += c0w[1] - k10; c0v[2] += c0w[2] - k00; c0v[3] += c0w[3] - k10;
+                c1v[0] += c1w[0] - k01; c1v[1] += c1w[1] - k11; c1v[2] += c1w[2] - k01; c1v[3] += c1w[3] - k11;
+              }
+              acc[r][0] += d0.x * c0v[0] + d1.x * c1v[0];
+              acc[r][1] += d0.x * c0v[1] + d1.x * c1v[1];
+              acc[r][2] += d0.y * c0v[2] + d1.y * c1v[2];
+              acc[r][3] += d0.y * c0v[3] + d1.y * c1v[3];
+              if constexpr (WF == WF_ASYM_INT4) {
+                const uint32_t m0 = *reinterpret_cast<const uint32_t*>(st_mins + c * MB + (0 * 16 + 2 * g) * 2);
+                const uint32_t m1 = *reinterpret_cast<const uint32_t*>(st_mins + c * MB + (1 * 16 + 2 * g) * 2);
+                const float2 mn0 = __half22float2(*reinterpret_cast<const __half2*>(&m0));
+                const float2 mn1 = __half22float2(*reinterpret_cast<const __half2*>(&m1));
+                const int groups = Kp / 64;
+                const int n0 = 2 * t, n1 = 2 * t + 1;
+                const float xs00 = n0 < a.M ? xsum[n0 * groups + 2 * cg] : 0.f;
+                const float xs01 = n0 < a.M ? xsum[n0 * groups + 2 * cg + 1] : 0.f;
+                const float xs10 = n1 < a.M ? xsum[n1 * groups + 2 * cg] : 0.f;
+                const float xs11 = n1 < a.M ? xsum[n1 * groups + 2 * cg + 1] : 0.f;
+                acc[r][0] += mn0.x * xs00 + mn1.x * xs01;
+                acc[r][1] += mn0.x * xs10 + mn1.x * xs11;
+                acc[r][2] += mn0.y * xs00 + mn1.y * xs01;
+                acc[r][3] += mn0.y * xs10 + mn1.y * xs11;
+              }
+            } else {
+              // 8-bit families: a 128-k chunk = two [16 rows][64 k] tiles of 1024 bytes
+              float cc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+              const uint4 xv[4] = {xa0, xa1, xb0, xb1};
+#pragma unroll
+              for (int h = 0; h < 2; h++) {
+                const uint8_t* tp = st + c * CB + h * 1024;
+                const uint4 qa = *reinterpret_cast<const uint4*>(tp + g * 64 + t * 16);
+                const uint4 qb = *reinterpret_cast<const uint4*>(tp + (g + 8) * 64 + t * 16);
+                const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w};
+                const uint32_t wb[4] = {qb.x, qb.y, qb.z, qb.w};
+                const uint32_t xw[8] = {xv[2 * h].x, xv[2 * h].y, xv[2 * h].z, xv[2 * h].w,
+                                        xv[2 * h + 1].x, xv[2 * h + 1].y, xv[2 * h + 1].z, xv[2 * h + 1].w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                  uint32_t a0, a1, a2, a3;
+                  if constexpr (WF == WF_INT8) {
+                    const uint32_t ua = wa[j] ^ 0x80808080u, ub = wb[j] ^ 0x80808080u;
+                    constexpr uint32_t k1152 = 0x64806480u;
+                    a0 = h2_sub(__byte_perm(ua, 0x64646464u, 0x4140), k1152);
+                    a2 = h2_sub(__byte_perm(ua, 0x64646464u, 0x4342), k1152);
+                    a1 = h2_sub(__byte_perm(ub, 0x64646464u, 0x4140), k1152);
+                    a3 = h2_sub(__byte_perm(ub, 0x64646464u, 0x4342), k1152);
+                  } else {
+                    constexpr __nv_fp8_interpretation_t kind = WF == WF_FP8_E4M3 ? __NV_E4M3 : __NV_E5M2;
+                    __half2_raw r0 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wa[j] & 0xFFFF), kind);
+                    __half2_raw r2 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wa[j] >> 16), kind);
+                    __half2_raw r1 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wb[j] & 0xFFFF), kind);
+                    __half2_raw r3 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wb[j] >> 16), kind);
+                    a0 = (uint32_t)r0.x | ((uint32_t)r0.y << 16);
+                    a2 = (uint32_t)r2.x | ((uint32_t)r2.y << 16);
+                    a1 = (uint32_t)r1.x | ((uint32_t)r1.y << 16);
+                    a3 = (uint32_t)r3.x | ((uint32_t)r3.y << 16);
+                  }
+                  mma_f16(cc[h], a0, a1, a2, a3, xw[2 * j], xw[2 * j + 1]);
+                }
+              }
+              if constexpr (WF == WF_INT8) {
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                  const uint32_t s = *reinterpret_cast<const uint32_t*>(st_scales + c * SB + h * 32 + 2 * g * 2);
+                  const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&s));
+                  acc[r][0] += d.x * cc[h][0];
+                  acc[r][1] += d.x * cc[h][1];
+                  acc[r][2] += d.y * cc[h][2];
+                  acc[r][3] += d.y * cc[h][3];
+                }
+              } else {
+                const float2 d = *reinterpret_cast<const float2*>(st_scales + c * SB + 2 * g * 4);
+                acc[r][0] += d.x * (cc[0][0] + cc[1][0]);
+                acc[r][1] += d.x * (cc[0][1] + cc[1][1]);
+                acc[r][2] += d.y * (cc[0][2] + cc[1][2]);
+                acc[r][3] += d.y * (cc[0][3] + cc[1][3]);
+              }
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&empty_bar[slot]);
+        }
+        if (!ok) break;
+      }
+      if (!ok) break;
+      if constexpr (kI8) {
+        const float dxa = dxs[2 * t], dxb = dxs[2 * t + 1];
+#pragma unroll
+        for (int r = 0; r < RT; r++) {
+          acc[r][0] *= dxa; acc[r][1] *= dxb; acc[r][2] *= dxa; acc[r][3] *= dxb;
+        }
+      }
+
+      // ---- cross-warp reduction without a CTA-wide barrier ----
+      // Every warp adds its partial tile into one of kNB zero-initialised shared accumulators (shared-memory
+      // float atomics) and then takes a ticket; the warp that draws the last ticket finalises the tile (reads
+      // and re-zeroes the accumulator with atomicExch, applies the epilogue, stores) and publishes the buffer
+      // for reuse by bumping its generation.  Fast warps run ahead into the next groups' buffers meanwhile.
+      const int b = giter % kNB;
+      {
+        volatile int* genp = red_gen + b;
+        bool ready = false;
+        for (int i = 0; i < kSpinLimit; i++) {
+          if (*genp == giter / kNB) { ready = true; break; }
+          __nanosleep(64);
+        }
+        if (!ready) {
+          atomicExch(a.err, 3);
           ok = false;
           break;
         }
-        const int c0 = sp * CPS;
-        const int nch = min(CPS, chunks - c0);
-        const uint8_t* st = ring + (size_t)slot * stage_bytes;
-        const uint8_t* st_scales = st + CPS * CB;
-        const uint8_t* st_mins = st + CPS * (CB + SB);
-        for (int c = warp; c < nch; c += kCW) {
-          const int cg = c0 + c;
-          if constexpr (kI8) {
-            const uint8_t* tp = st + c * CB;
-            const uint4 qa = *reinterpret_cast<const uint4*>(tp + g * 64 + t * 16);
-            const uint4 qb = *reinterpret_cast<const uint4*>(tp + (g + 8) * 64 + t * 16);
-            const uint32_t s0 = *reinterpret_cast<const uint32_t*>(st_scales + c * SB + (0 * 16 + 2 * g) * 2);
-            const uint32_t s1 = *reinterpret_cast<const uint32_t*>(st_scales + c * SB + (1 * 16 + 2 * g) * 2);
-            uint4 h0 = make_uint4(0, 0, 0, 0), h1 = h0, l0 = h0, l1 = h0;
-            if (has_x) {
-              const int8_t* ph = xh + (size_t)g * xs_stride + cg * 128 + 16 * t;
-              const int8_t* pl = xl + (size_t)g * xs_stride + cg * 128 + 16 * t;
-              h0 = *reinterpret_cast<const uint4*>(ph);
-              h1 = *reinterpret_cast<const uint4*>(ph + 64);
-              l0 = *reinterpret_cast<const uint4*>(pl);
-              l1 = *reinterpret_cast<const uint4*>(pl + 64);
-            }
-            const int4 sd0 = *reinterpret_cast<const int4*>(seeds + (2 * cg) * 8 + 2 * t);
-            const int4 sd1 = *reinterpret_cast<const int4*>(seeds + (2 * cg + 1) * 8 + 2 * t);
-            constexpr uint32_t kM = 0x0F0F0F0Fu;
-            // group 0 (words x, y), group 1 (words z, w)
-            int ah0[4] = {sd0.x, sd0.z, sd0.x, sd0.z}, al0[4] = {sd0.y, sd0.w, sd0.y, sd0.w};
-            int ah1[4] = {sd1.x, sd1.z, sd1.x, sd1.z}, al1[4] = {sd1.y, sd1.w, sd1.y, sd1.w};
-            {
-              const uint32_t a0 = qa.x & kM, a1 = qb.x & kM, a2 = (qa.x >> 4) & kM, a3 = (qb.x >> 4) & kM;
-              mma_s8(ah0, a0, a1, a2, a3, h0.x, h0.y);
-              mma_s8(al0, a0, a1, a2, a3, l0.x, l0.y);
-            }
-            {
-              const uint32_t a0 = qa.z & kM, a1 = qb.z & kM, a2 = (qa.z >> 4) & kM, a3 = (qb.z >> 4) & kM;
-              mma_s8(ah1, a0, a1, a2, a3, h1.x, h1.y);
-              mma_s8(al1, a0, a1, a2, a3, l1.x, l1.y);
-            }
-            {
-              const uint32_t a0 = qa.y & kM, a1 = qb.y & kM, a2 = (qa.y >> 4) & kM, a3 = (qb.y >> 4) & kM;
-              mma_s8(ah0, a0, a1, a2, a3, h0.z, h0.w);
-              mma_s8(al0, a0, a1, a2, a3, l0.z, l0.w);
-            }
-            {
-              const uint32_t a0 = qa.w & kM, a1 = qb.w & kM, a2 = (qa.w >> 4) & kM, a3 = (qb.w >> 4) & kM;
-              mma_s8(ah1, a0, a1, a2, a3, h1.z, h1.w);
-              mma_s8(al1, a0, a1, a2, a3, l1.z, l1.w);
-            }
-            const float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&s0));
-            const float2 d1 = __half22float2(*reinterpret_cast<const __half2*>(&s1));
-            acc[r][0] += d0.x * (float)(ah0[0] * 128 + al0[0]) + d1.x * (float)(ah1[0] * 128 + al1[0]);
-            acc[r][1] += d0.x * (float)(ah0[1] * 128 + al0[1]) + d1.x * (float)(ah1[1] * 128 + al1[1]);
-            acc[r][2] += d0.y * (float)(ah0[2] * 128 + al0[2]) + d1.y * (float)(ah1[2] * 128 + al1[2]);
-            acc[r][3] += d0.y * (float)(ah0[3] * 128 + al0[3]) + d1.y * (float)(ah1[3] * 128 + al1[3]);
-            continue;
-          }
-          uint4 xa0 = make_uint4(0, 0, 0, 0), xa1 = xa0, xb0 = xa0, xb1 = xa0;
-          if (has_x) {
-            const __half* xp = xs + g * xs_stride + cg * 128 + 16 * t;
-            xa0 = *reinterpret_cast<const uint4*>(xp);
-            xa1 = *reinterpret_cast<const uint4*>(xp + 8);
-            xb0 = *reinterpret_cast<const uint4*>(xp + 64);
-            xb1 = *reinterpret_cast<const uint4*>(xp + 72);
-          }
-          if constexpr (k4bit) {
-            const uint8_t* tp = st + c * CB;
-            const uint4 qa = *reinterpret_cast<const uint4*>(tp + g * 64 + t * 16);
-            const uint4 qb = *reinterpret_cast<const uint4*>(tp + (g + 8) * 64 + t * 16);
-            const uint32_t s0 = *reinterpret_cast<const uint32_t*>(st_scales + c * SB + (0 * 16 + 2 * g) * 2);
-            const uint32_t s1 = *reinterpret_cast<const uint32_t*>(st_scales + c * SB + (1 * 16 + 2 * g) * 2);
-            const float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&s0));
-            const float2 d1 = __half22float2(*reinterpret_cast<const __half2*>(&s1));
-            float c0v[4] = {0.f, 0.f, 0.f, 0.f}, c1v[4] = {0.f, 0.f, 0.f, 0.f};
-            if constexpr (WF == WF_LUT4) {
-              auto lp = [&](uint32_t word, int byte) { return lut256[(word >> (8 * byte)) & 0xFF]; };
-              mma_f16(c0v, lp(qa.x, 0), lp(qb.x, 0), lp(qa.x, 1), lp(qb.x, 1), xa0.x, xa0.y);
-              mma_f16(c0v, lp(qa.x, 2), lp(qb.x, 2), lp(qa.x, 3), lp(qb.x, 3), xa0.z, xa0.w);
-              mma_f16(c0v, lp(qa.y, 0), lp(qb.y, 0), lp(qa.y, 1), lp(qb.y, 1), xa1.x, xa1.y);
-              mma_f16(c0v, lp(qa.y, 2), lp(qb.y, 2), lp(qa.y, 3), lp(qb.y, 3), xa1.z, xa1.w);
-              mma_f16(c1v, lp(qa.z, 0), lp(qb.z, 0), lp(qa.z, 1), lp(qb.z, 1), xb0.x, xb0.y);
-              mma_f16(c1v, lp(qa.z, 2), lp(qb.z, 2), lp(qa.z, 3), lp(qb.z, 3), xb0.z, xb0.w);
-              mma_f16(c1v, lp(qa.w, 0), lp(qb.w, 0), lp(qa.w, 1), lp(qb.w, 1), xb1.x, xb1.y);
-              mma_f16(c1v, lp(qa.w, 2), lp(qb.w, 2), lp(qa.w, 3), lp(qb.w, 3), xb1.z, xb1.w);
-            } else {
-              // two independent accumulation chains per 64-group keep the tensor pipe busy
-              float c0w[4] = {0.f, 0.f, 0.f, 0.f}, c1w[4] = {0.f, 0.f, 0.f, 0.f};
-              {
-                Int4Raw A(qa.x), B(qb.x);
-                mma_f16(c0v, A.p[0], B.p[0], A.p[1], B.p[1], xa0.x, xa0.y);
-                mma_f16(c0w, A.p[2], B.p[2], A.p[3], B.p[3], xa0.z, xa0.w);
-              }
-              {
-                Int4Raw A(qa.z), B(qb.z);
-                mma_f16(c1v, A.p[0], B.p[0], A.p[1], B.p[1], xb0.x, xb0.y);
-                mma_f16(c1w, A.p[2], B.p[2], A.p[3], B.p[3], xb0.z, xb0.w);
-              }
-              {
-                Int4Raw A(qa.y), B(qb.y);
-                mma_f16(c0v, A.p[0], B.p[0], A.p[1], B.p[1], xa1.x, xa1.y);
-                mma_f16(c0w, A.p[2], B.p[2], A.p[3], B.p[3], xa1.z, xa1.w);
-              }
-              {
-                Int4Raw A(qa.w), B(qb.w);
-                mma_f16(c1v, A.p[0], B.p[0], A.p[1], B.p[1], xb1.x, xb1.y);
-                mma_f16(c1w, A.p[2], B.p[2], A.p[3], B.p[3], xb1.z, xb1.w);
-              }
-              const int groups = Kp / 64;
-              const int n0 = 2 * t, n1 = 2 * t + 1;
-              const float k00 = n0 < a.M ? xcorr[n0 * groups + 2 * cg] : 0.f;
-              const float k01 = n0 < a.M ? xcorr[n0 * groups + 2 * cg + 1] : 0.f;
-              const float k10 = n1 < a.M ? xcorr[n1 * groups + 2 * cg] : 0.f;
-              const float k11 = n1 < a.M ? xcorr[n1 * groups + 2 * cg + 1] : 0.f;
-              c0v[0] += c0w[0] - k00; c0v[1] += c0w[1] - k10; c0v[2] += c0w[2] - k00; c0v[3] += c0w[3] - k10;
-              c1v[0] += c1w[0] - k01; c1v[1] += c1w[1] - k11; c1v[2] += c1w[2] - k01; c1v[3] += c1w[3] - k11;
-            }
-            acc[r][0] += d0.x * c0v[0] + d1.x * c1v[0];
-            acc[r][1] += d0.x * c0v[1] + d1.x * c1v[1];
-            acc[r][2] += d0.y * c0v[2] + d1.y * c1v[2];
-            acc[r][3] += d0.y * c0v[3] + d1.y * c1v[3];
-            if constexpr (WF == WF_ASYM_INT4) {
-              const uint32_t m0 = *reinterpret_cast<const uint32_t*>(st_mins + c * MB + (0 * 16 + 2 * g) * 2);
-              const uint32_t m1 = *reinterpret_cast<const uint32_t*>(st_mins + c * MB + (1 * 16 + 2 * g) * 2);
-              const float2 mn0 = __half22float2(*reinterpret_cast<const __half2*>(&m0));
-              const float2 mn1 = __half22float2(*reinterpret_cast<const __half2*>(&m1));
-              const int groups = Kp / 64;
-              const int n0 = 2 * t, n1 = 2 * t + 1;
-              const float xs00 = n0 < a.M ? xsum[n0 * groups + 2 * cg] : 0.f;
-              const float xs01 = n0 < a.M ? xsum[n0 * groups + 2 * cg + 1] : 0.f;
-              const float xs10 = n1 < a.M ? xsum[n1 * groups + 2 * cg] : 0.f;
-              const float xs11 = n1 < a.M ? xsum[n1 * groups + 2 * cg + 1] : 0.f;
-              acc[r][0] += mn0.x * xs00 + mn1.x * xs01;
-              acc[r][1] += mn0.x * xs10 + mn1.x * xs11;
-              acc[r][2] += mn0.y * xs00 + mn1.y * xs01;
-              acc[r][3] += mn0.y * xs10 + mn1.y * xs11;
-            }
-          } else {
-            // 8-bit families: a 128-k chunk = two [16 rows][64 k] tiles of 1024 bytes
-            float cc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-            const uint4 xv[4] = {xa0, xa1, xb0, xb1};
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-              const uint8_t* tp = st + c * CB + h * 1024;
-              const uint4 qa = *reinterpret_cast<const uint4*>(tp + g * 64 + t * 16);
-              const uint4 qb = *reinterpret_cast<const uint4*>(tp + (g + 8) * 64 + t * 16);
-              const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w};
-              const uint32_t wb[4] = {qb.x, qb.y, qb.z, qb.w};
-              const uint32_t xw[8] = {xv[2 * h].x, xv[2 * h].y, xv[2 * h].z, xv[2 * h].w,
-                                      xv[2 * h + 1].x, xv[2 * h + 1].y, xv[2 * h + 1].z, xv[2 * h + 1].w};
-#pragma unroll
-              for (int j = 0; j < 4; j++) {
-                uint32_t a0, a1, a2, a3;
-                if constexpr (WF == WF_INT8) {
-                  const uint32_t ua = wa[j] ^ 0x80808080u, ub = wb[j] ^ 0x80808080u;
-                  constexpr uint32_t k1152 = 0x64806480u;
-                  a0 = h2_sub(__byte_perm(ua, 0x64646464u, 0x4140), k1152);
-                  a2 = h2_sub(__byte_perm(ua, 0x64646464u, 0x4342), k1152);
-                  a1 = h2_sub(__byte_perm(ub, 0x64646464u, 0x4140), k1152);
-                  a3 = h2_sub(__byte_perm(ub, 0x64646464u, 0x4342), k1152);
-                } else {
-                  constexpr __nv_fp8_interpretation_t kind = WF == WF_FP8_E4M3 ? __NV_E4M3 : __NV_E5M2;
-                  __half2_raw r0 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wa[j] & 0xFFFF), kind);
-                  __half2_raw r2 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wa[j] >> 16), kind);
-                  __half2_raw r1 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wb[j] & 0xFFFF), kind);
-                  __half2_raw r3 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wb[j] >> 16), kind);
-                  a0 = (uint32_t)r0.x | ((uint32_t)r0.y << 16);
-                  a2 = (uint32_t)r2.x | ((uint32_t)r2.y << 16);
-                  a1 = (uint32_t)r1.x | ((uint32_t)r1.y << 16);
-                  a3 = (uint32_t)r3.x | ((uint32_t)r3.y << 16);
-                }
-                mma_f16(cc[h], a0, a1, a2, a3, xw[2 * j], xw[2 * j + 1]);
-              }
-            }
-            if constexpr (WF == WF_INT8) {
-#pragma unroll
-              for (int h = 0; h < 2; h++) {
-                const uint32_t s = *reinterpret_cast<const uint32_t*>(st_scales + c * SB + h * 32 + 2 * g * 2);
-                const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&s));
-                acc[r][0] += d.x * cc[h][0];
-                acc[r][1] += d.x * cc[h][1];
-                acc[r][2] += d.y * cc[h][2];
-                acc[r][3] += d.y * cc[h][3];
-              }
-            } else {
-              const float2 d = *reinterpret_cast<const float2*>(st_scales + c * SB + 2 * g * 4);
-              acc[r][0] += d.x * (cc[0][0] + cc[1][0]);
-              acc[r][1] += d.x * (cc[0][1] + cc[1][1]);
-              acc[r][2] += d.y * (cc[0][2] + cc[1][2]);
-              acc[r][3] += d.y * (cc[0][3] + cc[1][3]);
-            }
-          }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty_bar[slot]);
       }
-      if (!ok) break;
-    }
-    if (!ok) break;
-    if constexpr (kI8) {
-      const float dxa = dxs[2 * t], dxb = dxs[2 * t + 1];
+      float* rbuf = red + (size_t)b * RT * 128;
 #pragma unroll
       for (int r = 0; r < RT; r++) {
-        acc[r][0] *= dxa; acc[r][1] *= dxb; acc[r][2] *= dxa; acc[r][3] *= dxb;
-      }
-    }
-
-    // ---- cross-warp reduction without a CTA-wide barrier ----
-    // Every warp adds its partial tile into one of kNB zero-initialised shared accumulators (shared-memory
-    // float atomics) and then takes a ticket; the warp that draws the last ticket finalises the tile (reads
-    // and re-zeroes the accumulator with atomicExch, applies the epilogue, stores) and publishes the buffer
-    // for reuse by bumping its generation.  Fast warps run ahead into the next groups' buffers meanwhile.
-    const int b = giter % kNB;
-    {
-      volatile int* genp = red_gen + b;
-      bool ready = false;
-      for (int i = 0; i < kSpinLimit; i++) {
-        if (*genp == giter / kNB) { ready = true; break; }
-        __nanosleep(64);
-      }
-      if (!ready) {
-        atomicExch(a.err, 3);
-        break;
-      }
-    }
-    float* rbuf = red + (size_t)b * RT * 128;
-#pragma unroll
-    for (int r = 0; r < RT; r++) {
-      float* rp = rbuf + (size_t)r * 128;
-      atomicAdd(&rp[g * 8 + 2 * t], acc[r][0]);
-      atomicAdd(&rp[g * 8 + 2 * t + 1], acc[r][1]);
-      atomicAdd(&rp[(g + 8) * 8 + 2 * t], acc[r][2]);
-      atomicAdd(&rp[(g + 8) * 8 + 2 * t + 1], acc[r][3]);
-    }
-    __threadfence_block();
-    __syncwarp();
-    int ticket = 0;
-    if (lane == 0) ticket = atomicAdd(red_cnt + b, 1);
-    ticket = __shfl_sync(0xffffffffu, ticket, 0);
-    if (ticket == kCW - 1) {
-      __threadfence_block();
-      if (a.tp_world > 1 && a.act == 0 && RT == 1) {
-        // ---- fused all-reduce of this 16-row tile over peer memory ----
-        // 1. push this rank's partial tile into slot [tp_rank] of EVERY rank's buffer (plain stores to the
-        //    peers' mapped memory), 2. release-increment the tile's arrival counter on every rank,
-        // 3. wait (bounded) until all tp_world partials of the tile have arrived here, 4. sum them locally.
-        // Other warps of the CTA keep streaming the next tiles meanwhile.
-        float pv[4];
-        int pn[4], pc[4];
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-          const int i = lane + 32 * j;
-          pc[j] = i % 8;
-          pn[j] = grp * 16 + i / 8;
-          pv[j] = atomicExch(&rbuf[i], 0.f);
-        }
-        for (int rk = 0; rk < a.tp_world; rk++) {
-          float* dst = a.tp_bufs[rk] + (size_t)a.tp_rank * 8 * a.tp_npad;
-#pragma unroll
-          for (int j = 0; j < 4; j++)
-            if (pn[j] < a.N && pc[j] < a.M) dst[(size_t)pc[j] * a.tp_npad + pn[j]] = pv[j];
-        }
-        __threadfence_system();
-        __syncwarp();
-        if (lane < a.tp_world) red_release_sys_add(a.tp_flags[lane] + grp, 1);
-        int* my_flag = a.tp_flags[a.tp_rank] + grp;
-        bool arrived = false;
-        if (lane == 0) {
-          for (int i = 0; i < kSpinLimit; i++) {
-            if (ld_acquire_sys(my_flag) >= a.tp_world) { arrived = true; break; }
-            __nanosleep(64);
-          }
-          if (arrived) *my_flag = 0;   // self-cleaning: the next user of this counter is two launches away
-          else atomicExch(a.err, 4);
-        }
-        arrived = __shfl_sync(0xffffffffu, (int)arrived, 0) != 0;
-        if (arrived) {
-          const float* src = a.tp_bufs[a.tp_rank];
-#pragma unroll
-          for (int j = 0; j < 4; j++) {
-            if (pn[j] < a.N && pc[j] < a.M) {
-              float sv = 0.f;
-              for (int rk = 0; rk < a.tp_world; rk++)
-                sv += ld_relaxed_sys_f32(src + ((size_t)rk * 8 + pc[j]) * a.tp_npad + pn[j]);
-              if (a.bias != nullptr) sv += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[pn[j]]);
-              if (a.residual != nullptr)
-                sv += DT<T>::to_f(reinterpret_cast<const T*>(a.residual)[(size_t)pc[j] * a.ldr + pn[j]]);
-              y[(size_t)pc[j] * a.ldy + pn[j]] = DT<T>::from_f(sv);
-            }
-          }
-        }
-      } else if (a.act == 0) {
-#pragma unroll
-        for (int j = 0; j < RT * 4; j++) {
-          const int i = lane + 32 * j;            // index into [RT][16 rows][8 cols]
-          const int r = i / 128, row = (i % 128) / 8, col = i % 8;
-          float sv = atomicExch(&rbuf[i], 0.f);
-          const int n = (grp * RT + r) * 16 + row;
-          if (n < a.N && col < a.M) {
-            if (a.bias != nullptr) sv += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[n]);
-            if (a.residual != nullptr)
-              sv += DT<T>::to_f(reinterpret_cast<const T*>(a.residual)[(size_t)col * a.ldr + n]);
-            y[(size_t)col * a.ldy + n] = DT<T>::from_f(sv);
-          }
-        }
-      } else if (RT == 2) {
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-          const int i = lane + 32 * j;
-          const int row = i / 8, col = i % 8;
-          float gsum = atomicExch(&rbuf[i], 0.f), usum = atomicExch(&rbuf[128 + i], 0.f);
-          const int n = grp * 16 + row;
-          if (n < a.N / 2 && col < a.M) {
-            if (a.bias != nullptr) {
-              gsum += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[(size_t)grp * 32 + row]);
-              usum += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[(size_t)grp * 32 + 16 + row]);
-            }
-            y[(size_t)col * a.ldy + n] = DT<T>::from_f(act_apply(gsum, a.act) * usum);
-          }
-        }
+        float* rp = rbuf + (size_t)r * 128;
+        atomicAdd(&rp[g * 8 + 2 * t], acc[r][0]);
+        atomicAdd(&rp[g * 8 + 2 * t + 1], acc[r][1]);
+        atomicAdd(&rp[(g + 8) * 8 + 2 * t], acc[r][2]);
+        atomicAdd(&rp[(g + 8) * 8 + 2 * t + 1], acc[r][3]);
       }
       __threadfence_block();
       __syncwarp();
-      if (lane == 0) {
-        red_cnt[b] = 0;
+      int ticket = 0;
+      if (lane == 0) ticket = atomicAdd(red_cnt + b, 1);
+      ticket = __shfl_sync(0xffffffffu, ticket, 0);
+      if (ticket == kCW - 1) {
         __threadfence_block();
-        *(volatile int*)(red_gen + b) = giter / kNB + 1;
+        if (a.tp_world > 1 && a.act == 0 && RT == 1) {
+          // ---- fused all-reduce of this 16-row tile over peer memory ----
+          // 1. push this rank's partial tile into slot [tp_rank] of EVERY rank's buffer (plain stores to the
+          //    peers' mapped memory), 2. release-increment the tile's arrival counter on every rank,
+          // 3. wait (bounded) until all tp_world partials of the tile have arrived here, 4. sum them locally.
+          // Other warps of the CTA keep streaming the next tiles meanwhile.
+          float pv[4];
+          int pn[4], pc[4];
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const int i = lane + 32 * j;
+            pc[j] = i % 8;
+            pn[j] = grp * 16 + i / 8;
+            pv[j] = atomicExch(&rbuf[i], 0.f);
+          }
+          for (int rk = 0; rk < a.tp_world; rk++) {
+            float* dst = a.tp_bufs[rk] + (size_t)a.tp_rank * 8 * a.tp_npad;
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+              if (pn[j] < a.N && pc[j] < a.M) dst[(size_t)pc[j] * a.tp_npad + pn[j]] = pv[j];
+          }
+          __threadfence_system();
+          __syncwarp();
+          if (lane < a.tp_world) red_release_sys_add(a.tp_flags[lane] + grp, 1);
+          int* my_flag = a.tp_flags[a.tp_rank] + grp;
+          bool arrived = false;
+          if (lane == 0) {
+            for (int i = 0; i < kSpinLimit; i++) {
+              if (ld_acquire_sys(my_flag) >= a.tp_world) { arrived = true; break; }
+              __nanosleep(64);
+            }
+            if (arrived) *my_flag = 0;   // self-cleaning: the next user of this counter is two launches away
+            else atomicExch(a.err, 4);
+          }
+          arrived = __shfl_sync(0xffffffffu, (int)arrived, 0) != 0;
+          if (arrived) {
+            const float* src = a.tp_bufs[a.tp_rank];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              if (pn[j] < a.N && pc[j] < a.M) {
+                float sv = 0.f;
+                for (int rk = 0; rk < a.tp_world; rk++)
+                  sv += ld_relaxed_sys_f32(src + ((size_t)rk * 8 + pc[j]) * a.tp_npad + pn[j]);
+                if (a.bias != nullptr) sv += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[pn[j]]);
+                if (a.residual != nullptr)
+                  sv += DT<T>::to_f(reinterpret_cast<const T*>(a.residual)[(size_t)pc[j] * a.ldr + pn[j]]);
+                y[(size_t)pc[j] * a.ldy + pn[j]] = DT<T>::from_f(sv);
+              }
+            }
+          }
+        } else if (a.act == 0) {
+#pragma unroll
+          for (int j = 0; j < RT * 4; j++) {
+            const int i = lane + 32 * j;            // index into [RT][16 rows][8 cols]
+            const int r = i / 128, row = (i % 128) / 8, col = i % 8;
+            float sv = atomicExch(&rbuf[i], 0.f);
+            const int n = (grp * RT + r) * 16 + row;
+            if (n < a.N && col < a.M) {
+              if (a.bias != nullptr) sv += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[n]);
+              if (a.residual != nullptr)
+                sv += DT<T>::to_f(reinterpret_cast<const T*>(a.residual)[(size_t)col * a.ldr + n]);
+              y[(size_t)(moe ? yrow[col] : col) * a.ldy + n] = DT<T>::from_f(sv);
+            }
+          }
+        } else if (RT == 2) {
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const int i = lane + 32 * j;
+            const int row = i / 8, col = i % 8;
+            float gsum = atomicExch(&rbuf[i], 0.f), usum = atomicExch(&rbuf[128 + i], 0.f);
+            const int n = grp * 16 + row;
+            if (n < a.N / 2 && col < a.M) {
+              if (a.bias != nullptr) {
+                gsum += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[(size_t)grp * 32 + row]);
+                usum += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[(size_t)grp * 32 + 16 + row]);
+              }
+              y[(size_t)(moe ? yrow[col] : col) * a.ldy + n] = DT<T>::from_f(act_apply(gsum, a.act) * usum);
+            }
+          }
+        }
+        __threadfence_block();
+        __syncwarp();
+        if (lane == 0) {
+          red_cnt[b] = 0;
+          __threadfence_block();
+          *(volatile int*)(red_gen + b) = giter / kNB + 1;
+        }
       }
     }
-  }
+    goff = (goff + ngroups) % gridDim.x;
+    if (moe && !ok && lane == 0) *(volatile int*)(pass_sync + 1) = 1;   // tell the warps waiting at the pass barrier
+  }  // passes
 }
 
 struct LaunchPlan {
@@ -800,8 +898,8 @@ LaunchPlan plan(const TmaArgs& a) {
   if (p.cps > chunks) p.cps = chunks;
   const size_t stage_bytes = (size_t)p.cps * (CB + 64 + MB);
   const size_t xrow = WF == WF_I8 ? (size_t)(Kp + kI8Pad) : (size_t)(Kp + 8);   // x 2 bytes (fp16, or two int8 planes)
-  size_t fixed = (((size_t)a.M * xrow * 2 + 15) & ~(size_t)15) + (size_t)kNB * RT * 128 * 4 + 2 * kNB * 4 + 128 + 32 +
-                 256;
+  size_t fixed = (((size_t)a.M * xrow * 2 + 15) & ~(size_t)15) + (size_t)kNB * RT * 128 * 4 + 2 * kNB * 4 + 128 +
+                 96 + 32 + 256;
   if (WF == WF_I8) fixed += (size_t)(Kp / 64) * 8 * 8;
   if (WF == WF_ASYM_INT4) fixed += (size_t)a.M * (Kp / 64) * 4;
   if (WF == WF_SYM_INT4 || WF == WF_ASYM_INT4) fixed += (size_t)a.M * (Kp / 64) * 4;
@@ -823,6 +921,11 @@ LaunchPlan plan(const TmaArgs& a) {
 template <int WF, typename T, int RT>
 cudaError_t launch_tma(TmaArgs a, cudaStream_t stream, bool pdl) {
   LaunchPlan p = plan<WF, RT>(a);
+  // expert mode: a.M is only the number of an expert's tokens multiplied per pass; shrink it until the rows fit
+  while (a.moe_ranges != nullptr && p.smem > 227 * 1024 && a.M > 1) {
+    a.M--;
+    p = plan<WF, RT>(a);
+  }
   if (p.smem > 227 * 1024) return cudaErrorInvalidValue;
   a.stages = p.stages;
   a.cps = p.cps;
@@ -898,6 +1001,37 @@ IPEX_API int ipex_gemv_lowbit_tma(const void* w, int wf, const void* x, void* y,
                                   int* err, void* stream) {
   return gemv_tma_entry(w, wf, x, y, M, N, K, ldx, ldy, norm_w, eps, norm_offset, bias, residual, ldr, act, lut, dtype,
                         pdl, err, stream, 0, 1, 0, nullptr, nullptr);
+}
+
+// Mixture-of-experts GEMV for small batches, ONE launch for all experts: the (token, choice) slots were sorted by
+// expert on the device (ipex_moe_sort_slots: `order` [slots], `ranges` [experts][2] = first position, count); the
+// persistent CTAs walk the experts that received tokens, stage those tokens' rows of x and stream the expert's
+// weights once for up to eight of them (`max_rows` = most tokens one expert can get, at most the token count).
+// gather: x row = order[pos] / x_div, else pos; scatter: y row = order[pos], else pos.  act != 0: gate/up
+// interleaved row tiles, N / 2 output columns.
+IPEX_API int ipex_moe_gemv_tma(const void* w_list, int wf, const void* ranges, const void* order, int experts,
+                               int slots, int max_rows, const void* x, int x_div, int gather, int scatter, void* y,
+                               int N, int K, int ldx, int ldy, int act, const float* lut, int dtype, int* err,
+                               void* stream) {
+  if (experts < 1 || slots < 1 || max_rows < 1 || x_div < 1 || (K % 64) != 0 || err == nullptr ||
+      w_list == nullptr || ranges == nullptr || order == nullptr || wf == WF_F16 || wf == WF_BF16)
+    return (int)cudaErrorInvalidValue;
+  if ((ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0) return (int)cudaErrorInvalidValue;
+  TmaArgs a;
+  a.w = nullptr; a.x = x; a.y = y; a.norm_w = nullptr; a.bias = nullptr; a.residual = nullptr; a.lut = lut;
+  a.err = err;
+  a.M = max_rows < 8 ? max_rows : 8;
+  a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy; a.ldr = 0; a.eps = 0.f; a.norm_offset = 0.f;
+  a.act = act; a.stages = 0; a.cps = 0;
+  a.tp_rank = 0; a.tp_world = 1; a.tp_npad = 0; a.tp_bufs = nullptr; a.tp_flags = nullptr;
+  a.moe_w = reinterpret_cast<const uint8_t* const*>(w_list);
+  a.moe_ranges = reinterpret_cast<const int*>(ranges);
+  a.moe_order = reinterpret_cast<const int*>(order);
+  a.moe_experts = experts; a.moe_slots = slots; a.moe_gather = gather; a.moe_scatter = scatter; a.moe_xdiv = x_div;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == DT_F16) return (int)dispatch_wf<__half>(wf, a, s, false);
+  if (dtype == DT_BF16) return (int)dispatch_wf<__nv_bfloat16>(wf, a, s, false);
+  return (int)cudaErrorInvalidValue;
 }
 
 // Row-parallel GEMV fused with its all-reduce (tensor parallelism): every rank runs the same launch on its K-slice

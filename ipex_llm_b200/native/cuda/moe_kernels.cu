@@ -75,14 +75,48 @@ __global__ void moe_softmax_topk_kernel(const T* __restrict__ logits, float* __r
 
 // out[t] = sum_r weights[t, r] * y[t * k + r]   (combining the experts' outputs)
 template <typename T>
-__global__ void moe_combine_kernel(const T* __restrict__ y, const float* __restrict__ w, T* __restrict__ out, int tokens,
-                                   int k, int H) {
+__global__ void moe_combine_kernel(const T* __restrict__ y, const float* __restrict__ w, const T* __restrict__ residual,
+                                   T* __restrict__ out, int tokens, int k, int H) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (int64_t)tokens * H) return;
   const int t = (int)(i / H), h = (int)(i % H);
-  float acc = 0.f;
+  float acc = residual != nullptr ? DT<T>::to_f(residual[i]) : 0.f;
   for (int r = 0; r < k; r++) acc += w[(size_t)t * k + r] * DT<T>::to_f(y[((size_t)t * k + r) * H + h]);
   out[i] = DT<T>::from_f(acc);
+}
+
+// Stable counting sort of up to kSortMaxSlots (token, choice) slots by expert id, in one CTA.
+// order[pos] = slot, ranges[e] = (first pos, count).
+constexpr int kSortMaxSlots = 1024;
+__global__ void moe_sort_slots_kernel(const int64_t* __restrict__ ids, int slots, int E, int* __restrict__ order,
+                                      int* __restrict__ ranges) {
+  __shared__ int s_id[kSortMaxSlots];
+  __shared__ int s_cnt[256], s_first[256];
+  const int tid = threadIdx.x;
+  for (int e = tid; e < E; e += blockDim.x) s_cnt[e] = 0;
+  __syncthreads();
+  for (int s = tid; s < slots; s += blockDim.x) {
+    int e = (int)ids[s];
+    e = e < 0 ? 0 : (e >= E ? E - 1 : e);
+    s_id[s] = e;
+    atomicAdd(&s_cnt[e], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0;
+    for (int e = 0; e < E; e++) { s_first[e] = run; run += s_cnt[e]; }
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += blockDim.x) {
+    ranges[2 * e] = s_first[e];
+    ranges[2 * e + 1] = s_cnt[e];
+  }
+  for (int s = tid; s < slots; s += blockDim.x) {
+    const int e = s_id[s];
+    int before = 0;
+    for (int j = 0; j < s; j++) before += s_id[j] == e;
+    order[s_first[e] + before] = s;
+  }
 }
 
 }  // namespace
@@ -104,16 +138,32 @@ IPEX_API int ipex_moe_softmax_topk(const void* logits, float* probs, float* w, i
   return (int)cudaGetLastError();
 }
 
-IPEX_API int ipex_moe_combine(const void* y, const float* w, void* out, int tokens, int k, int H, int dtype,
-                              void* stream) {
+// out[t] = (residual[t] +) sum_r w[t, r] * y[t * k + r]
+IPEX_API int ipex_moe_combine_add(const void* y, const float* w, const void* residual, void* out, int tokens, int k,
+                                  int H, int dtype, void* stream) {
   const int64_t n = (int64_t)tokens * H;
   const int threads = 256, blocks = (int)((n + threads - 1) / threads);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == DT_F16)
-    moe_combine_kernel<__half><<<blocks, threads, 0, s>>>((const __half*)y, w, (__half*)out, tokens, k, H);
+    moe_combine_kernel<__half><<<blocks, threads, 0, s>>>((const __half*)y, w, (const __half*)residual, (__half*)out,
+                                                          tokens, k, H);
   else if (dtype == DT_BF16)
-    moe_combine_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)y, w, (__nv_bfloat16*)out,
+    moe_combine_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)y, w,
+                                                                  (const __nv_bfloat16*)residual, (__nv_bfloat16*)out,
                                                                   tokens, k, H);
   else return (int)cudaErrorInvalidValue;
+  return (int)cudaGetLastError();
+}
+
+IPEX_API int ipex_moe_combine(const void* y, const float* w, void* out, int tokens, int k, int H, int dtype,
+                              void* stream) {
+  return ipex_moe_combine_add(y, w, nullptr, out, tokens, k, H, dtype, stream);
+}
+
+// Sort `slots` (token, choice) slots by expert on the device: order [slots] int32, ranges [E][2] int32
+// (first position, count).  slots <= 1024, E <= 256.
+IPEX_API int ipex_moe_sort_slots(const int64_t* expert_ids, int slots, int E, int* order, int* ranges, void* stream) {
+  if (slots < 1 || slots > kSortMaxSlots || E < 1 || E > 256) return (int)cudaErrorInvalidValue;
+  moe_sort_slots_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(expert_ids, slots, E, order, ranges);
   return (int)cudaGetLastError();
 }

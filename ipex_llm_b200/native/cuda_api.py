@@ -17,6 +17,7 @@ WF_SYM_INT4, WF_ASYM_INT4, WF_LUT4, WF_FP8_E4M3, WF_FP8_E5M2, WF_INT8, WF_F16, W
 _SIGS = {
     "ipex_gemv_lowbit": [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp, cf, cf, vp, vp, ci, ci, vp, ci, ci, vp],
     "ipex_gemv_lowbit_tma": [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp, cf, cf, vp, vp, ci, ci, vp, ci, ci, vp, vp],
+    "ipex_gemv_lowbit_stream": [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp, cf, cf, vp, vp, ci, ci, vp, ci, ci, vp, vp],
     "ipex_gemv_lowbit_tma_ar": [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp, cf, cf, vp, vp, ci, vp, ci, ci, vp, vp,
                                 ci, ci, ci, vp, vp],
     "ipex_allreduce_oneshot": [vp, vp, vp, i64, ci, ci, ci, vp, ci, ci, vp],

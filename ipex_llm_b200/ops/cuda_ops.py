@@ -31,7 +31,7 @@ QTYPE_TO_WF = {
 
 _lut_cache = {}
 _USE_PDL = os.environ.get("IPEX_LLM_PDL", "1") != "0"
-_GEMV_IMPL = os.environ.get("IPEX_LLM_GEMV", "tma")   # tma | direct | v1
+_GEMV_IMPL = os.environ.get("IPEX_LLM_GEMV", "stream")   # stream | tma | direct | v1
 _err_flags = {}
 
 
@@ -44,6 +44,11 @@ def error_flag(device) -> torch.Tensor:
         if tune:
             a, b, c = (int(v) for v in tune.split(","))
             cuda_lib().ipex_gemv_tma_tune(a, b, c)
+        tune = os.environ.get("IPEX_LLM_GEMV_STREAM_TUNE")  # "ring_kb,chunks_per_stage,warps_per_tile"
+        if tune and hasattr(cuda_lib(), "ipex_gemv_stream_tune"):
+            fn = cuda_lib().ipex_gemv_stream_tune
+            fn.argtypes, fn.restype = [ctypes.c_int] * 3, None
+            fn(*(int(v) for v in tune.split(",")))
     return _err_flags[key]
 
 
@@ -103,7 +108,19 @@ def gemv_lowbit(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K: in
             return out
         if rc != 1:
             api.check(rc, "gemv_int4_direct")
-    if _GEMV_IMPL == "tma" and wf not in (api.WF_F16, api.WF_BF16):
+    if _GEMV_IMPL == "stream" and wf in (api.WF_SYM_INT4, api.WF_FP8_E4M3) and x.stride(0) % 8 == 0 and \
+            getattr(lib, "ipex_gemv_lowbit_stream", None) is not None:
+        # warp-private rings, one tensor-core instruction per 512 weights for up to four tokens
+        rc = lib.ipex_gemv_lowbit_stream(ptr(w_data), wf, ptr(x), ptr(out), M, N, K, x.stride(0), out.stride(0),
+                                         ptr(norm_weight), eps, norm_offset, ptr(bias), ptr(residual),
+                                         residual.stride(0) if residual is not None else 0, act, None, _dt(x),
+                                         int(pdl and _USE_PDL), ptr(error_flag(x.device)), current_stream())
+        if rc == 0:
+            return out
+        if rc != 1:
+            api.check(rc, "gemv_lowbit_stream")
+        # cudaErrorInvalidValue: the staged activations leave no room for the rings -> the other kernels
+    if _GEMV_IMPL in ("tma", "stream") and wf not in (api.WF_F16, api.WF_BF16):
         rc = lib.ipex_gemv_lowbit_tma(ptr(w_data), wf, ptr(x), ptr(out), M, N, K, x.stride(0), out.stride(0),
                                       ptr(norm_weight), eps, norm_offset, ptr(bias), ptr(residual),
                                       residual.stride(0) if residual is not None else 0, act, ptr(lut), _dt(x),
@@ -656,15 +673,19 @@ def moe_supported(experts) -> bool:
         experts.intermediate_dim % 64 == 0 and experts.intermediate_dim % 16 == 0
 
 
-def moe_forward(experts, hidden_states, top_k_index, top_k_weights):
-    """Sparse-MoE block for few tokens: every (token, choice) slot is one GEMV whose expert is picked on the device
-    (no host synchronisation, two launches for all slots).  Larger token counts run expert by expert through the
-    tcgen05 GEMM."""
+def moe_forward(experts, hidden_states, top_k_index, top_k_weights, residual=None, out=None):
+    """Sparse-MoE block ``(residual +) sum_k w_k * expert_k(x)`` without host synchronisation.
+
+    * one token: every (token, choice) slot is a GEMV whose expert is picked on the device;
+    * a few tokens: the slots are sorted by expert on the device and each expert's weights are read once for up to
+      eight of its tokens (``ipex_moe_gemv_grouped``);
+    * prompts: expert-sorted rows through the tcgen05 GEMM with device-side row ranges."""
     lib = cuda_lib()
     T, k = top_k_index.shape
     slots = T * k
     if slots > _MOE_MAX_SLOTS:
-        return _moe_forward_grouped(experts, hidden_states, top_k_index, top_k_weights)
+        out = _moe_forward_grouped(experts, hidden_states, top_k_index, top_k_weights)
+        return out if residual is None else out.add_(residual)
     bank = _moe_bank(experts)
     x = hidden_states.contiguous()
     dt = x.dtype
@@ -673,23 +694,61 @@ def moe_forward(experts, hidden_states, top_k_index, top_k_weights):
     act = torch.empty((slots, bank.I), dtype=dt, device=x.device)
     y = torch.empty((slots, bank.H), dtype=dt, device=x.device)
     lut = lut_for(bank.qtype, x.device)
-    fn = lib.ipex_moe_gemv
-    fn.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
-                   ctypes.c_void_p] + [ctypes.c_int] * 5 + [ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
-                                                            ctypes.c_void_p]
-    fn.restype = ctypes.c_int
-    rc = fn(ptr(bank.gu_ptrs), bank.wf, ptr(ids), slots, ptr(x), k, ptr(act), 2 * bank.I, bank.H, x.stride(0),
-            act.stride(0), act_code, ptr(lut), _dt(x), 0, current_stream())
-    api.check(rc, "moe_gemv(gate_up)")
-    rc = fn(ptr(bank.dn_ptrs), bank.wf, ptr(ids), slots, ptr(act), 1, ptr(y), bank.H, bank.I, act.stride(0),
-            y.stride(0), 0, ptr(lut), _dt(x), 0, current_stream())
-    api.check(rc, "moe_gemv(down)")
-    out = torch.empty_like(x)
+    E = experts.num_experts
+    vp, ci = ctypes.c_void_p, ctypes.c_int
+    tfn = getattr(lib, "ipex_moe_gemv_tma", None)
+    gfn = getattr(lib, "ipex_moe_gemv_grouped", None)
+    mode = os.environ.get("IPEX_LLM_MOE_GROUPED_GEMV", "tma")        # tma | tiled | 0 (per-slot launches)
+    if (tfn is not None or gfn is not None) and T >= 2 and E <= 4 * slots and E <= 256 and mode != "0":
+        order = torch.empty(slots, dtype=torch.int32, device=x.device)
+        ranges = torch.empty((E, 2), dtype=torch.int32, device=x.device)
+        sfn = lib.ipex_moe_sort_slots
+        sfn.argtypes, sfn.restype = [vp, ci, ci, vp, vp, vp], ci
+        api.check(sfn(ptr(ids), slots, E, ptr(order), ptr(ranges), current_stream()), "moe_sort_slots")
+        if tfn is not None and mode != "tiled":
+            # one persistent launch per projection: the weight ring keeps streaming across the experts
+            tfn.argtypes = [vp, ci, vp, vp, ci, ci, ci, vp, ci, ci, ci, vp, ci, ci, ci, ci, ci, vp, ci, vp, vp]
+            tfn.restype = ci
+            err = ptr(error_flag(x.device))
+            rc = tfn(ptr(bank.gu_ptrs), bank.wf, ptr(ranges), ptr(order), E, slots, T, ptr(x), k, 1, 0, ptr(act),
+                     2 * bank.I, bank.H, x.stride(0), act.stride(0), act_code, ptr(lut), _dt(x), err,
+                     current_stream())
+            api.check(rc, "moe_gemv_tma(gate_up)")
+            rc = tfn(ptr(bank.dn_ptrs), bank.wf, ptr(ranges), ptr(order), E, slots, T, ptr(act), 1, 0, 1, ptr(y),
+                     bank.H, bank.I, act.stride(0), y.stride(0), 0, ptr(lut), _dt(x), err, current_stream())
+            api.check(rc, "moe_gemv_tma(down)")
+        else:
+            gfn.argtypes = [vp, ci, vp, vp, ci, ci, vp, ci, ci, ci, vp, ci, ci, ci, ci, ci, vp, ci, vp]
+            gfn.restype = ci
+            rows = lib.ipex_moe_gemv_group_rows      # a token picks an expert at most once: <= T slots per expert
+            rows.argtypes, rows.restype = [ci], ci
+            z = -(-T // rows(bank.H))
+            rc = gfn(ptr(bank.gu_ptrs), bank.wf, ptr(ranges), ptr(order), E, z, ptr(x), k, 1, 0, ptr(act),
+                     2 * bank.I, bank.H, x.stride(0), act.stride(0), act_code, ptr(lut), _dt(x), current_stream())
+            api.check(rc, "moe_gemv_grouped(gate_up)")
+            z = -(-T // rows(bank.I))
+            rc = gfn(ptr(bank.dn_ptrs), bank.wf, ptr(ranges), ptr(order), E, z, ptr(act), 1, 0, 1, ptr(y), bank.H,
+                     bank.I, act.stride(0), y.stride(0), 0, ptr(lut), _dt(x), current_stream())
+            api.check(rc, "moe_gemv_grouped(down)")
+    else:
+        fn = lib.ipex_moe_gemv
+        fn.argtypes = [vp, ci, vp, ci, vp, ci, vp] + [ci] * 5 + [vp, ci, ci, vp]
+        fn.restype = ci
+        rc = fn(ptr(bank.gu_ptrs), bank.wf, ptr(ids), slots, ptr(x), k, ptr(act), 2 * bank.I, bank.H, x.stride(0),
+                act.stride(0), act_code, ptr(lut), _dt(x), 0, current_stream())
+        api.check(rc, "moe_gemv(gate_up)")
+        rc = fn(ptr(bank.dn_ptrs), bank.wf, ptr(ids), slots, ptr(act), 1, ptr(y), bank.H, bank.I, act.stride(0),
+                y.stride(0), 0, ptr(lut), _dt(x), 0, current_stream())
+        api.check(rc, "moe_gemv(down)")
+    if out is None or not out.is_contiguous() or out.shape != x.shape or out.dtype != x.dtype:
+        out = torch.empty_like(x)
     w = top_k_weights.to(torch.float32).contiguous()
-    cfn = lib.ipex_moe_combine
-    cfn.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 4 + [ctypes.c_void_p]
-    cfn.restype = ctypes.c_int
-    rc = cfn(ptr(y), ptr(w), ptr(out), T, k, bank.H, _dt(x), current_stream())
+    if residual is not None:
+        residual = residual.contiguous()
+    cfn = lib.ipex_moe_combine_add
+    cfn.argtypes = [vp] * 4 + [ci] * 4 + [vp]
+    cfn.restype = ci
+    rc = cfn(ptr(y), ptr(w), ptr(residual), ptr(out), T, k, bank.H, _dt(x), current_stream())
     api.check(rc, "moe_combine")
     return out
 

@@ -7,6 +7,12 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True)
+def _force_fused_step(monkeypatch):
+    # on one GPU the engine prefers the separate kernels; these tests are about the fused step
+    monkeypatch.setenv("IPEX_LLM_DECODE_MEGA", "1")
+
+
 def _model(hidden, inter, heads, kv_heads, layers, low_bit, dtype, head_dim=None):
     from transformers import LlamaConfig
     from ipex_llm.transformers import AutoModelForCausalLM
