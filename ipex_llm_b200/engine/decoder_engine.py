@@ -294,8 +294,6 @@ class DecoderEngine:
         n = len(self.layers)
         if self.mega_step(getattr(self, "batch", 1) or 1) is not None:
             return 1                          # embedding ... arg-max in one persistent kernel
-        if self._use_chain(getattr(self, "batch", 1) or 1):
-            return 1 + 1 + 2 * n + 1          # embedding, first qkv, (attention + chained GEMVs) per layer, argmax
         if self.has_moe:
             # per layer: qkv, attention, o_proj, norm, router GEMM, softmax/top-k, two expert GEMVs, combine, residual
             n_moe = sum(1 for L in self.layers if L.moe is not None)
@@ -303,29 +301,6 @@ class DecoderEngine:
         if self.layers[0].o.tp is not None:
             return 1 + 7 * n + 2              # tensor parallel: + one all-reduce kernel after o_proj and down_proj
         return 1 + 5 * n + 2
-
-    def _use_chain(self, B: int) -> bool:
-        """The chained-GEMV kernel covers single-GPU models whose projections are all symmetric int4."""
-        cached = self.__dict__.get("_chain_ok")
-        if cached is None and self.has_moe:
-            cached = self._chain_ok = False
-        if cached is None:
-            ws = [w for L in self.layers for w in (L.qkv, L.o, L.gate_up, L.down)] + [self.lm_head]
-            # opt-in: at batch 1 on a 7B model the chained kernel measured 2.59 ms/token against 2.20 ms for the
-            # separate launches (its three grid barriers and per-op x staging cost more than the launches they save)
-            cached = os.environ.get("IPEX_LLM_GEMV_CHAIN", "0") == "1" and \
-                all(w.wf == api.WF_SYM_INT4 and w.tp is None and w.K % 64 == 0 for w in ws) and \
-                hasattr(self._lib, "ipex_gemv_chain")
-            self._chain_ok = cached
-        if not cached:
-            return False
-        kmax = max(self.layers[0].down.K, self.H)
-        kp = (kmax + 127) // 128 * 128
-        return 2 * B * (kp + 64) + 3 * 17408 + 8192 <= 200 * 1024     # x planes + a minimal ring fit shared memory
-
-    def _op(self, w: _W, x, y, norm_w=None, residual=None, act=0):
-        return {"w": w.data, "x": x, "y": y, "N": w.N, "K": w.K, "norm_w": norm_w, "bias": w.bias,
-                "residual": residual, "act": act, "eps": self.eps}
 
     def _moe_mlp(self, L: _Layer, h1, out):
         """``out = h1 + experts(norm(h1))`` of a sparse mixture-of-experts layer: router scores, fused softmax /
@@ -452,32 +427,16 @@ class DecoderEngine:
         h0, h1 = self.h[0][:B], self.h[1][:B]
         rc = lib.ipex_embedding(ptr(self.tokens), ptr(self.embed), ptr(h0), B, self.H, 1.0, dtc, 0, current_stream())
         api.check(rc, "embedding")
-        if self._use_chain(B):
-            # per layer: attention kernel + ONE persistent kernel for o_proj -> gate/up -> down -> next qkv (or lm_head)
-            self._gemv(self.layers[0].qkv, h0, self.qkv_buf[:B], norm_w=self.layers[0].ln1)
-            n = len(self.layers)
-            for i, L in enumerate(self.layers):
-                self._attention(L, B)
-                ops = [self._op(L.o, self.attn_buf[:B], h1, residual=h0),
-                       self._op(L.gate_up, h1, self.act_buf[:B], norm_w=L.ln2, act=1),
-                       self._op(L.down, self.act_buf[:B], h0, residual=h1)]
-                if i + 1 < n:
-                    nxt = self.layers[i + 1]
-                    ops.append(self._op(nxt.qkv, h0, self.qkv_buf[:B], norm_w=nxt.ln1))
-                else:
-                    ops.append(self._op(self.lm_head, h0, self.logits[:B], norm_w=self.final_norm))
-                cuda_ops.gemv_chain(ops, B, self.dtype, self.device, pdl=self.use_pdl)
-        else:
-            for L in self.layers:
-                self._gemv(L.qkv, h0, self.qkv_buf[:B], norm_w=L.ln1)
-                self._attention(L, B)
-                self._gemv(L.o, self.attn_buf[:B], h1, residual=h0)
-                if L.moe is not None:
-                    self._moe_mlp(L, h1, h0)
-                    continue
-                self._gemv(L.gate_up, h1, self.act_buf[:B], norm_w=L.ln2, act=1)
-                self._gemv(L.down, self.act_buf[:B], h0, residual=h1)
-            self._lm_head(h0, B)
+        for L in self.layers:
+            self._gemv(L.qkv, h0, self.qkv_buf[:B], norm_w=L.ln1)
+            self._attention(L, B)
+            self._gemv(L.o, self.attn_buf[:B], h1, residual=h0)
+            if L.moe is not None:
+                self._moe_mlp(L, h1, h0)
+                continue
+            self._gemv(L.gate_up, h1, self.act_buf[:B], norm_w=L.ln2, act=1)
+            self._gemv(L.down, self.act_buf[:B], h0, residual=h1)
+        self._lm_head(h0, B)
         rc = lib.ipex_argmax(ptr(self.logits), ptr(self.tokens), B, self.vocab, self.logits.stride(0), dtc, pdl,
                              current_stream())
         api.check(rc, "argmax")

@@ -43,7 +43,25 @@ struct StreamArgs {
   int stages;   // ring depth of a warp
   int cpw;      // 128-k chunks per stage
   int wpt;      // warps per tile
+  // row-parallel layers of a tensor-parallel model: all-reduce fused over NVLink peer memory (tp_world > 1)
+  int tp_rank, tp_world, tp_npad;
+  float* const* tp_bufs;   // [tp_world] device pointers: rank r's partial buffer [tp_world][8][tp_npad] fp32
+  int* const* tp_flags;    // [tp_world] device pointers: rank r's per-tile arrival counters
 };
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_relaxed_sys_f32(const float* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add(int* p, int v) {
+  asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -414,6 +432,43 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const StreamAr
   int slot = 0;
   uint32_t phase = 0;
   int nu = 0;   // units done (parity of the reduction buffer)
+
+  // ---- fused all-reduce (row-parallel layers, RT == 1): the finishing warp of a tile pushes its partial sums into
+  // slot [tp_rank] of EVERY rank's buffer (plain stores to the peers' mapped memory) and release-increments the
+  // tile's arrival counter on every rank.  It collects the tile one unit later (tp_collect), after it has streamed
+  // the next tile, so the NVLink round trip and the skew between the ranks hide behind its own work.
+  int tp_pending = -1;
+  auto tp_collect = [&](int unit) {
+    int* my_flag = a.tp_flags[a.tp_rank] + unit;
+    int arrived = 0;
+    if (lane == 0) {
+      for (int i = 0; i < kSpin; i++) {
+        if (ld_acquire_sys(my_flag) >= a.tp_world) { arrived = 1; break; }
+        __nanosleep(64);
+      }
+      if (arrived) *my_flag = 0;   // self-cleaning: the next user of this counter is two launches away
+      else atomicExch(a.err, 4);
+    }
+    arrived = __shfl_sync(0xffffffffu, arrived, 0);
+    if (!arrived) return;
+    const float* src = a.tp_bufs[a.tp_rank];
+#pragma unroll
+    for (int h = 0; h < MH; h++) {
+      const int m = t + 4 * h;
+      if (m >= a.M) continue;
+#pragma unroll
+      for (int half = 0; half < 2; half++) {
+        const int n = unit * 16 + g + 8 * half;
+        if (n >= a.N) continue;
+        float sv = 0.f;
+        for (int rk = 0; rk < a.tp_world; rk++) sv += ld_relaxed_sys_f32(src + ((size_t)rk * 8 + m) * a.tp_npad + n);
+        if (a.bias != nullptr) sv += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[n]);
+        if (a.residual != nullptr) sv += DT<T>::to_f(reinterpret_cast<const T*>(a.residual)[(size_t)m * a.ldr + n]);
+        y[(size_t)m * a.ldy + n] = DT<T>::from_f(sv);
+      }
+    }
+  };
+
   for (int unit = unit0; unit < nunits; unit += ustep, nu++) {
     float acc[RT][MH][2];
 #pragma unroll
@@ -469,6 +524,30 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const StreamAr
           }
       }
     }
+    if (RT == 1 && a.tp_world > 1) {
+      if (tp_pending >= 0) tp_collect(tp_pending);
+      tp_pending = -1;
+      if (!ok) continue;
+      for (int rk = 0; rk < a.tp_world; rk++) {
+        float* dst = a.tp_bufs[rk] + (size_t)a.tp_rank * 8 * a.tp_npad;
+#pragma unroll
+        for (int h = 0; h < MH; h++) {
+          const int m = t + 4 * h;
+          if (m >= a.M) continue;
+          const float dx = dxs[m];
+#pragma unroll
+          for (int half = 0; half < 2; half++) {
+            const int n = unit * 16 + g + 8 * half;
+            if (n < a.N) dst[(size_t)m * a.tp_npad + n] = acc[0][h][half] * dx;
+          }
+        }
+      }
+      __threadfence_system();
+      __syncwarp();
+      if (lane < a.tp_world) red_release_sys_add(a.tp_flags[lane] + unit, 1);
+      tp_pending = unit;
+      continue;
+    }
     if (!ok) continue;
     // ---- epilogue: lane (g, t) holds rows g and g + 8 of the unit's tiles for tokens t and t + 4 ----
 #pragma unroll
@@ -505,6 +584,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const StreamAr
       }
     }
   }
+  if (tp_pending >= 0) tp_collect(tp_pending);
 }
 
 struct Plan {
@@ -592,24 +672,29 @@ IPEX_API void ipex_gemv_stream_tune(int ring_kb, int chunks_per_stage, int warps
     g_wpt = warps_per_tile;
 }
 
-// Same arguments as ipex_gemv_lowbit_tma; weight families: symmetric int4 and fp8 e4m3.  Returns
-// cudaErrorInvalidValue for anything else or when the staged activations leave no room for the rings (the caller
-// then uses the other GEMV kernels).  *err: 2 = a bounded wait for weight data expired.
-IPEX_API int ipex_gemv_lowbit_stream(const void* w, int wf, const void* x, void* y, int M, int N, int K, int ldx,
-                                     int ldy, const void* norm_w, float eps, float norm_offset, const void* bias,
-                                     const void* residual, int ldr, int act, const float* lut, int dtype, int pdl,
-                                     int* err, void* stream) {
-  (void)lut;
+// Same arguments as ipex_gemv_lowbit_tma (+ the tensor-parallel ones of ipex_gemv_lowbit_tma_ar); weight families:
+// symmetric int4 and fp8 e4m3.  Returns cudaErrorInvalidValue for anything else or when the staged activations
+// leave no room for the rings (the caller then uses the other GEMV kernels).
+// *err: 2 = a bounded wait for weight data expired, 4 = a peer's partial tile never arrived.
+static int stream_entry(const void* w, int wf, const void* x, void* y, int M, int N, int K, int ldx, int ldy,
+                        const void* norm_w, float eps, float norm_offset, const void* bias, const void* residual,
+                        int ldr, int act, int dtype, int pdl, int* err, void* stream, int tp_rank, int tp_world,
+                        int tp_npad, const void* tp_bufs, const void* tp_flags) {
   if (M < 1 || M > 8 || N < 1 || (K % 64) != 0 || err == nullptr) return (int)cudaErrorInvalidValue;
   if ((ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0) return (int)cudaErrorInvalidValue;
   if (wf != WF_SYM_INT4 && wf != WF_FP8_E4M3) return (int)cudaErrorInvalidValue;
   if (wf == WF_FP8_E4M3 && (K % 128) != 0) return (int)cudaErrorInvalidValue;
   if (act != 0 && (N % 32) != 0) return (int)cudaErrorInvalidValue;
+  if (tp_world > 1 && (act != 0 || tp_bufs == nullptr || tp_flags == nullptr || tp_npad < N || tp_world > 8))
+    return (int)cudaErrorInvalidValue;
   StreamArgs a;
   a.w = (const uint8_t*)w; a.x = x; a.y = y; a.norm_w = norm_w; a.bias = bias; a.residual = residual;
   a.err = err;
   a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy; a.ldr = ldr; a.eps = eps; a.norm_offset = norm_offset;
   a.act = act; a.stages = 0; a.cpw = 0; a.wpt = 1;
+  a.tp_rank = tp_rank; a.tp_world = tp_world; a.tp_npad = tp_npad;
+  a.tp_bufs = reinterpret_cast<float* const*>(tp_bufs);
+  a.tp_flags = reinterpret_cast<int* const*>(tp_flags);
   cudaStream_t s = (cudaStream_t)stream;
   auto run = [&](const StreamArgs& b, bool dep) -> int {
     if (dtype == DT_F16) {
@@ -622,9 +707,10 @@ IPEX_API int ipex_gemv_lowbit_stream(const void* w, int wf, const void* x, void*
     return (int)cudaErrorInvalidValue;
   };
   int rc = run(a, pdl != 0);
-  if (rc != (int)cudaErrorInvalidValue || M <= 4) return rc;
+  if (rc != (int)cudaErrorInvalidValue || M <= 4 || tp_world > 1) return rc;
   // five to eight rows of a long contraction do not fit beside the rings: two launches of up to four rows each
-  // (the weights are streamed twice, still far cheaper than leaving the pipelined kernels)
+  // (the weights are streamed twice, still far cheaper than leaving the pipelined kernels).  Not under tensor
+  // parallelism: the arrival counters of a call serve one launch.
   const size_t es = 2;   // fp16 / bf16
   StreamArgs lo = a, hi = a;
   lo.M = 4;
@@ -635,4 +721,28 @@ IPEX_API int ipex_gemv_lowbit_stream(const void* w, int wf, const void* x, void*
   rc = run(lo, pdl != 0);
   if (rc != 0) return rc;
   return run(hi, pdl != 0);
+}
+
+IPEX_API int ipex_gemv_lowbit_stream(const void* w, int wf, const void* x, void* y, int M, int N, int K, int ldx,
+                                     int ldy, const void* norm_w, float eps, float norm_offset, const void* bias,
+                                     const void* residual, int ldr, int act, const float* lut, int dtype, int pdl,
+                                     int* err, void* stream) {
+  (void)lut;
+  return stream_entry(w, wf, x, y, M, N, K, ldx, ldy, norm_w, eps, norm_offset, bias, residual, ldr, act, dtype, pdl,
+                      err, stream, 0, 1, 0, nullptr, nullptr);
+}
+
+// Row-parallel GEMV fused with its all-reduce (tensor parallelism), same contract as ipex_gemv_lowbit_tma_ar: every
+// rank runs the same launch on its K-slice of the weight; the finishing warp of a 16-row tile stores its partial
+// sums into every rank's symmetric buffer over NVLink, bumps the tile's arrival counter on every rank, and collects
+// the full sum (+ bias, + residual) one tile later.  tp_bufs / tp_flags are device arrays of tp_world pointers for
+// the call's parity; the counters must be zero before the first call and are left zero.
+IPEX_API int ipex_gemv_lowbit_stream_ar(const void* w, int wf, const void* x, void* y, int M, int N, int K, int ldx,
+                                        int ldy, const void* norm_w, float eps, float norm_offset, const void* bias,
+                                        const void* residual, int ldr, const float* lut, int dtype, int pdl, int* err,
+                                        void* stream, int tp_rank, int tp_world, int tp_npad, const void* tp_bufs,
+                                        const void* tp_flags) {
+  (void)lut;
+  return stream_entry(w, wf, x, y, M, N, K, ldx, ldy, norm_w, eps, norm_offset, bias, residual, ldr, 0, dtype, pdl,
+                      err, stream, tp_rank, tp_world, tp_npad, tp_bufs, tp_flags);
 }

@@ -24,7 +24,6 @@ _SIGS = {
     "ipex_allreduce_oneshot_epi": [vp, vp, vp, i64, ci, ci, ci, vp, ci, ci, vp, vp, ci, vp],
     "ipex_symm_barrier": [vp, ci, ci, vp, vp],
     "ipex_wait_timeout_probe": [vp, ci, ci, vp, vp],
-    "ipex_gemv_int4_direct": [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp, cf, cf, vp, vp, ci, ci, vp, ci, ci, vp],
     "ipex_rms_norm": [vp, vp, vp, vp, vp, i64, ci, cf, cf, ci, ci, vp],
     "ipex_layer_norm": [vp, vp, vp, vp, i64, ci, cf, ci, vp],
     "ipex_act_mul": [vp, vp, vp, i64, ci, ci, ci, vp],
@@ -75,8 +74,6 @@ def declare(lib: ctypes.CDLL):
         fn.restype = i64
     lib.ipex_gemv_tma_tune.argtypes = [ci, ci, ci]
     lib.ipex_gemv_tma_tune.restype = None
-    lib.ipex_gemv_direct_tune.argtypes = [ci]
-    lib.ipex_gemv_direct_tune.restype = None
     for name, args in _OPTIONAL.items():
         fn = getattr(lib, name, None)
         if fn is not None:

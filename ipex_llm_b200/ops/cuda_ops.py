@@ -31,7 +31,7 @@ QTYPE_TO_WF = {
 
 _lut_cache = {}
 _USE_PDL = os.environ.get("IPEX_LLM_PDL", "1") != "0"
-_GEMV_IMPL = os.environ.get("IPEX_LLM_GEMV", "stream")   # stream | tma | direct | v1
+_GEMV_IMPL = os.environ.get("IPEX_LLM_GEMV", "stream")   # stream | tma | v1
 _err_flags = {}
 
 
@@ -99,15 +99,6 @@ def gemv_lowbit(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K: in
     if out is None:
         out = torch.empty((M, n_out), dtype=x.dtype, device=x.device)
     lut = lut_for(qtype, x.device) if wf == api.WF_LUT4 else None
-    if _GEMV_IMPL == "direct" and wf in (api.WF_SYM_INT4, api.WF_ASYM_INT4) and x.stride(0) % 8 == 0:
-        rc = lib.ipex_gemv_int4_direct(ptr(w_data), wf, ptr(x), ptr(out), M, N, K, x.stride(0), out.stride(0),
-                                       ptr(norm_weight), eps, norm_offset, ptr(bias), ptr(residual),
-                                       residual.stride(0) if residual is not None else 0, act, None, _dt(x),
-                                       int(pdl and _USE_PDL), current_stream())
-        if rc == 0:
-            return out
-        if rc != 1:
-            api.check(rc, "gemv_int4_direct")
     if _GEMV_IMPL == "stream" and wf in (api.WF_SYM_INT4, api.WF_FP8_E4M3) and x.stride(0) % 8 == 0 and \
             getattr(lib, "ipex_gemv_lowbit_stream", None) is not None:
         # warp-private rings, one tensor-core instruction per 512 weights for up to four tokens
@@ -138,51 +129,6 @@ def gemv_lowbit(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K: in
     return out
 
 
-class _ChainOpDesc(ctypes.Structure):
-    _fields_ = [("w", ctypes.c_void_p), ("x", ctypes.c_void_p), ("y", ctypes.c_void_p), ("norm_w", ctypes.c_void_p),
-                ("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("N", ctypes.c_int), ("K", ctypes.c_int),
-                ("ldx", ctypes.c_int), ("ldy", ctypes.c_int), ("ldr", ctypes.c_int), ("act", ctypes.c_int),
-                ("eps", ctypes.c_float), ("norm_offset", ctypes.c_float)]
-
-
-_chain_barriers = {}
-
-
-def chain_barrier(device) -> torch.Tensor:
-    """Arrival / exit counters of the chained-GEMV kernel's grid barrier (zero between launches)."""
-    key = str(device)
-    if key not in _chain_barriers:
-        _chain_barriers[key] = torch.zeros(2, dtype=torch.int32, device=device)
-    return _chain_barriers[key]
-
-
-def gemv_chain(ops, M: int, dtype, device, pdl: bool = False):
-    """Up to four dependent symmetric-int4 GEMVs in one persistent kernel.  ``ops``: dicts with ``w`` (packed
-    tiles), ``x`` ``[M, K]``, ``y``, ``N``, ``K`` and optional ``norm_w``, ``bias``, ``residual``, ``act``, ``eps``,
-    ``norm_offset``; op ``i + 1`` may read what op ``i`` wrote."""
-    lib = cuda_lib()
-    arr = (_ChainOpDesc * len(ops))()
-    for d, o in zip(arr, ops):
-        x, y, res = o["x"], o["y"], o.get("residual")
-        d.w, d.x, d.y = o["w"].data_ptr(), x.data_ptr(), y.data_ptr()
-        d.norm_w = o["norm_w"].data_ptr() if o.get("norm_w") is not None else None
-        d.bias = o["bias"].data_ptr() if o.get("bias") is not None else None
-        d.residual = res.data_ptr() if res is not None else None
-        d.N, d.K = int(o["N"]), int(o["K"])
-        d.ldx, d.ldy = x.stride(0), y.stride(0)
-        d.ldr = res.stride(0) if res is not None else 0
-        d.act = int(o.get("act", 0))
-        d.eps = float(o.get("eps", 1e-6))
-        d.norm_offset = float(o.get("norm_offset", 0.0))
-    fn = lib.ipex_gemv_chain
-    fn.argtypes = [ctypes.POINTER(_ChainOpDesc), ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
-                   ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
-    fn.restype = ctypes.c_int
-    rc = fn(arr, len(ops), M, api.dtype_code(dtype), ptr(chain_barrier(device)), int(pdl), ptr(error_flag(device)),
-            current_stream())
-    api.check(rc, "gemv_chain")
-
-
 def gemv_lowbit_ar(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K: int, out: torch.Tensor, comm,
                    bias: torch.Tensor = None, residual: torch.Tensor = None, pdl: bool = False, wf: int = None):
     """Row-parallel GEMV fused with its all-reduce: ``out = sum_over_ranks(x_r @ W_r.T) (+ bias) (+ residual)``.
@@ -194,11 +140,18 @@ def gemv_lowbit_ar(x: torch.Tensor, w_data: torch.Tensor, qtype: int, N: int, K:
         wf = QTYPE_TO_WF[qtype]
     lut = lut_for(qtype, x.device) if wf == api.WF_LUT4 else None
     rank, world, npad, bufs, flags = comm.gemv_ar_args()
-    rc = lib.ipex_gemv_lowbit_tma_ar(ptr(w_data), wf, ptr(x), ptr(out), M, N, K, x.stride(0), out.stride(0), None,
-                                     0.0, 0.0, ptr(bias), ptr(residual),
-                                     residual.stride(0) if residual is not None else 0, ptr(lut), _dt(x),
-                                     int(pdl and _USE_PDL), ptr(error_flag(x.device)), current_stream(), rank, world,
-                                     npad, ptr(bufs), ptr(flags))
+    args = (ptr(w_data), wf, ptr(x), ptr(out), M, N, K, x.stride(0), out.stride(0), None, 0.0, 0.0, ptr(bias),
+            ptr(residual), residual.stride(0) if residual is not None else 0, ptr(lut), _dt(x),
+            int(pdl and _USE_PDL), ptr(error_flag(x.device)), current_stream(), rank, world, npad, ptr(bufs),
+            ptr(flags))
+    rc = 1
+    sfn = getattr(lib, "ipex_gemv_lowbit_stream_ar", None)
+    if _GEMV_IMPL == "stream" and sfn is not None and wf in (api.WF_SYM_INT4, api.WF_FP8_E4M3) and \
+            x.stride(0) % 8 == 0:
+        sfn.argtypes, sfn.restype = lib.ipex_gemv_lowbit_tma_ar.argtypes, ctypes.c_int
+        rc = sfn(*args)         # 1 (invalid value) = shape it does not take; nothing was launched
+    if rc == 1:
+        rc = lib.ipex_gemv_lowbit_tma_ar(*args)
     api.check(rc, "gemv_lowbit_tma_ar")
     return out
 
