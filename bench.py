@@ -129,27 +129,28 @@ def other_config(args):
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
+    clocks_box = {}
+    # the clocks are sampled during the measured region only (model building idles the GPU at its lowest clock)
+    timed = ((lambda: sampler.start()), (lambda: clocks_box.update(c=sampler.stop()))) if rank == 0 else None
     if args.config == "mixtral-pp":
         from ipex_llm_b200.parallel import bench_pp
         argv = ["--model", args.model if args.model != "auto" else "mixtral-8x7b", "--batch", str(args.batch or 8),
                 "--prompt", str(args.prompt or 1024), "--new-tokens", str(max(8, args.steps))]
-        res = bench_pp.run(argv)
+        res = bench_pp.run(argv, timed=timed)
         extra = {"metric": "pipeline-parallel decode tokens/s (first_token_ms = prompt pass)", "scaling": "strong",
                  "dtype": "fp16", "parallelism": f"pp{world}"}
     elif args.config == "qlora-dp":
         from ipex_llm_b200.train import bench_qlora
         argv = ["--model", args.model if args.model != "auto" else "llama2-13b", "--steps", str(args.steps),
                 "--warmup", str(args.warmup)]
-        res = bench_qlora.run(argv)
+        res = bench_qlora.run(argv, timed=timed)
         extra = {"metric": "QLoRA finetune samples/s", "scaling": "weak", "dtype": "bf16", "parallelism": f"dp{world}"}
     else:
         from ipex_llm_b200.utils import bench_speculative
-        res = bench_speculative.run(["--new-tokens", str(max(32, args.steps))])
+        res = bench_speculative.run(["--new-tokens", str(max(32, args.steps))], timed=timed)
         extra = {"metric": "self-speculative decode tokens/s", "scaling": "strong", "dtype": "fp16",
                  "parallelism": "single"}
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = clocks_box.get("c")
     if rank == 0 and res is not None:
         base = BASELINE_SAMPLES_S.get((res.get("model"), world)) if args.config == "qlora-dp" else None
         line = {"metric": extra["metric"], "value": res.get("value"), "unit": res.get("unit"), "n_gpus": world,
@@ -316,7 +317,7 @@ def main():
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t0
         e2e = e2e_s
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = clocks_box.get("c")
 
     # ---- the reference harness's own metric: per-token cost of model.generate (first token / mean of the rest) ----
     gen_stats = None

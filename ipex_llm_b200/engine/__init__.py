@@ -35,7 +35,8 @@ def supports(model, kwargs) -> bool:
         if v is not None and v not in (False, 1):
             return False
     try:
-        blk = model.model.layers[0]
+        # (a pipeline stage keeps only its slice of the layers; the others are parameter-free stand-ins)
+        blk = next(b for b in model.model.layers if hasattr(b, "self_attn"))
     except Exception:  # noqa: BLE001
         return False
     if not hasattr(blk.self_attn, "qkv_proj"):

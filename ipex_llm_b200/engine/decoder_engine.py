@@ -99,10 +99,15 @@ class DecoderEngine:
         self.model = model
         self.cfg = cfg
         base = model.model
-        first = next(model.parameters())
-        self.device = base.embed_tokens.weight.device
-        self.dtype = base.norm.weight.dtype if base.norm.weight.dtype in (torch.float16, torch.bfloat16) \
-            else torch.float16
+        # a pipeline stage holds a slice of the layers; only the first stage has the embedding table and only the
+        # last one the final norm and lm_head (parallel/pp.py replaces the rest by parameter-free stand-ins)
+        real = [blk for blk in base.layers if hasattr(blk, "self_attn")]
+        self.first_stage = getattr(base.embed_tokens, "weight", None) is not None
+        self.last_stage = getattr(base.norm, "weight", None) is not None and \
+            getattr(model.lm_head, "weight", None) is not None
+        self.device = next(model.parameters()).device
+        ndt = base.norm.weight.dtype if self.last_stage else real[0].input_layernorm.weight.dtype
+        self.dtype = ndt if ndt in (torch.float16, torch.bfloat16) else torch.float16
         self.H = cfg.hidden_size
         self.n_heads_cfg = cfg.num_attention_heads
         self.n_kv_cfg = getattr(cfg, "num_key_value_heads", None) or cfg.num_attention_heads
@@ -118,18 +123,20 @@ class DecoderEngine:
         self.use_pdl = os.environ.get("IPEX_LLM_PDL", "1") != "0"
         dt = self.dtype
 
-        self.embed = base.embed_tokens.weight.data
-        if self.embed.dtype != dt:
-            self.embed = self.embed.to(dt)
-        self.final_norm = base.norm.weight.data.to(dt)
-        self.lm_head = _W.from_module(model.lm_head, dt)
+        self.embed = None
+        if self.first_stage:
+            self.embed = base.embed_tokens.weight.data
+            if self.embed.dtype != dt:
+                self.embed = self.embed.to(dt)
+        self.final_norm = base.norm.weight.data.to(dt) if self.last_stage else None
+        self.lm_head = _W.from_module(model.lm_head, dt) if self.last_stage else None
         # vocabulary-parallel lm_head: this rank scores rows [vocab_offset, vocab_offset + lm_head.N) of the vocabulary
         self.lm_gather = getattr(model.lm_head, "tp_gather", None)
         if self.lm_gather is not None and getattr(self.lm_gather, "world_size", 1) <= 1:
             self.lm_gather = None
         self.vocab_offset = self.lm_gather.rank * self.lm_head.N if self.lm_gather is not None else 0
         self.layers: List[_Layer] = []
-        for blk in base.layers:
+        for blk in real:
             L = _Layer()
             attn, mlp = blk.self_attn, blk.mlp
             if not hasattr(attn, "qkv_proj"):
@@ -184,7 +191,7 @@ class DecoderEngine:
         self.qkv_buf = torch.zeros(B, self.layers[0].qkv.N, dtype=dt, device=dev)
         self.attn_buf = torch.zeros(B, self.n_heads * self.hd, dtype=dt, device=dev)
         self.act_buf = torch.zeros(B, self.inter, dtype=dt, device=dev)
-        self.logits = torch.zeros(B, self.vocab, dtype=dt, device=dev)
+        self.logits = torch.zeros(B, self.vocab, dtype=dt, device=dev) if self.last_stage else None
         self.cache = None
         self._graphs = {}
         self._lib = cuda_lib()
@@ -425,8 +432,11 @@ class DecoderEngine:
         dtc = api.dtype_code(self.dtype)
         pdl = int(self.use_pdl)
         h0, h1 = self.h[0][:B], self.h[1][:B]
-        rc = lib.ipex_embedding(ptr(self.tokens), ptr(self.embed), ptr(h0), B, self.H, 1.0, dtc, 0, current_stream())
-        api.check(rc, "embedding")
+        if self.first_stage:
+            rc = lib.ipex_embedding(ptr(self.tokens), ptr(self.embed), ptr(h0), B, self.H, 1.0, dtc, 0,
+                                    current_stream())
+            api.check(rc, "embedding")
+        # (later pipeline stages: the previous stage's hidden states were received into h[0][:B])
         for L in self.layers:
             self._gemv(L.qkv, h0, self.qkv_buf[:B], norm_w=L.ln1)
             self._attention(L, B)
@@ -436,10 +446,12 @@ class DecoderEngine:
                 continue
             self._gemv(L.gate_up, h1, self.act_buf[:B], norm_w=L.ln2, act=1)
             self._gemv(L.down, self.act_buf[:B], h0, residual=h1)
-        self._lm_head(h0, B)
-        rc = lib.ipex_argmax(ptr(self.logits), ptr(self.tokens), B, self.vocab, self.logits.stride(0), dtc, pdl,
-                             current_stream())
-        api.check(rc, "argmax")
+        if self.last_stage:
+            self._lm_head(h0, B)
+            rc = lib.ipex_argmax(ptr(self.logits), ptr(self.tokens), B, self.vocab, self.logits.stride(0), dtc, pdl,
+                                 current_stream())
+            api.check(rc, "argmax")
+        # (earlier pipeline stages hand h[0][:B] to the next stage)
         self.past_len[:B].add_(1)
 
     def decode_step(self, B: int, use_graph: bool = True):
@@ -455,6 +467,7 @@ class DecoderEngine:
         if entry is None:
             # warm up outside capture (lazy allocations, cudaFuncSetAttribute), restoring the state it advances
             saved_tok, saved_len = self.tokens.clone(), self.past_len.clone()
+            saved_h = None if self.first_stage else self.h[0].clone()   # a later stage's input arrives in h[0]
             s = torch.cuda.Stream()
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
@@ -462,6 +475,8 @@ class DecoderEngine:
             torch.cuda.current_stream().wait_stream(s)
             self.tokens.copy_(saved_tok)
             self.past_len.copy_(saved_len)
+            if saved_h is not None:
+                self.h[0].copy_(saved_h)
             comm = self._tp_comm()
             parity = comm._parity if comm is not None else 0
             g = torch.cuda.CUDAGraph()
@@ -546,11 +561,54 @@ class DecoderEngine:
         return tcgen05_gemm.gemm_lowbit(x, w.data, w.qtype, w.N, w.K, bias=w.bias, residual=residual, act=act,
                                         wf=w.wf)
 
-    def _prefill_flat(self, input_ids: torch.Tensor, cache):
-        B, S = input_ids.shape
+    def clone_for_microbatch(self):
+        """A second engine over the SAME flattened weights with its own activations, KV cache and graphs (pipeline
+        stages keep one per micro-batch in flight)."""
+        import copy
+        other = copy.copy(self)
+        B, dev, dt = self.max_batch, self.device, self.dtype
+        other.tokens = torch.zeros(B, dtype=torch.int64, device=dev)
+        other.vtokens = torch.zeros(8, dtype=torch.int64, device=dev)
+        other.vout = torch.zeros(8, dtype=torch.int64, device=dev)
+        other.past_len = torch.zeros(B, dtype=torch.int32, device=dev)
+        other.h = [torch.zeros_like(self.h[0]) for _ in range(2)]
+        other.qkv_buf = torch.zeros_like(self.qkv_buf)
+        other.attn_buf = torch.zeros_like(self.attn_buf)
+        other.act_buf = torch.zeros_like(self.act_buf)
+        other.logits = torch.zeros_like(self.logits) if self.logits is not None else None
+        other.cache = None
+        other._graphs = {}
+        other._cache_pool = {}
+        other._mega = None
+        return other
+
+    @torch.no_grad()
+    def prefill_stage(self, x: torch.Tensor):
+        """Prompt pass of one pipeline stage.  ``x``: token ids ``[B, S]`` on the first stage, the previous stage's
+        hidden states ``[B, S, H]`` otherwise.  Returns the last position's logits ``[B, V]`` on the last stage and
+        the hidden states ``[B, S, H]`` to hand on elsewhere; K/V go into the engine's own cache."""
+        B, S = x.shape[0], x.shape[1]
+        if S + 1 > self.max_len:
+            raise ValueError(f"prompt of {S} tokens does not fit max_len={self.max_len}")
+        cache = self.new_cache(B)
+        self.bind_cache(cache, B)
+        if B * S >= 16 and B <= 8 and self._flat_prefill_ok():
+            return self._prefill_flat(x if self.first_stage else None, cache,
+                                      hidden=None if self.first_stage else x)
+        kw = {"input_ids": x} if self.first_stage else {"inputs_embeds": x}
+        out = self.model(past_key_values=cache, use_cache=True, **kw).logits
+        self.past_len[:B] = S
+        return out[:, -1, :] if self.last_stage else out
+
+    def _prefill_flat(self, input_ids: torch.Tensor, cache, hidden: torch.Tensor = None):
+        if hidden is None:
+            B, S = input_ids.shape
+            h = torch.nn.functional.embedding(input_ids.reshape(-1), self.embed)       # [T, H]
+        else:
+            B, S = hidden.shape[0], hidden.shape[1]
+            h = hidden.reshape(B * S, self.H).to(self.dtype)
         T, H, D = B * S, self.H, self.hd
         Hq, Hkv = self.n_heads, self.n_kv
-        h = torch.nn.functional.embedding(input_ids.reshape(-1), self.embed)           # [T, H]
         cos = torch.cat([self.cos[:S], self.cos[:S]], dim=-1).unsqueeze(0)             # [1, S, R] fp32
         sin = torch.cat([self.sin[:S], self.sin[:S]], dim=-1).unsqueeze(0)
         scale = 1.0 / math.sqrt(D)
@@ -571,9 +629,11 @@ class DecoderEngine:
             x = cuda_ops.rms_norm(h1, L.ln2, self.eps)
             act = self._gemm(L.gate_up, x, act=1)                                        # [T, I]
             h = self._gemm(L.down, act, residual=h1)
+        self.past_len[:B] = S
+        if not self.last_stage:
+            return h.view(B, S, H)
         last = h.view(B, S, H)[:, -1].contiguous()
         self._lm_head(last, B)
-        self.past_len[:B] = S
         return self.logits[:B].clone()
 
     def sync_cache_length(self, n: int):

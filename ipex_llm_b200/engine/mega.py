@@ -105,6 +105,8 @@ class MegaStep:
             return "kernel library has no fused step"
         if getattr(eng, "has_moe", False):
             return "mixture-of-experts layers"
+        if not (eng.first_stage and eng.last_stage):
+            return "pipeline stage"
         ws = [w for L in eng.layers for w in (L.qkv, L.o, L.gate_up, L.down)] + [eng.lm_head]
         wf = ws[0].wf
         if wf not in (api.WF_SYM_INT4, api.WF_FP8_E4M3):

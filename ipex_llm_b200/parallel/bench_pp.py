@@ -3,8 +3,9 @@
     torchrun --nproc-per-node N --master-addr 127.0.0.1 -m ipex_llm_b200.parallel.bench_pp --new-tokens 128
 
 Random-init sym_int4 weights created stage by stage on each rank's GPU, batch 8, 1024 random prompt tokens,
-greedy decoding through ``pipeline_parallel_generate`` (micro-batched, NCCL p2p).  Reports the first-token time and
-the decode throughput (max over ranks of the host-timed loop, which synchronises every step).
+greedy decoding through ``pipeline_parallel_generate`` (one graph-captured stage engine per micro-batch, NCCL p2p
+between the stages).  Reports the first-token time and the decode throughput (CUDA events around the decode steps,
+max over the stages).
 """
 from __future__ import annotations
 
@@ -27,8 +28,9 @@ ARCH = {
 }
 
 
-def run(argv=None):
-    """Run the benchmark; returns the result dictionary on rank 0 (None elsewhere)."""
+def run(argv=None, timed=None):
+    """Run the benchmark; returns the result dictionary on rank 0 (None elsewhere).  ``timed``: optional pair of
+    callables invoked right before and right after the measured generate call (clock sampling)."""
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="mixtral-8x7b", choices=list(ARCH))
     ap.add_argument("--batch", type=int, default=8)
@@ -49,7 +51,11 @@ def run(argv=None):
     g = torch.Generator().manual_seed(7)
     ids = torch.randint(0, cfg.vocab_size, (a.batch, a.prompt), generator=g)
     model.generate(ids[:, :32], max_new_tokens=4, do_sample=False)            # warm-up
+    if timed:
+        timed[0]()
     out = model.generate(ids, max_new_tokens=a.new_tokens, do_sample=False)
+    if timed:
+        timed[1]()
     first, rest = model.first_token_time, model.rest_cost_mean
     t = torch.tensor([first, rest], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -128,6 +128,137 @@ def _new_cache(model, batch_rows: int, device):
     return DynamicFp8Cache(cfg) if flag else DynamicNormalCache(cfg)
 
 
+def _back_group(model):
+    """Process group of the ids ring (last stage -> first stage).  With two stages the ring shares its rank pair
+    with the hidden-state hand-over; on one communicator the two directions would be queued on one stream in an
+    order the peer does not mirror (stage 0: send h0, send h1, recv ids0; stage 1: recv h0, send ids0, recv h1), which
+    only works while the messages fit the transport's buffers.  A second communicator keeps them independent."""
+    g = model.__dict__.get("_pp_back_group")
+    if g is None and model.pp_world > 1:
+        g = dist.new_group(ranks=list(range(model.pp_world)))
+        model.__dict__["_pp_back_group"] = g
+    return g
+
+
+def _stage_engines_ok(model, dev, attention_mask) -> bool:
+    """True when EVERY stage can run its slice on the flattened graph engine (all ranks take the same decision)."""
+    ok = dev.type == "cuda" and os.environ.get("IPEX_LLM_PP_ENGINE", "1") != "0" and \
+        (attention_mask is None or bool(attention_mask.all()))
+    if ok:
+        from ..engine import supports
+        ok = supports(model, {})
+    if model.pp_world > 1:
+        t = torch.tensor([int(ok)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        ok = bool(int(t.item()))
+    return ok
+
+
+@torch.no_grad()
+def _generate_with_stage_engines(model, input_ids, max_new_tokens, eos_ids, pad, streamer):
+    """Greedy pipeline generation on the flattened engines: every stage runs its slice of the layers as one
+    CUDA-graph replay per (micro-batch, token), hidden states travel stage to stage with NCCL p2p enqueued on the
+    stream, sampled ids go from the last stage back to the first, and the host never waits for the device between
+    tokens (one synchronisation after the prompt pass for the first-token time, one at the end).  Each micro-batch
+    has its own engine (activations, KV cache, graph) over the stage's shared flattened weights."""
+    from ..engine import DecoderEngine
+    rank, world = model.pp_rank, model.pp_world
+    dev = input_ids.device
+    B, S = input_ids.shape
+    H = model.config.hidden_size
+    first, last = rank == 0, rank == world - 1
+    n_mb = max(1, min(B, world))
+    bounds = [(B * i) // n_mb for i in range(n_mb + 1)]
+    rows = [bounds[i + 1] - bounds[i] for i in range(n_mb)]
+    need_len = (max(S + max_new_tokens + 1, 2048) + 255) // 256 * 256
+    engs = model.__dict__.get("_pp_engines") or []
+    if len(engs) < n_mb or engs[0].max_batch < max(rows) or engs[0].max_len < need_len:
+        base = DecoderEngine(model, max_batch=max(rows), max_len=need_len)
+        engs = [base] + [base.clone_for_microbatch() for _ in range(n_mb - 1)]
+        model.__dict__["_pp_engines"] = engs
+    dtype = engs[0].dtype
+    back = _back_group(model)
+    out_new = torch.full((B, max_new_tokens), pad, dtype=torch.long, device=dev)
+    finished = torch.zeros(B, dtype=torch.bool, device=dev)
+    eos_t = torch.tensor(eos_ids, device=dev) if eos_ids else None
+    sends = [None] * n_mb            # the isend that still reads each engine's hand-over buffer
+    keep = []                         # prompt-pass tensors an isend still reads
+    model.first_token_time = 0.0
+    model.next_token_time = []
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_start = time.perf_counter()
+    t_first = t_start
+    for step in range(max_new_tokens):
+        for m in range(n_mb):
+            e, r, b0, b1 = engs[m], rows[m], bounds[m], bounds[m + 1]
+            if sends[m] is not None:
+                sends[m].wait()               # stream-level: the next write of the buffer comes after the send
+                sends[m] = None
+            if step == 0:
+                if first:
+                    x = input_ids[b0:b1]
+                else:
+                    x = torch.empty((r, S, H), dtype=dtype, device=dev)
+                    dist.recv(x, src=rank - 1)
+                out = e.prefill_stage(x)
+                if last:
+                    e.tokens[:r] = torch.argmax(out, dim=-1)
+                else:
+                    out = out.contiguous()
+                    keep.append(out)
+                    sends[m] = dist.isend(out, rank + 1)
+            else:
+                if first and world > 1:
+                    dist.recv(e.tokens[:r], src=world - 1, group=back)
+                    out_new[b0:b1, step - 1] = e.tokens[:r]
+                elif not first:
+                    dist.recv(e.h[0][:r], src=rank - 1)
+                e.decode_step(r, use_graph=True)
+                if not last:
+                    sends[m] = dist.isend(e.h[0][:r], rank + 1)
+            if last:
+                nxt = e.tokens[:r]
+                if eos_t is not None:
+                    nxt = torch.where(finished[b0:b1], torch.full_like(nxt, pad), nxt)
+                    finished[b0:b1] |= torch.isin(nxt, eos_t)
+                    e.tokens[:r] = nxt
+                out_new[b0:b1, step] = nxt
+                if step < max_new_tokens - 1 and world > 1:
+                    ids = nxt.clone()
+                    keep.append(ids)
+                    sends[m] = dist.isend(ids, 0, group=back)
+        if len(keep) > 4 * n_mb:
+            del keep[:len(keep) - 4 * n_mb]   # older sends were waited for when their engine came round again
+        if streamer is not None and first:
+            if step == 0:
+                streamer.put(input_ids.cpu())
+            if world == 1:
+                streamer.put(out_new[:, step].cpu())
+            elif step > 0:
+                streamer.put(out_new[:, step - 1].cpu())
+        if step == 0:
+            torch.cuda.synchronize(dev)
+            t_first = time.perf_counter()
+            model.first_token_time = t_first - t_start
+            ev0.record()
+    for h in sends:
+        if h is not None:
+            h.wait()
+    ev1.record()                      # decode steps timed on the device (the caller takes the max over the stages)
+    if world > 1:
+        dist.broadcast(out_new, src=world - 1)
+    torch.cuda.synchronize(dev)
+    rest = ev0.elapsed_time(ev1) * 1e-3 / max(1, max_new_tokens - 1) if max_new_tokens > 1 else 0.0
+    model.next_token_time = [rest] * max(0, max_new_tokens - 1)
+    model.rest_cost_mean = rest
+    result = torch.cat([input_ids, out_new], dim=1)
+    if streamer is not None and first:
+        if world > 1:
+            streamer.put(out_new[:, max_new_tokens - 1].cpu())
+        streamer.end()
+    return result
+
+
 @torch.no_grad()
 def pipeline_parallel_generate(self, inputs: Optional[torch.Tensor] = None, max_new_tokens: int = 32,
                                generation_config=None, streamer=None, attention_mask=None, **kwargs):
@@ -149,6 +280,8 @@ def pipeline_parallel_generate(self, inputs: Optional[torch.Tensor] = None, max_
     dtype = next((p.dtype for p in self.parameters() if p.is_floating_point() and p.dim() == 1), torch.float32)
     input_ids = inputs.to(dev)
     B, S = input_ids.shape
+    if _stage_engines_ok(self, dev, attention_mask):
+        return _generate_with_stage_engines(self, input_ids, max_new_tokens, eos_ids, pad, streamer)
     H = self.config.hidden_size
     first, last = rank == 0, rank == world - 1
     n_mb = max(1, min(B, world))
@@ -166,11 +299,13 @@ def pipeline_parallel_generate(self, inputs: Optional[torch.Tensor] = None, max_
         if dev.type == "cuda":
             torch.cuda.synchronize(dev)
 
-    def send(t, dst):
+    back = _back_group(self)
+
+    def send(t, dst, group=None):
         if dst == rank:
             return
         t = t.contiguous()
-        pending.append((dist.isend(t, dst), t))
+        pending.append((dist.isend(t, dst, group=group), t))
 
     def drain(keep=0):
         while len(pending) > keep:
@@ -192,7 +327,7 @@ def pipeline_parallel_generate(self, inputs: Optional[torch.Tensor] = None, max_
                     ids = local_ids[m]
                 else:
                     ids = torch.empty((rows[m], 1), dtype=torch.long, device=dev)
-                    dist.recv(ids, src=world - 1)
+                    dist.recv(ids, src=world - 1, group=back)
                     out_new[b0:b1, step - 1] = ids[:, 0]
                 out = self(input_ids=ids, position_ids=position_ids, past_key_values=caches[m], use_cache=True)
             else:
@@ -210,7 +345,7 @@ def pipeline_parallel_generate(self, inputs: Optional[torch.Tensor] = None, max_
                     if world == 1:
                         local_ids[m] = nxt.view(-1, 1)
                     else:
-                        send(nxt.view(-1, 1), 0)
+                        send(nxt.view(-1, 1), 0, group=back)
             else:
                 send(res.to(dtype), rank + 1)
             drain(keep=2 * n_mb)

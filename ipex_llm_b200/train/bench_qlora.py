@@ -29,8 +29,9 @@ ARCH = {
 }
 
 
-def run(argv=None):
-    """Run the benchmark; returns the result dictionary on rank 0 (None elsewhere)."""
+def run(argv=None, timed=None):
+    """Run the benchmark; returns the result dictionary on rank 0 (None elsewhere).  ``timed``: optional pair of
+    callables invoked right before and right after the measured steps (clock sampling)."""
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="llama2-13b", choices=list(ARCH))
     ap.add_argument("--steps", type=int, default=8)
@@ -94,11 +95,16 @@ def run(argv=None):
         dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if timed:
+        timed[0]()
     e0.record()
     last = 0.0
     for i in range(a.steps):
         last = float(step(a.warmup + i))          # device -> host read of the loss every step
     e1.record()
+    if timed:
+        torch.cuda.synchronize()
+        timed[1]()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
