@@ -101,6 +101,15 @@ FAMILIES = {
                          post=[("Starcoder2Attention", D.decoder_attention_forward),
                                ("Starcoder2Model", D.decoder_model_forward)]),
     "stablelm": Family(post=[("StableLmModel", D.decoder_model_forward)]),
+    # families that reach the package kernels through the attention interface (transformers/convert.py) plus the
+    # norm / MLP replacements below; their attention modules keep their own projections and rotary handling
+    "cohere": Family(post=[("CohereMLP", C.mlp_silu_forward)]),
+    "gemma3_text": Family(post=[("Gemma3RMSNorm", C.gemma_rms_norm_forward), ("Gemma3MLP", C.mlp_gelu_forward)]),
+    "gemma3": Family(post=[("Gemma3RMSNorm", C.gemma_rms_norm_forward), ("Gemma3MLP", C.mlp_gelu_forward)]),
+    "olmo2": Family(post=[("Olmo2RMSNorm", C.rms_norm_forward), ("Olmo2MLP", C.mlp_silu_forward)]),
+    "granite": Family(post=[("GraniteRMSNorm", C.rms_norm_forward), ("GraniteMLP", C.mlp_silu_forward)]),
+    "qwen2_vl": Family(post=[("Qwen2VLRMSNorm", C.rms_norm_forward), ("Qwen2MLP", C.mlp_silu_forward)]),
+    "gptj": Family(post=[("LayerNorm", C.layer_norm_forward)]),
     "yi": _llama_like("Llama", engine="llama"),
     "deci": _llama_like("Llama"),
     "internlm2": Family(post=[("InternLM2RMSNorm", C.rms_norm_forward)]),

@@ -301,7 +301,10 @@ class _BaseAutoModelClass:
             extra = {}
             if torch_dtype is not None:
                 extra["dtype"] = torch_dtype
-            model = cls.HF_Model.from_pretrained(*args, **extra, **_strip_private(kwargs))
+            from .remote_archs import maybe_load_remote_arch
+            model = maybe_load_remote_arch(pretrained_model_name_or_path, extra.get("dtype"))
+            if model is None:
+                model = cls.HF_Model.from_pretrained(*args, **extra, **_strip_private(kwargs))
         return _attach_api(model)
 
     @classmethod
@@ -349,8 +352,14 @@ class _BaseAutoModelClass:
             extra = {}
             if torch_dtype is not None and torch_dtype != "auto":
                 extra["dtype"] = torch_dtype
+            from .remote_archs import maybe_load_remote_arch
+            path = args[0] if args else hf_kwargs.get("pretrained_model_name_or_path")
+            # ChatGLM / Baichuan / InternLM(2) / Qwen-v1 / MiniCPM / Aquila checkpoints: built natively, their remote
+            # modeling code is never executed
+            model = maybe_load_remote_arch(path, extra.get("dtype"))
             try:
-                model = cls.HF_Model.from_pretrained(*args, **extra, **hf_kwargs)
+                if model is None:
+                    model = cls.HF_Model.from_pretrained(*args, **extra, **hf_kwargs)
             except NotImplementedError:
                 logger.info("Failed to load models with `low_cpu_mem_usage` specified, retrying")
                 model = cls.HF_Model.from_pretrained(*args, **extra, **hf_kwargs)

@@ -170,6 +170,10 @@ FAMILY_CONFIGS = {
     "glm4": ("Glm4Config", dict(head_dim=32, pad_token_id=0)),
     "starcoder2": ("Starcoder2Config", dict()),
     "stablelm": ("StableLmConfig", dict()),
+    "cohere": ("CohereConfig", dict(pad_token_id=0)),
+    "gemma3_text": ("Gemma3TextConfig", dict(head_dim=32, sliding_window=16, query_pre_attn_scalar=32)),
+    "olmo2": ("Olmo2Config", dict(pad_token_id=0)),
+    "granite": ("GraniteConfig", dict()),
     "mixtral": ("MixtralConfig", dict(num_local_experts=4, num_experts_per_tok=2)),
     "qwen2_moe": ("Qwen2MoeConfig", dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=128,
                                         shared_expert_intermediate_size=128)),

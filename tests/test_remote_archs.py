@@ -1,0 +1,191 @@
+"""Checkpoints of remote-code families (ChatGLM2/3, Baichuan-7B / Baichuan2, InternLM, InternLM2, Qwen v1, MiniCPM,
+Aquila) load into the natively implemented architecture they are equivalent to.  Each test writes a checkpoint in
+the family's own tensor naming / layout (built here, independently of the loader, from a random native model) and
+checks that loading it reproduces the native model's logits, plain and quantized."""
+import json
+import math
+
+import pytest
+import torch
+
+
+def _save(tmp_path, config: dict, state: dict):
+    from safetensors.torch import save_file
+    d = tmp_path / config["model_type"]
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(config))
+    save_file({k: v.contiguous() for k, v in state.items()}, str(d / "model.safetensors"))
+    return str(d)
+
+
+def _check(path, native, atol=1e-5):
+    from ipex_llm.transformers import AutoModelForCausalLM
+    ids = torch.randint(0, native.config.vocab_size, (2, 12))
+    with torch.no_grad():
+        ref = native(ids).logits
+    m = AutoModelForCausalLM.from_pretrained(path)
+    with torch.no_grad():
+        out = m(ids).logits
+    assert torch.allclose(out, ref, atol=atol), (out - ref).abs().max()
+    q = AutoModelForCausalLM.from_pretrained(path, load_in_low_bit="sym_int8")
+    with torch.no_grad():
+        lq = q(ids).logits[:, -1]
+    cos = torch.nn.functional.cosine_similarity(lq.float(), ref[:, -1].float(), dim=-1)
+    assert cos.min() > 0.99, cos
+    return m
+
+
+def _native(cfg):
+    import transformers
+    torch.manual_seed(0)
+    return transformers.AutoModelForCausalLM.from_config(cfg).eval()
+
+
+def test_chatglm_checkpoint_loads_as_glm(tmp_path):
+    from transformers import GlmConfig
+    nh, ng, hd, H, I, L = 4, 2, 32, 128, 256, 2
+    native = _native(GlmConfig(vocab_size=1000, hidden_size=H, intermediate_size=I, num_hidden_layers=L,
+                               num_attention_heads=nh, num_key_value_heads=ng, head_dim=hd, attention_bias=True,
+                               partial_rotary_factor=0.5, rms_norm_eps=1e-5, max_position_embeddings=256,
+                               tie_word_embeddings=False, pad_token_id=0))
+    sd = native.state_dict()
+    st = {"transformer.embedding.word_embeddings.weight": sd["model.embed_tokens.weight"],
+          "transformer.encoder.final_layernorm.weight": sd["model.norm.weight"],
+          "transformer.output_layer.weight": sd["lm_head.weight"],
+          "transformer.rotary_pos_emb.inv_freq": torch.ones(8)}
+    for i in range(L):
+        p, r = f"model.layers.{i}.", f"transformer.encoder.layers.{i}."
+        for suffix in ("weight", "bias"):
+            st[r + "self_attention.query_key_value." + suffix] = torch.cat(
+                [sd[p + f"self_attn.{n}_proj.{suffix}"] for n in "qkv"], dim=0)
+        st[r + "self_attention.dense.weight"] = sd[p + "self_attn.o_proj.weight"]
+        st[r + "mlp.dense_h_to_4h.weight"] = sd[p + "mlp.gate_up_proj.weight"]
+        st[r + "mlp.dense_4h_to_h.weight"] = sd[p + "mlp.down_proj.weight"]
+        st[r + "input_layernorm.weight"] = sd[p + "input_layernorm.weight"]
+        st[r + "post_attention_layernorm.weight"] = sd[p + "post_attention_layernorm.weight"]
+    cfg = {"model_type": "chatglm", "num_layers": L, "hidden_size": H, "ffn_hidden_size": I, "kv_channels": hd,
+           "num_attention_heads": nh, "multi_query_attention": True, "multi_query_group_num": ng,
+           "padded_vocab_size": 1000, "layernorm_epsilon": 1e-5, "add_qkv_bias": True, "seq_length": 256,
+           "rmsnorm": True, "torch_dtype": "float32"}
+    m = _check(_save(tmp_path, cfg, st), native)
+    assert m.config.model_type == "glm" and m.config.ipex_remote_model_type == "chatglm"
+
+
+def _llama_cfg(**kw):
+    from transformers import LlamaConfig
+    base = dict(vocab_size=1000, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=4, max_position_embeddings=256, tie_word_embeddings=False, rms_norm_eps=1e-6)
+    base.update(kw)
+    return LlamaConfig(**base)
+
+
+def test_baichuan2_checkpoint_loads_as_llama(tmp_path):
+    native = _native(_llama_cfg(vocab_size=125696, hidden_size=64, intermediate_size=128))
+    sd = dict(native.state_dict())
+    # Baichuan2's NormHead stores unnormalised rows and normalises them at inference time
+    raw_head = sd["lm_head.weight"] * (1.0 + torch.rand(sd["lm_head.weight"].shape[0], 1))
+    native.lm_head.weight.data = torch.nn.functional.normalize(raw_head)
+    st = {}
+    for k, v in sd.items():
+        if ".self_attn.q_proj." in k:
+            st[k.replace("q_proj", "W_pack")] = torch.cat([sd[k], sd[k.replace("q_proj", "k_proj")],
+                                                           sd[k.replace("q_proj", "v_proj")]], dim=0)
+        elif ".self_attn.k_proj." in k or ".self_attn.v_proj." in k:
+            continue
+        elif k == "lm_head.weight":
+            st[k] = raw_head
+        else:
+            st[k] = v
+    cfg = {"model_type": "baichuan", "vocab_size": 125696, "hidden_size": 64, "intermediate_size": 128,
+           "num_hidden_layers": 2, "num_attention_heads": 4, "rms_norm_eps": 1e-6, "model_max_length": 256,
+           "max_position_embeddings": 256, "torch_dtype": "float32"}
+    _check(_save(tmp_path, cfg, st), native, atol=1e-4)
+
+
+def test_internlm_and_aquila_checkpoints_load_as_llama(tmp_path):
+    native = _native(_llama_cfg(attention_bias=True))
+    cfg = {"model_type": "internlm", "vocab_size": 1000, "hidden_size": 128, "intermediate_size": 256,
+           "num_hidden_layers": 2, "num_attention_heads": 4, "bias": True, "max_position_embeddings": 256,
+           "torch_dtype": "float32"}
+    _check(_save(tmp_path, cfg, dict(native.state_dict())), native)
+    native = _native(_llama_cfg())
+    cfg = {"model_type": "aquila", "vocab_size": 1000, "hidden_size": 128, "intermediate_size": 256,
+           "num_hidden_layers": 2, "num_attention_heads": 4, "max_position_embeddings": 256,
+           "torch_dtype": "float32"}
+    _check(_save(tmp_path, cfg, dict(native.state_dict())), native)
+
+
+def test_internlm2_checkpoint_loads_as_llama(tmp_path):
+    nh, nkv, hd, L = 4, 2, 32, 2
+    groups = nh // nkv
+    native = _native(_llama_cfg(num_key_value_heads=nkv))
+    sd = native.state_dict()
+    st = {"model.tok_embeddings.weight": sd["model.embed_tokens.weight"], "model.norm.weight": sd["model.norm.weight"],
+          "output.weight": sd["lm_head.weight"]}
+    for i in range(L):
+        p = f"model.layers.{i}."
+        q = sd[p + "self_attn.q_proj.weight"].view(nkv, groups, hd, -1)
+        k = sd[p + "self_attn.k_proj.weight"].view(nkv, 1, hd, -1)
+        v = sd[p + "self_attn.v_proj.weight"].view(nkv, 1, hd, -1)
+        st[p + "attention.wqkv.weight"] = torch.cat([q, k, v], dim=1).reshape((nh + 2 * nkv) * hd, -1)
+        st[p + "attention.wo.weight"] = sd[p + "self_attn.o_proj.weight"]
+        st[p + "feed_forward.w1.weight"] = sd[p + "mlp.gate_proj.weight"]
+        st[p + "feed_forward.w3.weight"] = sd[p + "mlp.up_proj.weight"]
+        st[p + "feed_forward.w2.weight"] = sd[p + "mlp.down_proj.weight"]
+        st[p + "attention_norm.weight"] = sd[p + "input_layernorm.weight"]
+        st[p + "ffn_norm.weight"] = sd[p + "post_attention_layernorm.weight"]
+    cfg = {"model_type": "internlm2", "vocab_size": 1000, "hidden_size": 128, "intermediate_size": 256,
+           "num_hidden_layers": L, "num_attention_heads": nh, "num_key_value_heads": nkv, "bias": False,
+           "max_position_embeddings": 256, "rms_norm_eps": 1e-6, "torch_dtype": "float32"}
+    _check(_save(tmp_path, cfg, st), native)
+
+
+def test_qwen_v1_checkpoint_loads_as_qwen2(tmp_path):
+    from transformers import Qwen2Config
+    H, I, L = 128, 256, 2
+    native = _native(Qwen2Config(vocab_size=1000, hidden_size=H, intermediate_size=I, num_hidden_layers=L,
+                                 num_attention_heads=4, num_key_value_heads=4, max_position_embeddings=256,
+                                 tie_word_embeddings=False, rms_norm_eps=1e-6))
+    sd = native.state_dict()
+    st = {"transformer.wte.weight": sd["model.embed_tokens.weight"], "transformer.ln_f.weight": sd["model.norm.weight"],
+          "lm_head.weight": sd["lm_head.weight"]}
+    for i in range(L):
+        p, r = f"model.layers.{i}.", f"transformer.h.{i}."
+        for suffix in ("weight", "bias"):
+            st[r + "attn.c_attn." + suffix] = torch.cat([sd[p + f"self_attn.{n}_proj.{suffix}"] for n in "qkv"], dim=0)
+        st[r + "attn.c_proj.weight"] = sd[p + "self_attn.o_proj.weight"]
+        st[r + "mlp.w1.weight"] = sd[p + "mlp.up_proj.weight"]          # a1 * silu(a2): w2 is the gate
+        st[r + "mlp.w2.weight"] = sd[p + "mlp.gate_proj.weight"]
+        st[r + "mlp.c_proj.weight"] = sd[p + "mlp.down_proj.weight"]
+        st[r + "ln_1.weight"] = sd[p + "input_layernorm.weight"]
+        st[r + "ln_2.weight"] = sd[p + "post_attention_layernorm.weight"]
+    cfg = {"model_type": "qwen", "vocab_size": 1000, "hidden_size": H, "intermediate_size": 2 * I,
+           "num_hidden_layers": L, "num_attention_heads": 4, "kv_channels": 32, "layer_norm_epsilon": 1e-6,
+           "rotary_emb_base": 10000, "seq_length": 256, "no_bias": True, "torch_dtype": "float32"}
+    _check(_save(tmp_path, cfg, st), native)
+
+
+def test_minicpm_checkpoint_loads_as_granite(tmp_path):
+    from transformers import GraniteConfig
+    H, L, nh = 128, 2, 4
+    scale_emb, scale_depth, dim_model_base = 12.0, 1.4, 64
+    native = _native(GraniteConfig(vocab_size=1000, hidden_size=H, intermediate_size=256, num_hidden_layers=L,
+                                   num_attention_heads=nh, num_key_value_heads=nh, max_position_embeddings=256,
+                                   rms_norm_eps=1e-5, embedding_multiplier=scale_emb,
+                                   residual_multiplier=scale_depth / math.sqrt(L), logits_scaling=H / dim_model_base,
+                                   attention_multiplier=1.0 / math.sqrt(H // nh), tie_word_embeddings=False))
+    native.lm_head.weight.data = native.model.embed_tokens.weight.data.clone()     # tied output layer
+    st = {k: v for k, v in native.state_dict().items() if k != "lm_head.weight"}
+    cfg = {"model_type": "minicpm", "vocab_size": 1000, "hidden_size": H, "intermediate_size": 256,
+           "num_hidden_layers": L, "num_attention_heads": nh, "num_key_value_heads": nh, "rms_norm_eps": 1e-5,
+           "scale_emb": scale_emb, "scale_depth": scale_depth, "dim_model_base": dim_model_base,
+           "max_position_embeddings": 256, "torch_dtype": "float32"}
+    _check(_save(tmp_path, cfg, st), native)
+
+
+def test_uncovered_variants_fall_through():
+    from ipex_llm_b200.transformers.remote_archs import REMOTE_ARCHS
+    assert REMOTE_ARCHS["chatglm"]({"model_type": "chatglm", "position_encoding_2d": True}) is None      # ChatGLM-6B v1
+    assert REMOTE_ARCHS["baichuan"]({"model_type": "baichuan", "hidden_size": 5120, "vocab_size": 64000,
+                                     "intermediate_size": 1, "num_hidden_layers": 1,
+                                     "num_attention_heads": 1}) is None                                   # 13B ALiBi
