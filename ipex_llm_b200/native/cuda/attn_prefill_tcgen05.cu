@@ -44,9 +44,21 @@ struct PrefillArgs {
   int B, S, Hq, Hkv;
   int causal;
   float scale_log2;   // softmax scale * log2(e)
+  // optional: tanh soft-cap of the scaled scores (Gemma-2), sliding window (a query sees the `window` newest keys up
+  // to itself), and left padding (batch b's keys and queries below kv_lo[b] do not exist)
+  float cap_log2;          // softcap * log2(e), 0 = off
+  float scale_over_cap;    // softmax scale / softcap
+  int window;              // 0 = off
+  const int* kv_lo;        // [B] or null
 };
 
-template <typename T, int D>
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <typename T, int D, bool EXT /* soft-cap / window / left padding compiled in */>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_vt, PrefillArgs a) {
@@ -83,6 +95,12 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int h = blockIdx.x, b = blockIdx.z;
   const int kvh = h / (a.Hq / a.Hkv);
   const int nkv = a.causal ? qb + 1 : (a.S + kBKV - 1) / kBKV;
+  // first key block any query of this block can see (sliding window, left padding); all roles walk [j0, nkv)
+  const int klo_b = EXT && a.kv_lo != nullptr ? a.kv_lo[b] : 0;
+  int j0 = klo_b / kBKV;
+  if (EXT && a.window > 0) j0 = max(j0, (qb * kBQ - a.window + 1) / kBKV);
+  j0 = EXT ? max(0, min(j0, nkv)) : 0;
+  const int nblk = nkv - j0;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -115,9 +133,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
       for (int kb = 0; kb < kDB; ++kb) tma_load_2d(sQ + kb * (kBQ * 128), &tm_q, h * D + kb * 64, row0, q_full);
       bool ok = true;
-      for (int j = 0; j < nkv && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+      for (int jj = 0; jj < nblk && ok; ++jj) {
+        const int j = j0 + jj;
+        const int st = jj & 1;
+        const uint32_t ph = (jj >> 1) & 1;
         if (!mbar_wait(&kv_empty[st], ph ^ 1, abort_flag)) { ok = false; report(a.err, 31); break; }
         uint8_t* sK = sKV + st * kStageBytes;
         uint8_t* sV = sK + kKBytes;
@@ -143,9 +162,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const uint32_t tm_s = tmem_base, tm_o = tmem_base + kBKV;
       bool ok = mbar_wait(q_full, 0, abort_flag);
       if (!ok) report(a.err, 32);
-      for (int j = 0; j < nkv && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1, jp = j & 1;
+      for (int jj = 0; jj < nblk && ok; ++jj) {
+        const int st = jj & 1;
+        const uint32_t ph = (jj >> 1) & 1, jp = jj & 1;
         uint8_t* sK = sKV + st * kStageBytes;
         uint8_t* sV = sK + kKBytes;
         if (!mbar_wait(&kv_full[st], ph, abort_flag)) { ok = false; report(a.err, 32); break; }
@@ -161,7 +180,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         umma_commit(s_full);
         // PV = P V: needs P(j) in shared memory and the previous PV read out of TMEM
         if (!mbar_wait(p_full, jp, abort_flag)) { ok = false; report(a.err, 32); break; }
-        if (j > 0 && !mbar_wait(o_free, jp ^ 1, abort_flag)) { ok = false; report(a.err, 32); break; }
+        if (jj > 0 && !mbar_wait(o_free, jp ^ 1, abort_flag)) { ok = false; report(a.err, 32); break; }
         tcgen05_fence_after();
 #pragma unroll
         for (int kb = 0; kb < kBKV / 64; ++kb) {
@@ -186,30 +205,43 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     for (int d = 0; d < kOH; ++d) o[d] = 0.f;
     float m = -INFINITY, l = 0.f;                     // m: row maximum (shared by the pair), l: this thread's part
     bool ok = true;
-    for (int j = 0; j < nkv; ++j) {
-      const uint32_t jp = j & 1;
+    // score -> exponent (base 2): plain scale, or the tanh soft-cap of the scaled score (monotonic, so the row
+    // maximum can be taken on the raw scores and transformed once)
+    const bool capped = EXT && a.cap_log2 > 0.f;
+    auto expo = [&](float sv) {
+      return capped ? a.cap_log2 * tanh_approx(sv * a.scale_over_cap) : sv * a.scale_log2;
+    };
+    for (int jj = 0; jj < nblk; ++jj) {
+      const int j = j0 + jj;
+      const uint32_t jp = jj & 1;
       if (!mbar_wait(s_full, jp, abort_flag)) { ok = false; if (lane == 0) report(a.err, 33); break; }
       tcgen05_fence_after();
       const int k0 = j * kBKV;
-      // keys this row may see in the block: [k0, k0 + klim); this thread looks at block columns [hf*64, hf*64+64)
+      // keys this row may see in the block: [k0 + klow, k0 + klim); this thread looks at block columns
+      // [hf*64, hf*64+64), of which the local columns in [lo, lim) are visible
       int klim = a.S - k0;
       if (a.causal) klim = min(klim, qpos - k0 + 1);
-      const int lim = min(klim, kBKV) - hf * 64;      // local columns below `lim` are visible
+      int klow = klo_b - k0;
+      if (EXT && a.window > 0) klow = max(klow, qpos - a.window + 1 - k0);
+      if (EXT && qpos < klo_b) klim = 0;              // a padding row sees nothing (its output is zero)
+      const int lim = min(klim, kBKV) - hf * 64;
+      const int lo = EXT ? klow - hf * 64 : 0;
       uint32_t v0[32], v1[32];
       tmem_ld_32x32(tmem_base + lane_addr + hf * 64, v0);
       tmem_ld_32x32(tmem_base + lane_addr + hf * 64 + 32, v1);
       float mx = -INFINITY;
-      if (lim >= 64) {
+      const bool full = lim >= 64 && (!EXT || lo <= 0);
+      if (full) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          if (i < lim) mx = fmaxf(mx, __uint_as_float(v0[i]));
-          if (32 + i < lim) mx = fmaxf(mx, __uint_as_float(v1[i]));
+          if (i < lim && (!EXT || i >= lo)) mx = fmaxf(mx, __uint_as_float(v0[i]));
+          if (32 + i < lim && (!EXT || 32 + i >= lo)) mx = fmaxf(mx, __uint_as_float(v1[i]));
         }
       }
-      mx *= a.scale_log2;                             // the scale is positive: max commutes with it
+      mx = mx == -INFINITY ? mx : expo(mx);           // the transform is increasing: max commutes with it
       xch[hf * 128 + r] = mx;
       mbar_arrive(x_full);
       if (!mbar_wait(x_full, jp, abort_flag)) { ok = false; if (lane == 0) report(a.err, 33); break; }
@@ -225,8 +257,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const float sv = __uint_as_float(half == 0 ? v0[i] : v1[i]);
-          float p = ex2(fmaf(sv, a.scale_log2, -mref));
-          if (lim < 64 && half * 32 + i >= lim) p = 0.f;
+          float p = ex2(expo(sv) - mref);
+          if (!full && (half * 32 + i >= lim || (EXT && half * 32 + i < lo))) p = 0.f;
           const T pt = from_float<T>(p);
           pk[i] = pt;
           psum += to_float<T>(pt);                   // the sum the tensor cores will see
@@ -259,7 +291,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       // the pair's row sum: one more exchange through the same slots
       xch[hf * 128 + r] = l;
       mbar_arrive(x_full);
-      ok = mbar_wait(x_full, nkv & 1, abort_flag);
+      ok = mbar_wait(x_full, nblk & 1, abort_flag);
       if (!ok && lane == 0) report(a.err, 33);
       l += xch[(hf ^ 1) * 128 + r];
     }
@@ -308,7 +340,8 @@ __global__ void __launch_bounds__(256) transpose_v_kernel(const T* __restrict__ 
 
 template <typename T, int D>
 int launch(const void* q, const void* k, const void* vt, void* out, int B, int S, int Hq, int Hkv, int64_t ldq,
-           int64_t ldk, int64_t s_pad, int64_t ldo, float scale, int causal, int* err, cudaStream_t stream) {
+           int64_t ldk, int64_t s_pad, int64_t ldo, float scale, int causal, float softcap, int window,
+           const int* kv_lo, int* err, cudaStream_t stream) {
   const CUtensorMapDataType dt =
       std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap tm_q, tm_k, tm_vt;
@@ -319,8 +352,13 @@ int launch(const void* q, const void* k, const void* vt, void* out, int B, int S
   PrefillArgs a;
   a.out = out; a.err = err; a.ldo = ldo; a.B = B; a.S = S; a.Hq = Hq; a.Hkv = Hkv; a.causal = causal;
   a.scale_log2 = scale * 1.4426950408889634f;
+  a.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+  a.scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
+  a.window = window > 0 ? window : 0;
+  a.kv_lo = kv_lo;
   const size_t smem = 1024 + (size_t)kBQ * D * 2 + (size_t)kBQ * kBKV * 2 + 2 * ((size_t)kBKV * D * 2 * 2) + 256 + 1024;
-  auto kern = attn_prefill_kernel<T, D>;
+  const bool ext = a.cap_log2 > 0.f || a.window > 0 || a.kv_lo != nullptr;
+  auto kern = ext ? attn_prefill_kernel<T, D, true> : attn_prefill_kernel<T, D, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   dim3 grid(Hq, (S + kBQ - 1) / kBQ, B);
@@ -334,25 +372,42 @@ int launch(const void* q, const void* k, const void* vt, void* out, int B, int S
 // with Hkv heads and row stride ldk; vt: V transposed, [B, Hkv, D, s_pad] contiguous with zeros past S (s_pad a
 // multiple of 8, >= S); out: [B, S, Hq, D] with token stride ldo.  D is 64 or 128, Hq a multiple of Hkv.  All base
 // pointers 16-byte aligned, ldq / ldk / ldo multiples of 8.  `err` receives a code when a bounded wait runs out.
-// Returns a cudaError_t.
-IPEX_API int ipex_attn_prefill_tcgen05(const void* q, const void* k, const void* vt, void* out, int B, int S, int Hq,
-                                       int Hkv, int D, int64_t ldq, int64_t ldk, int64_t s_pad, int64_t ldo,
-                                       float scale, int causal, int dtype, int* err, void* stream) {
+// softcap > 0: scores become softcap * tanh(score * scale / softcap); window > 0: a query sees only the `window`
+// newest keys up to itself; kv_lo (device, [B], may be null): keys and queries of batch b below kv_lo[b] are padding
+// (padding queries produce zeros).  Returns a cudaError_t.
+IPEX_API int ipex_attn_prefill_tcgen05_ex(const void* q, const void* k, const void* vt, void* out, int B, int S, int Hq,
+                                          int Hkv, int D, int64_t ldq, int64_t ldk, int64_t s_pad, int64_t ldo,
+                                          float scale, int causal, float softcap, int window, const int* kv_lo,
+                                          int dtype, int* err, void* stream) {
   if (B < 1 || S < 1 || Hq < 1 || Hkv < 1 || Hq % Hkv != 0 || B > 65535 || Hq > 65535) return (int)cudaErrorInvalidValue;
   if ((ldq % 8) != 0 || (ldk % 8) != 0 || (ldo % 8) != 0 || (s_pad % 8) != 0 || s_pad < S)
     return (int)cudaErrorInvalidValue;
   if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)vt | (uintptr_t)out) & 15) return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == DT_F16) {
-    if (D == 128) return launch<__half, 128>(q, k, vt, out, B, S, Hq, Hkv, ldq, ldk, s_pad, ldo, scale, causal, err, s);
-    if (D == 64) return launch<__half, 64>(q, k, vt, out, B, S, Hq, Hkv, ldq, ldk, s_pad, ldo, scale, causal, err, s);
+    if (D == 128)
+      return launch<__half, 128>(q, k, vt, out, B, S, Hq, Hkv, ldq, ldk, s_pad, ldo, scale, causal, softcap, window,
+                                 kv_lo, err, s);
+    if (D == 64)
+      return launch<__half, 64>(q, k, vt, out, B, S, Hq, Hkv, ldq, ldk, s_pad, ldo, scale, causal, softcap, window,
+                                kv_lo, err, s);
   } else if (dtype == DT_BF16) {
     if (D == 128)
-      return launch<__nv_bfloat16, 128>(q, k, vt, out, B, S, Hq, Hkv, ldq, ldk, s_pad, ldo, scale, causal, err, s);
+      return launch<__nv_bfloat16, 128>(q, k, vt, out, B, S, Hq, Hkv, ldq, ldk, s_pad, ldo, scale, causal, softcap,
+                                        window, kv_lo, err, s);
     if (D == 64)
-      return launch<__nv_bfloat16, 64>(q, k, vt, out, B, S, Hq, Hkv, ldq, ldk, s_pad, ldo, scale, causal, err, s);
+      return launch<__nv_bfloat16, 64>(q, k, vt, out, B, S, Hq, Hkv, ldq, ldk, s_pad, ldo, scale, causal, softcap,
+                                       window, kv_lo, err, s);
   }
   return (int)cudaErrorInvalidValue;
+}
+
+// Plain form: no soft-cap, no window, no padding.
+IPEX_API int ipex_attn_prefill_tcgen05(const void* q, const void* k, const void* vt, void* out, int B, int S, int Hq,
+                                       int Hkv, int D, int64_t ldq, int64_t ldk, int64_t s_pad, int64_t ldo,
+                                       float scale, int causal, int dtype, int* err, void* stream) {
+  return ipex_attn_prefill_tcgen05_ex(q, k, vt, out, B, S, Hq, Hkv, D, ldq, ldk, s_pad, ldo, scale, causal, 0.f, 0,
+                                      nullptr, dtype, err, stream);
 }
 
 // The transposed V the kernel above reads: v is token-major (row stride ldv elements), vt [B, Hkv, D, s_pad] gets

@@ -227,9 +227,26 @@ __global__ void argmax_kernel(const T* __restrict__ logits, int64_t* __restrict_
   const T* row = logits + (int64_t)blockIdx.x * ld;
   float best = -INFINITY;
   int besti = 0;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  int done = 0;
+  if constexpr (sizeof(T) == 2) {
+    // 16-byte loads, a few independent ones per thread (a scalar walk was a chain of ~30 dependent 2-byte loads)
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+      const int nvec = V / 8;
+      for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(row + (size_t)v * 8);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const float f = DT<T>::to_f(e[j]);
+          if (f > best) { best = f; besti = v * 8 + j; }     // ascending index inside a thread: first maximum wins
+        }
+      }
+      done = nvec * 8;
+    }
+  }
+  for (int i = done + threadIdx.x; i < V; i += blockDim.x) {
     float v = DT<T>::to_f(row[i]);
-    if (v > best) { best = v; besti = i; }
+    if (v > best || (v == best && i < besti)) { best = v; besti = i; }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {

@@ -526,11 +526,13 @@ def attn_prefill_tcgen05_ok(q, k, v) -> bool:
     return _token_major(q) and _token_major(k)
 
 
-def attn_prefill_tcgen05(q, k, v, scale: float, causal: bool = True) -> torch.Tensor:
+def attn_prefill_tcgen05(q, k, v, scale: float, causal: bool = True, softcap: float = 0.0, window: int = 0,
+                         kv_lo: torch.Tensor = None) -> torch.Tensor:
     """Prompt attention (Sq == Skv) on the tcgen05 kernel.  ``q [B, Hq, S, D]`` and ``k [B, Hkv, S, D]`` are
     token-major views (see ``_token_major``), already rotated; ``v`` any layout.  Returns ``[B, Hq, S, D]`` as a
     view of a ``[B, S, Hq, D]`` buffer, so the ``transpose(1, 2).reshape(T, Hq * D)`` that feeds the output
-    projection is free."""
+    projection is free.  ``softcap`` (Gemma-2 tanh cap of the scaled scores), ``window`` (sliding window) and
+    ``kv_lo`` (int32 ``[B]``: first real token of each left-padded row) are applied inside the kernel."""
     lib = cuda_lib()
     B, Hq, S, D = q.shape
     Hkv = k.shape[1]
@@ -546,11 +548,57 @@ def attn_prefill_tcgen05(q, k, v, scale: float, causal: bool = True) -> torch.Te
             torch.empty(B, Hkv, D, S, dtype=q.dtype, device=q.device)
         vt[..., :S].copy_(v.transpose(-1, -2))
     out = torch.empty(B, S, Hq, D, dtype=q.dtype, device=q.device)
-    rc = lib.ipex_attn_prefill_tcgen05(ptr(q), ptr(k), ptr(vt), ptr(out), B, S, Hq, Hkv, D, q.stride(2), k.stride(2),
-                                       s_pad, Hq * D, float(scale), int(bool(causal)), _dt(q),
-                                       ptr(error_flag(q.device)), current_stream())
+    if softcap or window or kv_lo is not None:
+        fn = lib.ipex_attn_prefill_tcgen05_ex
+        vp, ci, i64, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
+        fn.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, i64, i64, i64, i64, cf, ci, cf, ci, vp, ci, vp, vp]
+        fn.restype = ci
+        rc = fn(ptr(q), ptr(k), ptr(vt), ptr(out), B, S, Hq, Hkv, D, q.stride(2), k.stride(2), s_pad, Hq * D,
+                float(scale), int(bool(causal)), float(softcap or 0.0), int(window or 0), ptr(kv_lo), _dt(q),
+                ptr(error_flag(q.device)), current_stream())
+    else:
+        rc = lib.ipex_attn_prefill_tcgen05(ptr(q), ptr(k), ptr(vt), ptr(out), B, S, Hq, Hkv, D, q.stride(2),
+                                           k.stride(2), s_pad, Hq * D, float(scale), int(bool(causal)), _dt(q),
+                                           ptr(error_flag(q.device)), current_stream())
     api.check(rc, "attn_prefill_tcgen05")
     return out.transpose(1, 2)
+
+
+_mask_shape_cache = {}
+
+
+def left_pad_mask_bounds(mask: torch.Tensor, S: int, window: int = 0):
+    """If ``mask`` (``[B, 1, S, S]``, boolean "may attend" or additive) is exactly a left-padding mask, i.e.
+    ``key >= lo[b]`` (and ``key <= query`` when causal, and ``key > query - window`` with a sliding window) for
+    every real query row, return ``(lo int32 [B], causal)``; else ``None``.  Rows of padding queries are ignored
+    (their content differs between mask builders and their outputs are never used).  One comparison and one host
+    synchronisation per distinct mask: the result is cached for the layers that follow."""
+    if mask.dim() != 4 or mask.shape[1] != 1 or mask.shape[2] != S or mask.shape[3] < S:
+        return None
+    key = (mask.data_ptr(), mask._version, tuple(mask.shape), mask.dtype, S, window)
+    if key in _mask_shape_cache:
+        return _mask_shape_cache[key]
+    vis = mask[:, 0, :, :S]
+    vis = vis if vis.dtype == torch.bool else vis > torch.finfo(vis.dtype).min / 2
+    any_col = vis.any(dim=-2)                                   # keys somebody sees
+    lo = torch.where(any_col.any(dim=-1), any_col.int().argmax(dim=-1), torch.full_like(any_col[:, 0].int(), S))
+    qi = torch.arange(S, device=mask.device).view(1, S, 1)
+    ki = torch.arange(S, device=mask.device).view(1, 1, S)
+    real_q = qi >= lo.view(-1, 1, 1)
+    result = None
+    for causal in (True, False):
+        exp = ki >= lo.view(-1, 1, 1)
+        if causal:
+            exp = exp & (ki <= qi)
+        if window:
+            exp = exp & (ki > qi - window)
+        if bool(((vis == exp) | ~real_q).all()):
+            result = (lo.to(torch.int32).contiguous(), causal)
+            break
+    if len(_mask_shape_cache) > 8:
+        _mask_shape_cache.clear()
+    _mask_shape_cache[key] = result
+    return result
 
 
 def sdpa_prefill(q, k, v, mask, scale, softcap, sliding_window, causal=True):
@@ -559,6 +607,16 @@ def sdpa_prefill(q, k, v, mask, scale, softcap, sliding_window, causal=True):
     (models/common.py:288-305)."""
     from ..models.common import repeat_kv
     n_rep = q.shape[1] // k.shape[1]
+    if (softcap or sliding_window or mask is not None) and attn_prefill_tcgen05_ok(q, k, v) and \
+            hasattr(cuda_lib(), "ipex_attn_prefill_tcgen05_ex") and \
+            os.environ.get("IPEX_LLM_TCGEN05_ATTN_EXT", "1") != "0":
+        # soft-capped (Gemma-2), sliding-window and left-padded prompts stay on the tcgen05 kernel
+        S = q.shape[2]
+        window = int(sliding_window) if sliding_window and sliding_window < S else 0
+        bounds = left_pad_mask_bounds(mask, S, window) if mask is not None else (None, causal)
+        if bounds is not None:
+            lo, is_causal = bounds
+            return attn_prefill_tcgen05(q, k, v, scale, is_causal, softcap or 0.0, window, lo)
     if softcap or sliding_window:
         kk, vv = repeat_kv(k, n_rep), repeat_kv(v, n_rep)
         w = torch.matmul(q, kk.transpose(2, 3)).float() * scale

@@ -33,6 +33,8 @@ def init_pipeline_parallel():
     if "RANK" not in os.environ and "PMI_RANK" in os.environ:
         os.environ["RANK"] = os.environ["PMI_RANK"]
         os.environ["WORLD_SIZE"] = os.environ.get("PMI_SIZE", "1")
+    os.environ.setdefault("RANK", "0")             # plain `python` start: a pipeline of one stage
+    os.environ.setdefault("WORLD_SIZE", "1")
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29500")
     if torch.cuda.is_available():
