@@ -317,7 +317,7 @@ def main():
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t0
         e2e = e2e_s
-    clocks = clocks_box.get("c")
+    clocks = sampler.stop() if rank == 0 else None
 
     # ---- the reference harness's own metric: per-token cost of model.generate (first token / mean of the rest) ----
     gen_stats = None

@@ -49,7 +49,7 @@ def run(argv=None, timed=None):
     model = AutoModelForCausalLM.from_config(cfg, load_in_low_bit=a.low_bit, torch_dtype=torch.float16, device=dev,
                                              seed=0, pipeline_parallel_stages=world)
     g = torch.Generator().manual_seed(7)
-    ids = torch.randint(0, cfg.vocab_size, (a.batch, a.prompt), generator=g)
+    ids = torch.randint(0, cfg.vocab_size, (a.batch, a.prompt), generator=g).to(dev)
     model.generate(ids[:, :32], max_new_tokens=4, do_sample=False)            # warm-up
     if timed:
         timed[0]()
