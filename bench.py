@@ -323,6 +323,7 @@ def main():
     gen_stats = None
     if not args.no_e2e:
         n_new = min(32, max(4, args.steps))
+        model.generate(ids, max_new_tokens=n_new, do_sample=False)       # warm-up (the harness does one too)
         model.generate(ids, max_new_tokens=n_new, do_sample=False)
         gen_stats = {"first_cost_ms": round(1e3 * float(model.first_token_time), 3),
                      "rest_cost_mean_ms": round(1e3 * float(model.rest_cost_mean), 4), "new_tokens": n_new}

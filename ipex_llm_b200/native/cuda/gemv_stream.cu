@@ -47,6 +47,15 @@ struct StreamArgs {
   int tp_rank, tp_world, tp_npad;
   float* const* tp_bufs;   // [tp_world] device pointers: rank r's partial buffer [tp_world][8][tp_npad] fp32
   int* const* tp_flags;    // [tp_world] device pointers: rank r's per-tile arrival counters
+  // mixture-of-experts mode (moe_ranges != null): ONE launch walks every expert that received tokens.  The (token,
+  // choice) slots are sorted by expert: moe_ranges[e] = (first position, count) in moe_order.  A pass = one expert
+  // and up to M of its tokens: the CTA stages those rows of x and every warp group streams its share of the
+  // expert's row tiles; the rings run ahead across passes.  x row = moe_order[pos] / moe_xdiv (moe_gather) or pos;
+  // y row = moe_order[pos] (moe_scatter) or pos.
+  const uint8_t* const* moe_w;
+  const int* moe_ranges;
+  const int* moe_order;
+  int moe_experts, moe_slots, moe_gather, moe_scatter, moe_xdiv;
 };
 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
@@ -128,12 +137,13 @@ __device__ __forceinline__ float act_apply(float g, int act) {
 //   int8 : xi = round(x / dx) in [-16383, 16383], hi = xi >> 7, lo = xi & 127, bytes in the octet order
 //          (k0,k4,k1,k5 | k2,k6,k3,k7) of the masked weight words;
 //   fp8  : hi = e4m3(x / dx), lo = e4m3(x / dx - hi), natural k order.
-// RMS norm fused (norm_w != null); rows zero padded to Kp.  scratch: [M][2][kW] floats.
+// RMS norm fused (norm_w != null); rows zero padded to Kp.  scratch: [M][2][kW] floats.  xrow (expert mode): the rows
+// of x to stage; M rows (a.M is only the capacity there).
 // ------------------------------------------------------------------------------------------------------------------
 template <typename T, int WFK>
-__device__ void stage_x(const StreamArgs& a, uint8_t* xq, int2* seeds, int NT, float* dxs, float* scratch, int Kp) {
+__device__ void stage_x(const StreamArgs& a, int M, const int* xrow, uint8_t* xq, int2* seeds, int NT, float* dxs,
+                        float* scratch, int Kp) {
   const int tid = threadIdx.x;
-  const int M = a.M;
   const T* x = reinterpret_cast<const T*>(a.x);
   const T* nw = reinterpret_cast<const T*>(a.norm_w);
   const int nvec = a.K / 8;   // K % 64 == 0
@@ -148,7 +158,7 @@ __device__ void stage_x(const StreamArgs& a, uint8_t* xq, int2* seeds, int NT, f
   const int wpr = M <= 1 ? 16 : (M <= 2 ? 8 : (M <= 4 ? 4 : 2));   // warps per row
   const int m = warp / wpr;                                         // this thread's row (>= M: none)
   const int tr = (warp % wpr) * 32 + (tid & 31), team = wpr * 32;
-  const T* xr = x + (size_t)(m < M ? m : 0) * a.ldx;
+  const T* xr = x + (size_t)(m < M ? (xrow != nullptr ? xrow[m] : m) : 0) * a.ldx;
   // pass 1: sum of squares and largest |x * w| of the row
   if (m < M) {
     float ss = 0.f, mx = 0.f;
@@ -343,6 +353,10 @@ __device__ __forceinline__ void stage_mma_fp8(const uint8_t* st, int cpw, int nc
 // Position of a warp in its sequence of stages: unit (RT consecutive row tiles), tile of the unit, stage of the tile.
 struct Walk {
   int unit, r, sp;
+  // expert mode: the pass (expert e, its tokens [base, base + M) of cnt, first position `first` in the sorted
+  // order, pidx = passes so far); a plain GEMV is one pass
+  int e, base, cnt, first, pidx;
+  const uint8_t* w;   // weight matrix of the pass (looked up once per pass, not per stage)
 };
 
 template <typename T, int WFK, int RT, int MH>
@@ -368,7 +382,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const StreamAr
   const int cend = cbeg + cper < chunks ? cbeg + cper : chunks;
   const int spt = (cend - cbeg + CPW - 1) / CPW;
   const int ustep = gridDim.x * G;
-  const int unit0 = blockIdx.x + gridDim.x * grp;
 
   // shared memory: rings | barriers | xq | seeds | dxs | scratch | reduction buffers
   uint8_t* ring = smem_raw + (size_t)warp * S * stage_bytes;
@@ -384,14 +397,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const StreamAr
   off += 32;
   float* scratch = reinterpret_cast<float*>(smem_raw + off);
   off += (size_t)8 * 2 * kW * sizeof(float);
+  int* xrow = reinterpret_cast<int*>(smem_raw + off);      // expert mode: rows of x / y of the pass, [2][8]
+  int* yrow = xrow + 8;
+  off += 64;
   float* red = reinterpret_cast<float*>(smem_raw + off);   // [G][2][wpt][RT * MH * 2][32] when wpt > 1
 
-  const uint8_t* codes = a.w;
+  const bool moe = a.moe_ranges != nullptr;
+  const int Mcap = a.M;
   const size_t code_bytes = (size_t)Np * chunks * CB / 16;
-  const uint8_t* scales = a.w + code_bytes;
 
   // lane 0 requests stage `w` of this warp into ring slot `slot`
   auto issue = [&](const Walk& w, int slot) {
+    const uint8_t* codes = w.w;
+    const uint8_t* scales = codes + code_bytes;
     const int tile = w.unit * RT + w.r;
     const int c0 = cbeg + w.sp * CPW;
     const int nch = cend - c0 < CPW ? cend - c0 : CPW;
@@ -401,22 +419,68 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const StreamAr
     bulk_g2s(dst, codes + chunk_index * CB, (uint32_t)(nch * CB), &full[slot]);
     bulk_g2s(dst + CPW * CB, scales + chunk_index * SB, (uint32_t)(nch * SB), &full[slot]);
   };
-  // next stage of the warp's sequence; false when the sequence has ended
+  // next pass of the launch (false when there is none); sets the first unit of this warp's group in it.  Units are
+  // dealt round-robin over the CTAs, continuing where the previous pass stopped.
+  auto next_pass = [&](Walk& w) {
+    if (!moe) {
+      if (w.pidx >= 0) return false;
+      w.w = a.w;
+    } else {
+      bool found = false;
+      if (w.pidx >= 0) {
+        w.base += Mcap;
+        found = w.base < w.cnt;
+      }
+      if (!found) {
+        for (++w.e; w.e < a.moe_experts; ++w.e) {
+          int cnt = a.moe_ranges[2 * w.e + 1];
+          cnt = cnt < a.moe_slots ? cnt : a.moe_slots;
+          if (cnt > 0) {
+            w.cnt = cnt;
+            w.first = a.moe_ranges[2 * w.e];
+            w.base = 0;
+            w.w = a.moe_w[w.e];
+            found = true;
+            break;
+          }
+        }
+      }
+      if (!found) return false;
+    }
+    w.pidx++;
+    const int goff = moe ? (int)(((long long)w.pidx * nunits) % gridDim.x) : 0;
+    w.unit = (int)((blockIdx.x + gridDim.x - goff) % gridDim.x) + gridDim.x * grp;
+    w.r = 0;
+    w.sp = 0;
+    return true;
+  };
+  // first / next stage of the warp's sequence; false when the sequence has ended
+  auto first_stage = [&](Walk& w) {
+    if (spt <= 0) return false;
+    while (next_pass(w))
+      if (w.unit < nunits) return true;
+    return false;
+  };
   auto advance = [&](Walk& w) {
     if (++w.sp < spt) return true;
     w.sp = 0;
     if (++w.r < RT && w.unit * RT + w.r < ntiles) return true;
     w.r = 0;
     w.unit += ustep;
-    return w.unit < nunits;
+    if (w.unit < nunits) return true;
+    while (next_pass(w))
+      if (w.unit < nunits) return true;
+    return false;
   };
 
-  Walk iw = {unit0, 0, 0};
-  bool more = unit0 < nunits && spt > 0;   // stages left to request
+  Walk iw = {0, 0, 0, -1, 0, 0, 0, -1, nullptr};
+  bool more = false;   // stages left to request (lane 0)
+  if (moe) pdl_wait();   // the expert ranges come from the kernel before this one
   if (lane == 0) {
     for (int s = 0; s < S; s++) mbar_init(&full[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     // fill the ring before waiting for the previous kernel: the weights do not depend on it
+    more = first_stage(iw);
     for (int s = 0; s < S && more; s++) {
       issue(iw, s);
       more = advance(iw);
@@ -425,7 +489,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const StreamAr
   __syncwarp();
   pdl_launch_dependents();
   pdl_wait();
-  stage_x<T, WFK>(a, xq, seeds, NT, dxs, scratch, Kp);
+  if (!moe) stage_x<T, WFK>(a, a.M, nullptr, xq, seeds, NT, dxs, scratch, Kp);
 
   T* y = reinterpret_cast<T*>(a.y);
   bool ok = true;
@@ -469,121 +533,139 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const StreamAr
     }
   };
 
-  for (int unit = unit0; unit < nunits; unit += ustep, nu++) {
-    float acc[RT][MH][2];
+  Walk cw = {0, 0, 0, -1, 0, 0, 0, -1, nullptr};
+  int M = a.M;          // rows of the current pass
+  while (next_pass(cw)) {
+    if (moe) {
+      __syncthreads();    // every warp is done with the previous pass's rows
+      M = cw.cnt - cw.base < Mcap ? cw.cnt - cw.base : Mcap;
+      if (tid < M) {
+        const int pos = cw.first + cw.base + tid;
+        int slot = a.moe_order[pos];
+        slot = slot < 0 ? 0 : (slot >= a.moe_slots ? a.moe_slots - 1 : slot);
+        xrow[tid] = a.moe_gather ? slot / a.moe_xdiv : pos;
+        yrow[tid] = a.moe_scatter ? slot : pos;
+      }
+      __syncthreads();
+      stage_x<T, WFK>(a, M, xrow, xq, seeds, NT, dxs, scratch, Kp);
+    }
+    for (int unit = cw.unit; unit < nunits; unit += ustep, nu++) {
+      float acc[RT][MH][2];
 #pragma unroll
-    for (int r = 0; r < RT; r++)
+      for (int r = 0; r < RT; r++)
 #pragma unroll
-      for (int h = 0; h < MH; h++) acc[r][h][0] = acc[r][h][1] = 0.f;
+        for (int h = 0; h < MH; h++) acc[r][h][0] = acc[r][h][1] = 0.f;
 #pragma unroll
-    for (int r = 0; r < RT; r++) {
-      if (unit * RT + r >= ntiles) break;
-      for (int sp = 0; sp < spt; sp++) {
-        if (ok && !mbar_wait(&full[slot], phase)) {
-          if (lane == 0) atomicExch(a.err, 2);
-          ok = false;
+      for (int r = 0; r < RT; r++) {
+        if (unit * RT + r >= ntiles) break;
+        for (int sp = 0; sp < spt; sp++) {
+          if (ok && !mbar_wait(&full[slot], phase)) {
+            if (lane == 0) atomicExch(a.err, 2);
+            ok = false;
+          }
+          if (ok) {
+            const int c0 = cbeg + sp * CPW;
+            const int nch = cend - c0 < CPW ? cend - c0 : CPW;
+            const uint8_t* st = ring + (size_t)slot * stage_bytes;
+            if constexpr (WFK == WFK_I8) stage_mma_i8<MH>(st, CPW, nch, c0, xq, seeds, M, stride, acc[r]);
+            else stage_mma_fp8<MH>(st, CPW, nch, c0, xq, M, stride, acc[r]);
+          }
+          __syncwarp();
+          if (lane == 0 && ok && more) {
+            // the warp's reads of this slot (generic proxy) are ordered before the refill (async proxy)
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            issue(iw, slot);
+            more = advance(iw);
+          }
+          if (++slot == S) { slot = 0; phase ^= 1; }
         }
-        if (ok) {
-          const int c0 = cbeg + sp * CPW;
-          const int nch = cend - c0 < CPW ? cend - c0 : CPW;
-          const uint8_t* st = ring + (size_t)slot * stage_bytes;
-          if constexpr (WFK == WFK_I8) stage_mma_i8<MH>(st, CPW, nch, c0, xq, seeds, a.M, stride, acc[r]);
-          else stage_mma_fp8<MH>(st, CPW, nch, c0, xq, a.M, stride, acc[r]);
+      }
+      // ---- the wpt partial tiles meet in shared memory; warp 0 of the group finishes the unit ----
+      if (wpt > 1) {
+        float* buf = red + ((size_t)(grp * 2 + (nu & 1)) * wpt) * (RT * MH * 2 * 32);
+        if (wi != 0) {
+#pragma unroll
+          for (int r = 0; r < RT; r++)
+#pragma unroll
+            for (int h = 0; h < MH; h++) {
+              buf[((size_t)wi * RT * MH * 2 + (r * MH + h) * 2 + 0) * 32 + lane] = acc[r][h][0];
+              buf[((size_t)wi * RT * MH * 2 + (r * MH + h) * 2 + 1) * 32 + lane] = acc[r][h][1];
+            }
         }
+        group_sync(1 + grp, wpt * 32);
+        if (wi != 0) continue;
+        for (int w = 1; w < wpt; w++) {
+#pragma unroll
+          for (int r = 0; r < RT; r++)
+#pragma unroll
+            for (int h = 0; h < MH; h++) {
+              acc[r][h][0] += buf[((size_t)w * RT * MH * 2 + (r * MH + h) * 2 + 0) * 32 + lane];
+              acc[r][h][1] += buf[((size_t)w * RT * MH * 2 + (r * MH + h) * 2 + 1) * 32 + lane];
+            }
+        }
+      }
+      if (RT == 1 && a.tp_world > 1) {
+        if (tp_pending >= 0) tp_collect(tp_pending);
+        tp_pending = -1;
+        if (!ok) continue;
+        for (int rk = 0; rk < a.tp_world; rk++) {
+          float* dst = a.tp_bufs[rk] + (size_t)a.tp_rank * 8 * a.tp_npad;
+#pragma unroll
+          for (int h = 0; h < MH; h++) {
+            const int m = t + 4 * h;
+            if (m >= a.M) continue;
+            const float dx = dxs[m];
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+              const int n = unit * 16 + g + 8 * half;
+              if (n < a.N) dst[(size_t)m * a.tp_npad + n] = acc[0][h][half] * dx;
+            }
+          }
+        }
+        __threadfence_system();
         __syncwarp();
-        if (lane == 0 && ok && more) {
-          // the warp's reads of this slot (generic proxy) are ordered before the refill (async proxy)
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          issue(iw, slot);
-          more = advance(iw);
-        }
-        if (++slot == S) { slot = 0; phase ^= 1; }
+        if (lane < a.tp_world) red_release_sys_add(a.tp_flags[lane] + unit, 1);
+        tp_pending = unit;
+        continue;
       }
-    }
-    // ---- the wpt partial tiles meet in shared memory; warp 0 of the group finishes the unit ----
-    if (wpt > 1) {
-      float* buf = red + ((size_t)(grp * 2 + (nu & 1)) * wpt) * (RT * MH * 2 * 32);
-      if (wi != 0) {
-#pragma unroll
-        for (int r = 0; r < RT; r++)
-#pragma unroll
-          for (int h = 0; h < MH; h++) {
-            buf[((size_t)wi * RT * MH * 2 + (r * MH + h) * 2 + 0) * 32 + lane] = acc[r][h][0];
-            buf[((size_t)wi * RT * MH * 2 + (r * MH + h) * 2 + 1) * 32 + lane] = acc[r][h][1];
-          }
-      }
-      group_sync(1 + grp, wpt * 32);
-      if (wi != 0) continue;
-      for (int w = 1; w < wpt; w++) {
-#pragma unroll
-        for (int r = 0; r < RT; r++)
-#pragma unroll
-          for (int h = 0; h < MH; h++) {
-            acc[r][h][0] += buf[((size_t)w * RT * MH * 2 + (r * MH + h) * 2 + 0) * 32 + lane];
-            acc[r][h][1] += buf[((size_t)w * RT * MH * 2 + (r * MH + h) * 2 + 1) * 32 + lane];
-          }
-      }
-    }
-    if (RT == 1 && a.tp_world > 1) {
-      if (tp_pending >= 0) tp_collect(tp_pending);
-      tp_pending = -1;
       if (!ok) continue;
-      for (int rk = 0; rk < a.tp_world; rk++) {
-        float* dst = a.tp_bufs[rk] + (size_t)a.tp_rank * 8 * a.tp_npad;
+      // ---- epilogue: lane (g, t) holds rows g and g + 8 of the unit's tiles for tokens t and t + 4 ----
 #pragma unroll
-        for (int h = 0; h < MH; h++) {
-          const int m = t + 4 * h;
-          if (m >= a.M) continue;
-          const float dx = dxs[m];
-#pragma unroll
-          for (int half = 0; half < 2; half++) {
-            const int n = unit * 16 + g + 8 * half;
-            if (n < a.N) dst[(size_t)m * a.tp_npad + n] = acc[0][h][half] * dx;
-          }
-        }
-      }
-      __threadfence_system();
-      __syncwarp();
-      if (lane < a.tp_world) red_release_sys_add(a.tp_flags[lane] + unit, 1);
-      tp_pending = unit;
-      continue;
-    }
-    if (!ok) continue;
-    // ---- epilogue: lane (g, t) holds rows g and g + 8 of the unit's tiles for tokens t and t + 4 ----
-#pragma unroll
-    for (int h = 0; h < MH; h++) {
-      const int m = t + 4 * h;
-      if (m >= a.M) continue;
-      const float dx = dxs[m];
-      if (RT == 2 && a.act != 0) {
-#pragma unroll
-        for (int half = 0; half < 2; half++) {
-          const int row = g + 8 * half;
-          const int n = unit * 16 + row;
-          if (n >= a.N / 2) continue;
-          float gsum = acc[0][h][half] * dx, usum = acc[RT - 1][h][half] * dx;
-          if (a.bias != nullptr) {
-            gsum += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[(size_t)unit * 32 + row]);
-            usum += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[(size_t)unit * 32 + 16 + row]);
-          }
-          y[(size_t)m * a.ldy + n] = DT<T>::from_f(act_apply(gsum, a.act) * usum);
-        }
-      } else {
-#pragma unroll
-        for (int r = 0; r < RT; r++)
+      for (int h = 0; h < MH; h++) {
+        const int m = t + 4 * h;
+        if (m >= M) continue;
+        const float dx = dxs[m];
+        const size_t ym = moe ? (size_t)yrow[m] : (size_t)m;   // output row of token m
+        if (RT == 2 && a.act != 0) {
 #pragma unroll
           for (int half = 0; half < 2; half++) {
-            const int n = (unit * RT + r) * 16 + g + 8 * half;
-            if (n >= a.N) continue;
-            float sv = acc[r][h][half] * dx;
-            if (a.bias != nullptr) sv += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[n]);
-            if (a.residual != nullptr)
-              sv += DT<T>::to_f(reinterpret_cast<const T*>(a.residual)[(size_t)m * a.ldr + n]);
-            y[(size_t)m * a.ldy + n] = DT<T>::from_f(sv);
+            const int row = g + 8 * half;
+            const int n = unit * 16 + row;
+            if (n >= a.N / 2) continue;
+            float gsum = acc[0][h][half] * dx, usum = acc[RT - 1][h][half] * dx;
+            if (a.bias != nullptr) {
+              gsum += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[(size_t)unit * 32 + row]);
+              usum += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[(size_t)unit * 32 + 16 + row]);
+            }
+            y[ym * a.ldy + n] = DT<T>::from_f(act_apply(gsum, a.act) * usum);
           }
+        } else {
+#pragma unroll
+          for (int r = 0; r < RT; r++)
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+              const int n = (unit * RT + r) * 16 + g + 8 * half;
+              if (n >= a.N) continue;
+              float sv = acc[r][h][half] * dx;
+              if (a.bias != nullptr) sv += DT<T>::to_f(reinterpret_cast<const T*>(a.bias)[n]);
+              if (a.residual != nullptr)
+                sv += DT<T>::to_f(reinterpret_cast<const T*>(a.residual)[(size_t)m * a.ldr + n]);
+              y[ym * a.ldy + n] = DT<T>::from_f(sv);
+            }
+        }
       }
     }
-  }
+  }  // passes
   if (tp_pending >= 0) tp_collect(tp_pending);
 }
 
@@ -616,7 +698,7 @@ bool make_plan(const StreamArgs& a, Plan& p) {
   p.wpt = wpt;
   const int cper = (chunks + wpt - 1) / wpt;
   size_t fixed = (size_t)kW * 16 * 8 + 16 + (((size_t)2 * a.M * (Kp + kPad) + 15) & ~(size_t)15) + 32 +
-                 (size_t)8 * 2 * kW * 4 + 128;
+                 (size_t)8 * 2 * kW * 4 + 64 + 128;
   if (WFK == WFK_I8) fixed += (size_t)(Kp / 64) * 4 * MH * 8;
   if (wpt > 1) fixed += (size_t)kW * 2 * RT * MH * 2 * 32 * 4;
   const size_t cap = 227 * 1024;
@@ -695,6 +777,8 @@ static int stream_entry(const void* w, int wf, const void* x, void* y, int M, in
   a.tp_rank = tp_rank; a.tp_world = tp_world; a.tp_npad = tp_npad;
   a.tp_bufs = reinterpret_cast<float* const*>(tp_bufs);
   a.tp_flags = reinterpret_cast<int* const*>(tp_flags);
+  a.moe_w = nullptr; a.moe_ranges = nullptr; a.moe_order = nullptr;
+  a.moe_experts = 0; a.moe_slots = 0; a.moe_gather = 0; a.moe_scatter = 0; a.moe_xdiv = 1;
   cudaStream_t s = (cudaStream_t)stream;
   auto run = [&](const StreamArgs& b, bool dep) -> int {
     if (dtype == DT_F16) {
@@ -745,4 +829,44 @@ IPEX_API int ipex_gemv_lowbit_stream_ar(const void* w, int wf, const void* x, vo
   (void)lut;
   return stream_entry(w, wf, x, y, M, N, K, ldx, ldy, norm_w, eps, norm_offset, bias, residual, ldr, 0, dtype, pdl,
                       err, stream, tp_rank, tp_world, tp_npad, tp_bufs, tp_flags);
+}
+
+// Mixture-of-experts GEMV for small batches, ONE launch for all experts (same contract as ipex_moe_gemv_tma): the
+// (token, choice) slots were sorted by expert on the device (ipex_moe_sort_slots: `order` [slots], `ranges`
+// [experts][2] = first position, count); the CTAs walk the experts that received tokens, stage up to four of an
+// expert's rows of x at a time and stream its weights through the warp-private rings, which keep running ahead
+// across experts.  gather: x row = order[pos] / x_div, else pos; scatter: y row = order[pos], else pos.
+// Weight families: symmetric int4 and fp8 e4m3; anything else returns cudaErrorInvalidValue (use the other kernel).
+IPEX_API int ipex_moe_gemv_stream(const void* w_list, int wf, const void* ranges, const void* order, int experts,
+                                  int slots, int max_rows, const void* x, int x_div, int gather, int scatter, void* y,
+                                  int N, int K, int ldx, int ldy, int act, const float* lut, int dtype, int* err,
+                                  void* stream) {
+  (void)lut;
+  if (experts < 1 || slots < 1 || max_rows < 1 || x_div < 1 || (K % 64) != 0 || err == nullptr ||
+      w_list == nullptr || ranges == nullptr || order == nullptr)
+    return (int)cudaErrorInvalidValue;
+  if (wf != WF_SYM_INT4 && wf != WF_FP8_E4M3) return (int)cudaErrorInvalidValue;
+  if (wf == WF_FP8_E4M3 && (K % 128) != 0) return (int)cudaErrorInvalidValue;
+  if ((ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0) return (int)cudaErrorInvalidValue;
+  if (act != 0 && (N % 32) != 0) return (int)cudaErrorInvalidValue;
+  StreamArgs a;
+  a.w = nullptr; a.x = x; a.y = y; a.norm_w = nullptr; a.bias = nullptr; a.residual = nullptr;
+  a.err = err;
+  a.M = max_rows < 4 ? max_rows : 4;      // rows of one pass (one MMA per 512 weights serves four tokens)
+  a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy; a.ldr = 0; a.eps = 0.f; a.norm_offset = 0.f;
+  a.act = act; a.stages = 0; a.cpw = 0; a.wpt = 1;
+  a.tp_rank = 0; a.tp_world = 1; a.tp_npad = 0; a.tp_bufs = nullptr; a.tp_flags = nullptr;
+  a.moe_w = reinterpret_cast<const uint8_t* const*>(w_list);
+  a.moe_ranges = reinterpret_cast<const int*>(ranges);
+  a.moe_order = reinterpret_cast<const int*>(order);
+  a.moe_experts = experts; a.moe_slots = slots; a.moe_gather = gather; a.moe_scatter = scatter; a.moe_xdiv = x_div;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == DT_F16) {
+    return wf == WF_SYM_INT4 ? (int)dispatch<__half, WFK_I8>(a, s, false) : (int)dispatch<__half, WFK_FP8>(a, s, false);
+  }
+  if (dtype == DT_BF16) {
+    return wf == WF_SYM_INT4 ? (int)dispatch<__nv_bfloat16, WFK_I8>(a, s, false)
+                             : (int)dispatch<__nv_bfloat16, WFK_FP8>(a, s, false);
+  }
+  return (int)cudaErrorInvalidValue;
 }

@@ -718,16 +718,27 @@ def moe_forward(experts, hidden_states, top_k_index, top_k_weights, residual=Non
         api.check(sfn(ptr(ids), slots, E, ptr(order), ptr(ranges), current_stream()), "moe_sort_slots")
         if tfn is not None and mode != "tiled":
             # one persistent launch per projection: the weight ring keeps streaming across the experts
-            tfn.argtypes = [vp, ci, vp, vp, ci, ci, ci, vp, ci, ci, ci, vp, ci, ci, ci, ci, ci, vp, ci, vp, vp]
-            tfn.restype = ci
+            sig = [vp, ci, vp, vp, ci, ci, ci, vp, ci, ci, ci, vp, ci, ci, ci, ci, ci, vp, ci, vp, vp]
+            tfn.argtypes, tfn.restype = sig, ci
+            sfn2 = getattr(lib, "ipex_moe_gemv_stream", None)      # warp-private rings (sym_int4 / fp8_e4m3)
+            if sfn2 is not None:
+                sfn2.argtypes, sfn2.restype = sig, ci
             err = ptr(error_flag(x.device))
-            rc = tfn(ptr(bank.gu_ptrs), bank.wf, ptr(ranges), ptr(order), E, slots, T, ptr(x), k, 1, 0, ptr(act),
-                     2 * bank.I, bank.H, x.stride(0), act.stride(0), act_code, ptr(lut), _dt(x), err,
-                     current_stream())
-            api.check(rc, "moe_gemv_tma(gate_up)")
-            rc = tfn(ptr(bank.dn_ptrs), bank.wf, ptr(ranges), ptr(order), E, slots, T, ptr(act), 1, 0, 1, ptr(y),
-                     bank.H, bank.I, act.stride(0), y.stride(0), 0, ptr(lut), _dt(x), err, current_stream())
-            api.check(rc, "moe_gemv_tma(down)")
+
+            def walk(args, what):
+                rc = 1
+                if sfn2 is not None and mode != "tma-shared":
+                    rc = sfn2(*args)            # 1 (invalid value): a format or shape it does not take
+                if rc == 1:
+                    rc = tfn(*args)
+                api.check(rc, what)
+
+            walk((ptr(bank.gu_ptrs), bank.wf, ptr(ranges), ptr(order), E, slots, T, ptr(x), k, 1, 0, ptr(act),
+                  2 * bank.I, bank.H, x.stride(0), act.stride(0), act_code, ptr(lut), _dt(x), err,
+                  current_stream()), "moe_gemv(gate_up)")
+            walk((ptr(bank.dn_ptrs), bank.wf, ptr(ranges), ptr(order), E, slots, T, ptr(act), 1, 0, 1, ptr(y),
+                  bank.H, bank.I, act.stride(0), y.stride(0), 0, ptr(lut), _dt(x), err, current_stream()),
+                 "moe_gemv(down)")
         else:
             gfn.argtypes = [vp, ci, vp, vp, ci, ci, vp, ci, ci, ci, vp, ci, ci, ci, ci, ci, vp, ci, vp]
             gfn.restype = ci
