@@ -255,6 +255,7 @@ def main():
     max_steps = max(args.steps, min(4096, 1536 // max(1, batch)))
     total_len = prompt + args.warmup * 2 + max_steps + args.steps + 48
     eng = get_engine(model, batch, total_len)
+    kv_fp8 = eng.kv_fp8
 
     # ---- prompt pass (1st token), timed on the device ----
     ids = ids_host.to(dev)
@@ -334,6 +335,44 @@ def main():
         e2e_m, first_ms = t.tolist()
         e2e = e2e_m if e2e is not None else None
 
+    # ---- tensor-parallel numerics: a two-layer model of the same shape, sharded over the ranks, against the same
+    # (seeded) model held whole by rank 0: logits of the prompt pass and of one decode step ----
+    tp_check = None
+    if world > 1 and not args.no_e2e:
+        import copy
+        launches = eng.kernel_launches_per_step
+        del eng
+        model._ipex_engine = None
+        cfg2 = copy.deepcopy(cfg)
+        cfg2.num_hidden_layers = 2
+        ids2 = ids[:1, :96]
+
+        def two_steps(m):
+            e = get_engine(m, 1, 256)
+            lg0 = e.prefill(ids2).float().clone()
+            e.tokens[:1] = torch.argmax(lg0, dim=-1)
+            e.decode_step(1)
+            torch.cuda.synchronize()
+            return lg0, e.gather_logits(1).float().clone()
+
+        small_tp = AutoModelForCausalLM.from_config(cfg2, load_in_low_bit=low_bit, device=f"cuda:{local_rank}",
+                                                    torch_dtype=dtype, seed=0, tp_group=tp_group)
+        a0, a1 = two_steps(small_tp)
+        del small_tp
+        if rank == 0:
+            whole = AutoModelForCausalLM.from_config(cfg2, load_in_low_bit=low_bit, device=f"cuda:{local_rank}",
+                                                     torch_dtype=dtype, seed=0)
+            b0, b1 = two_steps(whole)
+            cos = torch.nn.functional.cosine_similarity
+            tp_check = {"layers": 2, "prompt_tokens": int(ids2.shape[1]),
+                        "prefill_logits_cos": round(float(cos(a0, b0, dim=-1).min()), 5),
+                        "decode_logits_cos": round(float(cos(a1, b1, dim=-1).min()), 5),
+                        "decode_max_abs_err": round(float((a1 - b1).abs().max()), 4),
+                        "same_argmax": bool(torch.equal(a1.argmax(-1), b1.argmax(-1)))}
+        dist.barrier()
+    else:
+        launches = eng.kernel_launches_per_step
+
     if rank == 0:
         ms_per_step = dev_ms / steps_timed
         value = batch * 1000.0 / ms_per_step
@@ -348,17 +387,18 @@ def main():
             "data": "synthetic random token ids, random-init N(0,0.02) weights of the named architecture",
             "impl": "ours",
             "config": {"model": name, "low_bit": low_bit, "global_batch": batch, "seq_len": prompt,
-                       "kv_cache": "fp8_e5m2" if eng.kv_fp8 else str(dtype).replace("torch.", ""),
+                       "kv_cache": "fp8_e5m2" if kv_fp8 else str(dtype).replace("torch.", ""),
                        "parallelism": f"tp{n_gpus}" if n_gpus > 1 else "single",
                        "l2_policy": "inputs larger than L2: every step streams the full packed weights "
                                     f"({sum(p.numel() * p.element_size() for p in model.parameters()) / 1e9:.2f} GB)",
                        "decode_engine": "one persistent kernel per token (cuda-graph replay)"
-                       if eng.kernel_launches_per_step == 1 else "cuda-graph + programmatic dependent launch"},
+                       if launches == 1 else "cuda-graph + programmatic dependent launch"},
             "first_token_ms": round(first_ms, 3),
             "first_token_cold_ms": round(first_cold_ms, 3),
             "model_build_s": round(load_s, 2),
-            "gpu_launches": int(steps_timed * eng.kernel_launches_per_step),
+            "gpu_launches": int(steps_timed * launches),
             "generate": gen_stats,
+            "tp_check": tp_check,
             "clocks": clocks,
         }
         if e2e is not None:

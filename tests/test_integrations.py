@@ -125,3 +125,32 @@ def test_ipex_llm_init_settings(capsys):
     assert ipex_llm_init.main(["--gpu", "--threads", "3"]) == 0
     out = capsys.readouterr().out
     assert "export OMP_NUM_THREADS=3" in out and "export NCCL_NVLS_ENABLE=1" in out
+
+
+def test_langchain_vllm_wrapper_builds_sampling_params():
+    """``langchain.vllm.VLLM`` turns a generate call into sampling parameters + ``client.generate`` (a double stands in
+    for the vLLM engine; nothing is loaded)."""
+    from ipex_llm_b200.langchain.vllm import VLLM
+
+    class _Out:
+        def __init__(self, text):
+            self.text = text
+            self.outputs = [self]
+
+    class _Client:
+        def __init__(self):
+            self.calls = []
+
+        def generate(self, prompts, params):
+            self.calls.append((list(prompts), params))
+            return [_Out(p + "!") for p in prompts]
+
+    client = _Client()
+    llm = VLLM(client=client, model="unused", temperature=0.5, max_new_tokens=7)
+    texts = llm.generate_texts(["a", "bc"], stop=["\n"], top_p=0.9)
+    assert texts == ["a!", "bc!"]
+    prompts, params = client.calls[0]
+    get = (lambda k: params[k]) if isinstance(params, dict) else (lambda k: getattr(params, k))
+    assert prompts == ["a", "bc"] and get("temperature") == 0.5 and get("max_tokens") == 7 and get("top_p") == 0.9
+    assert list(get("stop")) == ["\n"]
+    assert llm._llm_type == "vllm"
