@@ -85,6 +85,91 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const float* __restr
   out[i] = DT<T>::from_f(acc);
 }
 
+// DeepSeek-V3 grouped routing, one warp per token: s = sigmoid(score), sb = s + bias; a group's score is the sum of
+// its two largest sb; the topk_group best groups stay; the top_k largest sb among them are chosen (descending); the
+// weights are the UNBIASED s of the chosen experts, optionally renormalised, times `scale`.
+template <typename T>
+__global__ void moe_group_topk_kernel(const T* __restrict__ scores, const float* __restrict__ bias,
+                                      int64_t* __restrict__ idx, float* __restrict__ w, int tokens, int E, int n_group,
+                                      int topk_group, int k, int renorm, float scale) {
+  extern __shared__ float sm_gt[];                 // per warp: sb [E] | group score [32] | group kept [32]
+  const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tok = blockIdx.x * (blockDim.x >> 5) + wib;
+  if (tok >= tokens) return;
+  float* sb = sm_gt + (size_t)wib * (E + 64);
+  float* gscore = sb + E;
+  float* gkeep = gscore + 32;
+  const int gs = E / n_group;
+  float s[kMaxPerLane], v[kMaxPerLane];
+#pragma unroll
+  for (int j = 0; j < kMaxPerLane; j++) {
+    const int i = lane + 32 * j;
+    s[j] = 0.f;
+    v[j] = -INFINITY;
+    if (i < E) {
+      s[j] = 1.0f / (1.0f + __expf(-DT<T>::to_f(scores[(size_t)tok * E + i])));
+      v[j] = s[j] + bias[i];
+      sb[i] = v[j];
+    }
+  }
+  __syncwarp();
+  if (lane < n_group) {
+    float a = -INFINITY, b = -INFINITY;            // two largest of the group
+    for (int i = 0; i < gs; i++) {
+      const float x = sb[lane * gs + i];
+      if (x > a) { b = a; a = x; } else if (x > b) { b = x; }
+    }
+    gscore[lane] = a + b;
+    gkeep[lane] = 0.f;
+  }
+  __syncwarp();
+  if (lane == 0) {
+    for (int r = 0; r < topk_group; r++) {
+      int best = -1;
+      float bv = -INFINITY;
+      for (int g = 0; g < n_group; g++)
+        if (gkeep[g] == 0.f && (best < 0 || gscore[g] > bv)) { best = g; bv = gscore[g]; }
+      if (best >= 0) gkeep[best] = 1.f;
+    }
+  }
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < kMaxPerLane; j++) {
+    const int i = lane + 32 * j;
+    if (i >= E || gkeep[i / gs] == 0.f) v[j] = -INFINITY;
+  }
+  float chosen[8];
+  int chosen_i[8];
+  float tot = 0.f;
+  for (int r = 0; r < k; r++) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; j++)
+      if (v[j] > bv) { bv = v[j]; bi = lane + 32 * j; }
+    warp_argmax(bv, bi);
+    bi = bi == 0x7fffffff ? 0 : bi;
+    // the weight is the unbiased score of the winner: its owner broadcasts it
+    float sw = 0.f;
+    if ((bi & 31) == lane) {
+#pragma unroll
+      for (int j = 0; j < kMaxPerLane; j++)
+        if (j == (bi >> 5)) { sw = s[j]; v[j] = -INFINITY; }
+    }
+    sw = __shfl_sync(0xffffffffu, sw, bi & 31);
+    chosen[r] = sw;
+    chosen_i[r] = bi;
+    tot += sw;
+  }
+  if (lane == 0) {
+    const float f = (renorm ? 1.0f / (tot + 1e-20f) : 1.0f) * scale;
+    for (int r = 0; r < k; r++) {
+      w[(size_t)tok * k + r] = chosen[r] * f;
+      idx[(size_t)tok * k + r] = chosen_i[r];
+    }
+  }
+}
+
 // Stable counting sort of up to kSortMaxSlots (token, choice) slots by expert id, in one CTA.
 // order[pos] = slot, ranges[e] = (first pos, count).
 constexpr int kSortMaxSlots = 1024;
@@ -158,6 +243,30 @@ IPEX_API int ipex_moe_combine_add(const void* y, const float* w, const void* res
 IPEX_API int ipex_moe_combine(const void* y, const float* w, void* out, int tokens, int k, int H, int dtype,
                               void* stream) {
   return ipex_moe_combine_add(y, w, nullptr, out, tokens, k, H, dtype, stream);
+}
+
+// scores [tokens, E] (dtype), bias [E] fp32 -> idx [tokens, k] int64 (descending biased score), w [tokens, k] fp32.
+// E <= 256 and divisible by n_group <= 32, topk_group <= n_group, k <= 8.
+IPEX_API int ipex_moe_group_topk(const void* scores, const float* bias, int64_t* idx, float* w, int tokens, int E,
+                                 int n_group, int topk_group, int k, int renorm, float scale, int dtype, void* stream) {
+  if (tokens < 1 || E < 1 || E > 32 * kMaxPerLane || n_group < 1 || n_group > 32 || E % n_group != 0 ||
+      topk_group < 1 || topk_group > n_group || k < 1 || k > 8 || k > topk_group * (E / n_group))
+    return (int)cudaErrorInvalidValue;
+  const int warps = 4, threads = warps * 32, blocks = (tokens + warps - 1) / warps;
+  const size_t smem = (size_t)warps * (E + 64) * sizeof(float);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == DT_F16)
+    moe_group_topk_kernel<__half><<<blocks, threads, smem, s>>>((const __half*)scores, bias, idx, w, tokens, E, n_group,
+                                                                 topk_group, k, renorm, scale);
+  else if (dtype == DT_BF16)
+    moe_group_topk_kernel<__nv_bfloat16><<<blocks, threads, smem, s>>>((const __nv_bfloat16*)scores, bias, idx, w,
+                                                                        tokens, E, n_group, topk_group, k, renorm,
+                                                                        scale);
+  else if (dtype == DT_F32)
+    moe_group_topk_kernel<float><<<blocks, threads, smem, s>>>((const float*)scores, bias, idx, w, tokens, E, n_group,
+                                                                topk_group, k, renorm, scale);
+  else return (int)cudaErrorInvalidValue;
+  return (int)cudaGetLastError();
 }
 
 // Sort `slots` (token, choice) slots by expert on the device: order [slots] int32, ranges [E][2] int32

@@ -882,6 +882,23 @@ def moe_softmax_topk(router_logits, top_k, renormalize):
 
 
 def moe_group_topk(scores, bias, n_group, topk_group, top_k, norm_topk_prob, routed_scaling_factor):
-    """DeepSeek-V3 grouped routing on the device (tensor ops; no host round trip)."""
+    """DeepSeek-V3 grouped routing on the device: one kernel (a warp per token) when the shape fits it, tensor ops
+    otherwise.  Returns ``(indices [T, k] int64, weights [T, k] fp32)``."""
     from .moe import _group_topk_impl
-    return _group_topk_impl(scores, bias, n_group, topk_group, top_k, norm_topk_prob, routed_scaling_factor)
+    lib = cuda_lib()
+    fn = getattr(lib, "ipex_moe_group_topk", None)
+    T, E = scores.shape
+    if fn is None or not scores.is_cuda or scores.requires_grad or E > 256 or n_group > 32 or E % n_group or \
+            top_k > 8 or top_k > topk_group * (E // n_group) or \
+            scores.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        return _group_topk_impl(scores, bias, n_group, topk_group, top_k, norm_topk_prob, routed_scaling_factor)
+    sc = scores.contiguous()
+    b = bias.to(torch.float32).contiguous()
+    idx = torch.empty((T, top_k), dtype=torch.int64, device=sc.device)
+    w = torch.empty((T, top_k), dtype=torch.float32, device=sc.device)
+    vp, ci, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+    fn.argtypes, fn.restype = [vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, cf, ci, vp], ci
+    rc = fn(ptr(sc), ptr(b), ptr(idx), ptr(w), T, E, int(n_group), int(topk_group), int(top_k),
+            int(bool(norm_topk_prob)), float(routed_scaling_factor), _dt(sc), current_stream())
+    api.check(rc, "moe_group_topk")
+    return idx, w

@@ -110,7 +110,12 @@ def moe_group_topk(scores: torch.Tensor, bias: torch.Tensor, n_group: int, topk_
                    norm_topk_prob: bool, routed_scaling_factor: float):
     """DeepSeek-V3 routing: sigmoid scores + per-expert bias choose ``topk_group`` of ``n_group`` expert groups
     (group score = sum of its two best biased scores), then ``top_k`` experts inside them; weights are the
-    unbiased scores, renormalised and scaled."""
+    unbiased scores, renormalised and scaled.  On the GPU this is one kernel (``ipex_moe_group_topk``, a warp per
+    token; the reference's ``xe_addons.moe_group_topk``, models/deepseek.py:283-287)."""
+    if scores.is_cuda and not scores.requires_grad:
+        from . import cuda_ops
+        return cuda_ops.moe_group_topk(scores, bias, n_group, topk_group, top_k, norm_topk_prob,
+                                       routed_scaling_factor)
     return _group_topk_impl(scores, bias, n_group, topk_group, top_k, norm_topk_prob, routed_scaling_factor)
 
 

@@ -22,6 +22,24 @@ def test_router_softmax_topk(E, k, dtype):
     assert torch.allclose(w2, torch.topk(ref_p, k, dim=-1).values, atol=1e-5)
 
 
+@pytest.mark.parametrize("cfg", [(256, 8, 4, 8), (64, 8, 3, 6), (160, 8, 3, 6), (16, 4, 2, 4)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_group_topk_kernel(cfg, dtype):
+    """DeepSeek-V3 grouped routing kernel against the tensor-op formulation."""
+    from ipex_llm_b200.ops import cuda_ops
+    from ipex_llm_b200.ops.moe import _group_topk_impl
+    E, n_group, topk_group, k = cfg
+    torch.manual_seed(E + k)
+    scores = (torch.randn(37, E, device="cuda") * 2).to(dtype)
+    bias = torch.randn(E, device="cuda") * 0.3
+    assert hasattr(cuda_ops.cuda_lib(), "ipex_moe_group_topk")
+    for renorm in (True, False):
+        idx, w = cuda_ops.moe_group_topk(scores, bias, n_group, topk_group, k, renorm, 2.5)
+        ref_idx, ref_w = _group_topk_impl(scores, bias, n_group, topk_group, k, renorm, 2.5)
+        assert torch.equal(idx, ref_idx)
+        assert torch.allclose(w, ref_w.float(), atol=1e-5, rtol=1e-4)
+
+
 def _bank(E, H, I, qname, dtype):
     from ipex_llm_b200.ops.moe import LowBitExperts
     from ipex_llm_b200.quant import qtypes as qt
