@@ -845,11 +845,11 @@ IPEX_API int ipex_gemv_lowbit_stream_ar(const void* w, int wf, const void* x, vo
 // expert's rows of x at a time and stream its weights through the warp-private rings, which keep running ahead
 // across experts.  gather: x row = order[pos] / x_div, else pos; scatter: y row = order[pos], else pos.
 // Weight families: symmetric int4 and fp8 e4m3; anything else returns cudaErrorInvalidValue (use the other kernel).
-IPEX_API int ipex_moe_gemv_stream(const void* w_list, int wf, const void* ranges, const void* order, int experts,
-                                  int slots, int max_rows, const void* x, int x_div, int gather, int scatter, void* y,
-                                  int N, int K, int ldx, int ldy, int act, const float* lut, int dtype, int* err,
-                                  void* stream) {
-  (void)lut;
+// norm_w != null: every staged row is RMS-normalised with that weight first (the layer's post-attention norm).
+IPEX_API int ipex_moe_gemv_stream_norm(const void* w_list, int wf, const void* ranges, const void* order,
+                                       int experts, int slots, int max_rows, const void* x, int x_div, int gather,
+                                       int scatter, void* y, int N, int K, int ldx, int ldy, int act, int dtype,
+                                       int* err, void* stream, const void* norm_w, float eps, float norm_offset) {
   if (experts < 1 || slots < 1 || max_rows < 1 || x_div < 1 || (K % 64) != 0 || err == nullptr ||
       w_list == nullptr || ranges == nullptr || order == nullptr)
     return (int)cudaErrorInvalidValue;
@@ -858,10 +858,10 @@ IPEX_API int ipex_moe_gemv_stream(const void* w_list, int wf, const void* ranges
   if ((ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0) return (int)cudaErrorInvalidValue;
   if (act != 0 && (N % 32) != 0) return (int)cudaErrorInvalidValue;
   StreamArgs a;
-  a.w = nullptr; a.x = x; a.y = y; a.norm_w = nullptr; a.bias = nullptr; a.residual = nullptr;
+  a.w = nullptr; a.x = x; a.y = y; a.norm_w = norm_w; a.bias = nullptr; a.residual = nullptr;
   a.err = err;
   a.M = max_rows < 4 ? max_rows : 4;      // rows of one pass (one MMA per 512 weights serves four tokens)
-  a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy; a.ldr = 0; a.eps = 0.f; a.norm_offset = 0.f;
+  a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy; a.ldr = 0; a.eps = eps; a.norm_offset = norm_offset;
   a.act = act; a.stages = 0; a.cpw = 0; a.wpt = 1;
   a.tp_rank = 0; a.tp_world = 1; a.tp_npad = 0; a.tp_bufs = nullptr; a.tp_flags = nullptr;
   a.moe_w = reinterpret_cast<const uint8_t* const*>(w_list);
@@ -877,4 +877,14 @@ IPEX_API int ipex_moe_gemv_stream(const void* w_list, int wf, const void* ranges
                              : (int)dispatch<__nv_bfloat16, WFK_FP8>(a, s, false);
   }
   return (int)cudaErrorInvalidValue;
+}
+
+// Without a fused norm (the rows of x are used as they are).
+IPEX_API int ipex_moe_gemv_stream(const void* w_list, int wf, const void* ranges, const void* order, int experts,
+                                  int slots, int max_rows, const void* x, int x_div, int gather, int scatter, void* y,
+                                  int N, int K, int ldx, int ldy, int act, const float* lut, int dtype, int* err,
+                                  void* stream) {
+  (void)lut;
+  return ipex_moe_gemv_stream_norm(w_list, wf, ranges, order, experts, slots, max_rows, x, x_div, gather, scatter, y, N,
+                                   K, ldx, ldy, act, dtype, err, stream, nullptr, 0.f, 0.f);
 }
