@@ -385,7 +385,7 @@ class _BaseAutoModelClass:
     @classmethod
     def from_config(cls, config, load_in_low_bit="sym_int4", load_in_4bit=False, optimize_model=True,
                     device="cuda", torch_dtype=torch.float16, seed=0, init_std=0.02, modules_to_not_convert=None,
-                    tp_group=None, speculative=False, **kwargs):
+                    tp_group=None, speculative=False, consistent_tp_shards=False, **kwargs):
         """Random-initialised model of ``config``'s architecture, created layer by layer on ``device`` and
         quantized there (weights ~ N(0, init_std), seeded).  Peak memory = one layer in ``torch_dtype`` plus the
         packed model, so a 70B fp8 model is built on one 180-GB GPU without ever existing in half precision."""
@@ -397,7 +397,7 @@ class _BaseAutoModelClass:
                 else cls.HF_Model(config)
         from .random_init import convert_random_init
         model = convert_random_init(model, qtype, optimize_model, device, torch_dtype, seed, init_std,
-                                    modules_to_not_convert or [], tp_group)
+                                    modules_to_not_convert or [], tp_group, consistent_shards=consistent_tp_shards)
         model.config.update({"bigdl_transformers_low_bit": q_k, "bigdl_disk_embedding": False,
                              "tie_word_embeddings": False})
         stages = kwargs.pop("pipeline_parallel_stages", 1)

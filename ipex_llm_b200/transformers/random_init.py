@@ -21,21 +21,44 @@ def _seed_for(name: str, seed: int) -> int:
 
 
 def convert_random_init(model, qtype, optimize_model, device, dtype, seed, std, modules_to_not_convert,
-                        tp_group=None):
+                        tp_group=None, consistent_shards=False):
+    """``consistent_shards``: under tensor parallelism, draw every sharded matrix whole (with the seed an unsharded
+    model would use) and keep this rank's slice, so that the sharded model IS the unsharded one; off by default
+    because every rank then generates the full model (the default draws each shard independently).  Replicated
+    parameters (embeddings, norms) always use the same seed on every rank."""
     from .model import _rebuild_nonpersistent
     device = torch.device(device)
+    shard_seed = seed
+    col_cls = row_cls = ()
+    world = rank = 1
     if tp_group is not None:
-        from ..parallel.tp import auto_tp
+        from ..parallel.tp import ColumnParallelLinear, RowParallelLinear, auto_tp
         model = auto_tp(model, tp_group)
-        seed = seed + 7919 * tp_group.rank
+        shard_seed = seed + 7919 * tp_group.rank
+        col_cls, row_cls = ColumnParallelLinear, RowParallelLinear
+        world, rank = tp_group.world_size, tp_group.rank
     gen = torch.Generator(device=device)
 
     def materialize(module, full_name):
+        is_col, is_row = isinstance(module, col_cls), isinstance(module, row_cls)
         for pname, p in list(module._parameters.items()):
             if p is None or p.device.type != "meta" or isinstance(p, FP4Params):
                 continue
-            gen.manual_seed(_seed_for(f"{full_name}.{pname}", seed))
-            if p.dim() >= 2:
+            sharded = (is_col or (is_row and p.dim() >= 2)) and world > 1
+            whole = sharded and consistent_shards
+            gen.manual_seed(_seed_for(f"{full_name}.{pname}", shard_seed if sharded and not whole else seed))
+            if whole and p.dim() >= 2:
+                # the matrix an unsharded model holds under this name; this rank keeps its rows (column-parallel)
+                # or columns (row-parallel)
+                n, k = p.shape
+                if is_col:
+                    full = torch.empty((n * world, k), dtype=dtype, device=device).normal_(0.0, std, generator=gen)
+                    t = full[rank * n:(rank + 1) * n].contiguous()
+                else:
+                    full = torch.empty((n, k * world), dtype=dtype, device=device).normal_(0.0, std, generator=gen)
+                    t = full[:, rank * k:(rank + 1) * k].contiguous()
+                del full
+            elif p.dim() >= 2:
                 t = torch.empty(tuple(p.shape), dtype=dtype, device=device).normal_(0.0, std, generator=gen)
             elif pname == "weight" and "norm" in type(module).__name__.lower():
                 t = torch.ones(tuple(p.shape), dtype=dtype, device=device)
