@@ -607,6 +607,22 @@ def sdpa_prefill(q, k, v, mask, scale, softcap, sliding_window, causal=True):
     (models/common.py:288-305)."""
     from ..models.common import repeat_kv
     n_rep = q.shape[1] // k.shape[1]
+    D = q.shape[-1]
+    if D in (72, 80, 96, 112) and q.is_cuda and not q.requires_grad and q.shape[2] == k.shape[2] and \
+            q.shape[2] >= 64 and q.dtype in (torch.float16, torch.bfloat16) and \
+            hasattr(cuda_lib(), "ipex_attn_prefill_tcgen05") and os.environ.get("IPEX_LLM_TCGEN05_ATTN", "1") != "0":
+        # head dims between the kernel's sizes (Phi-2 / StableLM 80, Phi-3-mini 96, SigLIP 72): zero-pad to 128 in a
+        # token-major buffer (the padded dims add nothing to q.k and produce zero output columns), as the
+        # reference pads them for its own kernels (models/utils.py:218-240)
+        B, Hq, S, _ = q.shape
+        Hkv = k.shape[1]
+        buf = torch.zeros(B, S, Hq + 2 * Hkv, 128, dtype=q.dtype, device=q.device)
+        buf[:, :, :Hq, :D] = q.transpose(1, 2)
+        buf[:, :, Hq:Hq + Hkv, :D] = k.transpose(1, 2)
+        buf[:, :, Hq + Hkv:, :D] = v.transpose(1, 2)
+        out = sdpa_prefill(buf[:, :, :Hq].transpose(1, 2), buf[:, :, Hq:Hq + Hkv].transpose(1, 2),
+                           buf[:, :, Hq + Hkv:].transpose(1, 2), mask, scale, softcap, sliding_window, causal)
+        return out[..., :D]
     if (softcap or sliding_window or mask is not None) and attn_prefill_tcgen05_ok(q, k, v) and \
             hasattr(cuda_lib(), "ipex_attn_prefill_tcgen05_ex") and \
             os.environ.get("IPEX_LLM_TCGEN05_ATTN_EXT", "1") != "0":

@@ -137,3 +137,21 @@ def test_irregular_mask_is_not_taken_for_padding():
     m = torch.ones(1, 1, S, S, dtype=torch.bool, device="cuda").tril()
     m[0, 0, 100, 50] = False                    # a hole: not a left-padding mask
     assert cuda_ops.left_pad_mask_bounds(m, S) is None
+
+
+@pytest.mark.parametrize("D", [80, 96])
+def test_head_dims_between_kernel_sizes_are_padded(D):
+    """Head dims 80 / 96 (Phi-2, StableLM-3B, Phi-3-mini) run on the tcgen05 kernel through a zero-padded copy."""
+    from ipex_llm_b200.ops import cuda_ops
+    B, Hq, Hkv, S = 2, 8, 4, 200
+    torch.manual_seed(D)
+    q = torch.randn(B, Hq, S, D, device="cuda").half()
+    k = torch.randn(B, Hkv, S, D, device="cuda").half()
+    v = torch.randn(B, Hkv, S, D, device="cuda").half()
+    scale = 1.0 / math.sqrt(D)
+    out = cuda_ops.sdpa_prefill(q, k, v, None, scale, None, None, causal=True)
+    torch.cuda.synchronize()
+    cuda_ops.check_error_flag(q.device)
+    ref = _reference(q, k, v, scale, True)
+    assert out.shape == ref.shape
+    assert (out.float() - ref).abs().max().item() < 4e-3
