@@ -190,3 +190,48 @@ def test_audio_transcription_endpoint(monkeypatch):
     assert seen == {"n": len(x) * 2, "language": "en"}
     bad = client.post("/v1/audio/transcriptions", content=b"x", headers={"content-type": "text/plain"})
     assert bad.status_code == 400
+
+
+def test_tgi_api_server_relays_fastchat_worker_stream():
+    """``TGIApp`` turns a FastChat worker's NUL-delimited cumulative-text stream into TGI ``/generate`` and
+    ``/generate_stream`` responses (worker looked up through a controller; the transport is a double)."""
+    import json as _json
+    from starlette.testclient import TestClient
+    from ipex_llm_b200.serving.fastchat.tgi_api_server import TGIApp
+
+    class _Transport:
+        def __init__(self):
+            self.posts = []
+
+        async def post_json(self, url, payload):
+            self.posts.append((url, payload))
+            if url.endswith("/list_models"):
+                return {"models": ["tiny"]}
+            return {"address": "http://worker:1"}
+
+        async def post_stream(self, url, payload):
+            self.posts.append((url, payload))
+            chunks = [{"text": "Hel", "error_code": 0}, {"text": "Hello", "error_code": 0},
+                      {"text": "Hello!", "error_code": 0, "finish_reason": "stop",
+                       "usage": {"completion_tokens": 3}}]
+            raw = b"".join(_json.dumps(c).encode() + b"\0" for c in chunks)
+            yield raw[:20]                      # chunks split across reads
+            yield raw[20:]
+
+    tr = _Transport()
+    client = TestClient(TGIApp(controller_address="http://ctl", transport=tr).app)
+    r = client.post("/generate", json={"inputs": "Hi", "parameters": {"max_new_tokens": 5, "details": True,
+                                                                      "do_sample": False, "stop": ["\n"]}})
+    assert r.status_code == 200
+    body = r.json()
+    assert body["generated_text"] == "Hello!" and body["details"]["finish_reason"] == "stop"
+    assert body["details"]["generated_tokens"] == 3
+    url, payload = [p for p in tr.posts if p[0].endswith("/worker_generate_stream")][0]
+    assert url == "http://worker:1/worker_generate_stream"
+    assert payload["prompt"] == "Hi" and payload["max_new_tokens"] == 5 and payload["temperature"] == 0.0
+    assert payload["stop"] == ["\n"] and payload["model"] == ""
+    with client.stream("POST", "/generate_stream", json={"inputs": "Hi"}) as s:
+        events = [_json.loads(line[6:]) for line in s.iter_lines() if line.startswith("data: ")]
+    assert [e["token"]["text"] for e in events] == ["Hel", "lo", "!"]
+    assert events[-1]["generated_text"] == "Hello!" and events[-1]["details"]["finish_reason"] == "stop"
+    assert client.get("/v1/models").json()["data"][0]["id"] == "tiny"
