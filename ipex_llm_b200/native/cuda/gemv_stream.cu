@@ -367,7 +367,7 @@ struct Walk {
   const uint8_t* w;   // weight matrix of the pass (looked up once per pass, not per stage)
 };
 
-template <typename T, int WFK, int RT, int MH>
+template <typename T, int WFK, int RT, int MH, bool MOE /* expert walk compiled in */>
 __global__ void __launch_bounds__(kThreads, kCtasPerSM) gemv_stream_kernel(const StreamArgs a) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   constexpr int CB = WFK == WFK_I8 ? 1024 : 2048;   // code bytes per 128-k chunk of a row tile
@@ -410,7 +410,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSM) gemv_stream_kernel(const
   off += 64;
   float* red = reinterpret_cast<float*>(smem_raw + off);   // [G][2][wpt][RT * MH * 2][32] when wpt > 1
 
-  const bool moe = a.moe_ranges != nullptr;
+  const bool moe = MOE;
   const int Mcap = a.M;
   const size_t code_bytes = (size_t)Np * chunks * CB / 16;
 
@@ -735,7 +735,7 @@ cudaError_t launch_stream(StreamArgs a, cudaStream_t stream, bool pdl) {
   a.stages = p.stages;
   a.cpw = p.cpw;
   a.wpt = p.wpt;
-  auto kern = gemv_stream_kernel<T, WFK, RT, MH>;
+  auto kern = a.moe_ranges != nullptr ? gemv_stream_kernel<T, WFK, RT, 1, true> : gemv_stream_kernel<T, WFK, RT, MH, false>;
   if (p.smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
     if (e != cudaSuccess) return e;
