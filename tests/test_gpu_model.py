@@ -64,6 +64,42 @@ def test_engine_logits_close_to_module_path(tiny_llama_dir, monkeypatch):
     assert torch.allclose(eng.logits[:1].float(), step_logits, atol=1e-3)
 
 
+@pytest.mark.parametrize("low_bit,dtype", [("sym_int4", torch.float16), ("fp8_e4m3", torch.bfloat16)])
+def test_decode_of_many_sequences_uses_the_gemm_path(low_bit, dtype, monkeypatch):
+    """Large decode batches run on the tcgen05 low-bit GEMMs (weights read once per step); the logits
+    agree with the module tree and with the eight-row GEMV chunks, eagerly and under graph replay."""
+    from transformers import LlamaConfig
+    from ipex_llm.transformers import AutoModelForCausalLM
+    from ipex_llm_b200.engine import get_engine
+    monkeypatch.setenv("IPEX_LLM_QUANTIZE_KV_CACHE", "0")
+    cfg = LlamaConfig(hidden_size=512, intermediate_size=1408, num_hidden_layers=2, num_attention_heads=8,
+                      num_key_value_heads=2, vocab_size=32000, max_position_embeddings=1024,
+                      tie_word_embeddings=False)
+    m = AutoModelForCausalLM.from_config(cfg, load_in_low_bit=low_bit, device="cuda", torch_dtype=dtype)
+    B = 28
+    torch.manual_seed(B)
+    ids = torch.randint(0, 32000, (B, 25), device="cuda")
+    eng = get_engine(m, B, 128)
+    assert eng._gemm_decode_ok()
+    with torch.no_grad():
+        ref = m(ids).logits[:, -1].float()
+
+    def step(graph):
+        eng.prefill(ids[:, :24])
+        eng.tokens[:B] = ids[:, 24]
+        eng.decode_step(B, use_graph=graph)
+        torch.cuda.synchronize()
+        return eng.logits[:B].float().clone()
+
+    a = step(False)
+    cos = torch.nn.functional.cosine_similarity(a, ref, dim=-1)
+    assert cos.min() > 0.995, cos
+    assert torch.allclose(step(True), a, atol=2e-3)
+    monkeypatch.setenv("IPEX_LLM_DECODE_GEMM", "0")
+    b = step(False)
+    assert torch.nn.functional.cosine_similarity(a, b, dim=-1).min() > 0.995
+
+
 def test_from_config_and_step_api():
     from transformers import LlamaConfig
     from ipex_llm.transformers import AutoModelForCausalLM
