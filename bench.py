@@ -56,7 +56,8 @@ MODELS = {
 }
 
 
-# Decode throughput of the cuBLAS + NCCL stand-in recorded in BASELINE.md (tokens/s at batch 1), by (model, GPUs):
+# Decode throughput of the cuBLAS + NCCL stand-in (baseline/constructed.py) measured on this hardware, tokens/s at
+# batch 1, by (model, GPUs):
 # the denominator of ``vs_baseline``.  Set-ups without a recorded number report null.
 BASELINE_TOK_S = {("llama2-7b", 1): 171.0, ("llama3-70b", 2): 23.0, ("llama3-70b", 8): 22.1}
 BASELINE_SAMPLES_S = {("llama2-13b", 1): 10.17}

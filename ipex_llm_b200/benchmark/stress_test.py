@@ -36,7 +36,7 @@ def main(argv=None):
         total = time.perf_counter() - t
         rest = float(getattr(model, "rest_cost_mean", total / out_len))
         mem = torch.cuda.memory_reserved() / 2 ** 30 if device == "cuda" else 0.0
-        if r == 1:                                      # round 0 pays graph capture and allocator growth
+        if r == 1:                                      # the first pass pays graph capture and allocator growth
             base_lat, base_mem = rest, mem
         drift = base_lat is not None and (rest > base_lat * a.max_latency_drift or
                                           (base_mem and mem > base_mem * a.max_memory_drift))
