@@ -37,6 +37,13 @@ def quantize_kv_cache_flag():
     return v
 
 
+def kv_cache_format():
+    """``"int4"`` when IPEX_LLM_QUANTIZE_KV_CACHE=int4 asks for the 4-bit cache (4.25 bits per element), else None
+    (``"1"`` keeps meaning the e5m2 byte cache of the reference)."""
+    v = _flag("IPEX_LLM_QUANTIZE_KV_CACHE")
+    return "int4" if v is not None and v.strip().lower() == "int4" else None
+
+
 def compress_kv_cache_flag():
     return env_bool("IPEX_LLM_COMPRESS_KV_CACHE")
 

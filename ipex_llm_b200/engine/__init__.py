@@ -30,6 +30,9 @@ def supports(model, kwargs) -> bool:
         return False
     if getattr(model, "_ipex_engine_disabled", False):
         return False
+    from .. import config as _cfg
+    if _cfg.kv_cache_format() == "int4":
+        return False            # the 4-bit KV cache lives on the module path (the fused kernels read fp16 / e5m2)
     for k in _UNSUPPORTED_KW:
         v = kwargs.get(k)
         if v is not None and v not in (False, 1):

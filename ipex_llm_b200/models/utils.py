@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from .. import config as cfg
-from ..ops.kv_cache import (DynamicCompressCache, DynamicCompressFp8Cache, DynamicFp8Cache,
+from ..ops.kv_cache import (DynamicCompressCache, DynamicCompressFp8Cache, DynamicFp8Cache, DynamicInt4Cache,
                             DynamicNormalCache)
 from ..quant import qtypes as qt
 
@@ -87,6 +87,8 @@ def select_cache(config, hidden_states: torch.Tensor, past_key_values, probe_lin
         return past_key_values
     if use_compress:
         return DynamicCompressFp8Cache(config) if use_quantize else DynamicCompressCache(config)
+    if cfg.kv_cache_format() == "int4":
+        return DynamicInt4Cache(config)
     if use_quantize:
         return DynamicFp8Cache(config)
     return DynamicNormalCache(config)

@@ -163,6 +163,55 @@ class Fp8Layer(NormalLayer):
         return fp8_e5m2_dequantize(self.keys, dtype), fp8_e5m2_dequantize(self.values, dtype)
 
 
+def int4_kv_quantize(x: torch.Tensor) -> torch.Tensor:
+    """``[..., D]`` float -> ``[..., D/2 + 2]`` uint8: symmetric 4-bit codes of every row (scale = amax / 7, two codes
+    per byte, even element in the low nibble) followed by the row's fp16 scale."""
+    xf = x.float()
+    scale = (xf.abs().amax(dim=-1, keepdim=True) / 7.0).clamp_min(1e-8).to(torch.float16)
+    q = torch.clamp(torch.round(xf / scale.float()), -8, 7).to(torch.int16) + 8
+    packed = (q[..., 0::2] | (q[..., 1::2] << 4)).to(torch.uint8)
+    return torch.cat([packed, scale.view(torch.uint8).reshape(*scale.shape[:-1], 2)], dim=-1)
+
+
+def int4_kv_dequantize(p: torch.Tensor, dtype=torch.float16) -> torch.Tensor:
+    codes, scale = p[..., :-2], p[..., -2:].contiguous().view(torch.float16)
+    lo = (codes & 0xF).to(torch.int16) - 8
+    hi = (codes >> 4).to(torch.int16) - 8
+    q = torch.stack([lo, hi], dim=-1).reshape(*codes.shape[:-1], codes.shape[-1] * 2)
+    return (q.to(torch.float32) * scale.float()).to(dtype)
+
+
+class Int4Layer(NormalLayer):
+    """Four bits per element plus one fp16 scale per (token, head): each stored row is ``D/2`` code bytes followed by
+    the scale's two bytes, so the block-grown storage of ``NormalLayer`` serves unchanged.  ``update`` hands the
+    attention the prompt's own K / V on the first call (like the engines, which attend to what they have just
+    computed) and the dequantized cache afterwards; the fused decode kernels do not read this format."""
+
+    storage_dtype = torch.uint8
+    extra_alloc = 2 * KV_CACHE_ALLOC_BLOCK_LENGTH
+
+    def _alloc(self, bsz, heads, cap, dk, dv, dtype, device):
+        if getattr(self, "_pk", None) is None:
+            self._pk, self._pv = dk // 2 + 2, dv // 2 + 2        # first call: widths of the float rows
+        k = torch.empty(bsz, heads, cap, self._pk, dtype=torch.uint8, device=device)
+        v = torch.empty(bsz, heads, cap, self._pv, dtype=torch.uint8, device=device)
+        return k, v
+
+    def _encode(self, x):
+        return int4_kv_quantize(x)
+
+    def update(self, key_states, value_states, *args, **kwargs):
+        fresh = self.length == 0
+        super().update(key_states, value_states, *args, **kwargs)
+        if fresh:
+            return key_states, value_states
+        return self.restore(key_states.dtype)
+
+    def restore(self, dtype=None):
+        dtype = dtype or self.dtype
+        return int4_kv_dequantize(self.keys, dtype), int4_kv_dequantize(self.values, dtype)
+
+
 def compress_kv(query_states, key_states, value_states, attention_mask, num_key_value_groups, window_size=32,
                 max_capacity_prompt=1024, kernel_size=7, pooling="maxpool"):
     """SnapKV prompt compression: keep the ``max_capacity_prompt - window_size`` prompt positions with the highest
@@ -256,6 +305,11 @@ class DynamicNormalCache(_BlockCache):
 
 class DynamicFp8Cache(_BlockCache):
     layer_cls = Fp8Layer
+
+
+class DynamicInt4Cache(_BlockCache):
+    """4-bit KV cache (IPEX_LLM_QUANTIZE_KV_CACHE=int4): 4.25 bits per element at head dim 128."""
+    layer_cls = Int4Layer
 
 
 class DynamicCompressCache(_BlockCache):

@@ -233,6 +233,41 @@ def test_kv_caches():
     assert k_ret.shape[2] == 2000 and s.get_seq_length() == 1024 and s.real_kv_len == 2000
 
 
+def test_int4_kv_cache(tiny_llama_dir, monkeypatch):
+    """IPEX_LLM_QUANTIZE_KV_CACHE=int4: codes + per-row scale round-trip within the 4-bit step, the cache keeps
+    D/2 + 2 bytes per row, and generation through it stays close to the fp16 cache."""
+    from ipex_llm.transformers import AutoModelForCausalLM
+    from ipex_llm_b200.ops.kv_cache import DynamicInt4Cache, int4_kv_dequantize, int4_kv_quantize
+    x = torch.randn(2, 3, 5, 64)
+    p = int4_kv_quantize(x)
+    assert p.dtype == torch.uint8 and p.shape == (2, 3, 5, 34)
+    step = x.abs().amax(-1, keepdim=True) / 7
+    assert ((int4_kv_dequantize(p, torch.float32) - x).abs() <= 0.51 * step + 1e-3).all()
+    c = DynamicInt4Cache()
+    k, v = torch.randn(1, 2, 6, 64), torch.randn(1, 2, 6, 64)
+    kk, vv = c.update(k, v, 0)
+    assert torch.equal(kk, k)                                   # the prompt attends to its own K / V
+    kk, vv = c.update(k[:, :, :1], v[:, :, :1], 0)
+    assert kk.shape == (1, 2, 7, 64) and c.get_seq_length() == 7 and c.layers[0]._k.shape[-1] == 34
+    assert (kk[:, :, :6] - k).abs().max() < 0.51 * float(k.abs().max()) / 7 + 1e-3
+    c.crop(4)
+    assert c.get_seq_length() == 4
+    m = AutoModelForCausalLM.from_pretrained(tiny_llama_dir, load_in_low_bit="sym_int8")
+    ids = torch.randint(0, 1000, (1, 24))
+    ref = m.generate(ids, max_new_tokens=8, do_sample=False)
+    monkeypatch.setenv("IPEX_LLM_QUANTIZE_KV_CACHE", "int4")
+    seen = []
+    orig = DynamicInt4Cache.__init__
+
+    def spy(self, *a, **kw):
+        seen.append(1)
+        orig(self, *a, **kw)
+    monkeypatch.setattr(DynamicInt4Cache, "__init__", spy)
+    out = m.generate(ids, max_new_tokens=8, do_sample=False)
+    assert seen, "generation did not pick the 4-bit cache"
+    assert out.shape == ref.shape and torch.equal(out[:, :26], ref[:, :26])
+
+
 def test_env_flags(monkeypatch):
     from ipex_llm_b200 import config as cfg
     monkeypatch.setenv("IPEX_LLM_QUANTIZE_KV_CACHE", "1")
