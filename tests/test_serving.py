@@ -235,3 +235,43 @@ def test_tgi_api_server_relays_fastchat_worker_stream():
     assert [e["token"]["text"] for e in events] == ["Hel", "lo", "!"]
     assert events[-1]["generated_text"] == "Hello!" and events[-1]["details"]["finish_reason"] == "stop"
     assert client.get("/v1/models").json()["data"][0]["id"] == "tiny"
+
+
+def test_fastchat_vllm_worker_streams_engine_outputs():
+    """``VLLMWorker`` maps FastChat parameters to vLLM sampling arguments and streams the engine's cumulative outputs
+    as NUL-delimited chunks (an async double stands in for the vLLM engine)."""
+    import json as _json
+    from starlette.testclient import TestClient
+    from ipex_llm_b200.serving.fastchat.vllm_worker import VLLMWorker, create_app
+
+    class _Out:
+        def __init__(self, text, ids, finished):
+            self.outputs = [type("O", (), {"text": text, "token_ids": ids, "cumulative_logprob": -1.0,
+                                           "finish_reason": "stop" if finished else None})()]
+            self.prompt_token_ids = [1, 2, 3]
+            self.finished = finished
+
+    class _Engine:
+        def __init__(self):
+            self.calls = []
+
+        async def generate(self, prompt, sampling, request_id):
+            self.calls.append((prompt, sampling, request_id))
+            yield _Out(" a", [5], False)
+            yield _Out(" a b", [5, 6], True)
+
+    eng = _Engine()
+    w = VLLMWorker(None, "http://w", "id0", "/models/tiny", engine=eng)
+    kw = VLLMWorker.sampling_kwargs({"temperature": 0.0, "top_p": 0.3, "max_new_tokens": 9, "stop": "###"})
+    assert kw["temperature"] == 0.0 and kw["top_p"] == 1.0 and kw["max_tokens"] == 9 and kw["stop"] == ["###"]
+    client = TestClient(create_app(w))
+    r = client.post("/worker_generate", json={"prompt": "x", "max_new_tokens": 4, "echo": False})
+    body = r.json()
+    assert body["text"] == " a b" and body["finish_reason"] == "stop"
+    assert body["usage"] == {"prompt_tokens": 3, "completion_tokens": 2, "total_tokens": 5}
+    with client.stream("POST", "/worker_generate_stream", json={"prompt": "x", "echo": True}) as s:
+        raw = b"".join(s.iter_bytes())
+    chunks = [_json.loads(c) for c in raw.split(b"\0") if c]
+    assert [c["text"] for c in chunks] == ["x a", "x a b"] and chunks[0]["finish_reason"] is None
+    assert client.post("/worker_get_status").json()["model_names"] == ["tiny"]
+    assert eng.calls[0][0] == "x"
