@@ -575,13 +575,20 @@ def left_pad_mask_bounds(mask: torch.Tensor, S: int, window: int = 0):
     synchronisation per distinct mask: the result is cached for the layers that follow."""
     if mask.dim() != 4 or mask.shape[1] != 1 or mask.shape[2] != S or mask.shape[3] < S:
         return None
-    key = (mask.data_ptr(), mask._version, tuple(mask.shape), mask.dtype, S, window)
-    if key in _mask_shape_cache:
-        return _mask_shape_cache[key]
+    # cached per live tensor object (a weak reference, not the address: the allocator hands a freed mask's memory to
+    # the next one) and per in-place version
+    import weakref
+    key = (id(mask), mask._version, S, window)
+    hit = _mask_shape_cache.get(key)
+    if hit is not None and hit[0]() is mask:
+        return hit[1]
     vis = mask[:, 0, :, :S]
     vis = vis if vis.dtype == torch.bool else vis > torch.finfo(vis.dtype).min / 2
-    any_col = vis.any(dim=-2)                                   # keys somebody sees
-    lo = torch.where(any_col.any(dim=-1), any_col.int().argmax(dim=-1), torch.full_like(any_col[:, 0].int(), S))
+    # keys that some query sees; rows that see everything are left out (mask builders "unmask" the rows of padding
+    # queries completely), and a batch row without any other kind of row has no padding
+    partial = vis & ~vis.all(dim=-1, keepdim=True)
+    any_col = partial.any(dim=-2)
+    lo = torch.where(any_col.any(dim=-1), any_col.int().argmax(dim=-1), torch.zeros_like(any_col[:, 0].int()))
     qi = torch.arange(S, device=mask.device).view(1, S, 1)
     ki = torch.arange(S, device=mask.device).view(1, 1, S)
     real_q = qi >= lo.view(-1, 1, 1)
@@ -597,7 +604,7 @@ def left_pad_mask_bounds(mask: torch.Tensor, S: int, window: int = 0):
             break
     if len(_mask_shape_cache) > 8:
         _mask_shape_cache.clear()
-    _mask_shape_cache[key] = result
+    _mask_shape_cache[key] = (weakref.ref(mask), result)
     return result
 
 
