@@ -39,15 +39,32 @@ def convert_random_init(model, qtype, optimize_model, device, dtype, seed, std, 
         world, rank = tp_group.world_size, tp_group.rank
     gen = torch.Generator(device=device)
 
+    cfg = model.config
+    n_heads = getattr(cfg, "num_attention_heads", 1)
+    n_kv = getattr(cfg, "num_key_value_heads", None) or n_heads
+    head_dim = getattr(cfg, "head_dim", None) or getattr(cfg, "hidden_size", n_heads) // n_heads
+
     def materialize(module, full_name):
         is_col, is_row = isinstance(module, col_cls), isinstance(module, row_cls)
+        # q / k / v of a sharded model were merged into one matrix before this point: [q_shard; k_shard; v_shard]
+        merged_qkv = world > 1 and full_name.endswith("qkv_proj") and not is_col and not is_row
         for pname, p in list(module._parameters.items()):
             if p is None or p.device.type != "meta" or isinstance(p, FP4Params):
                 continue
-            sharded = (is_col or (is_row and p.dim() >= 2)) and world > 1
+            sharded = (is_col or merged_qkv or (is_row and p.dim() >= 2)) and world > 1
             whole = sharded and consistent_shards
             gen.manual_seed(_seed_for(f"{full_name}.{pname}", shard_seed if sharded and not whole else seed))
-            if whole and p.dim() >= 2:
+            if whole and merged_qkv:
+                # the unsharded model's merged matrix (or bias) holds all q heads, then all k heads, then all v
+                # heads; this rank keeps its contiguous block of each
+                full_shape = (p.shape[0] * world,) + tuple(p.shape[1:])
+                full = torch.empty(full_shape, dtype=dtype, device=device)
+                full = full.normal_(0.0, std, generator=gen) if p.dim() >= 2 else full.zero_()
+                q_l, kv_l = n_heads // world * head_dim, n_kv // world * head_dim
+                q0, k0, v0 = rank * q_l, n_heads * head_dim + rank * kv_l, (n_heads + n_kv) * head_dim + rank * kv_l
+                t = torch.cat([full[q0:q0 + q_l], full[k0:k0 + kv_l], full[v0:v0 + kv_l]], dim=0).contiguous()
+                del full
+            elif whole and p.dim() >= 2:
                 # the matrix an unsharded model holds under this name; this rank keeps its rows (column-parallel)
                 # or columns (row-parallel)
                 n, k = p.shape

@@ -172,6 +172,29 @@ def main():
     dist.all_gather(toks, out)
     for t in toks:
         assert torch.equal(t, toks[0]), "ranks generated different tokens"
+    # 3b. random-init models: with consistent_tp_shards the sharded model IS the whole model of the same seed
+    # (every sharded matrix drawn whole, this rank keeps its rows / columns), and replicated parameters
+    # (embeddings, norms) are the same on every rank with or without the switch
+    from transformers import LlamaConfig
+    cfg = LlamaConfig(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=512, max_position_embeddings=128, tie_word_embeddings=False)
+    ids_small = torch.randint(0, 512, (2, 16))
+    whole = AutoModelForCausalLM.from_config(cfg, load_in_low_bit="sym_int8", device=str(dev), torch_dtype=dtype,
+                                             seed=3)
+    parts = AutoModelForCausalLM.from_config(cfg, load_in_low_bit="sym_int8", device=str(dev), torch_dtype=dtype,
+                                             seed=3, tp_group=tp, consistent_tp_shards=True)
+    with torch.no_grad():
+        lw = whole(ids_small.to(dev)).logits[:, -1].float()
+        lp = parts(ids_small.to(dev)).logits[:, -1].float()
+    cos = torch.nn.functional.cosine_similarity(lw, lp, dim=-1).min().item()
+    assert cos > 0.999, f"consistent shards do not reproduce the whole model: {cos}"
+    loose = AutoModelForCausalLM.from_config(cfg, load_in_low_bit="sym_int8", device=str(dev), torch_dtype=dtype,
+                                             seed=3, tp_group=tp)
+    emb = loose.model.embed_tokens.weight.data.float()
+    embs = [torch.empty_like(emb) for _ in range(world)]
+    dist.all_gather(embs, emb)
+    for e in embs:
+        assert torch.equal(e, embs[0]), "replicated parameters differ between ranks"
     if cuda:
         assert getattr(shard, "_ipex_engine", None) is not None
         from ipex_llm_b200.ops import cuda_ops
