@@ -84,17 +84,16 @@ def test_left_padding_masks_are_recognised():
     qi, ki = torch.arange(S).view(1, S, 1), torch.arange(S).view(1, 1, S)
     lo = torch.tensor([0, 7, 25])
     for causal, window in ((True, 0), (True, 9), (False, 0)):
-        if True:
-            ok = (ki >= lo.view(-1, 1, 1)).expand(3, S, S)
-            if causal:
-                ok = ok & (ki <= qi)
-            if window:
-                ok = ok & (ki > qi - window)
-            ok = ok.clone()
-            ok[1, :7] = True                       # rows of padding queries may hold anything
-            for mask in (ok.unsqueeze(1), torch.zeros(3, 1, S, S).masked_fill(~ok.unsqueeze(1), float("-inf"))):
-                found = left_pad_mask_bounds(mask, S, window)
-                assert found is not None and found[0].tolist() == lo.tolist() and found[1] == causal
+        ok = (ki >= lo.view(-1, 1, 1)).expand(3, S, S)
+        if causal:
+            ok = ok & (ki <= qi)
+        if window:
+            ok = ok & (ki > qi - window)
+        ok = ok.clone()
+        ok[1, :7] = True                           # rows of padding queries may hold anything
+        for mask in (ok.unsqueeze(1), torch.zeros(3, 1, S, S).masked_fill(~ok.unsqueeze(1), float("-inf"))):
+            found = left_pad_mask_bounds(mask, S, window)
+            assert found is not None and found[0].tolist() == lo.tolist() and found[1] == causal
     holed = (ki <= qi).expand(1, S, S).clone()
     holed[0, 30, 10] = False
     assert left_pad_mask_bounds(holed.unsqueeze(1), S) is None
