@@ -158,6 +158,12 @@ QInfo qinfo(int qtype) {
     case QT_Q4_K: return {256, 144};
     case QT_Q5_K: return {256, 176};
     case QT_Q6_K: return {256, 210};
+    // code-book super-blocks: geometry only; their codecs live in quant/iq_codebooks.py (the grids come from
+    // the gguf package at run time), so ipex_qtype_supported() stays 0 for them
+    case QT_IQ2_XXS: return {256, 66};
+    case QT_IQ2_XS: return {256, 74};
+    case QT_IQ1_S: return {256, 50};
+    case QT_IQ1_M: return {256, 56};
     // per-output-channel round-to-nearest containers: one code byte (or nibble pair) per weight
     case QT_SYM_INT8_RTN: return {1, 1};
     case QT_SYM_INT4_RTN: return {2, 1};

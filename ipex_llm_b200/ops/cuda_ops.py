@@ -251,8 +251,12 @@ def lowbit_linear_backward(grad_output: torch.Tensor, weight: FP4Params) -> torc
 
 def dequantize_device(w_data: torch.Tensor, shape, qtype: int, dtype=torch.float16) -> torch.Tensor:
     """Full dense weight from device-resident packed bytes."""
-    lib = cuda_lib()
     N, K = int(shape[0]), int(shape[1])
+    if qtype in qt.IQ_QTYPES:
+        # code-book formats: the look-up is tensor code (quant/iq_codebooks.py), the product then runs dense
+        from ..quant import iq_codebooks
+        return iq_codebooks.dequantize(w_data, (N, K), qtype, dtype)
+    lib = cuda_lib()
     out = torch.empty((N, K), dtype=dtype, device=w_data.device)
     if is_tiled(qtype):
         rc = lib.ipex_dequantize_tiles(ptr(w_data), ptr(out), N, K, K, QTYPE_TO_WF[qtype],

@@ -99,6 +99,28 @@ class LowBitEmbedding(nn.Embedding):
         self.weight = FP4Params(self.weight.data, requires_grad=False, quantized=False, _shape=None,
                                 convert_shape_only=bool(convert_shape_only), qtype=qtype, in_features=embedding_dim)
 
+    def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys,
+                              error_msgs):
+        """A packed table from a low-bit checkpoint is installed as ``FP4Params`` (``assign=True`` would otherwise
+        leave a plain parameter behind, without qtype and shape)."""
+        key = prefix + "weight"
+        if key in state_dict and isinstance(self.weight, FP4Params) and state_dict[key].dtype == torch.uint8:
+            data = state_dict[key]
+            w = self.weight
+            want = self.num_embeddings * self.embedding_dim // get_block_size(w.qtype) * get_type_size(w.qtype)
+            if data.numel() != want:
+                error_msgs.append(f"size mismatch for {key}: a packed [{self.num_embeddings}, {self.embedding_dim}] "
+                                  f"table needs {want} bytes, the checkpoint holds {data.numel()}")
+                return
+            new = FP4Params(data.detach(), requires_grad=False, quantized=True,
+                            _shape=torch.Size((self.num_embeddings, self.embedding_dim)), qtype=w.qtype,
+                            in_features=self.embedding_dim)
+            new.keep_canonical = True                          # tables are read row-wise on every device
+            self._parameters["weight"] = new
+            return
+        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys,
+                                      error_msgs)
+
     def _row_view(self):
         w = self.weight
         row_bytes = self.embedding_dim // get_block_size(w.qtype) * get_type_size(w.qtype)

@@ -23,6 +23,7 @@ import ctypes
 import torch
 
 from ..native import lib as _nl
+from . import iq_codebooks as iq
 from . import qtypes as qt
 
 RTN_DTYPE = {qt.SYM_INT4_RTN: torch.uint8, qt.ASYM_INT4_RTN: torch.uint8, qt.SYM_INT8_RTN: torch.int8}
@@ -50,10 +51,9 @@ def device_nbytes(rows: int, cols: int, qtype: int) -> int:
 
 
 def _check_supported(qtype: int):
-    if qtype in qt.UNSUPPORTED_QTYPES:
-        raise NotImplementedError(
-            f"qtype {qt.qtype_name(qtype)} needs the llama.cpp iq code-book grids, which this build does not ship; "
-            "use q2_k / sym_int4 / nf4 instead")
+    if iq.is_iq(qtype):
+        iq.grid(qtype, "cpu")          # raises NotImplementedError when the grids cannot be had
+        return
     if not _nl.host_lib().ipex_qtype_supported(qtype) and qtype not in RTN_DTYPE:
         raise NotImplementedError(f"qtype id {qtype} has no block codec")
 
@@ -83,6 +83,11 @@ def ggml_convert_qtype(tensor: torch.Tensor, qtype: int, device=None, convert_sh
     if k % QK != 0:
         raise ValueError(f"Last dim of input tensor must be multiple of {QK}")
     dst_size = (n // QK) * ts
+    if iq.is_iq(qtype):
+        if convert_shape_only or device == "meta":
+            return torch.empty(dst_size, dtype=torch.uint8, device=device)
+        src = tensor.view(-1, in_features) if in_features and in_features != k else tensor
+        return iq.quantize(src, qtype, imatrix)
     if qtype == qt.NF4:
         dst = torch.empty(dst_size // 2, dtype=torch.bfloat16, device=device)
     else:
@@ -104,6 +109,8 @@ def ggml_convert_qtype(tensor: torch.Tensor, qtype: int, device=None, convert_sh
 def ggml_convert_fp32(tensor: torch.Tensor, weight_shape, k: int, qtype: int) -> torch.Tensor:
     """canonical packed CPU tensor -> fp32 tensor of ``weight_shape``."""
     lib = _nl.host_lib()
+    if iq.is_iq(qtype):
+        return iq.dequantize(tensor, tuple(weight_shape), qtype, torch.float32)
     src = tensor.contiguous()
     dst = torch.empty(tuple(weight_shape), dtype=torch.float32)
     lib.ggml_dequantize(src.data_ptr(), dst.data_ptr(), k, qtype)
@@ -159,6 +166,9 @@ def ggml_matmul_src1_x_src0_t(src0: torch.Tensor, src1: torch.Tensor, src0_shape
         raise RuntimeError(f"packed weight holds {have} bytes on {w.device}, a [{N}, {K}] "
                            f"{qt.qtype_name(src0_qtype)} matrix needs {need} on cpu: the checkpoint does not match "
                            "the module layout (was it saved with another `optimize_model` setting?)")
+    if iq.is_iq(src0_qtype):
+        torch.matmul(src1.view(M, K), iq.dequantize(w, (N, K), src0_qtype).t(), out=out)
+        return out.view(*lead, N)
     lib.ggml_compute_forward_mul_mat_q_fp32(ne0, w.data_ptr(), src0_qtype, ne1, src1.data_ptr(), out.data_ptr())
     return out.view(*lead, N)
 
@@ -242,6 +252,13 @@ class FP4Params(torch.nn.Parameter):
         self.qtype = qtype
         self._shape = w.shape
         meta = device is not None and str(device) == "meta"
+        if not meta and w.is_cuda and iq.is_iq(qtype):
+            # the code-book search is tensor code: it runs where the weight is, and block order is also what the
+            # device keeps for these formats
+            src = w.view(-1, self.in_features) if self.in_features and self.in_features != w.shape[-1] else w
+            self.data = iq.quantize(src, qtype, self.imatrix)
+            self.quantized = True
+            return self
         if not meta and w.is_cuda:
             from ..ops import cuda_quant
             if cuda_quant.can_quantize_on_gpu(qtype) and self.imatrix is None:
@@ -286,8 +303,8 @@ class FP4Params(torch.nn.Parameter):
             if not self.quantized:
                 if not self.data.is_cuda:
                     from ..ops import cuda_quant
-                    if cuda_quant.can_quantize_on_gpu(self.qtype) and self.imatrix is None \
-                            and self.qtype not in (qt.MOFQ4, qt.MOFQ8):
+                    if iq.is_iq(self.qtype) or (cuda_quant.can_quantize_on_gpu(self.qtype) and self.imatrix is None
+                                                and self.qtype not in (qt.MOFQ4, qt.MOFQ8)):
                         self.data = self.data.to(device, non_blocking=non_blocking)
                 self.quantize(device)
             if self.layout == "canonical":

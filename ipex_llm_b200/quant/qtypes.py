@@ -77,8 +77,9 @@ WOQ_INT4 = ggml_tensor_qtype["woq_int4"]
 # qtypes whose block codec is implemented by the host library and the CUDA kernels
 BLOCK_QTYPES = (SYM_INT4, ASYM_INT4, SYM_INT5, ASYM_INT5, SYM_INT8, NF4, NF3, FP4, FP6, FP6_K,
                 FP8E4, FP8E5, Q2_K, Q4_K, Q5_K, Q6_K, WOQ_INT4)
-# code-book formats that need tables this build does not ship (llama.cpp iq grids)
-UNSUPPORTED_QTYPES = (IQ2_XXS, IQ2_XS, IQ1_S, IQ1_M)
+# code-book super-blocks: codecs in quant/iq_codebooks.py, grids from the `gguf` package at run time
+IQ_QTYPES = (IQ2_XXS, IQ2_XS, IQ1_S, IQ1_M)
+UNSUPPORTED_QTYPES = ()
 # qtypes whose device layout is the tensor-core tile layout (fast GEMV / GEMM kernels)
 TILED_4BIT = (SYM_INT4, ASYM_INT4, NF4, FP4)
 TILED_8BIT = (FP8E4, FP8E5, SYM_INT8)

@@ -4,7 +4,8 @@ Counterpart of python/llm/src/ipex_llm/transformers/gguf/gguf.py:1-424 (``GGUFFi
 ``tensor_loader``, ``tokenizer_pieces``).  The file is memory-mapped; tensors are decoded to float one at a time, so
 peak host memory is one tensor.  Block decoders for the classic ggml formats (q4_0, q4_1, q5_0, q5_1, q8_0, 32 values
 per block as in llama.cpp files) are written here with numpy; the k-quant super-blocks go through the package's host
-library, whose q2_k..q6_k block layouts are the ggml ones.
+library, whose q2_k..q6_k block layouts are the ggml ones, and the code-book super-blocks (iq2_xxs, iq2_xs, iq1_s,
+iq1_m) through ``quant/iq_codebooks.py``.
 """
 from __future__ import annotations
 
@@ -26,6 +27,7 @@ GGML_TYPES = {
     0: ("f32", 1, 4), 1: ("f16", 1, 2), 2: ("q4_0", 32, 18), 3: ("q4_1", 32, 20), 6: ("q5_0", 32, 22),
     7: ("q5_1", 32, 24), 8: ("q8_0", 32, 34), 10: ("q2_k", 256, 84), 11: ("q3_k", 256, 110), 12: ("q4_k", 256, 144),
     13: ("q5_k", 256, 176), 14: ("q6_k", 256, 210), 30: ("bf16", 1, 2),
+    16: ("iq2_xxs", 256, 66), 17: ("iq2_xs", 256, 74), 19: ("iq1_s", 256, 50), 29: ("iq1_m", 256, 56),
 }
 _NAME_TO_TYPE = {v[0]: k for k, v in GGML_TYPES.items()}
 
@@ -105,10 +107,12 @@ def dequantize_blocks(raw: np.ndarray, ttype: int, n_values: int) -> np.ndarray:
             return ((q - 16.0) * d).reshape(-1)
         m = _f16(blk[:, 2:4].copy()).reshape(nb, 1)
         return (q * d + m).reshape(-1)
-    # k-quants: the host library's decoders use the ggml super-block layouts
+    # k-quants: the host library's decoders use the ggml super-block layouts; the code-book formats go through
+    # quant/iq_codebooks.py, whose byte layout is the GGUF one
     from ...quant import qtypes as qt
     from ...quant.params import ggml_convert_fp32
-    kq = {"q2_k": "q2_k", "q4_k": "q4_k", "q5_k": "q5_k", "q6_k": "q6_k"}.get(name)
+    kq = {"q2_k": "q2_k", "q4_k": "q4_k", "q5_k": "q5_k", "q6_k": "q6_k", "iq2_xxs": "gguf_iq2_xxs",
+          "iq2_xs": "gguf_iq2_xs", "iq1_s": "gguf_iq1_s", "iq1_m": "gguf_iq1_m"}.get(name)
     invalidInputError(kq is not None, f"GGUF tensor type {name} is not supported")
     t = torch.from_numpy(raw.copy())
     return ggml_convert_fp32(t, (1, n_values), n_values, qt.qtype_from_name(kq)).reshape(-1).numpy()
@@ -228,6 +232,12 @@ def quantize_blocks(x: np.ndarray, name: str) -> bytes:
         return x.tobytes()
     if name == "f16":
         return x.astype(np.float16).tobytes()
+    if name in ("iq2_xxs", "iq2_xs", "iq1_s", "iq1_m", "q2_k", "q4_k", "q5_k", "q6_k"):
+        from ...quant import qtypes as qt
+        from ...quant.params import ggml_convert_qtype
+        qname = name if name.endswith("_k") else "gguf_" + name
+        packed = ggml_convert_qtype(torch.from_numpy(x.copy()).view(1, -1), qt.qtype_from_name(qname))
+        return packed.view(torch.uint8).numpy().tobytes()
     b = x.reshape(-1, 32)
     if name == "q8_0":
         d = np.abs(b).max(axis=1, keepdims=True) / 127.0

@@ -309,3 +309,52 @@ def test_load_low_bit_rejects_absent_or_truncated_tensor(int4_model, tmp_path, w
         os.remove(os.path.join(d, "load_keys.json"))
     with pytest.raises(RuntimeError):
         AutoModelForCausalLM.load_low_bit(d)
+
+
+def _write_imatrix(path, n_layers, hidden, inter):
+    """A llama.cpp importance-matrix file with one record per projection."""
+    import struct
+    recs = []
+    for l in range(n_layers):
+        for name, n in (("attn_q", hidden), ("attn_k", hidden), ("attn_v", hidden), ("attn_qkv", hidden),
+                        ("attn_output", hidden), ("ffn_gate", hidden), ("ffn_up", hidden), ("ffn_down", inter)):
+            recs.append((f"blk.{l}.{name}.weight", torch.rand(n) + 0.1))
+    with open(path, "wb") as f:
+        f.write(struct.pack("<i", len(recs)))
+        for name, vals in recs:
+            b = name.encode()
+            f.write(struct.pack("<i", len(b)) + b + struct.pack("<ii", 2, vals.numel()))
+            f.write((vals * 2).numpy().astype("float32").tobytes())
+
+
+@pytest.mark.parametrize("low_bit", ["gguf_iq2_xxs", "gguf_iq1_s"])
+def test_codebook_low_bit_model(tiny_llama_dir, tmp_path, low_bit):
+    """load_in_low_bit="gguf_iq2_xxs" / "gguf_iq1_s" with an importance matrix (reference model.py:325-341,
+    utils.py:286-356): per-layer types follow the policy, the model runs, and the packed model reloads bit-exactly."""
+    pytest.importorskip("gguf.quants")
+    from ipex_llm.transformers import AutoModelForCausalLM
+    from ipex_llm_b200.quant import qtypes as qt
+    with pytest.raises(Exception):
+        AutoModelForCausalLM.from_pretrained(tiny_llama_dir, load_in_low_bit=low_bit)        # imatrix is required
+    im = str(tmp_path / "imatrix.dat")
+    _write_imatrix(im, 2, 256, 688)
+    m = AutoModelForCausalLM.from_pretrained(tiny_llama_dir, load_in_low_bit=low_bit, imatrix=im)
+    attn = m.model.layers[0].self_attn
+    want = qt.qtype_from_name(low_bit)
+    assert attn.qkv_proj.weight.qtype == want
+    assert m.model.layers[0].mlp.gate_proj.weight.qtype == want
+    assert attn.o_proj.weight.qtype == (qt.IQ2_XXS if low_bit == "gguf_iq1_s" else want)
+    assert m.lm_head.weight.qtype == qt.SYM_INT8
+    ids = torch.randint(0, 32000, (1, 12))
+    with torch.no_grad():
+        logits = m(ids).logits
+    assert torch.isfinite(logits).all()
+    out = m.generate(ids, max_new_tokens=4, do_sample=False)
+    assert out.shape == (1, 16)
+    d = str(tmp_path / "packed")
+    m.save_low_bit(d)
+    again = AutoModelForCausalLM.load_low_bit(d)
+    from ipex_llm_b200.quant.params import FP4Params
+    assert isinstance(again.model.embed_tokens.weight, FP4Params) and again.model.embed_tokens.weight.qtype == qt.Q2_K
+    with torch.no_grad():
+        assert torch.equal(again(ids).logits, logits)

@@ -1,6 +1,7 @@
 """GGUF import: write a tiny llama-shaped file (f32 / f16 / q8_0 / q4_0 tensors), read it back, compare with the
 source model."""
 import numpy as np
+import pytest
 import torch
 
 
@@ -46,6 +47,23 @@ def test_block_codecs_roundtrip():
         raw = np.frombuffer(quantize_blocks(x, name), dtype=np.uint8)
         y = dequantize_blocks(raw, _NAME_TO_TYPE[name], x.size)
         assert np.abs(x - y).max() <= tol * max(1.0, np.abs(x).max()) + 1e-12, name
+
+
+def test_superblock_tensor_types_read_back(tmp_path):
+    """k-quant and code-book tensors in a GGUF file decode through the reader (type ids 10-14, 16, 17, 19, 29)."""
+    pytest.importorskip("gguf.quants")
+    from ipex_llm_b200.transformers.gguf.gguf import GGUFFileLoader, write_gguf
+    torch.manual_seed(0)
+    w = torch.randn(8, 512)
+    kinds = {"q4_k": 0.12, "q6_k": 0.03, "iq2_xxs": 0.4, "iq2_xs": 0.35, "iq1_s": 0.5, "iq1_m": 0.5}
+    path = str(tmp_path / "t.gguf")
+    write_gguf(path, {"general.architecture": "llama"}, {f"w.{k}": (w, k) for k in kinds})
+    loader = GGUFFileLoader(path)
+    got = dict(loader.tensors())
+    for k, tol in kinds.items():
+        y = got[f"w.{k}"]
+        assert y.shape == w.shape and ((y - w).norm() / w.norm()).item() < tol, k
+    loader.close()
 
 
 def test_load_gguf_llama(tmp_path):

@@ -159,6 +159,63 @@ def test_rtn_formats():
     assert codes4.shape == (8, 32) and scale4.shape == (16,)
 
 
-def test_unsupported_codebook_qtypes_raise():
-    with pytest.raises(NotImplementedError):
-        ggml_convert_qtype(torch.randn(4, 256), qt.IQ2_XXS)
+IQ_CASES = [("gguf_iq2_xxs", 66, 0.36), ("gguf_iq2_xs", 74, 0.32), ("gguf_iq1_s", 50, 0.48), ("gguf_iq1_m", 56, 0.45)]
+
+
+@pytest.mark.parametrize("name,type_size,max_rel", IQ_CASES)
+def test_codebook_formats_round_trip_and_read_like_gguf(name, type_size, max_rel):
+    """The four code-book formats: bytes per super-block, error of our quantizer on Gaussian weights, and the packed
+    bytes decode to the same values through the `gguf` package's own reader (format compatibility)."""
+    gq = pytest.importorskip("gguf.quants")
+    from gguf.constants import GGMLQuantizationType as T
+    from ipex_llm_b200.quant import iq_codebooks as iq
+    from ipex_llm_b200.quant.params import get_block_size, get_type_size
+    q = qt.qtype_from_name(name)
+    assert get_block_size(q) == 256 and get_type_size(q) == type_size == iq.TYPE_SIZE[q]
+    torch.manual_seed(3)
+    w = torch.randn(24, 512)
+    w[5] = 0                                                    # an all-zero row must survive
+    packed = ggml_convert_qtype(w, q)
+    assert packed.dtype == torch.uint8 and packed.numel() == 24 * 2 * type_size
+    back = ggml_convert_fp32(packed, w.shape, w.numel(), q)
+    assert torch.isfinite(back).all() and back[5].abs().max() == 0
+    assert ((back - w).norm() / w.norm()).item() < max_rel
+    theirs = gq.dequantize(packed.numpy().reshape(24, -1), getattr(T, name[5:].upper()))
+    assert torch.equal(back, torch.from_numpy(theirs))
+
+
+def test_codebook_importance_weights_lower_the_weighted_error():
+    pytest.importorskip("gguf.quants")
+    torch.manual_seed(4)
+    w = torch.randn(16, 512)
+    im = torch.rand(512) ** 4 + 1e-3                            # a few columns matter much more than the rest
+    for name in ("gguf_iq2_xxs", "gguf_iq1_s"):
+        q = qt.qtype_from_name(name)
+        plain = ggml_convert_fp32(ggml_convert_qtype(w, q), w.shape, w.numel(), q)
+        weighted = ggml_convert_fp32(ggml_convert_qtype(w, q, imatrix=im, in_features=512), w.shape, w.numel(), q)
+
+        def werr(x):
+            return float((im * (x - w) ** 2).sum())
+        assert werr(weighted) < werr(plain)
+
+
+def test_codebook_linear_on_cpu():
+    """LowBitLinear over a code-book weight: same numbers as the dense product with the dequantized weight, and the
+    packed bytes survive a state-dict round trip."""
+    pytest.importorskip("gguf.quants")
+    from ipex_llm_b200.ops.linear import LowBitLinear
+    from ipex_llm_b200.quant.params import FP4Params
+    torch.manual_seed(5)
+    lin = torch.nn.Linear(256, 48, bias=True)
+    q = qt.qtype_from_name("gguf_iq2_xs")
+    low = LowBitLinear(256, 48, q, bias=True)
+    low._parameters["weight"] = FP4Params(lin.weight.data.clone(), qtype=q, in_features=256).to("cpu")
+    low._parameters["bias"] = lin.bias
+    x = torch.randn(3, 256)
+    want = torch.nn.functional.linear(x, low.weight.dequantize(), lin.bias)
+    assert torch.allclose(low(x), want, atol=1e-4)
+    many = torch.randn(600, 256)                                # the dequantize-then-dense branch
+    assert torch.allclose(low(many), torch.nn.functional.linear(many, low.weight.dequantize(), lin.bias), atol=1e-3)
+    assert torch.nn.functional.cosine_similarity(low(x).flatten(), lin(x).flatten(), dim=0) > 0.93
+    sd = low.state_dict()
+    assert sd["weight"].dtype == torch.uint8 and sd["weight"].numel() == 48 * 74
