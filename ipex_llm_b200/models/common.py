@@ -299,17 +299,27 @@ def register_attention_interface() -> bool:
         return False
 
 
+def _uses_attention_registry(mod) -> bool:
+    """Does the modeling file of this module dispatch its attention through the interface registry?  Files that do
+    import ``ALL_ATTENTION_FUNCTIONS``; the others (GPT-J, CodeGen, ...) run their own eager attention and only
+    read ``_attn_implementation`` to build the mask, which must then stay in the additive form they expect."""
+    import sys
+    pymod = sys.modules.get(type(mod).__module__)
+    return pymod is not None and hasattr(pymod, "ALL_ATTENTION_FUNCTIONS")
+
+
 def use_attention_interface(model) -> bool:
-    """Point the model (and its sub-configs) at the registered interface.  Models whose attention classes do not go
-    through the registry simply ignore the setting."""
+    """Point every sub-model whose attention goes through the registry at the registered interface; the rest keep
+    their own attention path and mask format."""
     if not register_attention_interface():
         return False
     done = False
     seen = set()
-    stack = [getattr(model, "config", None)]
-    while stack:
-        cfg = stack.pop()
-        if cfg is None or id(cfg) in seen:
+    for mod in model.modules():
+        cfg = getattr(mod, "config", None)
+        if cfg is None or id(cfg) in seen or not hasattr(cfg, "to_dict"):
+            continue
+        if not _uses_attention_registry(mod):
             continue
         seen.add(id(cfg))
         try:
@@ -317,16 +327,4 @@ def use_attention_interface(model) -> bool:
             done = True
         except Exception:  # noqa: BLE001
             pass
-        for name in ("text_config", "vision_config", "audio_config", "decoder", "encoder", "llm_config"):
-            sub = getattr(cfg, name, None)
-            if sub is not None and hasattr(sub, "to_dict"):
-                stack.append(sub)
-    for mod in model.modules():
-        cfg = getattr(mod, "config", None)
-        if cfg is not None and id(cfg) not in seen and hasattr(cfg, "to_dict"):
-            seen.add(id(cfg))
-            try:
-                cfg._attn_implementation = ATTN_INTERFACE_NAME
-            except Exception:  # noqa: BLE001
-                pass
     return done

@@ -112,6 +112,14 @@ def is_linear_module(module):
     return result, (in_features, out_features, mp_group)
 
 
+def _is_moe_router(parent, name, module) -> bool:
+    """The expert-selection projection of a sparse-MoE block: a Linear called ``gate`` / ``router`` beside an
+    ``experts`` container, or any Linear subclass named ``*Router``."""
+    if type(module).__name__.endswith("Router"):
+        return True
+    return name in ("gate", "router") and hasattr(parent, "experts") and isinstance(module, nn.Linear)
+
+
 def _linear_weight(module) -> torch.Tensor:
     """The ``[out, in]`` weight of a module ``is_linear_module`` accepted (Conv1D stores the transpose)."""
     w = module.weight.data
@@ -196,6 +204,10 @@ def _replace_with_low_bit_linear(model, qtype, modules_to_not_convert=None, conv
         skip = modules_to_not_convert is not None and any(k in full_name for k in modules_to_not_convert)
         if skip and not isinstance(module, nn.Embedding):
             # substring match on the dotted name (reference convert.py:489-491)
+            continue
+        if is_linear and _is_moe_router(model, name, module):
+            # routers stay in full precision: their modeling code multiplies by ``.weight`` directly or carries the
+            # top-k selection in a Linear subclass (the reference keeps them out per family, convert.py:1100-1135)
             continue
         if is_fused_experts(module) and qtype not in qt.FLOAT_QTYPES:
             new_mod = convert_fused_experts(module, qtype, device=device, convert_shape_only=convert_shape_only,

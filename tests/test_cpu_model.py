@@ -159,6 +159,11 @@ def test_modules_to_not_convert_and_mixed_precision(tiny_llama_dir):
     assert isinstance(m.lm_head, LowBitLinear) and m.lm_head.weight.qtype == qt.Q6_K
 
 
+# multi-head latent attention + routed / shared experts of the DeepSeek families, at toy size
+_MLA = dict(kv_lora_rank=32, q_lora_rank=48, qk_nope_head_dim=16, qk_rope_head_dim=16, v_head_dim=32,
+            n_routed_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, n_shared_experts=1,
+            first_k_dense_replace=1, num_key_value_heads=4)
+
 FAMILY_CONFIGS = {
     "mistral": ("MistralConfig", dict(sliding_window=None)),
     "qwen2": ("Qwen2Config", dict()),
@@ -177,6 +182,10 @@ FAMILY_CONFIGS = {
     "mixtral": ("MixtralConfig", dict(num_local_experts=4, num_experts_per_tok=2)),
     "qwen2_moe": ("Qwen2MoeConfig", dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=128,
                                         shared_expert_intermediate_size=128)),
+    "deepseek_v2": ("DeepseekV2Config", dict(_MLA, n_group=1, topk_group=1)),
+    "deepseek_v3": ("DeepseekV3Config", dict(_MLA, n_group=2, topk_group=1)),
+    "phimoe": ("PhimoeConfig", dict(num_local_experts=4, num_experts_per_tok=2)),
+    "gptj": ("GPTJConfig", dict(n_embd=128, n_layer=2, n_head=4, rotary_dim=16)),
 }
 
 
@@ -187,9 +196,10 @@ def test_family_forward_replacement(family):
     import transformers
     from ipex_llm import optimize_model
     cls_name, extra = FAMILY_CONFIGS[family]
-    cfg = getattr(transformers, cls_name)(hidden_size=128, intermediate_size=256, num_hidden_layers=2,
-                                          num_attention_heads=4, num_key_value_heads=2, vocab_size=1000,
-                                          max_position_embeddings=256, **extra)
+    kw = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, vocab_size=1000, max_position_embeddings=256)
+    kw.update(extra)
+    cfg = getattr(transformers, cls_name)(**kw)
     torch.manual_seed(0)
     base = transformers.AutoModelForCausalLM.from_config(cfg).eval()
     a = optimize_model(copy.deepcopy(base), low_bit="sym_int8", optimize_llm=True)
