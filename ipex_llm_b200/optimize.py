@@ -131,7 +131,18 @@ def optimize_model(model, low_bit="sym_int4", optimize_llm=True, modules_to_not_
     invalidInputError(low_bit is None or low_bit in qt.ggml_tensor_qtype,
                       f"Unknown load_in_low_bit value: {low_bit}, expected:"
                       f" sym_int4, asym_int4, sym_int5, asym_int5 or sym_int8.")
-    invalidInputError(isinstance(model, torch.nn.Module) or "StableDiffusion" in model.__class__.__name__,
+    from .models.sd import is_diffusion_pipeline, optimize_pipeline
+    if is_diffusion_pipeline(model):
+        # a diffusers pipeline (reference convert.py:1253-1265): UNet attention on the package's SDPA; with a low_bit
+        # the UNet's linears are packed as well
+        if optimize_llm:
+            optimize_pipeline(model)
+        if low_bit is not None:
+            model.unet = ggml_convert_low_bit(model.unet, qtype=qt.qtype_from_name(low_bit), optimize_model=False,
+                                              modules_to_not_convert=modules_to_not_convert,
+                                              device=kwargs.pop("device", None) or "cpu")
+        return model
+    invalidInputError(isinstance(model, torch.nn.Module),
                       f"model should be an instance of `torch.nn.Module`, but got {type(model)} at last.")
     if hasattr(model, "device") and isinstance(getattr(model, "device"), torch.device):
         invalidInputError(model.device.type in ("cpu", "meta", "cuda"),
