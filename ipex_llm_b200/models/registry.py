@@ -11,6 +11,7 @@ from typing import Callable, List, Optional, Tuple
 
 from . import common as C
 from . import decoder as D
+from . import phi3 as P3
 from . import rwkv as R
 
 
@@ -38,7 +39,7 @@ def _split_fused_gate_up(mlp_cls):
 
 
 def _llama_like(prefix, mlp_forward=C.mlp_silu_forward, norm_forward=C.rms_norm_forward, spec=None, engine=None,
-                extra_post=(), merge=True):
+                extra_post=(), merge=True, post_hook=None):
     attrs = []
     if spec is not None:
         attrs.append((f"{prefix}Attention", "_ipex_attn", spec))
@@ -49,6 +50,7 @@ def _llama_like(prefix, mlp_forward=C.mlp_silu_forward, norm_forward=C.rms_norm_
               *extra_post],
         attrs=attrs,
         engine=engine,
+        post_hook=post_hook,
     )
 
 
@@ -92,7 +94,7 @@ FAMILIES = {
     "gemma": _llama_like("Gemma", mlp_forward=C.mlp_gelu_forward, norm_forward=C.gemma_rms_norm_forward),
     "gemma2": _llama_like("Gemma2", mlp_forward=C.mlp_gelu_forward, norm_forward=C.gemma_rms_norm_forward,
                           spec=D.AttnSpec(softcap_attr="attn_logit_softcapping", sliding=True)),
-    "phi3": _llama_like("Phi3", merge=False),
+    "phi3": _llama_like("Phi3", merge=False, post_hook=P3.install),
     # GLM: GPT-J style ("two") rotary on half of the head dims, fused gate_up_proj (reference models/glm.py,
     # chatglm2.py:225-262 for the rotary pairing)
     "glm": _llama_like("Glm", spec=D.AttnSpec(interleaved_rope=True)),

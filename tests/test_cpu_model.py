@@ -368,3 +368,33 @@ def test_codebook_low_bit_model(tiny_llama_dir, tmp_path, low_bit):
     assert isinstance(again.model.embed_tokens.weight, FP4Params) and again.model.embed_tokens.weight.qtype == qt.Q2_K
     with torch.no_grad():
         assert torch.equal(again(ids).logits, logits)
+
+
+def test_phi3_longrope_generation_switches_factor_sets():
+    """Phi-3 LongRoPE (reference models/phi3.py:62-86): forward agrees with the fp32 model below and above
+    ``original_max_position_embeddings``, and greedy generation that crosses the switch point equals greedy decoding by
+    full recomputation (the cache is rebuilt once with the long factors)."""
+    import copy
+    import transformers
+    from ipex_llm import optimize_model
+    hd = 32
+    rope = {"rope_type": "longrope", "rope_theta": 10000.0, "original_max_position_embeddings": 32,
+            "short_factor": [1.0 + 0.05 * i for i in range(hd // 2)],
+            "long_factor": [2.0 + 0.3 * i for i in range(hd // 2)]}
+    cfg = transformers.Phi3Config(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                                  num_key_value_heads=2, vocab_size=1000, max_position_embeddings=256,
+                                  original_max_position_embeddings=32, pad_token_id=0, rope_parameters=rope)
+    torch.manual_seed(0)
+    base = transformers.AutoModelForCausalLM.from_config(cfg).eval()
+    low = optimize_model(copy.deepcopy(base), low_bit="sym_int8")
+    for n in (20, 80):
+        ids = torch.randint(0, 1000, (2, n))
+        with torch.no_grad():
+            assert _cos(low(ids).logits[:, -1], base(ids).logits[:, -1]) > 0.999, n
+    ids = torch.randint(0, 1000, (1, 28))
+    out = low.generate(ids, max_new_tokens=10, do_sample=False)
+    cur = ids
+    with torch.no_grad():
+        for _ in range(10):
+            cur = torch.cat([cur, low(cur).logits[:, -1].argmax(-1, keepdim=True)], 1)
+    assert torch.equal(out, cur)
