@@ -31,7 +31,7 @@ def test_names_behind_the_paths():
     from ipex_llm.transformers.models.utils import should_use_compresskv, use_quantize_kv_cache  # noqa: F401
     from ipex_llm.transformers.models.common import merge_qkv_base, rms_norm_forward  # noqa: F401
     from ipex_llm.utils.common.log4Error import invalidInputError
-    from ipex_llm.utils.lazy_load_torch import LazyLoadTensors
+    from ipex_llm.utils.lazy_load_torch import DisableTorchAllocTensor
     from ipex_llm.ops.linear import LowBitLinear as impl
     assert LowBitLinear is impl and ggml_tensor_qtype["sym_int4"] == 2
     packed = ggml_convert_qtype(torch.randn(4, 64), ggml_tensor_qtype["sym_int8"])
@@ -39,7 +39,7 @@ def test_names_behind_the_paths():
     assert issubclass(FP4Params, torch.nn.Parameter)
     with pytest.raises(RuntimeError):
         invalidInputError(False, "boom")
-    with LazyLoadTensors():
+    with DisableTorchAllocTensor():
         lin = torch.nn.Linear(8, 8)
     assert lin.weight.device.type == "meta"
     import bigdl.llm.transformers.low_bit_linear as legacy
@@ -77,3 +77,34 @@ def test_torch_library_ops_have_fake_kernels_and_match_eager():
         return torch.ops.ipex_llm.rms_norm(torch.ones(48), a, 1e-6) * 2
     out = torch.compile(f, backend="eager")(g)
     assert torch.allclose(out, n * 2, atol=1e-5)
+
+
+def test_lazy_tensor_loader(tmp_path):
+    """``ipex_llm.utils.lazy_load_torch``: tensors of a zip checkpoint are file-backed until loaded, a stacked dtype
+    conversion runs at load time, and inside ``LazyLoadTensors`` a plain ``torch.load`` is memory-mapped."""
+    import torch
+    from ipex_llm.utils.lazy_load_torch import LazyLoadTensors, LazyTensor, lazyload
+    sd = {"a.weight": torch.randn(64, 32), "b": {"bias": torch.arange(8, dtype=torch.int32)}, "step": 7}
+    path = str(tmp_path / "ckpt.bin")
+    torch.save(sd, path)
+    lazy = lazyload(path)
+    assert isinstance(lazy["a.weight"], LazyTensor) and lazy["a.weight"].shape == [64, 32] and lazy["step"] == 7
+    assert torch.equal(lazy["a.weight"].load(), sd["a.weight"])
+    half = lazy["a.weight"].to(torch.float16)
+    assert half.data_type == torch.float16 and half.load().dtype == torch.float16
+    assert torch.equal(lazy["b"]["bias"].load(), sd["b"]["bias"])
+    orig, seen = torch.load, []
+
+    def recorder(f, *a, **kw):
+        seen.append(kw.get("mmap"))
+        return orig(f, *a, **kw)
+    torch.load = recorder
+    try:
+        with LazyLoadTensors():
+            mapped = torch.load(path, weights_only=True)
+            assert torch.load is not recorder
+        assert torch.load is recorder
+    finally:
+        torch.load = orig
+    assert seen == [True]                                        # the archive was mapped, not read
+    assert torch.equal(mapped["a.weight"], sd["a.weight"])
