@@ -24,6 +24,8 @@ TORCH_LINEAR_THRESHOLD = int(os.getenv("BIGDL_LLM_LINEAR_THRESHOLD", "512"))
 
 def reshape_lm_head_input(x: torch.Tensor) -> torch.Tensor:
     """Only the last position goes through lm_head (reference low_bit_linear.py:262-269)."""
+    if x.dim() < 3:
+        return x            # [tokens, hidden] from a serving engine that already selected the positions it wants
     if x.dim() > 3:
         x = x.reshape([-1, x.shape[-2], x.shape[-1]])
     shape = list(x.size())

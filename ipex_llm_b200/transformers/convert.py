@@ -23,7 +23,8 @@ import warnings
 import torch
 from torch import nn
 
-from ..ops.linear import BF16Linear, FP16Linear, LowBitLinear
+from ..ops.linear import (BF16Linear, FP16Linear, LowBitLinear, vLLMBF16Linear, vLLMFP16Linear,
+                          vLLMLowBitLinear)
 from ..ops.embedding import CPUEmbedding, DiskEmbedding, LowBitEmbedding
 from ..ops.moe import LowBitExperts, convert_fused_experts, is_fused_experts
 from ..quant import qtypes as qt
@@ -112,6 +113,14 @@ def is_linear_module(module):
     return result, (in_features, out_features, mp_group)
 
 
+_VLLM_LINEARS = ("RowParallelLinear", "ColumnParallelLinear", "QKVParallelLinear", "MergedColumnParallelLinear",
+                 "ReplicatedLinear")
+
+
+def _is_vllm_linear(module) -> bool:
+    return type(module).__name__ in _VLLM_LINEARS and type(module).__module__.startswith("vllm.")
+
+
 def _is_moe_router(parent, name, module) -> bool:
     """The expert-selection projection of a sparse-MoE block: a Linear called ``gate`` / ``router`` beside an
     ``experts`` container, or any Linear subclass named ``*Router``."""
@@ -168,9 +177,12 @@ def use_scale_search(model_config, qtype):
 def _make_low_bit(module, name, in_features, out_features, mp_group, cur_qtype, cur_imatrix, model_config,
                   convert_shape_only, device, optimize_lm_head, enable_scale_search, act_order):
     has_bias = getattr(module, "bias", None) is not None
-    new_linear = LowBitLinear(in_features, out_features, cur_qtype, has_bias, mp_group=mp_group,
-                              optimize_lm_head=optimize_lm_head, act_order=act_order,
-                              enable_scale_search=enable_scale_search)
+    # vLLM's parallel linears return ``(output, output_bias)``; their replacements keep that contract
+    # (reference convert.py:538-560 picks vLLMLowBitLinear for them)
+    cls = vLLMLowBitLinear if _is_vllm_linear(module) else LowBitLinear
+    new_linear = cls(in_features, out_features, cur_qtype, has_bias, mp_group=mp_group,
+                     optimize_lm_head=optimize_lm_head, act_order=act_order,
+                     enable_scale_search=enable_scale_search)
     if is_gptq_linear(module) or module.__class__.__name__ == "WQLinear_GEMM":
         awq = module.__class__.__name__ == "WQLinear_GEMM"
         packed = convert_gptq(module, awq=awq, llm_awq=getattr(module, "backend", "") == "llm-awq",
@@ -236,6 +248,8 @@ def _replace_with_low_bit_linear(model, qtype, modules_to_not_convert=None, conv
                                            act_order)
             else:
                 cls = FP16Linear if qtype == qt.FP16 else BF16Linear
+                if _is_vllm_linear(module):
+                    cls = vLLMFP16Linear if qtype == qt.FP16 else vLLMBF16Linear
                 has_bias = getattr(module, "bias", None) is not None
                 new_linear = cls(in_features, out_features, has_bias, mp_group=mp_group,
                                  optimize_lm_head=optimize_lm_head)

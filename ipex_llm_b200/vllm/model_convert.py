@@ -42,6 +42,23 @@ def _get_logits(self, hidden_states, lm_head, embedding_bias=None):
     return logits
 
 
+def patch_runner_class(cls, load_in_low_bit: str):
+    """Wrap ``cls.load_model``: the original loads the checkpoint, then the linears of ``self.model`` are packed."""
+    if cls in _PATCHED:
+        return
+    orig = cls.load_model
+    _PATCHED[cls] = orig
+
+    def load_model(self, *args, _orig=orig, **kwargs):
+        _orig(self, *args, **kwargs)
+        model = getattr(self, "model", None)
+        if model is not None:
+            dtype = getattr(getattr(self, "model_config", None), "dtype", torch.float16)
+            self.model = convert_vllm_model(model, load_in_low_bit, dtype)
+
+    cls.load_model = load_model
+
+
 def _ipex_llm_convert(load_in_low_bit: str):
     """Install the patches.  Call before constructing ``LLM`` / the engine."""
     from vllm.model_executor.layers.logits_processor import LogitsProcessor
@@ -55,19 +72,7 @@ def _ipex_llm_convert(load_in_low_bit: str):
         except Exception:  # noqa: BLE001 - layout differs between vLLM versions
             continue
     for cls in runners:
-        if cls in _PATCHED:
-            continue
-        orig = cls.load_model
-        _PATCHED[cls] = orig
-
-        def load_model(self, *args, _orig=orig, **kwargs):
-            _orig(self, *args, **kwargs)
-            model = getattr(self, "model", None)
-            if model is not None:
-                dtype = getattr(getattr(self, "model_config", None), "dtype", torch.float16)
-                self.model = convert_vllm_model(model, load_in_low_bit, dtype)
-
-        cls.load_model = load_model
+        patch_runner_class(cls, load_in_low_bit)
     if LogitsProcessor not in _PATCHED:
         _PATCHED[LogitsProcessor] = getattr(LogitsProcessor, "_get_logits", None)
         LogitsProcessor._get_logits = _get_logits

@@ -154,3 +154,25 @@ def test_langchain_vllm_wrapper_builds_sampling_params():
     assert prompts == ["a", "bc"] and get("temperature") == 0.5 and get("max_tokens") == 7 and get("top_p") == 0.9
     assert list(get("stop")) == ["\n"]
     assert llm._llm_type == "vllm"
+
+
+def test_vllm_adapter_against_the_installed_vllm():
+    """The vLLM adapter on the installed vLLM, in a child process (vLLM keeps process-wide state and takes tens of
+    seconds to import): vLLM's QKV / row / merged-column parallel linears and ``ParallelLMHead`` are built on the CPU,
+    packed by ``convert_vllm_model`` and compared with the dense product; the loader / logits patches land on vLLM's
+    classes; the ``IPEXLLM*`` engine classes subclass vLLM's and pass arguments through."""
+    import importlib.util
+    import os
+    import socket
+    import subprocess
+    import sys
+    import pytest
+    if importlib.util.find_spec("vllm") is None:
+        pytest.skip("vllm is not installed")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    worker = os.path.join(os.path.dirname(__file__), "dist_workers", "vllm_layers_worker.py")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", CUDA_VISIBLE_DEVICES="")
+    res = subprocess.run([sys.executable, worker, str(port)], capture_output=True, text=True, timeout=600, env=env)
+    assert res.returncode == 0 and res.stdout.strip().endswith("OK"), res.stderr[-3000:]
