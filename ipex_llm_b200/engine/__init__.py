@@ -30,6 +30,8 @@ def supports(model, kwargs) -> bool:
         return False
     if getattr(model, "_ipex_engine_disabled", False):
         return False
+    if getattr(getattr(model, "config", None), "ipex_alibi", False):
+        return False            # linear attention biases instead of rotary positions: module path
     from .. import config as _cfg
     if _cfg.kv_cache_format() == "int4":
         return False            # the 4-bit KV cache lives on the module path (the fused kernels read fp16 / e5m2)

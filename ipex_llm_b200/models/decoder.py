@@ -15,6 +15,7 @@ the package's SDPA.  ``decoder_model_forward`` wraps the HF ``*Model.forward`` t
 from __future__ import annotations
 
 import functools
+import math
 
 import torch
 
@@ -56,6 +57,39 @@ def _split_heads(self, hidden_states):
     return q, k, v
 
 
+def alibi_slopes(n_heads: int) -> torch.Tensor:
+    """Per-head slopes of "attention with linear biases": a geometric series for a power-of-two head count, and for
+    other counts the series of the next lower power of two followed by every other slope of the next higher one
+    (Baichuan-13B has 40 heads; reference models/baichuan.py:403-447 builds the same mask)."""
+    def series(n):
+        start = 2.0 ** (-(2.0 ** -(math.log2(n) - 3)))
+        return [start * start ** i for i in range(n)]
+    if math.log2(n_heads).is_integer():
+        vals = series(n_heads)
+    else:
+        low = 2 ** math.floor(math.log2(n_heads))
+        vals = series(low) + series(2 * low)[0::2][: n_heads - low]
+    return torch.tensor(vals, dtype=torch.float32)
+
+
+def alibi_mask(n_heads, q_len, kv_len, mask, dtype, device):
+    """Additive ``[B or 1, H, q_len, kv_len]`` mask: slope_h * (key position - last position) plus the causal /
+    padding mask.  Soft-max is invariant to a shift per row, so the distance to the query reduces to the key position;
+    counting from the last key keeps the magnitudes small near the diagonal of a decode step."""
+    slopes = alibi_slopes(n_heads).to(device)
+    kj = torch.arange(kv_len, device=device, dtype=torch.float32)
+    bias = slopes.view(1, n_heads, 1, 1) * (kj - (kv_len - 1)).view(1, 1, 1, kv_len)
+    if mask is None:
+        qi = torch.arange(kv_len - q_len, kv_len, device=device).view(q_len, 1)
+        allowed = (kj.view(1, kv_len) <= qi).view(1, 1, q_len, kv_len)
+        bias = bias.expand(1, n_heads, q_len, kv_len).masked_fill(~allowed, float("-inf"))
+    elif mask.dtype == torch.bool:
+        bias = bias.expand(mask.shape[0], n_heads, q_len, kv_len).masked_fill(~mask, float("-inf"))
+    else:
+        bias = bias + mask.float()
+    return bias.to(dtype)
+
+
 def decoder_attention_forward(self, hidden_states, position_embeddings=None, attention_mask=None,
                               past_key_values=None, **kwargs):
     spec: AttnSpec = getattr(self, "_ipex_attn", DEFAULT_SPEC)
@@ -66,7 +100,8 @@ def decoder_attention_forward(self, hidden_states, position_embeddings=None, att
         q = self.q_norm(q)
         k = self.k_norm(k)
 
-    if position_embeddings is not None:
+    alibi = bool(getattr(self.config, "ipex_alibi", False))
+    if position_embeddings is not None and not alibi:
         cos, sin = position_embeddings
         q, k = apply_rotary_pos_emb(q, k, cos, sin, interleaved=spec.interleaved_rope)
 
@@ -90,6 +125,8 @@ def decoder_attention_forward(self, hidden_states, position_embeddings=None, att
     mask = attention_mask
     if mask is not None and mask.dim() == 4 and mask.shape[-1] != kv_len:
         mask = mask[..., :kv_len] if mask.shape[-1] > kv_len else None
+    if alibi:
+        mask = alibi_mask(q.shape[1], q_len, kv_len, mask, q.dtype, q.device)
     attn_output = scaled_dot_product_attention(q, k, v, mask, is_causal=(mask is None and q_len > 1),
                                                scale=scaling, softcap=softcap, sliding_window=sliding_window)
     attn_output = attn_output.transpose(1, 2).reshape(bsz, q_len, -1).contiguous()

@@ -7,7 +7,8 @@ qwen, :1676 aquila, :1876 minicpm; models/chatglm2.py, baichuan.py, internlm.py,
 architectures is, tensor for tensor, an architecture that ``transformers`` implements natively under another name:
 
     chatglm (v2 / v3 / glm-4-9b)  ->  Glm      (interleaved rotary on half of every head, fused gate/up, qkv bias)
-    baichuan (7B, Baichuan2-7B)   ->  Llama    (fused W_pack; Baichuan2 normalises the lm_head rows)
+    baichuan (7B / 13B, v1 / v2)  ->  Llama    (fused W_pack; Baichuan2 normalises the lm_head rows; the 13B
+                                               models replace rotary positions by linear attention biases)
     internlm                      ->  Llama    (biases on q, k, v, o)
     internlm2                     ->  Llama    (wqkv interleaved per kv head)
     qwen (v1)                     ->  Qwen2    (fused c_attn with bias; w2 is the gate, w1 the up projection)
@@ -17,7 +18,7 @@ architectures is, tensor for tensor, an architecture that ``transformers`` imple
 So this module reads ``config.json`` and the weight shards, renames / splits the tensors, and builds the native class;
 from there the family's registry entry (merged qkv, fused kernels, graph engine for the llama-like ones) applies as for
 any other checkpoint, and nothing of the checkpoint's Python files is executed.  Not covered: ChatGLM-6B v1 (2-D
-positions), Baichuan-13B (ALiBi), MiniCPM3 (latent attention), Yuan (convolutional filter) - those return ``None``
+positions), MiniCPM3 (latent attention), Yuan (convolutional filter) - those return ``None``
 here and fall through to ``transformers``' own loader.
 """
 from __future__ import annotations
@@ -98,8 +99,9 @@ def _chatglm(c: dict):
 # ------------------------------------------------------------------------------------------------
 def _baichuan(c: dict):
     from transformers import LlamaConfig
-    if c["hidden_size"] not in (2048, 4096) and "max_position_embeddings" not in c:
-        return None          # 13B: ALiBi instead of rotary positions
+    # 13B checkpoints have no rotary positions: attention carries linear biases (ALiBi).  The Llama classes are kept
+    # and the config field ``ipex_alibi`` tells the package's attention forward to skip the rotation and add the bias.
+    alibi = "max_position_embeddings" not in c and "model_max_length" in c
     v2 = c.get("vocab_size") == 125696
     cfg = LlamaConfig(vocab_size=c["vocab_size"], hidden_size=c["hidden_size"],
                       intermediate_size=c["intermediate_size"], num_hidden_layers=c["num_hidden_layers"],
@@ -107,6 +109,8 @@ def _baichuan(c: dict):
                       max_position_embeddings=c.get("max_position_embeddings", c.get("model_max_length", 4096)),
                       tie_word_embeddings=False, pad_token_id=c.get("pad_token_id", 0),
                       bos_token_id=c.get("bos_token_id", 1), eos_token_id=c.get("eos_token_id", 2))
+    if alibi:
+        cfg.ipex_alibi = True
     H = c["hidden_size"]
 
     def convert(state):
@@ -304,4 +308,10 @@ def maybe_load_remote_arch(path, torch_dtype=None):
             if hasattr(mod, "original_inv_freq"):
                 mod.original_inv_freq = fresh.inv_freq
     model.config.update({"ipex_remote_model_type": mt})
+    if getattr(cfg, "ipex_alibi", False):
+        # the native class would rotate q / k: a model with linear attention biases always runs the package's
+        # attention forward, also when no low-bit conversion (and with it no forward replacement) was asked for
+        from ..models.decoder import decoder_attention_forward
+        from .convert import convert_forward
+        convert_forward(model, "LlamaAttention", decoder_attention_forward)
     return model.eval()

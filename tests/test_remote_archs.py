@@ -102,6 +102,68 @@ def test_baichuan2_checkpoint_loads_as_llama(tmp_path):
     _check(_save(tmp_path, cfg, st), native, atol=1e-4)
 
 
+def test_baichuan_13b_checkpoint_runs_with_linear_attention_biases(tmp_path):
+    """Baichuan-13B / Baichuan2-13B (reference models/baichuan.py:403-447): no rotary positions, every head adds
+    slope_h * key position to its scores.  Compared with a plain restatement of that architecture."""
+    import math
+    from ipex_llm.transformers import AutoModelForCausalLM
+    from ipex_llm_b200.models.decoder import alibi_slopes
+    assert torch.allclose(alibi_slopes(8), torch.tensor([2.0 ** -(i + 1) for i in range(8)]))
+    s12 = alibi_slopes(12)                               # 8 of the 8-head series, then every other one of the 16-head series
+    assert torch.allclose(s12[:8], alibi_slopes(8)) and torch.allclose(s12[8:], alibi_slopes(16)[0::2][:4])
+    H, nh, L, V, I = 96, 6, 2, 500, 192
+    hd = H // nh
+    native = _native(_llama_cfg(vocab_size=V, hidden_size=H, intermediate_size=I, num_attention_heads=nh,
+                                num_key_value_heads=nh))
+    sd = dict(native.state_dict())
+    st = {}
+    for k, v in sd.items():
+        if ".self_attn.q_proj." in k:
+            st[k.replace("q_proj", "W_pack")] = torch.cat([sd[k], sd[k.replace("q_proj", "k_proj")],
+                                                           sd[k.replace("q_proj", "v_proj")]], dim=0)
+        elif ".self_attn.k_proj." not in k and ".self_attn.v_proj." not in k:
+            st[k] = v
+    cfg = {"model_type": "baichuan", "vocab_size": V, "hidden_size": H, "intermediate_size": I,
+           "num_hidden_layers": L, "num_attention_heads": nh, "rms_norm_eps": 1e-6, "model_max_length": 256,
+           "torch_dtype": "float32"}
+    d = _save(tmp_path, cfg, st)
+
+    def rms(x, w):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+
+    def plain(ids):
+        x = sd["model.embed_tokens.weight"][ids]
+        B, S, _ = x.shape
+        slopes = alibi_slopes(nh).view(1, nh, 1, 1)
+        bias = slopes * torch.arange(S).view(1, 1, 1, S) + torch.full((S, S), float("-inf")).triu(1)
+        for i in range(L):
+            p = f"model.layers.{i}."
+            h = rms(x, sd[p + "input_layernorm.weight"])
+            q, k, v = [(h @ sd[p + f"self_attn.{n}_proj.weight"].t()).view(B, S, nh, hd).transpose(1, 2) for n in "qkv"]
+            a = torch.softmax(q @ k.transpose(-1, -2) / math.sqrt(hd) + bias, -1) @ v
+            x = x + a.transpose(1, 2).reshape(B, S, H) @ sd[p + "self_attn.o_proj.weight"].t()
+            h = rms(x, sd[p + "post_attention_layernorm.weight"])
+            g = torch.nn.functional.silu(h @ sd[p + "mlp.gate_proj.weight"].t()) * (h @ sd[p + "mlp.up_proj.weight"].t())
+            x = x + g @ sd[p + "mlp.down_proj.weight"].t()
+        return rms(x, sd["model.norm.weight"]) @ sd["lm_head.weight"].t()
+
+    m = AutoModelForCausalLM.from_pretrained(d, load_in_low_bit="bf16", torch_dtype=torch.float32)
+    assert m.config.ipex_alibi is True
+    ids = torch.randint(0, V, (2, 17))
+    with torch.no_grad():
+        got, want = m(ids).logits.float(), plain(ids)
+    got = got[:, -1] if got.shape[1] == 1 else got[:, -1]
+    assert torch.nn.functional.cosine_similarity(got.flatten(), want[:, -1].flatten(), dim=0) > 0.999
+    plain_load = AutoModelForCausalLM.from_pretrained(d)             # no conversion asked for: biases all the same
+    with torch.no_grad():
+        assert torch.allclose(plain_load(ids).logits, want, atol=1e-4)
+    # incremental decoding adds the same biases as a full pass
+    out = m.generate(ids[:1], max_new_tokens=5, do_sample=False)
+    with torch.no_grad():
+        again = m(out[:, :-1]).logits[:, -1].argmax(-1)
+    assert torch.equal(again, out[:, -1])
+
+
 def test_internlm_and_aquila_checkpoints_load_as_llama(tmp_path):
     native = _native(_llama_cfg(attention_bias=True))
     cfg = {"model_type": "internlm", "vocab_size": 1000, "hidden_size": 128, "intermediate_size": 256,
@@ -186,6 +248,3 @@ def test_minicpm_checkpoint_loads_as_granite(tmp_path):
 def test_uncovered_variants_fall_through():
     from ipex_llm_b200.transformers.remote_archs import REMOTE_ARCHS
     assert REMOTE_ARCHS["chatglm"]({"model_type": "chatglm", "position_encoding_2d": True}) is None      # ChatGLM-6B v1
-    assert REMOTE_ARCHS["baichuan"]({"model_type": "baichuan", "hidden_size": 5120, "vocab_size": 64000,
-                                     "intermediate_size": 1, "num_hidden_layers": 1,
-                                     "num_attention_heads": 1}) is None                                   # 13B ALiBi
