@@ -102,5 +102,15 @@ def chat_main(argv=None):
     return main((argv if argv is not None else sys.argv[1:]) + ["--chat"])
 
 
+def quantize_main(argv=None):
+    """``ipex-quantize in.gguf out.gguf q4_k [--keep substr] [--output-type q6_k]``: hands over to the native
+    executable (built on first use), the counterpart of the reference's ``quantize-<family>`` binaries."""
+    import os
+    import sys
+    from ..native.build import build_tools
+    exe = build_tools()
+    os.execv(exe, [exe, *(sys.argv[1:] if argv is None else argv)])
+
+
 if __name__ == "__main__":
     sys.exit(main())

@@ -1,9 +1,10 @@
 """In-tree build of the native libraries.
 
-Two shared objects are produced next to this file:
+Two shared objects and one executable are produced next to this file:
 
 * ``libipex_quant_core.so``  — C++ host library (quantizers, layout transforms, CPU matmul oracle)
 * ``libipex_llm_cuda.so``    — every sm_100a CUDA kernel of the package, plain C ABI launchers
+* ``bin/ipex-quantize``      — GGUF -> k-quant GGUF rewriter on the host library (``tools/quantize_main.cpp``)
 
 Both are loaded through ctypes (``ipex_llm_b200.native.lib``).  A content hash of the sources is kept
 beside each library so that an unchanged tree is never recompiled (the libraries travel with the
@@ -24,6 +25,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 HOST_DIR = os.path.join(HERE, "host")
 CUDA_DIR = os.path.join(HERE, "cuda")
 OBJ_DIR = os.path.join(HERE, "build")
+
+TOOLS_DIR = os.path.join(HERE, "tools")
+BIN_DIR = os.path.join(HERE, "bin")
+QUANTIZE_BIN = os.path.join(BIN_DIR, "ipex-quantize")
 
 HOST_LIB = os.path.join(HERE, "libipex_quant_core.so")
 CUDA_LIB = os.path.join(HERE, "libipex_llm_cuda.so")
@@ -82,6 +87,23 @@ def build_host(force=False, verbose=False):
     return HOST_LIB
 
 
+def build_tools(force=False, verbose=False):
+    """Stand-alone executables: ``bin/ipex-quantize`` (GGUF -> k-quant GGUF), statically carrying the quant core."""
+    srcs = _sources(TOOLS_DIR, (".cpp",)) + _sources(HOST_DIR, (".cpp",))
+    deps = srcs + _sources(HOST_DIR, (".h",))
+    flags = ["-O3", "-fopenmp", "-std=c++17", "-Wall"]
+    digest = _hash_files(deps, " ".join(flags))
+    if not force and _stamp_ok(QUANTIZE_BIN, digest):
+        return QUANTIZE_BIN
+    os.makedirs(BIN_DIR, exist_ok=True)
+    cmd = ["g++", *flags, "-o", QUANTIZE_BIN, *srcs]
+    if verbose:
+        print(" ".join(cmd))
+    subprocess.check_call(cmd)
+    _write_stamp(QUANTIZE_BIN, digest)
+    return QUANTIZE_BIN
+
+
 def cuda_flags(verbose=False):
     flags = [*NVCC_ARCH, "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
              "--expt-relaxed-constexpr", "-I", CUDA_DIR]
@@ -129,7 +151,7 @@ def build_cuda(force=False, verbose=False):
 
 
 def build_all(force=False, verbose=False):
-    return build_host(force, verbose), build_cuda(force, verbose)
+    return build_host(force, verbose), build_tools(force, verbose), build_cuda(force, verbose)
 
 
 if __name__ == "__main__":

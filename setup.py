@@ -9,7 +9,7 @@ setup(
     description="Blackwell-native low-bit LLM library with the API surface of ipex-llm",
     packages=find_packages(include=["ipex_llm_b200*", "ipex_llm*", "bigdl*"]),
     package_data={"ipex_llm_b200": ["native/*.so", "native/cuda/*.cu", "native/cuda/*.cuh", "native/cuda/*.h",
-                                    "native/cuda/common/*.cuh", "native/host/*.cpp", "native/host/*.h"]},
+                                    "native/cuda/common/*.cuh", "native/host/*.cpp", "native/host/*.h", "native/tools/*.cpp", "native/bin/*"]},
     python_requires=">=3.10",
     install_requires=["torch", "transformers", "numpy"],
     extras_require={"serving": ["fastapi", "uvicorn", "pydantic"], "all": ["sentencepiece", "pyyaml", "safetensors"]},
@@ -18,5 +18,6 @@ setup(
         "llm-chat=ipex_llm_b200.cli.llm_cli:chat_main",
         "llm-convert=ipex_llm_b200.convert_model:main",
         "ipex-llm-init=ipex_llm_b200.cli.ipex_llm_init:main",
+        "ipex-quantize=ipex_llm_b200.cli.llm_cli:quantize_main",
     ]},
 )

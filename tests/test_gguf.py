@@ -1,5 +1,7 @@
 """GGUF import: write a tiny llama-shaped file (f32 / f16 / q8_0 / q4_0 tensors), read it back, compare with the
 source model."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -64,6 +66,37 @@ def test_superblock_tensor_types_read_back(tmp_path):
         y = got[f"w.{k}"]
         assert y.shape == w.shape and ((y - w).norm() / w.norm()).item() < tol, k
     loader.close()
+
+
+def test_native_quantize_executable_rewrites_a_gguf_file(tmp_path):
+    """``ipex-quantize`` (C++): metadata kept, matrices with rows of a multiple of 256 packed to the k-quant asked for
+    (``output.weight`` to q6_k), small and kept tensors copied; the result reads back through the GGUF reader."""
+    from ipex_llm_b200.ggml.quantize import quantize, quantize_gguf
+    from ipex_llm_b200.transformers.gguf.gguf import GGUFFileLoader, write_gguf
+    torch.manual_seed(0)
+    tensors = {"blk.0.attn_q.weight": (torch.randn(64, 512), "f32"), "blk.0.ffn_down.weight": (torch.randn(32, 256), "f16"),
+               "blk.0.attn_norm.weight": (torch.randn(512), "f32"), "output.weight": (torch.randn(40, 512), "f32"),
+               "blk.0.odd.weight": (torch.randn(8, 96), "f32"), "blk.0.keepme.weight": (torch.randn(4, 256), "f32")}
+    src, dst = str(tmp_path / "in.gguf"), str(tmp_path / "out.gguf")
+    write_gguf(src, {"general.architecture": "llama", "llama.block_count": 1, "tokenizer.ggml.tokens": ["a", "b"]}, tensors)
+    quantize_gguf(src, dst, "q4_k", keep=["keepme"])
+    loader = GGUFFileLoader(dst)
+    assert loader.config["general.architecture"] == "llama" and loader.config["tokenizer.ggml.tokens"] == ["a", "b"]
+    types = {name: t for name, _, t, _ in loader.tensor_loader.infos}
+    assert types["blk.0.attn_q.weight"] == 12 and types["blk.0.ffn_down.weight"] == 12 and types["output.weight"] == 14
+    assert types["blk.0.attn_norm.weight"] == 0 and types["blk.0.odd.weight"] == 0 and types["blk.0.keepme.weight"] == 0
+    got = loader.tensors()
+    for name, (t, kind) in tensors.items():
+        ref = t.half().float() if kind == "f16" else t
+        err = ((got[name] - ref).norm() / ref.norm()).item()
+        assert got[name].shape == t.shape and err < (0.12 if types[name] in (12, 14) else 1e-6), (name, err)
+    loader.close()
+    assert os.path.getsize(dst) < 0.35 * os.path.getsize(src)
+    # the Python entry point takes the same route for file-to-file k-quant requests
+    dst2 = str(tmp_path / "out2.gguf")
+    assert quantize(src, dst2, "llama", "q6_k") == dst2 and os.path.getsize(dst2) > os.path.getsize(dst)
+    with pytest.raises(RuntimeError):
+        quantize_gguf(str(tmp_path / "out.gguf"), str(tmp_path / "x.gguf"), "q9_k")
 
 
 def test_load_gguf_llama(tmp_path):
