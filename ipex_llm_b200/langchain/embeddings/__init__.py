@@ -1,3 +1,6 @@
+from .bigdlllm import (BigdlNativeEmbeddings, BloomEmbeddings, GptneoxEmbeddings, LlamaEmbeddings,  # noqa: F401
+                       StarcoderEmbeddings)
 from .transformersembeddings import TransformersEmbeddings  # noqa: F401
 
-__all__ = ["TransformersEmbeddings"]
+__all__ = ["BigdlNativeEmbeddings", "LlamaEmbeddings", "BloomEmbeddings", "GptneoxEmbeddings", "StarcoderEmbeddings",
+           "TransformersEmbeddings"]

@@ -176,3 +176,33 @@ def test_vllm_adapter_against_the_installed_vllm():
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", CUDA_VISIBLE_DEVICES="")
     res = subprocess.run([sys.executable, worker, str(port)], capture_output=True, text=True, timeout=600, env=env)
     assert res.returncode == 0 and res.stdout.strip().endswith("OK"), res.stderr[-3000:]
+
+
+def test_langchain_native_class_wrappers(tiny):
+    """``LlamaLLM`` / ``BigdlNativeLLM`` / ``LlamaEmbeddings`` over the llama-cpp-python style classes (reference
+    langchain/llms/bigdlllm.py, langchain/embeddings/bigdlllm.py): blocking and streaming calls agree, stop words cut
+    the text, the family table rejects unknown names."""
+    from ipex_llm.langchain.embeddings import BigdlNativeEmbeddings, LlamaEmbeddings
+    from ipex_llm.langchain.llms import BigdlNativeLLM, LlamaLLM, type_to_cls_dict
+    from ipex_llm.langchain.llms.transformerspipelinellm import TransformersPipelineLLM  # noqa: F401
+    llm = LlamaLLM(model_path=tiny, max_tokens=6, temperature=0.0, streaming=False, low_bit="sym_int8", device="cpu")
+    assert llm._llm_type == "BigDL" and llm._identifying_params["model_family"] == "llama"
+    text = llm._call("w1 w2 w3")
+    assert isinstance(text, str) and llm.get_num_tokens("w1 w2 w3") >= 3
+    pieces = list(llm.stream("w1 w2 w3"))
+    assert "".join(pieces).strip() == text.strip()
+    words = text.split()
+    if len(words) >= 2:                                     # a stop word cuts the completion before it
+        cut = llm._call("w1 w2 w3", stop=[words[-1]])
+        assert words[-1] not in cut and cut.strip() == text[:text.find(words[-1])].strip()
+    with pytest.raises(ValueError):
+        LlamaLLM(client=llm.client, stop=["a"])._get_parameters(stop=["b"])
+    same = BigdlNativeLLM(model_family="llama", client=llm.client, max_tokens=6, temperature=0.0, streaming=True)
+    assert same._call("w1 w2 w3").strip() == text.strip()
+    with pytest.raises(ValueError):
+        BigdlNativeLLM(model_family="mamba", model_path=tiny)
+    assert type_to_cls_dict["LlamaLLM"] is LlamaLLM
+    emb = LlamaEmbeddings(client=llm.client)
+    v = emb.embed_query("w1 w2")
+    assert len(v) == 64 and len(emb.embed_documents(["w1", "w2 w3"])) == 2
+    assert BigdlNativeEmbeddings(model_family="llama", client=llm.client).embed_query("w1 w2") == v
