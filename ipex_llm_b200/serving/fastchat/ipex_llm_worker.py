@@ -2,7 +2,7 @@
 
 Reference: python/llm/src/ipex_llm/serving/fastchat/ipex_llm_worker.py (``BigDLLLMWorker`` with
 ``generate_stream_gate`` / ``generate_gate``, heart-beats to the controller, ``/worker_generate_stream``,
-``/worker_generate``, ``/worker_get_status``, ``/count_token``, ``/model_details``).  FastChat itself is not a
+``/worker_generate``, ``/worker_get_embeddings``, ``/worker_get_status``, ``/count_token``, ``/model_details``).  FastChat itself is not a
 dependency: the endpoints and JSON payloads are implemented here on FastAPI, generation runs on this package's
 ``ModelWorker``, and registration with a controller is a plain HTTP POST when ``controller_addr`` is given.
 
@@ -117,6 +117,24 @@ class BigDLLLMWorker:
         finally:
             self.in_flight -= 1
 
+    def get_embeddings(self, params):
+        """FastChat's ``/worker_get_embeddings``: mean of the last hidden states over the real tokens of every input,
+        L2-normalised; ``token_num`` counts the tokens that were embedded."""
+        import torch
+        texts = params["input"]
+        texts = [texts] if isinstance(texts, str) else list(texts)
+        tok, model = self.tokenizer, self.worker.model
+        enc = tok(texts, return_tensors="pt", padding=True, truncation=True, max_length=self.context_len)
+        dev = next(model.parameters()).device
+        ids, mask = enc["input_ids"].to(dev), enc["attention_mask"].to(dev)
+        with torch.no_grad():
+            out = model(input_ids=ids, attention_mask=mask, output_hidden_states=True)
+        h = out.hidden_states[-1].float()
+        m = mask.unsqueeze(-1).float()
+        emb = (h * m).sum(1) / m.sum(1).clamp_min(1.0)
+        emb = torch.nn.functional.normalize(emb, p=2, dim=1)
+        return {"embedding": emb.cpu().tolist(), "token_num": int(mask.sum())}
+
     async def generate_gate(self, params):
         last = None
         async for chunk in self.generate_stream_gate(params):
@@ -134,6 +152,10 @@ def create_app(w: BigDLLLMWorker) -> FastAPI:
     @app.post("/worker_generate")
     async def api_generate(request: Request):
         return JSONResponse(await w.generate_gate(await request.json()))
+
+    @app.post("/worker_get_embeddings")
+    async def api_get_embeddings(request: Request):
+        return JSONResponse(w.get_embeddings(await request.json()))
 
     @app.post("/worker_get_status")
     async def api_get_status(request: Request):

@@ -142,6 +142,36 @@ def test_fastchat_protocol_worker(worker):
         assert chunks[-1]["text"] == r["text"] and chunks[-1]["finish_reason"] in ("length", "stop")
 
 
+def test_fastchat_embeddings_adapters_and_generic_worker(worker, tmp_path):
+    """``/worker_get_embeddings``; the ``bigdl`` / ``bigdl-lowbit`` path adapters (reference
+    serving/fastchat/bigdl_llm_model.py); the generic ``model_worker.ModelWorker`` on an adapter-loaded model."""
+    from fastapi.testclient import TestClient
+    from ipex_llm_b200.serving.fastchat import bigdl_llm_model as adapters
+    from ipex_llm_b200.serving.fastchat.model_worker import ModelWorker, create_app
+    w = ModelWorker(None, "http://localhost:21002", "w0", "tiny", worker=worker, no_register=True,
+                    conv_template="vicuna_v1.1")
+    with TestClient(create_app(w)) as c:
+        r = c.post("/worker_get_embeddings", json={"input": ["w1 w2 w3", "w4"]}).json()
+        assert len(r["embedding"]) == 2 and r["token_num"] == 4
+        n0 = sum(x * x for x in r["embedding"][0]) ** 0.5
+        assert abs(n0 - 1.0) < 1e-4
+        assert c.post("/worker_get_conv_template").json()["conv"]["name"] == "vicuna_v1.1"
+    assert isinstance(adapters.get_model_adapter("/models/bigdl-7b"), adapters.BigDLLLMAdapter)
+    assert isinstance(adapters.get_model_adapter("/models/BigDL-LowBit-7b"), adapters.BigDLLMLOWBITAdapter)
+    assert adapters.get_model_adapter("/models/vicuna") is None
+    assert adapters.patch_fastchat() in (True, False)            # FastChat is optional
+    # both adapters load the same tiny checkpoint to the same logits
+    import torch
+    src = str(tmp_path / "bigdl-tiny")
+    worker.model.save_low_bit(str(tmp_path / "bigdl-lowbit-tiny"))
+    worker.tokenizer.save_pretrained(str(tmp_path / "bigdl-lowbit-tiny"))
+    m_low, tok = adapters.load_model(str(tmp_path / "bigdl-lowbit-tiny"), device="cpu")
+    ids = torch.tensor([[5, 6, 7]])
+    with torch.no_grad():
+        assert torch.equal(m_low(ids).logits, worker.model(ids).logits)
+    assert tok.decode([5]) == worker.tokenizer.decode([5]) and src
+
+
 def test_audio_transcription_endpoint(monkeypatch):
     """multipart upload of a WAV file -> decoded, resampled to 16 kHz, handed to the worker's speech model."""
     import io
