@@ -12,6 +12,12 @@ __version__ = "0.1.0"
 
 _logging.getLogger("ipex_llm").addHandler(_logging.NullHandler())
 
+import os as _os  # noqa: E402
+
+if _os.environ.get("BIGDL_GLIBC_CHECK", "False").lower() in ("1", "true", "yes"):
+    from .utils.glibc_checker import check_glibc_version as _check_glibc_version
+    _check_glibc_version()
+
 from .optimize import load_low_bit, low_memory_init, optimize_model  # noqa: E402,F401
 
 _LAZY = {

@@ -108,3 +108,11 @@ def test_lazy_tensor_loader(tmp_path):
         torch.load = orig
     assert seen == [True]                                        # the archive was mapped, not read
     assert torch.equal(mapped["a.weight"], sd["a.weight"])
+
+
+def test_glibc_checker():
+    from ipex_llm.utils.glibc_checker import GlibcChecker, check_glibc_version
+    check_glibc_version()                                   # the build machine satisfies its own requirement
+    assert GlibcChecker.get_glibc_version()[0].isdigit()
+    with pytest.raises(RuntimeError):
+        GlibcChecker("999.0").check_requirements()
