@@ -122,7 +122,8 @@ FAMILIES = {
     "deepseek_v3": Family(post=[("DeepseekV3RMSNorm", C.rms_norm_forward), ("DeepseekV3MLP", C.mlp_silu_forward)]),
     # multi-head latent attention keeps its own projections (q_a / q_b, kv_a / kv_b) and reaches the package's SDPA
     # through the attention interface; experts are converted as a fused bank, the router stays in full precision
-    "deepseek_v2": Family(post=[("DeepseekV2RMSNorm", C.rms_norm_forward), ("DeepseekV2MLP", C.mlp_silu_forward)]),
+    "deepseek_v2": Family(post=[("DeepseekV2RMSNorm", C.rms_norm_forward), ("DeepseekV2MLP", C.mlp_silu_forward)],
+                          post_hook=P3.install),      # MiniCPM3 checkpoints arrive here with LongRoPE factors
     "phimoe": Family(post=[("LayerNorm", C.layer_norm_forward)]),
     "mllama": Family(post=[("MllamaTextRMSNorm", C.rms_norm_forward), ("MllamaTextMLP", C.mlp_silu_forward)]),
     "rwkv": Family(pre=[R.rescale_before_quantization],

@@ -1,6 +1,6 @@
 """Checkpoints of "remote code" families loaded WITHOUT their remote code.
 
-The reference supports ChatGLM2/3 / GLM-4, Baichuan(2)-7B, InternLM / InternLM2, Qwen (v1), MiniCPM and Aquila by
+The reference supports ChatGLM2/3 / GLM-4, Baichuan(2), InternLM / InternLM2, Qwen (v1), MiniCPM(3) and Aquila by
 patching the forwards of the modeling files those checkpoints ship (``trust_remote_code=True``;
 python/llm/src/ipex_llm/transformers/convert.py:1337 chatglm, :1463 baichuan, :1513-1524 internlm / internlm2, :1559
 qwen, :1676 aquila, :1876 minicpm; models/chatglm2.py, baichuan.py, internlm.py, qwen.py, minicpm.py).  Each of these
@@ -13,12 +13,13 @@ architectures is, tensor for tensor, an architecture that ``transformers`` imple
     internlm2                     ->  Llama    (wqkv interleaved per kv head)
     qwen (v1)                     ->  Qwen2    (fused c_attn with bias; w2 is the gate, w1 the up projection)
     minicpm (1B / 2B)             ->  Granite  (embedding, residual and logit multipliers)
+    minicpm3                      ->  DeepseekV2, dense (latent attention; multipliers folded into the weights)
     aquila / aquila2              ->  Llama
 
 So this module reads ``config.json`` and the weight shards, renames / splits the tensors, and builds the native class;
 from there the family's registry entry (merged qkv, fused kernels, graph engine for the llama-like ones) applies as for
 any other checkpoint, and nothing of the checkpoint's Python files is executed.  Not covered: ChatGLM-6B v1 (2-D
-positions), MiniCPM3 (latent attention), Yuan (convolutional filter) - those return ``None``
+positions), Yuan (convolutional filter) - those return ``None``
 here and fall through to ``transformers``' own loader.
 """
 from __future__ import annotations
@@ -263,9 +264,79 @@ def _minicpm(c: dict):
     return cfg, convert
 
 
+# ------------------------------------------------------------------------------------------------
+# minicpm3  ->  DeepseekV2 (dense): multi-head latent attention with the MiniCPM multipliers folded into the weights
+# ------------------------------------------------------------------------------------------------
+def _interleave_rows(w, start: int, n: int):
+    """Rows ``start .. start+n`` hold a rotary block in half-split order (pair = (i, i + n/2), what ``rotate_half``
+    rotates); reorder them to interleaved order (pair = (2i, 2i+1), what a complex multiplication rotates).  Applied
+    to the rows that produce q and k alike, the scores do not change."""
+    half = n // 2
+    idx = torch.arange(n).view(2, half).t().reshape(-1) + start
+    out = w.clone()
+    out[start:start + n] = w[idx]
+    return out
+
+
+def _minicpm3(c: dict):
+    """MiniCPM3 (reference models/minicpm3.py:116-230) is DeepSeek-V2's latent attention on a dense MLP, plus the
+    MiniCPM multipliers.  The native DeepseekV2 classes have no multipliers, so they are folded into weights that
+    follow them: ``scale_emb`` into the embedding, ``scale_depth / sqrt(layers)`` into ``o_proj`` and ``down_proj`` (the
+    last linear of each residual branch), ``dim_model_base / hidden`` into the output layer.  MiniCPM3 rotates the
+    two halves of the rotary block, the native class rotates adjacent pairs: the rotary rows of ``q_b_proj`` and
+    ``kv_a_proj_with_mqa`` are reordered accordingly."""
+    from transformers import DeepseekV2Config
+    L, H, nh = c["num_hidden_layers"], c["hidden_size"], c["num_attention_heads"]
+    nope, rope_d = c["qk_nope_head_dim"], c["qk_rope_head_dim"]
+    v_dim = c.get("v_head_dim") or H // nh
+    rp = {"rope_type": "default", "rope_theta": float(c.get("rope_theta", 10000.0))}
+    rs = c.get("rope_scaling") or {}
+    if (rs.get("type") or rs.get("rope_type")) == "longrope":
+        rp.update(rope_type="longrope", short_factor=list(rs["short_factor"]), long_factor=list(rs["long_factor"]),
+                  original_max_position_embeddings=int(rs["original_max_position_embeddings"]))
+    cfg = DeepseekV2Config(vocab_size=c["vocab_size"], hidden_size=H, intermediate_size=c["intermediate_size"],
+                           num_hidden_layers=L, num_attention_heads=nh, num_key_value_heads=nh,
+                           max_position_embeddings=c.get("max_position_embeddings", 32768),
+                           rms_norm_eps=c.get("rms_norm_eps", 1e-5), rope_parameters=rp,
+                           q_lora_rank=c.get("q_lora_rank"), kv_lora_rank=c["kv_lora_rank"], qk_nope_head_dim=nope,
+                           qk_rope_head_dim=rope_d, v_head_dim=v_dim, head_dim=rope_d,
+                           first_k_dense_replace=L, n_routed_experts=1, n_shared_experts=0, num_experts_per_tok=1,
+                           moe_intermediate_size=c["intermediate_size"], tie_word_embeddings=False,
+                           pad_token_id=c.get("pad_token_id", 0), bos_token_id=c.get("bos_token_id", 1),
+                           eos_token_id=c.get("eos_token_id", 2))
+    if rp["rope_type"] == "longrope":
+        cfg.original_max_position_embeddings = rp["original_max_position_embeddings"]
+    scale_emb = float(c.get("scale_emb", 1.0))
+    resid = float(c.get("scale_depth", 1.0)) / math.sqrt(L)
+    logit = float(c.get("dim_model_base", H)) / float(H)
+    qk = nope + rope_d
+    kv_rank = c["kv_lora_rank"]
+
+    def convert(state):
+        out = {}
+        emb = state["model.embed_tokens.weight"]
+        head = state.get("lm_head.weight", emb)                       # tied in the released checkpoints
+        for k, v in state.items():
+            if k.endswith("rotary_emb.inv_freq") or k == "lm_head.weight":
+                continue
+            if k.endswith("self_attn.q_b_proj.weight") or k.endswith("self_attn.q_proj.weight"):
+                for h in range(nh):
+                    v = _interleave_rows(v, h * qk + nope, rope_d)
+            elif k.endswith("self_attn.kv_a_proj_with_mqa.weight"):
+                v = _interleave_rows(v, kv_rank, rope_d)
+            elif k.endswith("self_attn.o_proj.weight") or k.endswith("mlp.down_proj.weight"):
+                v = (v.float() * resid).to(v.dtype)
+            elif k == "model.embed_tokens.weight":
+                v = (v.float() * scale_emb).to(v.dtype)
+            out[k] = v
+        out["lm_head.weight"] = (head.float() * logit).to(head.dtype)
+        return out
+    return cfg, convert
+
+
 REMOTE_ARCHS: Dict[str, Callable[[dict], Optional[Tuple[object, Callable]]]] = {
     "chatglm": _chatglm, "baichuan": _baichuan, "internlm": _internlm, "internlm2": _internlm2, "qwen": _qwen,
-    "minicpm": _minicpm, "aquila": _aquila,
+    "minicpm": _minicpm, "minicpm3": _minicpm3, "aquila": _aquila,
 }
 
 

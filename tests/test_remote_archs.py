@@ -245,6 +245,104 @@ def test_minicpm_checkpoint_loads_as_granite(tmp_path):
     _check(_save(tmp_path, cfg, st), native)
 
 
+def test_minicpm3_checkpoint_loads_as_dense_deepseek_v2(tmp_path):
+    """MiniCPM3 (reference models/minicpm3.py:116-230): latent attention with half-split rotary on the rope block,
+    LongRoPE factors, and the embedding / residual / logit multipliers.  The checkpoint is random; the expected logits
+    come from a plain restatement of that architecture, written independently of the mapping."""
+    from ipex_llm.transformers import AutoModelForCausalLM
+    torch.manual_seed(0)
+    V, H, I, L, nh = 300, 64, 128, 2, 4
+    nope, rope_d, qr, kvr = 16, 8, 24, 16
+    vd = H // nh
+    qk = nope + rope_d
+    scale_emb, scale_depth, dmb, eps, theta, orig = 12.0, 1.4, 16, 1e-5, 10000.0, 32
+    short = [1.0 + 0.1 * i for i in range(rope_d // 2)]
+    long = [2.0 + 0.5 * i for i in range(rope_d // 2)]
+    st = {"model.embed_tokens.weight": torch.randn(V, H) * 0.1, "model.norm.weight": 1 + 0.1 * torch.randn(H)}
+    for i in range(L):
+        p = f"model.layers.{i}."
+        st.update({p + "input_layernorm.weight": 1 + 0.1 * torch.randn(H),
+                   p + "post_attention_layernorm.weight": 1 + 0.1 * torch.randn(H),
+                   p + "self_attn.q_a_proj.weight": torch.randn(qr, H) * 0.1,
+                   p + "self_attn.q_a_layernorm.weight": 1 + 0.1 * torch.randn(qr),
+                   p + "self_attn.q_b_proj.weight": torch.randn(nh * qk, qr) * 0.2,
+                   p + "self_attn.kv_a_proj_with_mqa.weight": torch.randn(kvr + rope_d, H) * 0.1,
+                   p + "self_attn.kv_a_layernorm.weight": 1 + 0.1 * torch.randn(kvr),
+                   p + "self_attn.kv_b_proj.weight": torch.randn(nh * (nope + vd), kvr) * 0.2,
+                   p + "self_attn.o_proj.weight": torch.randn(H, nh * vd) * 0.1,
+                   p + "mlp.gate_proj.weight": torch.randn(I, H) * 0.1, p + "mlp.up_proj.weight": torch.randn(I, H) * 0.1,
+                   p + "mlp.down_proj.weight": torch.randn(H, I) * 0.1})
+    cfg = {"model_type": "minicpm3", "vocab_size": V, "hidden_size": H, "intermediate_size": I, "num_hidden_layers": L,
+           "num_attention_heads": nh, "num_key_value_heads": nh, "q_lora_rank": qr, "kv_lora_rank": kvr,
+           "qk_nope_head_dim": nope, "qk_rope_head_dim": rope_d, "rms_norm_eps": eps, "scale_emb": scale_emb,
+           "scale_depth": scale_depth, "dim_model_base": dmb, "max_position_embeddings": 128, "rope_theta": theta,
+           "rope_scaling": {"type": "longrope", "short_factor": short, "long_factor": long,
+                            "original_max_position_embeddings": orig}, "torch_dtype": "float32"}
+    d = _save(tmp_path, cfg, st)
+
+    def rms(x, w):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w
+
+    def rot_half(x):
+        a, b = x[..., : x.shape[-1] // 2], x[..., x.shape[-1] // 2:]
+        return torch.cat((-b, a), dim=-1)
+
+    def plain(ids):
+        B, S = ids.shape
+        ext = torch.tensor(long if S > orig else short)
+        inv = 1.0 / (ext * theta ** (torch.arange(0, rope_d, 2).float() / rope_d))
+        ang = torch.outer(torch.arange(S).float(), inv)
+        mscale = math.sqrt(1 + math.log(128 / orig) / math.log(orig))
+        cos, sin = torch.cat((ang, ang), -1).cos() * mscale, torch.cat((ang, ang), -1).sin() * mscale
+        x = st["model.embed_tokens.weight"][ids] * scale_emb
+        causal = torch.full((S, S), float("-inf")).triu(1)
+        for i in range(L):
+            p = f"model.layers.{i}."
+            h = rms(x, st[p + "input_layernorm.weight"])
+            q = rms(h @ st[p + "self_attn.q_a_proj.weight"].t(), st[p + "self_attn.q_a_layernorm.weight"])
+            q = (q @ st[p + "self_attn.q_b_proj.weight"].t()).view(B, S, nh, qk).transpose(1, 2)
+            q_nope, q_pe = q.split([nope, rope_d], -1)
+            ckv = h @ st[p + "self_attn.kv_a_proj_with_mqa.weight"].t()
+            ckv, k_pe = ckv.split([kvr, rope_d], -1)
+            k_pe = k_pe.view(B, S, 1, rope_d).transpose(1, 2)
+            kv = (rms(ckv, st[p + "self_attn.kv_a_layernorm.weight"]) @ st[p + "self_attn.kv_b_proj.weight"].t())
+            kv = kv.view(B, S, nh, nope + vd).transpose(1, 2)
+            k_nope, v = kv.split([nope, vd], -1)
+            q_pe = q_pe * cos + rot_half(q_pe) * sin
+            k_pe = k_pe * cos + rot_half(k_pe) * sin
+            qf = torch.cat((q_nope, q_pe), -1)
+            kf = torch.cat((k_nope, k_pe.expand(B, nh, S, rope_d)), -1)
+            a = torch.softmax(qf @ kf.transpose(-1, -2) / math.sqrt(qk) + causal, -1) @ v
+            a = a.transpose(1, 2).reshape(B, S, nh * vd) @ st[p + "self_attn.o_proj.weight"].t()
+            x = x + a * (scale_depth / math.sqrt(L))
+            h = rms(x, st[p + "post_attention_layernorm.weight"])
+            m = torch.nn.functional.silu(h @ st[p + "mlp.gate_proj.weight"].t()) * (h @ st[p + "mlp.up_proj.weight"].t())
+            x = x + (m @ st[p + "mlp.down_proj.weight"].t()) * (scale_depth / math.sqrt(L))
+        x = rms(x, st["model.norm.weight"])
+        return (x / (H / dmb)) @ st["model.embed_tokens.weight"].t()           # tied output layer
+
+    m = AutoModelForCausalLM.from_pretrained(d)
+    assert m.config.model_type == "deepseek_v2" and m.config.ipex_remote_model_type == "minicpm3"
+    for n in (12, 40):                                   # below and above the LongRoPE switch point
+        ids = torch.randint(0, V, (2, n))
+        with torch.no_grad():
+            got, want = m(ids).logits, plain(ids)
+        assert torch.allclose(got, want, atol=2e-4, rtol=1e-3), (n, (got - want).abs().max())
+    q8 = AutoModelForCausalLM.from_pretrained(d, load_in_low_bit="sym_int8")
+    ids = torch.randint(0, V, (2, 12))
+    with torch.no_grad():
+        lq = q8(ids).logits[:, -1]
+    assert torch.nn.functional.cosine_similarity(lq.float(), plain(ids)[:, -1], dim=-1).min() > 0.99
+    # generation across the switch point rebuilds the cache with the long factors (as for Phi-3)
+    ids = torch.randint(0, V, (1, 29))
+    out = q8.generate(ids, max_new_tokens=8, do_sample=False)
+    cur = ids
+    with torch.no_grad():
+        for _ in range(8):
+            cur = torch.cat([cur, q8(cur).logits[:, -1].argmax(-1, keepdim=True)], 1)
+    assert torch.equal(out, cur)
+
+
 def test_uncovered_variants_fall_through():
     from ipex_llm_b200.transformers.remote_archs import REMOTE_ARCHS
     assert REMOTE_ARCHS["chatglm"]({"model_type": "chatglm", "position_encoding_2d": True}) is None      # ChatGLM-6B v1
