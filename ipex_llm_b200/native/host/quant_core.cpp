@@ -121,10 +121,19 @@ struct Tables {
   float fp6[32];      // e3m2 magnitudes, ascending
   float e4m3[127];    // e4m3 magnitudes 0..0x7e (0x7f is NaN in the OCP format)
   float e5m2[124];    // e5m2 magnitudes 0..0x7b (0x7c.. are inf/nan)
+  float e4m3_byte[256], e5m2_byte[256];   // signed value of every code byte (codes without a finite value: 0)
+  float fp6_signed[64];                   // signed value of every 6-bit code
   Tables() {
     for (int i = 0; i < 32; i++) fp6[i] = MiniFloat<3, 2, 3>::decode_mag(i);
     for (int i = 0; i < 127; i++) e4m3[i] = MiniFloat<4, 3, 7>::decode_mag(i);
     for (int i = 0; i < 124; i++) e5m2[i] = MiniFloat<5, 2, 15>::decode_mag(i);
+    for (int c = 0; c < 64; c++) fp6_signed[c] = (c & 32) ? -fp6[c & 31] : fp6[c & 31];
+    for (int b = 0; b < 256; b++) {
+      int c = b & 0x7f;
+      float m4 = c < 127 ? e4m3[c] : 0.0f, m5 = c < 124 ? e5m2[c] : 0.0f;
+      e4m3_byte[b] = (b & 0x80) ? -m4 : m4;
+      e5m2_byte[b] = (b & 0x80) ? -m5 : m5;
+    }
   }
 };
 const Tables& tables() { static Tables t; return t; }
@@ -349,13 +358,21 @@ void q_lut4(const float* x, uint8_t* y, const float* w, bool search, int64_t* hi
 
 inline float fp4_value(int c) { float m = kFP4[c & 7]; return (c & 8) ? -m : m; }
 
+// signed value of all 16 codes: the decoders index it instead of branching on the (random) sign bit
+struct Fp4Signed {
+  float v[16];
+  Fp4Signed() { for (int c = 0; c < 16; c++) v[c] = fp4_value(c); }
+};
+inline const float* fp4_signed() { static Fp4Signed t; return t.v; }
+
 template <bool NF>
 void dq_lut4(const uint8_t* y, float* x) {
   float d = get_f16(y);
+  const float* lut = NF ? kNF4 : fp4_signed();
   for (int j = 0; j < 32; j++) {
     int a = y[2 + j] & 0xF, b = y[2 + j] >> 4;
-    x[j] = (NF ? kNF4[a] : fp4_value(a)) * d;
-    x[j + 32] = (NF ? kNF4[b] : fp4_value(b)) * d;
+    x[j] = lut[a] * d;
+    x[j + 32] = lut[b] * d;
   }
 }
 
@@ -424,15 +441,11 @@ void q_fp6(const float* x, uint8_t* y, const float* w, bool search, int64_t*) {
 }
 
 void dq_fp6(const uint8_t* y, float* x) {
-  const float* mags = tables().fp6;
+  const float* val = tables().fp6_signed;
   float d = get_f16(y);
   for (int g = 0; g < 16; g++) {
     uint32_t pack = y[2 + 3 * g] | ((uint32_t)y[2 + 3 * g + 1] << 8) | ((uint32_t)y[2 + 3 * g + 2] << 16);
-    for (int k = 0; k < 4; k++) {
-      uint32_t c = (pack >> (6 * k)) & 63;
-      float m = mags[c & 31] * d;
-      x[4 * g + k] = (c & 32) ? -m : m;
-    }
+    for (int k = 0; k < 4; k++) x[4 * g + k] = val[(pack >> (6 * k)) & 63] * d;
   }
 }
 
@@ -470,14 +483,10 @@ void q_fp8(const float* x, uint8_t* y, const float* w, bool search, int64_t*) {
 
 template <bool E4M3>
 void dq_fp8(const uint8_t* y, float* x) {
-  const float* mags = E4M3 ? tables().e4m3 : tables().e5m2;
-  const int ncodes = E4M3 ? 127 : 124;
+  // one table look-up per byte: the sign of a weight is random, so a branch on it mispredicts half of the time
+  const float* val = E4M3 ? tables().e4m3_byte : tables().e5m2_byte;
   float d = get_f32(y);
-  for (int i = 0; i < 128; i++) {
-    int c = y[4 + i] & 0x7f;
-    float m = (c < ncodes ? mags[c] : 0.0f) * d;
-    x[i] = (y[4 + i] & 0x80) ? -m : m;
-  }
+  for (int i = 0; i < 128; i++) x[i] = val[y[4 + i]] * d;
 }
 
 // ---------------------------- k-quants (ggml super-block layouts) ------------------------------
