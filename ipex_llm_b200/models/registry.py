@@ -81,6 +81,21 @@ def _moe_block_forward(self, hidden_states):
     return out.reshape(bsz, seq, hid)
 
 
+def _deepseek_v3_route(self, router_logits):
+    """``DeepseekV3MoE.route_tokens_to_experts`` through the grouped top-k router (one kernel on the GPU; reference
+    models/deepseek.py:283-287 calls ``xe_addons.moe_group_topk`` at the same place)."""
+    from ..ops.moe import moe_group_topk
+    idx, w = moe_group_topk(router_logits, self.gate.e_score_correction_bias, self.n_group, self.topk_group,
+                            self.top_k, bool(self.norm_topk_prob), float(self.routed_scaling_factor))
+    return idx, w
+
+
+def _deepseek_v3_hook(model):
+    from ..transformers.convert import replace_func
+    replace_func(model, "DeepseekV3MoE", "route_tokens_to_experts", _deepseek_v3_route)
+    return model
+
+
 FAMILIES = {
     "llama": _llama_like("Llama", engine="llama"),
     "mistral": _llama_like("Mistral", engine="llama"),
@@ -119,7 +134,8 @@ FAMILIES = {
     "chatglm": Family(post=[("RMSNorm", C.rms_norm_forward)]),
     "minicpm": _llama_like("MiniCPM"),
     "aquila": Family(post=[("AquilaRMSNorm", C.rms_norm_forward)]),
-    "deepseek_v3": Family(post=[("DeepseekV3RMSNorm", C.rms_norm_forward), ("DeepseekV3MLP", C.mlp_silu_forward)]),
+    "deepseek_v3": Family(post=[("DeepseekV3RMSNorm", C.rms_norm_forward), ("DeepseekV3MLP", C.mlp_silu_forward)],
+                          post_hook=_deepseek_v3_hook),
     # multi-head latent attention keeps its own projections (q_a / q_b, kv_a / kv_b) and reaches the package's SDPA
     # through the attention interface; experts are converted as a fused bank, the router stays in full precision
     "deepseek_v2": Family(post=[("DeepseekV2RMSNorm", C.rms_norm_forward), ("DeepseekV2MLP", C.mlp_silu_forward)],

@@ -398,3 +398,31 @@ def test_phi3_longrope_generation_switches_factor_sets():
         for _ in range(10):
             cur = torch.cat([cur, low(cur).logits[:, -1].argmax(-1, keepdim=True)], 1)
     assert torch.equal(out, cur)
+
+
+def test_deepseek_v3_routing_goes_through_the_grouped_topk_router():
+    """The converted DeepSeek-V3 MoE block routes with ``ops.moe.moe_group_topk`` (reference models/deepseek.py:283-287)
+    and picks the same experts and weights as the transformers formulation, also with a non-zero correction bias."""
+    import copy
+    import transformers
+    from ipex_llm import optimize_model
+    kw = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4, vocab_size=1000,
+              max_position_embeddings=256)
+    kw.update(dict(_MLA, n_routed_experts=8, n_group=4, topk_group=2, num_experts_per_tok=3, norm_topk_prob=True,
+                   routed_scaling_factor=2.5))
+    cfg = transformers.DeepseekV3Config(**kw)
+    torch.manual_seed(0)
+    base = transformers.AutoModelForCausalLM.from_config(cfg).eval()
+    moe = [m for m in base.modules() if type(m).__name__ == "DeepseekV3MoE"][0]
+    moe.gate.e_score_correction_bias.copy_(torch.rand(8) * 0.2)
+    low = optimize_model(copy.deepcopy(base), low_bit="sym_int8")
+    low_moe = [m for m in low.modules() if type(m).__name__ == "DeepseekV3MoE"][0]
+    assert low_moe.route_tokens_to_experts.__func__.__name__ == "_deepseek_v3_route"
+    logits = torch.randn(11, 8)
+    i0, w0 = moe.route_tokens_to_experts(logits.clone())
+    i1, w1 = low_moe.route_tokens_to_experts(logits.clone())
+    assert torch.equal(i0.sort(-1).values, i1.sort(-1).values)
+    assert torch.allclose(w0.gather(1, i0.argsort(-1)), w1.gather(1, i1.argsort(-1)).to(w0.dtype), atol=1e-6)
+    ids = torch.randint(0, 1000, (2, 16))
+    with torch.no_grad():
+        assert _cos(low(ids).logits[:, -1], base(ids).logits[:, -1]) > 0.999
