@@ -31,9 +31,8 @@ from ..native import cuda_api as api
 from ..native.lib import cuda_lib, current_stream, ptr
 from ..ops import cuda_ops
 from ..ops.kv_cache import DynamicFp8Cache, DynamicNormalCache
-from ..ops.linear import BF16Linear, FP16Linear, LowBitLinear
+from ..ops.linear import LowBitLinear
 from ..quant import qtypes as qt
-from ..quant.params import device_nbytes
 
 
 class _W:

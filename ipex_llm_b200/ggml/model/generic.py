@@ -8,7 +8,6 @@ checkpoint directory, a ``save_low_bit`` directory (what ``llm_convert`` writes)
 """
 from __future__ import annotations
 
-import json
 import os
 import time
 import uuid

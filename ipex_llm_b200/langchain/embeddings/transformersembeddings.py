@@ -2,7 +2,7 @@
 (reference: python/llm/src/ipex_llm/langchain/embeddings/transformersembeddings.py:56-180)."""
 from __future__ import annotations
 
-from typing import Any, List, Optional
+from typing import List, Optional
 
 DEFAULT_MODEL_NAME = "gpt2"
 

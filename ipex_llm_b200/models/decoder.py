@@ -14,7 +14,6 @@ the package's SDPA.  ``decoder_model_forward`` wraps the HF ``*Model.forward`` t
 """
 from __future__ import annotations
 
-import functools
 import math
 
 import torch

@@ -5,7 +5,6 @@ Counterparts of ``CPUEmbedding``, ``DiskEmbedding`` and ``LowBitEmbedding`` of t
 """
 from __future__ import annotations
 
-import os
 
 import numpy as np
 import torch

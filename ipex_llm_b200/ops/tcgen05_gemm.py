@@ -14,7 +14,6 @@ import torch
 
 from ..native import cuda_api as api
 from ..native.lib import cuda_lib, current_stream, ptr
-from ..quant import qtypes as qt
 
 
 def _err(device):

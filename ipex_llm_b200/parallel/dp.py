@@ -14,7 +14,6 @@ reduce-scatter + AdamW + all-gather over NVLink (``native/cuda/lora_rs_adamw.cu`
 """
 from __future__ import annotations
 
-import math
 from typing import Iterable, List
 
 import torch

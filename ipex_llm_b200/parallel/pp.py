@@ -16,7 +16,7 @@ from __future__ import annotations
 import math
 import os
 import time
-from typing import List, Optional
+from typing import Optional
 
 import torch
 import torch.distributed as dist

@@ -12,7 +12,7 @@ import argparse
 import uuid
 
 from ..model_worker import ModelWorker as _BatchingWorker
-from .bigdl_llm_model import get_model_adapter, load_model
+from .bigdl_llm_model import load_model
 from .ipex_llm_worker import BigDLLLMWorker, create_app  # noqa: F401
 
 

@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import queue
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Optional
 
 import torch

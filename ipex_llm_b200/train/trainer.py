@@ -12,7 +12,7 @@ import json
 import math
 import os
 import time
-from typing import Callable, Dict, Iterable, List, Optional
+from typing import Callable, Dict, List, Optional
 
 import torch
 import torch.distributed as dist

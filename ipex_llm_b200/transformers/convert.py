@@ -14,7 +14,6 @@ Design differences from the reference:
 """
 from __future__ import annotations
 
-import copy
 import logging
 import os
 import types

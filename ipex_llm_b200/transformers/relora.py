@@ -19,7 +19,7 @@ import torch
 from ..ops.linear import LowBitLinear
 from ..quant.params import FP4Params
 from ..train.trainer import Trainer, TrainerCallback
-from .qlora import LoraBF16Linear, LoraLowBitLinear, _LoraBase
+from .qlora import _LoraBase
 
 
 def is_distributed() -> bool:

@@ -20,7 +20,7 @@ from typing import Optional
 
 import torch
 
-from ..ops.kv_cache import DynamicFp8Cache, DynamicNormalCache, is_ipex_cache
+from ..ops.kv_cache import DynamicFp8Cache, DynamicNormalCache
 from ..utils.common import invalidInputError
 
 

@@ -3,7 +3,6 @@ adapter save / load, trainer checkpoint + resume."""
 import copy
 import os
 
-import pytest
 import torch
 
 

@@ -5,7 +5,6 @@ checks that loading it reproduces the native model's logits, plain and quantized
 import json
 import math
 
-import pytest
 import torch
 
 
