@@ -77,7 +77,14 @@ inline uint16_t fp32_to_fp16(float f) {
   return (uint16_t)(sign | half);
 }
 
-inline void put_f16(uint8_t* p, float v) { uint16_t h = fp32_to_fp16(v); memcpy(p, &h, 2); }
+// Block scales and minima: a value beyond the fp16 range is stored as the largest finite fp16, so such a block clips
+// instead of decoding to inf / NaN.
+inline void put_f16(uint8_t* p, float v) {
+  if (v > 65504.0f) v = 65504.0f;
+  else if (v < -65504.0f) v = -65504.0f;
+  uint16_t h = fp32_to_fp16(v);
+  memcpy(p, &h, 2);
+}
 inline float get_f16(const uint8_t* p) { uint16_t h; memcpy(&h, p, 2); return fp16_to_fp32(h); }
 inline void put_f32(uint8_t* p, float v) { memcpy(p, &v, 4); }
 inline float get_f32(const uint8_t* p) { float v; memcpy(&v, p, 4); return v; }

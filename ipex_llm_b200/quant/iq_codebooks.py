@@ -35,6 +35,7 @@ QK = 256
 TYPE_SIZE = {qt.IQ2_XXS: 66, qt.IQ2_XS: 74, qt.IQ1_S: 50, qt.IQ1_M: 56}
 IQ_QTYPES = tuple(TYPE_SIZE)
 _DELTA = 0.125
+_F16_MAX = 65504.0          # block scales beyond the fp16 range saturate: the block clips instead of decoding to inf
 # candidate scales, as fractions of (largest magnitude of the scale group / largest grid magnitude)
 _IQ2_FRACTIONS = (0.7, 0.8, 0.9, 1.0, 1.1, 1.25)
 _IQ1_FRACTIONS = (0.4, 0.55, 0.7, 0.9)
@@ -208,7 +209,7 @@ def _quantize_chunk(x: torch.Tensor, w: torch.Tensor, qtype: int) -> torch.Tenso
         def assign(sc):
             return _pick(P, Q, sc)
         sc = _fit_scales(assign, amax, _IQ2_FRACTIONS, 43.0, per).view(nb, nsc)
-        d = (sc.amax(1, keepdim=True) * (8.0 / 31.0)).to(torch.float16)
+        d = (sc.amax(1, keepdim=True) * (8.0 / 31.0)).clamp_max(_F16_MAX).to(torch.float16)
         df = d.float()
         s = torch.where(df > 0, ((sc * 8.0 / df.clamp_min(1e-30) - 1.0) * 0.5).round(), torch.zeros_like(sc))
         s = s.clamp_(0, 15)
@@ -218,7 +219,7 @@ def _quantize_chunk(x: torch.Tensor, w: torch.Tensor, qtype: int) -> torch.Tenso
         coef = ((2.0 * s + 1.0) * 0.125).reshape(-1).repeat_interleave(per)
         num = (coef * Pm).view(nb, 32).sum(1, keepdim=True)
         den = (coef * coef * Qm).view(nb, 32).sum(1, keepdim=True)
-        d = torch.where(den > 0, num / den.clamp_min(1e-30), df).clamp_min(0.0).to(torch.float16)
+        d = torch.where(den > 0, num / den.clamp_min(1e-30), df).clamp(0.0, _F16_MAX).to(torch.float16)
         pw = (1 << torch.arange(7, device=dev)).to(torch.int64)
         sidx = (neg[:, :7].to(torch.int64) * pw).sum(1)                      # the eighth sign is the parity
         out = torch.empty((nb, TYPE_SIZE[qtype]), dtype=torch.uint8, device=dev)
@@ -270,7 +271,7 @@ def _quantize_chunk(x: torch.Tensor, w: torch.Tensor, qtype: int) -> torch.Tenso
         sc = torch.where(minus_sub, fits[1][0], fits[0][0]).view(nb, nsc)
     else:
         sc = _fit_scales(assign_free, amax, _IQ1_FRACTIONS, 1.0, per).view(nb, nsc)
-    d = (sc.amax(1, keepdim=True) / 15.0).to(torch.float16)
+    d = (sc.amax(1, keepdim=True) / 15.0).clamp_max(_F16_MAX).to(torch.float16)
     df = d.float()
     s = torch.where(df > 0, ((sc / df.clamp_min(1e-30) - 1.0) * 0.5).round(), torch.zeros_like(sc)).clamp_(0, 7)
     dl = (df * (2.0 * s + 1.0)).reshape(-1).repeat_interleave(per).unsqueeze(1).clamp_min(1e-30)
@@ -284,7 +285,7 @@ def _quantize_chunk(x: torch.Tensor, w: torch.Tensor, qtype: int) -> torch.Tenso
     coef = (2.0 * s + 1.0).reshape(-1).repeat_interleave(per)
     num = (coef * Pm).view(nb, 32).sum(1, keepdim=True)
     den = (coef * coef * Qm).view(nb, 32).sum(1, keepdim=True)
-    d = torch.where(den > 0, num / den.clamp_min(1e-30), df).clamp_min(0.0).to(torch.float16)
+    d = torch.where(den > 0, num / den.clamp_min(1e-30), df).clamp(0.0, _F16_MAX).to(torch.float16)
     out = torch.empty((nb, TYPE_SIZE[qtype]), dtype=torch.uint8, device=dev)
     s = s.to(torch.int64)
     hi = idx >> 8

@@ -219,3 +219,37 @@ def test_codebook_linear_on_cpu():
     assert torch.nn.functional.cosine_similarity(low(x).flatten(), lin(x).flatten(), dim=0) > 0.93
     sd = low.state_dict()
     assert sd["weight"].dtype == torch.uint8 and sd["weight"].numel() == 48 * 74
+
+
+ALL_BLOCK_FORMATS = ["sym_int4", "asym_int4", "sym_int5", "asym_int5", "sym_int8", "nf4", "nf3", "fp4", "fp6", "fp8_e4m3",
+                     "fp8_e5m2", "q2_k", "q4_k", "q5_k", "q6_k", "gguf_iq2_xxs", "gguf_iq2_xs", "gguf_iq1_s",
+                     "gguf_iq1_m"]
+
+
+@pytest.mark.parametrize("name", ALL_BLOCK_FORMATS)
+def test_quantizers_survive_degenerate_and_extreme_blocks(name):
+    """All-zero, constant, one-hot, denormal, beyond-fp16 and wildly mixed-magnitude rows: every format decodes to
+    finite values, zeros stay zeros, and no element is off by more than the largest magnitude of the input (a scale
+    beyond the fp16 range saturates, so such a block clips instead of decoding to inf)."""
+    if name.startswith("gguf_iq"):
+        pytest.importorskip("gguf.quants")
+    q = qt.qtype_from_name(name)
+    k = 512
+    g = torch.Generator().manual_seed(7)
+    rnd = torch.randn(2, k, generator=g)
+    cases = {
+        "zeros": torch.zeros(2, k), "const": torch.full((2, k), 3.0), "negconst": torch.full((2, k), -7.5),
+        "one_hot": torch.nn.functional.one_hot(torch.tensor([5, 300]), k).float(),
+        "tiny": rnd * 1e-30, "denormal": rnd * 1e-42, "beyond_fp16": rnd * 6e4, "huge": rnd * 1e30,
+        "mixed": rnd * torch.exp(torch.rand(2, k, generator=g) * 40 - 20),
+        "outlier": torch.cat([rnd[:, :-1], torch.full((2, 1), 1e4)], 1),
+    }
+    for cname, x in cases.items():
+        p = ggml_convert_qtype(x.contiguous(), q)
+        y = ggml_convert_fp32(p.view(torch.uint8) if p.dtype != torch.uint8 else p, x.shape, x.numel(), q)
+        assert torch.isfinite(y).all(), cname
+        amax = x.abs().max().item()
+        if amax == 0:
+            assert y.abs().max().item() == 0, cname
+        else:
+            assert (y - x).abs().max().item() <= 1.01 * amax, cname
