@@ -252,4 +252,4 @@ def test_quantizers_survive_degenerate_and_extreme_blocks(name):
         if amax == 0:
             assert y.abs().max().item() == 0, cname
         else:
-            assert (y - x).abs().max().item() <= 1.01 * amax, cname
+            assert (y - x).abs().max().item() <= 1.01 * amax + 1e-38, cname      # (denormal scales lose bits)
