@@ -24,9 +24,13 @@ namespace {
 constexpr uint32_t kMagic = 0x46554747u;  // "GGUF"
 enum GgmlType : uint32_t { T_F32 = 0, T_F16 = 1, T_Q2_K = 10, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_BF16 = 30 };
 
+// Every count and length of the file is checked against the bytes that are left, so a truncated or corrupt file ends
+// in an error message instead of a huge allocation or a loop over billions of absent entries.
 struct Reader {
   FILE* f;
+  uint64_t size = 0;
   bool ok = true;
+  uint64_t left() const { long p = ftell(f); return p < 0 || (uint64_t)p > size ? 0 : size - (uint64_t)p; }
   template <typename T> T get() {
     T v{};
     if (fread(&v, sizeof(T), 1, f) != 1) ok = false;
@@ -35,12 +39,12 @@ struct Reader {
   std::string str() {
     uint64_t n = get<uint64_t>();
     std::string s;
-    if (!ok || n > (1u << 28)) { ok = false; return s; }
+    if (!ok || n > left()) { ok = false; return s; }
     s.resize(n);
     if (n && fread(&s[0], 1, n, f) != n) ok = false;
     return s;
   }
-  void skip(uint64_t n) { if (fseek(f, (long)n, SEEK_CUR) != 0) ok = false; }
+  void skip(uint64_t n) { if (n > left() || fseek(f, (long)n, SEEK_CUR) != 0) ok = false; }
 };
 
 // bytes of one scalar GGUF metadata value type (0 for string / array)
@@ -60,9 +64,13 @@ bool skip_value(Reader& r, uint32_t t, uint32_t* u32_out) {
     uint32_t et = r.get<uint32_t>();
     uint64_t n = r.get<uint64_t>();
     if (!r.ok) return false;
-    if (et == 8) { for (uint64_t i = 0; i < n && r.ok; i++) r.str(); return r.ok; }
+    if (et == 8) {
+      if (n > r.left() / 8) return false;                  // every string carries an 8-byte length
+      for (uint64_t i = 0; i < n && r.ok; i++) r.str();
+      return r.ok;
+    }
     size_t sz = scalar_size(et);
-    if (!sz) return false;
+    if (!sz || n > r.left() / sz) return false;
     r.skip(n * sz);
     return r.ok;
   }
@@ -158,10 +166,15 @@ int main(int argc, char** argv) {
   FILE* in = fopen(argv[1], "rb");
   if (!in) return fail("cannot open the input file");
   Reader r{in};
+  fseek(in, 0, SEEK_END);
+  r.size = (uint64_t)ftell(in);
+  fseek(in, 0, SEEK_SET);
   if (r.get<uint32_t>() != kMagic) return fail("not a GGUF file");
   uint32_t version = r.get<uint32_t>();
   if (version != 2 && version != 3) return fail("unsupported GGUF version");
   uint64_t n_tensors = r.get<uint64_t>(), n_kv = r.get<uint64_t>();
+  // a metadata entry takes at least 13 bytes (key length, type, one byte), a tensor entry at least 24
+  if (!r.ok || n_kv > r.left() / 13 || n_tensors > r.left() / 24) return fail("malformed header");
   long kv_begin = ftell(in);
   uint32_t alignment = 32;
   for (uint64_t i = 0; i < n_kv; i++) {
@@ -184,10 +197,18 @@ int main(int argc, char** argv) {
     int qk, ts;
     if (!r.ok || !type_geometry(ti.type, &qk, &ts)) return fail("tensor of an unknown ggml type");
     uint64_t n = 1;
-    for (auto d : ti.dims) n *= d;
+    for (auto d : ti.dims) {
+      // no format stores less than one bit per element: more elements than bits in the file cannot be real
+      if (d == 0 || n > r.size * 8 / d) return fail("tensor larger than the file");  // (also guards the product)
+      n *= d;
+    }
     ti.nbytes = n / qk * ts;
   }
+  if (alignment == 0 || alignment > (1u << 20)) return fail("implausible general.alignment");
   uint64_t data_start = align_up((uint64_t)ftell(in), alignment);
+  for (auto& ti : infos)
+    if (ti.offset > r.size || ti.nbytes > r.size || data_start + ti.offset + ti.nbytes > r.size)
+      return fail("tensor data reaches beyond the end of the file");
 
   // decide the output type of every tensor and lay the output data section out
   uint64_t off = 0;

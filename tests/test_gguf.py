@@ -97,6 +97,24 @@ def test_native_quantize_executable_rewrites_a_gguf_file(tmp_path):
     assert quantize(src, dst2, "llama", "q6_k") == dst2 and os.path.getsize(dst2) > os.path.getsize(dst)
     with pytest.raises(RuntimeError):
         quantize_gguf(str(tmp_path / "out.gguf"), str(tmp_path / "x.gguf"), "q9_k")
+    # truncated and corrupt files end in an error message: no crash, no giant allocation, no endless loop
+    import random
+    import subprocess
+    from ipex_llm_b200.native.build import build_tools
+    data = open(src, "rb").read()
+    rnd = random.Random(0)
+    blobs = [data[:n] for n in (0, 3, 8, 24, 60, 150, len(data) // 2, len(data) - 10)]
+    for _ in range(40):
+        b = bytearray(data)
+        for _ in range(rnd.randint(1, 4)):
+            b[rnd.randrange(0, 300)] = rnd.randrange(256)
+        blobs.append(bytes(b))
+    bad = str(tmp_path / "bad.gguf")
+    for blob in blobs:
+        with open(bad, "wb") as f:
+            f.write(blob)
+        r = subprocess.run([build_tools(), bad, str(tmp_path / "o.gguf"), "q4_k"], capture_output=True, timeout=60)
+        assert r.returncode in (0, 1), (r.returncode, r.stderr[-200:])
 
 
 def test_load_gguf_llama(tmp_path):
