@@ -243,6 +243,55 @@ def test_kv_caches():
     assert k_ret.shape[2] == 2000 and s.get_seq_length() == 1024 and s.real_kv_len == 2000
 
 
+def test_kv_caches_random_walk():
+    """Random sequences of appends (prompt-sized and single-token, several layers) and crops on the normal, e5m2 and
+    4-bit caches against a list-concatenation model: shapes, sequence length, old rows bit-stable, new rows within the
+    format's step."""
+    import random
+    from ipex_llm_b200.ops.kv_cache import (DynamicFp8Cache, DynamicInt4Cache, DynamicNormalCache, fp8_e5m2_dequantize,
+                                            fp8_e5m2_quantize, int4_kv_dequantize, int4_kv_quantize)
+    rnd = random.Random(0)
+    torch.manual_seed(0)
+
+    def roundtrip(kind, x):
+        if kind == "fp8":
+            return fp8_e5m2_dequantize(fp8_e5m2_quantize(x), torch.float32)
+        if kind == "int4":
+            return int4_kv_dequantize(int4_kv_quantize(x), torch.float32)
+        return x
+
+    for trial in range(60):
+        kind = rnd.choice(["normal", "fp8", "int4"])
+        cache = {"normal": DynamicNormalCache, "fp8": DynamicFp8Cache, "int4": DynamicInt4Cache}[kind]()
+        L, B, H, D = rnd.randint(1, 3), rnd.randint(1, 2), rnd.randint(1, 3), rnd.choice([16, 64])
+        ref = [None] * L
+        n = 0
+        for step in range(rnd.randint(1, 10)):
+            if rnd.random() < 0.75 or n == 0:
+                s = rnd.choice([1, 1, 1, 2, 5, 17, 300]) if n else rnd.choice([1, 7, 33, 257, 600])
+                for l in range(L):
+                    k, v = torch.randn(B, H, s, D), torch.randn(B, H, s, D)
+                    kk, vv = cache.update(k, v, l)
+                    rk, rv = roundtrip(kind, k), roundtrip(kind, v)
+                    ref[l] = (rk, rv) if ref[l] is None else (torch.cat([ref[l][0], rk], 2), torch.cat([ref[l][1], rv], 2))
+                    if kind == "fp8":
+                        kk, vv = fp8_e5m2_dequantize(kk, torch.float32), fp8_e5m2_dequantize(vv, torch.float32)
+                    kk, vv = kk.float(), vv.float()
+                    assert kk.shape == ref[l][0].shape, (kind, trial, step)
+                    old = ref[l][0].shape[2] - s
+                    if old:                  # (a prompt pass may hand back its own unquantized rows; old rows never change)
+                        assert torch.allclose(kk[:, :, :old], ref[l][0][:, :, :old], atol=1e-6), (kind, trial, step)
+                        assert torch.allclose(vv[:, :, :old], ref[l][1][:, :, :old], atol=1e-6), (kind, trial, step)
+                    tol = {"normal": 1e-6, "fp8": 0.6, "int4": 1.0}[kind]
+                    assert (kk[:, :, old:] - ref[l][0][:, :, old:]).abs().max() <= tol, (kind, trial, step)
+                n += s
+            else:
+                n = rnd.randint(0, n)
+                cache.crop(n)
+                ref = [None if r is None or n == 0 else (r[0][:, :, :n], r[1][:, :, :n]) for r in ref]
+            assert cache.get_seq_length() == n, (kind, trial, step)
+
+
 def test_int4_kv_cache(tiny_llama_dir, monkeypatch):
     """IPEX_LLM_QUANTIZE_KV_CACHE=int4: codes + per-row scale round-trip within the 4-bit step, the cache keeps
     D/2 + 2 bytes per row, and generation through it stays close to the fp16 cache."""
