@@ -587,7 +587,15 @@ def left_pad_mask_bounds(mask: torch.Tensor, S: int, window: int = 0):
     if hit is not None and hit[0]() is mask:
         return hit[1]
     vis = mask[:, 0, :, :S]
-    vis = vis if vis.dtype == torch.bool else vis > torch.finfo(vis.dtype).min / 2
+    if vis.dtype == torch.bool:
+        other = None
+    else:
+        # an additive mask is 0 where a key may be seen and a large negative number where not (-inf, the dtype's
+        # minimum, the minimum of another dtype after a cast, the -10000 of older models); any other value is a bias
+        # that the kernel cannot express
+        add = vis
+        vis = add == 0
+        other = ~(vis | (add <= -1e4))
     # keys that some query sees; rows that see everything are left out (mask builders "unmask" the rows of padding
     # queries completely), and a batch row without any other kind of row has no padding
     partial = vis & ~vis.all(dim=-1, keepdim=True)
@@ -603,7 +611,10 @@ def left_pad_mask_bounds(mask: torch.Tensor, S: int, window: int = 0):
             exp = exp & (ki <= qi)
         if window:
             exp = exp & (ki > qi - window)
-        if bool(((vis == exp) | ~real_q).all()):
+        agree = (vis == exp) | ~real_q
+        if other is not None:
+            agree = agree & ~other
+        if bool(agree.all()):
             result = (lo.to(torch.int32).contiguous(), causal)
             break
     if len(_mask_shape_cache) > 8:
@@ -641,6 +652,9 @@ def sdpa_prefill(q, k, v, mask, scale, softcap, sliding_window, causal=True):
         S = q.shape[2]
         window = int(sliding_window) if sliding_window and sliding_window < S else 0
         bounds = left_pad_mask_bounds(mask, S, window) if mask is not None else (None, causal)
+        if bounds is not None and bounds[0] is not None and bounds[0].shape[0] != q.shape[0]:
+            # a mask shared by the whole batch ([1, 1, S, S]): the kernel reads one bound per batch row
+            bounds = (bounds[0].expand(q.shape[0]).contiguous(), bounds[1]) if bounds[0].shape[0] == 1 else None
         if bounds is not None:
             lo, is_causal = bounds
             return attn_prefill_tcgen05(q, k, v, scale, is_causal, softcap or 0.0, window, lo)

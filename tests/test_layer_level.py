@@ -97,3 +97,33 @@ def test_left_padding_masks_are_recognised():
     holed = (ki <= qi).expand(1, S, S).clone()
     holed[0, 30, 10] = False
     assert left_pad_mask_bounds(holed.unsqueeze(1), S) is None
+
+
+def test_mask_recognition_is_exact_for_every_fill_value_and_rejects_biases():
+    """An additive mask may mark hidden keys with -inf, its dtype's minimum, another dtype's minimum or the -10000 of
+    older models: all are recognised with the same bounds.  Masks that carry a bias (ALiBi) and masks that differ from
+    a left-padding mask in one element are refused, so they take the generic path instead of the wrong kernel mode."""
+    import random
+    from ipex_llm_b200.ops.cuda_ops import left_pad_mask_bounds
+    S = 24
+    qi, ki = torch.arange(S).view(1, S, 1), torch.arange(S).view(1, 1, S)
+    lo = torch.tensor([0, 9])
+    ok = ((ki >= lo.view(-1, 1, 1)) & (ki <= qi))
+    for fill in (float("-inf"), torch.finfo(torch.float32).min, float(torch.finfo(torch.float16).min), -10000.0):
+        mask = torch.zeros(2, 1, S, S).masked_fill(~ok.unsqueeze(1), fill)
+        found = left_pad_mask_bounds(mask, S)
+        assert found is not None and found[0].tolist() == [0, 9] and found[1] is True, fill
+    alibi = torch.zeros(2, 1, S, S).masked_fill(~ok.unsqueeze(1), float("-inf")) - 0.01 * (qi - ki).clamp_min(0).float()
+    assert left_pad_mask_bounds(alibi, S) is None
+    rnd = random.Random(0)
+    for _ in range(200):                               # one flipped element: refused, or the flip sits in a padding row
+        b, r, c = rnd.randrange(2), rnd.randrange(S), rnd.randrange(S)
+        m = ok.clone()
+        m[b, r, c] = ~m[b, r, c]
+        found = left_pad_mask_bounds(m.unsqueeze(1), S)
+        if found is not None:
+            got = (ki >= found[0].view(-1, 1, 1).long())
+            if found[1]:
+                got = got & (ki <= qi)
+            real = qi >= found[0].view(-1, 1, 1).long()
+            assert bool(((got == m) | ~real).all()), (b, r, c)
