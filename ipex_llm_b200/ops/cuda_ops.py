@@ -459,9 +459,16 @@ def sdpa_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask, scale: 
                 causal: bool = True) -> torch.Tensor:
     """Module-path decode attention: the cache views ``k``/``v`` ``[B,Hkv,Skv,D]`` (activation dtype or e5m2
     bytes) already hold every token; ``q [B,Hq,Sq<=32,D]`` is already rotated."""
-    if mask is not None and (mask.dtype == torch.bool and not bool(mask.all()) or
-                             mask.dtype != torch.bool and bool((mask != 0).any()) and
-                             not _is_causal_mask(mask, q.shape[2], k.shape[2])):
+    generic = False
+    if mask is not None:
+        if mask.dtype == torch.bool:
+            generic = not bool(mask.all())
+        elif bool((mask != 0).any()):
+            if _is_causal_mask(mask, q.shape[2], k.shape[2]):
+                causal = True            # the mask spells out the causal pattern: the kernel applies it itself
+            else:
+                generic = True
+    if generic:
         # arbitrary masks (padding) take the generic path
         from .kv_cache import fp8_e5m2_dequantize
         from ..models.common import repeat_kv
