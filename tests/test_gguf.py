@@ -237,3 +237,45 @@ def test_load_gguf_layernorm_families(tmp_path, arch):
     assert cos > 0.995, (arch, cos)
     out = model.generate(ids, max_new_tokens=3, do_sample=False)
     assert out.shape == (2, 13)
+
+
+def test_interoperates_with_the_official_gguf_package(tmp_path):
+    """Against the ``gguf`` Python package (the format's own reader / writer): k-quant bytes packed by the quant core
+    decode identically through its decoder, and a file its writer produced (metadata incl. non-ASCII strings and
+    arrays; f32, f16, bf16, q8_0, q4_0, q4_1, q5_0, q5_1 tensors) reads back exactly through this package's reader."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants as gq
+    from gguf.constants import GGMLQuantizationType as T
+    from ipex_llm_b200.quant import qtypes as qt
+    from ipex_llm_b200.quant.params import ggml_convert_fp32, ggml_convert_qtype
+    from ipex_llm_b200.transformers.gguf.gguf import GGUFFileLoader
+    torch.manual_seed(0)
+    w = torch.randn(16, 512)
+    for name, t in (("q2_k", T.Q2_K), ("q4_k", T.Q4_K), ("q5_k", T.Q5_K), ("q6_k", T.Q6_K)):
+        q = qt.qtype_from_name(name)
+        p = ggml_convert_qtype(w, q)
+        ours = ggml_convert_fp32(p, w.shape, w.numel(), q)
+        theirs = torch.from_numpy(gq.dequantize(p.numpy().reshape(16, -1), t))
+        assert torch.equal(ours, theirs), name
+    path = str(tmp_path / "official.gguf")
+    wr = gguf.GGUFWriter(path, "llama")
+    wr.add_block_count(1)
+    wr.add_string("custom.note", "héllo")
+    wr.add_array("custom.list", [1, 2, 3])
+    expect = {}
+    for name, t in (("f32", T.F32), ("f16", T.F16), ("bf16", T.BF16), ("q8_0", T.Q8_0), ("q4_0", T.Q4_0),
+                    ("q4_1", T.Q4_1), ("q5_0", T.Q5_0), ("q5_1", T.Q5_1)):
+        data = gq.quantize(w.numpy(), t)
+        wr.add_tensor(f"t.{name}", data, raw_shape=None if t in (T.F32, T.F16) else data.shape, raw_dtype=t)
+        expect[f"t.{name}"] = gq.dequantize(data, t)
+    wr.write_header_to_file()
+    wr.write_kv_data_to_file()
+    wr.write_tensors_to_file()
+    wr.close()
+    loader = GGUFFileLoader(path)
+    assert loader.config["custom.note"] == "héllo" and loader.config["custom.list"] == [1, 2, 3]
+    assert loader.config["llama.block_count"] == 1
+    got = loader.tensors()
+    for k, e in expect.items():
+        assert tuple(got[k].shape) == (16, 512) and np.array_equal(got[k].numpy(), e), k
+    loader.close()
