@@ -497,6 +497,46 @@ void dq_fp8(const uint8_t* y, float* x) {
 }
 
 // ---------------------------- k-quants (ggml super-block layouts) ------------------------------
+// Scale and minimum of one k-quant sub-block: codes 0..nmax, value = scale * code + min with min <= 0 (the formats
+// store -min as an unsigned multiple of dmin).  Starts from the min / max fit, then tries code grids that are a little
+// finer than the range (the largest values clip, the bulk gets smaller steps): for every assignment the scale and
+// the minimum are re-fitted by weighted least squares and the pair with the smallest weighted error is kept.
+// `w` are importance weights of the elements (NULL = all equal).  Returns the scale, *neg_min = -min.
+float fit_scale_min(int n, int nmax, const float* x, const float* w, float* neg_min) {
+  float mn = x[0], mx = x[0];
+  for (int i = 1; i < n; i++) { mn = std::min(mn, x[i]); mx = std::max(mx, x[i]); }
+  if (mn > 0) mn = 0;
+  if (!(mx > mn)) { *neg_min = -mn; return 0.f; }
+  float best_s = (mx - mn) / (float)nmax, best_m = mn;
+  double best_err = 0;
+  for (int i = 0; i < n; i++) {
+    int l = std::min(nmax, std::max(0, (int)std::nearbyint((x[i] - best_m) / best_s)));
+    double e = (double)best_s * l + best_m - x[i];
+    best_err += wsel(w, i) * e * e;
+  }
+  int L[64];
+  for (int step = 1; step <= 10; step++) {
+    float iscale = ((float)nmax + 0.15f * (float)step) / (mx - mn);
+    double sw = 0, sl = 0, sl2 = 0, sx = 0, sxl = 0;
+    for (int i = 0; i < n; i++) {
+      int l = std::min(nmax, std::max(0, (int)std::nearbyint(iscale * (x[i] - mn))));
+      L[i] = l;
+      double wi = wsel(w, i);
+      sw += wi; sl += wi * l; sl2 += wi * l * l; sx += wi * x[i]; sxl += wi * x[i] * l;
+    }
+    double det = sw * sl2 - sl * sl;
+    if (det <= 0) continue;
+    double sc = (sw * sxl - sx * sl) / det, m = (sl2 * sx - sl * sxl) / det;
+    if (m > 0) { m = 0; sc = sl2 > 0 ? sxl / sl2 : 0; }
+    if (sc <= 0) continue;
+    double err = 0;
+    for (int i = 0; i < n; i++) { double e = sc * L[i] + m - x[i]; err += wsel(w, i) * e * e; }
+    if (err < best_err) { best_err = err; best_s = (float)sc; best_m = (float)m; }
+  }
+  *neg_min = -best_m;
+  return best_s;
+}
+
 // q4_k: [fp16 d][fp16 dmin][12 B scales/mins 6-bit][128 B qs]
 inline void get_scale_min_k4(int j, const uint8_t* q, uint8_t* d, uint8_t* m) {
   if (j < 4) { *d = q[j] & 63; *m = q[j + 4] & 63; }
@@ -530,15 +570,10 @@ void dq_q4_k(const uint8_t* y, float* x) {
 }
 
 void q_q4_k(const float* x, uint8_t* y, const float* w, bool, int64_t*) {
-  (void)w;
   float scales[8], mins[8];
   float max_scale = 0, max_min = 0;
   for (int j = 0; j < 8; j++) {
-    float mn = x[32 * j], mx = x[32 * j];
-    for (int l = 1; l < 32; l++) { mn = std::min(mn, x[32 * j + l]); mx = std::max(mx, x[32 * j + l]); }
-    if (mn > 0) mn = 0;
-    scales[j] = (mx - mn) / 15.0f;
-    mins[j] = -mn;
+    scales[j] = fit_scale_min(32, 15, x + 32 * j, w ? w + 32 * j : nullptr, &mins[j]);
     max_scale = std::max(max_scale, scales[j]);
     max_min = std::max(max_min, mins[j]);
   }
@@ -590,15 +625,11 @@ void dq_q5_k(const uint8_t* y, float* x) {
   }
 }
 
-void q_q5_k(const float* x, uint8_t* y, const float*, bool, int64_t*) {
+void q_q5_k(const float* x, uint8_t* y, const float* w, bool, int64_t*) {
   float scales[8], mins[8];
   float max_scale = 0, max_min = 0;
   for (int j = 0; j < 8; j++) {
-    float mn = x[32 * j], mx = x[32 * j];
-    for (int l = 1; l < 32; l++) { mn = std::min(mn, x[32 * j + l]); mx = std::max(mx, x[32 * j + l]); }
-    if (mn > 0) mn = 0;
-    scales[j] = (mx - mn) / 31.0f;
-    mins[j] = -mn;
+    scales[j] = fit_scale_min(32, 31, x + 32 * j, w ? w + 32 * j : nullptr, &mins[j]);
     max_scale = std::max(max_scale, scales[j]);
     max_min = std::max(max_min, mins[j]);
   }
@@ -717,15 +748,11 @@ void dq_q2_k(const uint8_t* y, float* x) {
   }
 }
 
-void q_q2_k(const float* x, uint8_t* y, const float*, bool, int64_t*) {
+void q_q2_k(const float* x, uint8_t* y, const float* w, bool, int64_t*) {
   float scales[16], mins[16];
   float max_scale = 0, max_min = 0;
   for (int j = 0; j < 16; j++) {
-    float mn = x[16 * j], mx = x[16 * j];
-    for (int l = 1; l < 16; l++) { mn = std::min(mn, x[16 * j + l]); mx = std::max(mx, x[16 * j + l]); }
-    if (mn > 0) mn = 0;
-    scales[j] = (mx - mn) / 3.0f;
-    mins[j] = -mn;
+    scales[j] = fit_scale_min(16, 3, x + 16 * j, w ? w + 16 * j : nullptr, &mins[j]);
     max_scale = std::max(max_scale, scales[j]);
     max_min = std::max(max_min, mins[j]);
   }
