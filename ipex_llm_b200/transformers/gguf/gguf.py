@@ -32,6 +32,22 @@ GGML_TYPES = {
 _NAME_TO_TYPE = {v[0]: k for k, v in GGML_TYPES.items()}
 
 
+def _library_types():
+    """Tensor types this module has no decoder of its own for (iq3_xxs, iq3_s, iq2_s, iq4_nl, iq4_xs, tq1_0, tq2_0,
+    mxfp4, ...): geometry and decoder of the ``gguf`` package when it is installed."""
+    try:
+        import gguf
+        return {int(t): (t.name.lower(), qk, bs) for t, (qk, bs) in gguf.GGML_QUANT_SIZES.items()
+                if int(t) not in GGML_TYPES}
+    except Exception:  # noqa: BLE001
+        return {}
+
+
+def type_geometry(ttype: int):
+    """``(name, values per block, bytes per block)`` of a ggml tensor type, or None when nothing here can read it."""
+    return GGML_TYPES.get(ttype) or _library_types().get(ttype)
+
+
 class _Cursor:
     def __init__(self, buf):
         self.buf, self.pos = buf, 0
@@ -72,6 +88,11 @@ def _f16(buf: np.ndarray) -> np.ndarray:
 
 def dequantize_blocks(raw: np.ndarray, ttype: int, n_values: int) -> np.ndarray:
     """Raw bytes of a ggml tensor -> float32 vector of ``n_values``."""
+    if ttype not in GGML_TYPES:
+        import gguf
+        from gguf import quants as gq
+        name, qk, bs = _library_types()[ttype]
+        return gq.dequantize(raw.reshape(n_values // qk, bs), gguf.GGMLQuantizationType(ttype)).reshape(-1)
     name, qk, bs = GGML_TYPES[ttype]
     if name == "f32":
         return raw.view(np.float32).copy()
@@ -107,6 +128,8 @@ def dequantize_blocks(raw: np.ndarray, ttype: int, n_values: int) -> np.ndarray:
             return ((q - 16.0) * d).reshape(-1)
         m = _f16(blk[:, 2:4].copy()).reshape(nb, 1)
         return (q * d + m).reshape(-1)
+    if name == "q3_k":
+        return _dequantize_q3_k(blk)
     # k-quants: the host library's decoders use the ggml super-block layouts; the code-book formats go through
     # quant/iq_codebooks.py, whose byte layout is the GGUF one
     from ...quant import qtypes as qt
@@ -116,6 +139,25 @@ def dequantize_blocks(raw: np.ndarray, ttype: int, n_values: int) -> np.ndarray:
     invalidInputError(kq is not None, f"GGUF tensor type {name} is not supported")
     t = torch.from_numpy(raw.copy())
     return ggml_convert_fp32(t, (1, n_values), n_values, qt.qtype_from_name(kq)).reshape(-1).numpy()
+
+
+def _dequantize_q3_k(blk: np.ndarray) -> np.ndarray:
+    """q3_k super-blocks (110 bytes: 32 B high bits, 64 B low 2-bit codes, 12 B packed 6-bit scales, fp16 d).  A value
+    is ``d * (scale - 32) * (low2 - (0 if its high bit is set else 4))``; 16 scales, one per 16 values."""
+    nb = blk.shape[0]
+    hmask, qs, sc = blk[:, :32], blk[:, 32:96], blk[:, 96:108]
+    d = _f16(blk[:, 108:110].copy()).reshape(nb, 1, 1)
+    # 16 six-bit scales: low nibbles in bytes 0..7, the upper two bits of scale j in bytes 8..11
+    low = np.concatenate([sc[:, :8] & 0x0F, sc[:, :8] >> 4], axis=1)                        # [nb, 16]
+    hi = np.stack([(sc[:, 8:12] >> s) & 3 for s in (0, 2, 4, 6)], axis=1).reshape(nb, 16)   # [nb, 16]
+    scales = (low | (hi << 4)).astype(np.int8).astype(np.float32) - 32.0
+    # values: two halves of 128; inside a half four 2-bit planes of the same 32 bytes, each plane 32 values
+    q = qs.reshape(nb, 2, 1, 32) >> np.array([0, 2, 4, 6], dtype=np.uint8).reshape(1, 1, 4, 1) & 3  # [nb, 2, 4, 32]
+    bit = np.arange(8, dtype=np.uint8).reshape(1, 2, 4, 1)                                    # plane p of half n: bit 4n+p
+    h = (hmask.reshape(nb, 1, 1, 32) >> bit) & 1
+    vals = q.astype(np.float32) - np.where(h == 1, 0.0, 4.0).astype(np.float32)              # [nb, 2, 4, 32]
+    vals = vals.reshape(nb, 16, 16) * scales.reshape(nb, 16, 1) * d
+    return vals.reshape(-1)
 
 
 class GGUFTensorLoader:
@@ -132,9 +174,10 @@ class GGUFTensorLoader:
         if isinstance(index_or_name, str):
             index_or_name = self.names().index(index_or_name)
         name, dims, ttype, off = self.infos[index_or_name]
-        invalidInputError(ttype in GGML_TYPES, f"tensor {name}: unsupported ggml type {ttype}")
+        geom = type_geometry(ttype)
+        invalidInputError(geom is not None, f"tensor {name}: unsupported ggml type {ttype}")
         n = int(np.prod(dims))
-        _, qk, bs = GGML_TYPES[ttype]
+        _, qk, bs = geom
         nbytes = n // qk * bs
         raw = np.frombuffer(self.buf, dtype=np.uint8, count=nbytes, offset=self.base + off)
         vals = dequantize_blocks(raw, ttype, n)

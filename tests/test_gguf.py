@@ -279,3 +279,24 @@ def test_interoperates_with_the_official_gguf_package(tmp_path):
     for k, e in expect.items():
         assert tuple(got[k].shape) == (16, 512) and np.array_equal(got[k].numpy(), e), k
     loader.close()
+
+
+def test_q3_k_decoder_and_library_types_match_the_official_decoder():
+    """q3_k super-blocks are decoded by this module's own numpy code, the rarer types (iq3 / iq4 / iq2_s / ternary) by
+    the ``gguf`` package when it is installed: both against that package on random blocks."""
+    pytest.importorskip("gguf")
+    from gguf import quants as gq
+    from gguf.constants import GGMLQuantizationType as T
+    from ipex_llm_b200.transformers.gguf.gguf import GGML_TYPES, dequantize_blocks, type_geometry
+    assert 11 in GGML_TYPES and type_geometry(int(T.IQ4_XS)) == ("iq4_xs", 256, 136)
+    rng = np.random.default_rng(0)
+    for t, bs, qk, tail in ((T.Q3_K, 110, 256, True), (T.IQ4_NL, 18, 32, False), (T.IQ4_XS, 136, 256, False),
+                            (T.IQ3_XXS, 98, 256, False), (T.TQ2_0, 66, 256, True)):
+        raw = rng.integers(0, 256, size=(9, bs), dtype=np.uint8)
+        d = np.array([0.0123], dtype=np.float16).view(np.uint8)
+        if tail:
+            raw[:, -2:] = d
+        else:
+            raw[:, :2] = d
+        ours = dequantize_blocks(raw.reshape(-1), int(t), 9 * qk)
+        assert np.array_equal(ours, gq.dequantize(raw, t).reshape(-1)), t.name
