@@ -2,9 +2,9 @@
 
 Counterpart of python/llm/src/ipex_llm/transformers/gguf/api.py:30-75 and the per-family loaders under
 ``gguf/models/`` (llama, mistral, mixtral, baichuan, bloom, falcon, mpt, yuan2).  One table-driven loader covers the
-llama-shaped families (llama, mistral, mixtral, qwen2, gemma, baichuan, yuan2's llama base): the GGUF tensor names are
-mapped to Hugging Face module names, q/k projections are un-permuted (llama.cpp stores them in the interleaved
-rotary order), every matrix is re-quantized to ``low_bit`` as it is read, and nothing of the model is ever held in
+llama-shaped families (llama, mistral, mixtral, qwen2, qwen3, gemma, gemma2, phi3, baichuan, yuan2's llama base): the
+GGUF tensor names are mapped to Hugging Face module names, the conventions of llama.cpp's exporter are undone (q / k
+rows re-ordered for the llama-type architectures, Gemma norm weights stored as 1 + w), every matrix is re-quantized to ``low_bit`` as it is read, and nothing of the model is ever held in
 full precision beyond one tensor.
 """
 from __future__ import annotations
@@ -20,7 +20,12 @@ from ...utils.common import invalidInputError
 qtype_map = {2: "sym_int4", 3: "asym_int4", 7: "sym_int8", 8: "sym_int5", 9: "asym_int5", 0: "fp32", 1: "fp16",
              15: "q4_k", 17: "q5_k", 18: "q6_k", 10: "q2_k"}
 
-_LLAMA_LIKE = ("llama", "mistral", "mixtral", "qwen2", "gemma", "baichuan", "yuan")
+_LLAMA_LIKE = ("llama", "mistral", "mixtral", "qwen2", "qwen3", "gemma", "gemma2", "phi3", "baichuan", "yuan")
+# llama.cpp's exporter re-orders the q / k rows of these architectures for its interleaved rotary kernel; the others
+# (qwen2, qwen3, gemma, gemma2, phi3: "neox" rotary there) keep the Hugging Face row order
+_PERMUTED_QK = ("llama", "mistral", "mixtral", "baichuan", "yuan")
+# its Gemma exporter stores norm weights as (1 + w), because its RMSNorm multiplies by the stored value
+_NORM_PLUS_ONE = ("gemma", "gemma2")
 
 _BLOCK_MAP = {
     "attn_norm.weight": "input_layernorm.weight",
@@ -32,10 +37,21 @@ _BLOCK_MAP = {
     "ffn_gate.weight": "mlp.gate_proj.weight", "ffn_up.weight": "mlp.up_proj.weight",
     "ffn_down.weight": "mlp.down_proj.weight",
     "ffn_gate_inp.weight": "block_sparse_moe.gate.weight",
+    "attn_q_norm.weight": "self_attn.q_norm.weight", "attn_k_norm.weight": "self_attn.k_norm.weight",      # qwen3
+    "attn_qkv.weight": "self_attn.qkv_proj.weight",                                                        # phi3
+}
+# per-architecture differences from the table above
+_BLOCK_MAP_ARCH = {
+    # four norms per layer: around attention and around the MLP
+    "gemma2": {"post_attention_norm.weight": "post_attention_layernorm.weight",
+               "ffn_norm.weight": "pre_feedforward_layernorm.weight",
+               "post_ffw_norm.weight": "post_feedforward_layernorm.weight"},
+    # gate and up projections fused in one matrix, stored under the "up" name
+    "phi3": {"ffn_up.weight": "mlp.gate_up_proj.weight"},
 }
 
 
-def get_llama_module_name(name: str) -> Optional[str]:
+def get_llama_module_name(name: str, arch: str = "llama") -> Optional[str]:
     """GGUF tensor name -> Hugging Face parameter name (None for tensors that have no counterpart)."""
     if name == "token_embd.weight":
         return "model.embed_tokens.weight"
@@ -47,6 +63,8 @@ def get_llama_module_name(name: str) -> Optional[str]:
     if not m:
         return None
     layer, rest = m.group(1), m.group(2)
+    if rest in _BLOCK_MAP_ARCH.get(arch, {}):
+        return f"model.layers.{layer}.{_BLOCK_MAP_ARCH[arch][rest]}"
     if rest in _BLOCK_MAP:
         return f"model.layers.{layer}.{_BLOCK_MAP[rest]}"
     e = re.match(r"ffn_(gate|up|down)\.(\d+)\.weight", rest)     # mixtral experts stored one by one
@@ -78,9 +96,24 @@ def _hf_config(cfg: dict, arch: str, vocab: int):
     name = str(cfg.get("general.name", "")).lower()
     if arch == "qwen2":
         return transformers.Qwen2Config(**common), "qwen2"
+    if arch == "qwen3":
+        common["head_dim"] = g("attention.key_length", common["hidden_size"] // common["num_attention_heads"])
+        return transformers.Qwen3Config(**common), "qwen3"
     if arch == "gemma":
         common["head_dim"] = g("attention.key_length", common["hidden_size"] // common["num_attention_heads"])
         return transformers.GemmaConfig(**common), "gemma"
+    if arch == "gemma2":
+        common["head_dim"] = g("attention.key_length", common["hidden_size"] // common["num_attention_heads"])
+        extra = dict(attn_logit_softcapping=g("attn_logit_softcapping", 50.0),
+                     final_logit_softcapping=g("final_logit_softcapping", 30.0),
+                     sliding_window=g("attention.sliding_window", 4096),
+                     query_pre_attn_scalar=common["head_dim"])
+        return transformers.Gemma2Config(**common, **extra), "gemma2"
+    if arch == "phi3":
+        if g("attention.sliding_window"):
+            common["sliding_window"] = g("attention.sliding_window")
+        common["pad_token_id"] = cfg.get("tokenizer.ggml.padding_token_id", 0)
+        return transformers.Phi3Config(**common), "phi3"
     if g("expert_count"):
         return transformers.MixtralConfig(num_local_experts=g("expert_count"),
                                           num_experts_per_tok=g("expert_used_count", 2), **common), "mixtral"
@@ -257,13 +290,16 @@ def load_gguf_model(fpath: str, dtype: torch.dtype = torch.float, low_bit: str =
                 params[target].copy_(tensor.to(params[target].dtype).reshape(params[target].shape))
             loaded.add(target)
             return
-        target = get_llama_module_name(name)
+        target = get_llama_module_name(name, arch)
         if target is None or target not in params:
             return
-        if target.endswith("q_proj.weight") or target.endswith("q_proj.bias"):
-            tensor = _unpermute(tensor, n_head)
-        elif target.endswith("k_proj.weight") or target.endswith("k_proj.bias"):
-            tensor = _unpermute(tensor, n_kv)
+        if arch in _PERMUTED_QK:
+            if target.endswith("q_proj.weight") or target.endswith("q_proj.bias"):
+                tensor = _unpermute(tensor, n_head)
+            elif target.endswith("k_proj.weight") or target.endswith("k_proj.bias"):
+                tensor = _unpermute(tensor, n_kv)
+        if arch in _NORM_PLUS_ONE and target.endswith("norm.weight"):
+            tensor = tensor - 1.0
         with torch.no_grad():
             params[target].copy_(tensor.to(params[target].dtype).reshape(params[target].shape))
         loaded.add(target)

@@ -146,9 +146,13 @@ def _meta_init():
 
 
 def _rebuild_nonpersistent(model, device="cpu"):
-    """Modules whose buffers are computed in ``__init__`` (rotary embeddings) were built on ``meta``:
-    re-create them for real."""
+    """Buffers that are computed in ``__init__`` and not stored in checkpoints were built on ``meta`` (or left
+    uninitialised by ``to_empty``): re-create them for real.  Rotary embeddings are re-instantiated from their config;
+    scaled word embeddings (Gemma family: ``embed_scale = sqrt(hidden)``) get their scalar back."""
     for name, mod in list(model.named_modules()):
+        if "embed_scale" in getattr(mod, "_non_persistent_buffers_set", ()) and hasattr(mod, "scalar_embed_scale"):
+            mod._buffers["embed_scale"] = torch.tensor(float(mod.scalar_embed_scale), device=device)
+            continue
         if "RotaryEmbedding" in type(mod).__name__ and hasattr(mod, "config"):
             try:
                 new = type(mod)(config=mod.config)

@@ -475,3 +475,26 @@ def test_deepseek_v3_routing_goes_through_the_grouped_topk_router():
     ids = torch.randint(0, 1000, (2, 16))
     with torch.no_grad():
         assert _cos(low(ids).logits[:, -1], base(ids).logits[:, -1]) > 0.999
+
+
+@pytest.mark.parametrize("family", ["gemma", "gemma2", "gemma3_text", "qwen3", "glm", "phi3", "mixtral"])
+def test_low_bit_checkpoint_round_trip_across_families(family, tmp_path):
+    """``save_low_bit`` -> ``load_low_bit`` reproduces the logits bit for bit for families with buffers that are not
+    part of a checkpoint (rotary tables, Gemma's embedding scale) and with fused expert banks."""
+    import transformers
+    from ipex_llm.transformers import AutoModelForCausalLM
+    cls_name, extra = FAMILY_CONFIGS[family]
+    kw = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, vocab_size=1000, max_position_embeddings=256)
+    kw.update(extra)
+    torch.manual_seed(0)
+    src = transformers.AutoModelForCausalLM.from_config(getattr(transformers, cls_name)(**kw)).eval()
+    d0, d1 = str(tmp_path / "hf"), str(tmp_path / "low")
+    src.save_pretrained(d0)
+    m = AutoModelForCausalLM.from_pretrained(d0, load_in_low_bit="sym_int8")
+    m.save_low_bit(d1)
+    again = AutoModelForCausalLM.load_low_bit(d1)
+    ids = torch.randint(0, 1000, (2, 11))
+    with torch.no_grad():
+        a, b = m(ids).logits, again(ids).logits
+    assert torch.equal(a, b) and a.abs().max() > 0

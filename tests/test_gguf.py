@@ -300,3 +300,96 @@ def test_q3_k_decoder_and_library_types_match_the_official_decoder():
             raw[:, :2] = d
         ours = dequantize_blocks(raw.reshape(-1), int(t), 9 * qk)
         assert np.array_equal(ours, gq.dequantize(raw, t).reshape(-1)), t.name
+
+
+def _export_llama_cpp_style(model, arch, path):
+    """A GGUF file of a llama-shaped model as llama.cpp's exporter lays it out: q / k rows re-ordered only for the
+    llama-type architectures, Gemma norms stored as 1 + w, Phi-3's fused matrices under ``attn_qkv`` / ``ffn_up``,
+    Gemma-2's four norms per layer, Qwen-3's q / k norms."""
+    from ipex_llm_b200.transformers.gguf.gguf import write_gguf
+    cfg = model.config
+    n_head, n_kv = cfg.num_attention_heads, cfg.num_key_value_heads
+
+    def permute(t, heads):
+        rows = t.shape[0]
+        return t.reshape(heads, 2, rows // heads // 2, *t.shape[1:]).swapaxes(1, 2).reshape(t.shape)
+    names = {"input_layernorm.weight": "attn_norm.weight", "self_attn.q_proj.weight": "attn_q.weight",
+             "self_attn.k_proj.weight": "attn_k.weight", "self_attn.v_proj.weight": "attn_v.weight",
+             "self_attn.q_proj.bias": "attn_q.bias", "self_attn.k_proj.bias": "attn_k.bias",
+             "self_attn.v_proj.bias": "attn_v.bias", "self_attn.o_proj.weight": "attn_output.weight",
+             "self_attn.q_norm.weight": "attn_q_norm.weight", "self_attn.k_norm.weight": "attn_k_norm.weight",
+             "self_attn.qkv_proj.weight": "attn_qkv.weight", "mlp.gate_up_proj.weight": "ffn_up.weight",
+             "mlp.gate_proj.weight": "ffn_gate.weight", "mlp.up_proj.weight": "ffn_up.weight",
+             "mlp.down_proj.weight": "ffn_down.weight", "post_attention_layernorm.weight": "ffn_norm.weight"}
+    if arch == "gemma2":
+        names.update({"post_attention_layernorm.weight": "post_attention_norm.weight",
+                      "pre_feedforward_layernorm.weight": "ffn_norm.weight",
+                      "post_feedforward_layernorm.weight": "post_ffw_norm.weight"})
+    tensors = {}
+    for k, v in model.state_dict().items():
+        v = v.clone()
+        if arch in ("gemma", "gemma2") and k.endswith("norm.weight"):
+            v = v + 1.0
+        kind = "f32" if v.dim() == 1 else "f16"
+        if k == "model.embed_tokens.weight":
+            tensors["token_embd.weight"] = (v, kind)
+        elif k == "model.norm.weight":
+            tensors["output_norm.weight"] = (v, kind)
+        elif k == "lm_head.weight":
+            if not cfg.tie_word_embeddings:
+                tensors["output.weight"] = (v, kind)
+        else:
+            _, _, layer, rest = k.split(".", 3)
+            if arch == "llama" and "q_proj" in rest:
+                v = permute(v, n_head)
+            elif arch == "llama" and "k_proj" in rest:
+                v = permute(v, n_kv)
+            tensors[f"blk.{layer}.{names[rest]}"] = (v, kind)
+    hd = getattr(cfg, "head_dim", None) or cfg.hidden_size // n_head
+    meta = {"general.architecture": arch, "general.name": "tiny", f"{arch}.embedding_length": cfg.hidden_size,
+            f"{arch}.feed_forward_length": cfg.intermediate_size, f"{arch}.block_count": cfg.num_hidden_layers,
+            f"{arch}.attention.head_count": n_head, f"{arch}.attention.head_count_kv": n_kv,
+            f"{arch}.attention.key_length": hd, f"{arch}.context_length": 256,
+            f"{arch}.attention.layer_norm_rms_epsilon": float(cfg.rms_norm_eps), f"{arch}.rope.freq_base": 10000.0,
+            "tokenizer.ggml.bos_token_id": 1, "tokenizer.ggml.eos_token_id": 2}
+    if arch == "gemma2":
+        meta.update({"gemma2.attn_logit_softcapping": 50.0, "gemma2.final_logit_softcapping": 30.0,
+                     "gemma2.attention.sliding_window": 16})
+    write_gguf(path, meta, tensors)
+
+
+@pytest.mark.parametrize("arch", ["llama", "qwen2", "qwen3", "gemma", "gemma2", "phi3"])
+def test_load_gguf_llama_shaped_architectures(tmp_path, arch):
+    """Every llama-shaped architecture the loader names, exported with the conventions llama.cpp uses for it, loads
+    to the logits of the source model."""
+    import transformers
+    from ipex_llm.transformers import AutoModelForCausalLM
+    base = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, vocab_size=320, max_position_embeddings=256, rms_norm_eps=1e-5,
+                bos_token_id=1, eos_token_id=2)
+    cfgs = {"llama": transformers.LlamaConfig(**base, tie_word_embeddings=False),
+            "qwen2": transformers.Qwen2Config(**base, tie_word_embeddings=False),
+            "qwen3": transformers.Qwen3Config(**base, head_dim=32, tie_word_embeddings=False),
+            "gemma": transformers.GemmaConfig(**base, head_dim=32, tie_word_embeddings=True),
+            "gemma2": transformers.Gemma2Config(**base, head_dim=32, sliding_window=16, query_pre_attn_scalar=32,
+                                                tie_word_embeddings=True),
+            "phi3": transformers.Phi3Config(**base, pad_token_id=0, tie_word_embeddings=False)}
+    torch.manual_seed(0)
+    src = transformers.AutoModelForCausalLM.from_config(cfgs[arch]).eval()
+    with torch.no_grad():
+        for n, p in src.named_parameters():
+            if p.dim() > 1:
+                p.normal_(0, 0.05)
+            elif "norm" in n:
+                p.add_(torch.randn_like(p) * 0.1)                  # norms that are not the identity
+            else:
+                p.normal_(0, 0.05)                                 # biases (qwen2)
+    path = str(tmp_path / f"{arch}.gguf")
+    _export_llama_cpp_style(src, arch, path)
+    model, _ = AutoModelForCausalLM.from_gguf(path, low_bit="sym_int8")
+    assert model.config.model_type == arch
+    ids = torch.randint(0, 320, (2, 12))
+    with torch.no_grad():
+        a = src(ids).logits[:, -1].float()
+        b = model(ids).logits[:, -1].float()
+    assert torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item() > 0.995
