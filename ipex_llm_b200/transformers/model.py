@@ -163,6 +163,34 @@ def _rebuild_nonpersistent(model, device="cpu"):
             for p in parts[:-1]:
                 parent = getattr(parent, p)
             parent._modules[parts[-1]] = new.to(device)
+            continue
+        # any other module with buffers that no checkpoint holds and that still sit on ``meta`` (GPT-J's sinusoidal
+        # table, ...): build one fresh instance of that module alone and take its buffers
+        lost = [b for b in getattr(mod, "_non_persistent_buffers_set", ())
+                if mod._buffers.get(b) is not None and mod._buffers[b].device.type == "meta"]
+        if lost:
+            fresh = None
+            attempts = []
+            if hasattr(mod, "config"):
+                attempts += [((mod.config, getattr(mod, "layer_idx", None)), {}), ((mod.config,), {})]
+            # small helper modules (vision rotary tables, ...) keep their constructor arguments as attributes
+            import inspect
+            try:
+                names = [p for p in inspect.signature(type(mod).__init__).parameters if p != "self"]
+                if names and all(hasattr(mod, n) for n in names):
+                    attempts.append(((), {n: getattr(mod, n) for n in names}))
+            except (TypeError, ValueError):
+                pass
+            for args, kwargs in attempts:
+                try:
+                    with torch.device("cpu"):
+                        fresh = type(mod)(*args, **kwargs)
+                    break
+                except Exception:  # noqa: BLE001 - another constructor signature
+                    continue
+            invalidInputError(fresh is not None, f"cannot rebuild the buffers {lost} of {name} ({type(mod).__name__})")
+            for b in lost:
+                mod._buffers[b] = fresh._buffers[b].to(device)
 
 
 def _materialize_meta(model, device, dtype, seed=0, std=0.02):

@@ -477,10 +477,11 @@ def test_deepseek_v3_routing_goes_through_the_grouped_topk_router():
         assert _cos(low(ids).logits[:, -1], base(ids).logits[:, -1]) > 0.999
 
 
-@pytest.mark.parametrize("family", ["gemma", "gemma2", "gemma3_text", "qwen3", "glm", "phi3", "mixtral"])
+@pytest.mark.parametrize("family", list(FAMILY_CONFIGS))
 def test_low_bit_checkpoint_round_trip_across_families(family, tmp_path):
-    """``save_low_bit`` -> ``load_low_bit`` reproduces the logits bit for bit for families with buffers that are not
-    part of a checkpoint (rotary tables, Gemma's embedding scale) and with fused expert banks."""
+    """``save_low_bit`` -> ``load_low_bit`` reproduces the logits bit for bit for every family, including those with
+    buffers that are not part of a checkpoint (rotary tables, Gemma's embedding scale, GPT-J's sinusoidal table) and
+    with fused expert banks."""
     import transformers
     from ipex_llm.transformers import AutoModelForCausalLM
     cls_name, extra = FAMILY_CONFIGS[family]

@@ -140,3 +140,17 @@ def test_multimodal_family_converts_and_matches(name):
     if media is not None:
         with torch.no_grad():
             assert _cos(low(**media).logits[:, -1], base(**media).logits[:, -1]) > 0.999
+    # the packed model reloads into a shell built without allocating weights and answers the same, bit for bit
+    # (vision rotary tables and the like are rebuilt, they are in no checkpoint)
+    import tempfile
+    from ipex_llm.optimize import load_low_bit, low_memory_init
+    with tempfile.TemporaryDirectory() as d:
+        low.save_low_bit(d)
+        with low_memory_init():
+            shell = cls(cfg)
+        again = load_low_bit(shell, d)
+    with torch.no_grad():
+        assert torch.equal(again(input_ids=ids).logits, low(input_ids=ids).logits)
+        if media is not None:
+            assert torch.equal(again(**media).logits, low(**media).logits)
+
