@@ -85,3 +85,28 @@ def test_performance_mode_enables_lookup(target_and_draft, monkeypatch):
     target.n_token_generated = -1
     out = target.generate(ids, max_new_tokens=6, do_sample=False)
     assert out.shape[1] == 126 and target.n_token_generated == 6
+
+
+@pytest.mark.parametrize("family", ["qwen3", "gemma2", "mixtral", "deepseek_v3", "gptj"])
+def test_speculative_and_lookup_equal_greedy_across_families(family):
+    """Self-speculative and prompt-lookup decoding are exact for greedy search whatever the family's cache and
+    attention path (package cache, soft-capped / sliding-window attention, MoE blocks, latent attention, a family
+    with its own eager attention)."""
+    import transformers
+    from ipex_llm.transformers import AutoModelForCausalLM
+    from test_cpu_model import FAMILY_CONFIGS
+    cls_name, extra = FAMILY_CONFIGS[family]
+    kw = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, vocab_size=1000, max_position_embeddings=256)
+    kw.update(extra)
+    cfg = getattr(transformers, cls_name)(**kw)
+    torch.manual_seed(0)
+    m = AutoModelForCausalLM.from_config(cfg, load_in_low_bit="bf16", device="cpu", torch_dtype=torch.float32,
+                                         speculative=True)
+    ids = torch.randint(0, 900, (1, 20))
+    greedy = m._hf_generate(inputs=ids, max_new_tokens=12, do_sample=False)
+    spec = m.generate(ids, max_new_tokens=12, do_sample=False)
+    assert torch.equal(spec[:, :greedy.shape[1]], greedy[:, :spec.shape[1]])
+    m.draft_model = None
+    look = m.generate(ids, max_new_tokens=12, do_sample=False, lookahead=3, max_matching_ngram_size=2)
+    assert torch.equal(look[:, :greedy.shape[1]], greedy[:, :look.shape[1]])
