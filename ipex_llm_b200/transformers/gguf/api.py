@@ -242,6 +242,51 @@ class GGUFTokenizer:
                 "attention_mask": mask if not isinstance(text, str) else mask[0]}
 
 
+# split patterns of the byte-level BPE vocabularies llama.cpp names in ``tokenizer.ggml.pre`` (they are part of each
+# model's published tokenizer definition); anything else falls back to the GPT-2 pattern
+_BPE_SPLIT = {
+    "llama-bpe": r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+"
+                 r"|\s+(?!\S)|\s+",
+    "qwen2": r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+"
+             r"|\s+(?!\S)|\s+",
+}
+
+
+def build_bpe_tokenizer(cfg: dict):
+    """Byte-level BPE tokenizer (``tokenizer.ggml.model == "gpt2"``: Llama-3, Qwen2, GPT-2, Falcon, ...) rebuilt from the
+    vocabulary and merge list of the file as a ``PreTrainedTokenizerFast``."""
+    from tokenizers import Regex, Tokenizer, decoders, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+    tokens = cfg["tokenizer.ggml.tokens"]
+    merges = [tuple(m.split(" ", 1)) for m in cfg.get("tokenizer.ggml.merges", [])]
+    tk = Tokenizer(models.BPE(vocab={t: i for i, t in enumerate(tokens)}, merges=merges, fuse_unk=False,
+                              byte_fallback=False))
+    pattern = _BPE_SPLIT.get(str(cfg.get("tokenizer.ggml.pre", "")))
+    if pattern is None:
+        tk.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+    else:
+        tk.pre_tokenizer = pre_tokenizers.Sequence([
+            pre_tokenizers.Split(Regex(pattern), behavior="isolated"),
+            pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+    tk.decoder = decoders.ByteLevel()
+    types = cfg.get("tokenizer.ggml.token_type") or []
+    special = [tokens[i] for i, ty in enumerate(types) if ty in (3, 4)]          # control / user-defined tokens
+    if special:
+        tk.add_special_tokens(special)
+
+    def tok(key):
+        i = cfg.get(key)
+        return tokens[i] if isinstance(i, int) and 0 <= i < len(tokens) else None
+    fast = PreTrainedTokenizerFast(tokenizer_object=tk, bos_token=tok("tokenizer.ggml.bos_token_id"),
+                                   eos_token=tok("tokenizer.ggml.eos_token_id"),
+                                   pad_token=tok("tokenizer.ggml.padding_token_id") or tok("tokenizer.ggml.eos_token_id"))
+    fast.padding_side = "left"
+    template = cfg.get("tokenizer.chat_template")
+    if template:
+        fast.chat_template = template
+    return fast
+
+
 def load_gguf_model(fpath: str, dtype: torch.dtype = torch.float, low_bit: str = "sym_int4"):
     """Returns ``(model, tokenizer)``; ``model`` is a low-bit model ready for ``.to('cuda')`` / ``generate``."""
     from ..convert import ggml_convert_low_bit
@@ -315,8 +360,13 @@ def load_gguf_model(fpath: str, dtype: torch.dtype = torch.float, low_bit: str =
     model = ggml_convert_low_bit(model.eval(), qt.qtype_from_name(low_bit), optimize_model=True)
     model = _attach_api(model, low_bit)
     try:
-        tokenizer = GGUFTokenizer(loader) if "tokenizer.ggml.tokens" in cfg else None
-    except Exception:  # noqa: BLE001 - vocabulary kinds without a sentencepiece form (byte-level BPE): model only
+        if "tokenizer.ggml.tokens" not in cfg:
+            tokenizer = None
+        elif cfg.get("tokenizer.ggml.model") == "gpt2":
+            tokenizer = build_bpe_tokenizer(cfg)
+        else:
+            tokenizer = GGUFTokenizer(loader)
+    except Exception:  # noqa: BLE001 - a vocabulary kind that cannot be rebuilt here: model only
         tokenizer = None
     loader.close()
     return model, tokenizer

@@ -393,3 +393,39 @@ def test_load_gguf_llama_shaped_architectures(tmp_path, arch):
         a = src(ids).logits[:, -1].float()
         b = model(ids).logits[:, -1].float()
     assert torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item() > 0.995
+
+
+@pytest.mark.parametrize("pre", ["gpt-2", "llama-bpe", "qwen2"])
+def test_byte_level_bpe_tokenizer_is_rebuilt_from_gguf_metadata(pre):
+    """A byte-level BPE vocabulary (``tokenizer.ggml.model = gpt2``) stored as token and merge lists gives back a
+    tokenizer with the encodings of the original, including the split pattern named by ``tokenizer.ggml.pre``."""
+    from tokenizers import Regex, Tokenizer, decoders, models, pre_tokenizers, trainers
+    from ipex_llm_b200.transformers.gguf.api import _BPE_SPLIT, build_bpe_tokenizer
+    corpus = ["The quick brown fox jumps over 12345 lazy dogs.", "Qu'est-ce que c'est? It's 2024-01-05!",
+              "def f(x):\n    return x ** 2  # squared\n", "naïve café — 你好，世界 9876543210", "    indented\tline\r\n"] * 20
+    orig = Tokenizer(models.BPE())
+    if pre == "gpt-2":
+        orig.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+    else:
+        orig.pre_tokenizer = pre_tokenizers.Sequence([
+            pre_tokenizers.Split(Regex(_BPE_SPLIT[pre]), behavior="isolated"),
+            pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+    orig.decoder = decoders.ByteLevel()
+    trainer = trainers.BpeTrainer(vocab_size=400, special_tokens=["<|begin|>", "<|end|>"],
+                                  initial_alphabet=pre_tokenizers.ByteLevel.alphabet())
+    orig.train_from_iterator(corpus, trainer)
+    vocab = orig.get_vocab()
+    tokens = [t for t, _ in sorted(vocab.items(), key=lambda kv: kv[1])]
+    import json
+    merges = [" ".join(m) if not isinstance(m, str) else m for m in json.loads(orig.to_str())["model"]["merges"]]
+    cfg = {"tokenizer.ggml.model": "gpt2", "tokenizer.ggml.pre": pre, "tokenizer.ggml.tokens": tokens,
+           "tokenizer.ggml.merges": merges, "tokenizer.ggml.token_type": [3, 3] + [1] * (len(tokens) - 2),
+           "tokenizer.ggml.bos_token_id": 0, "tokenizer.ggml.eos_token_id": 1}
+    tok = build_bpe_tokenizer(cfg)
+    assert tok.bos_token == "<|begin|>" and tok.eos_token == "<|end|>" and tok.padding_side == "left"
+    for text in corpus[:5] + ["unseen words 007, mixed CASE and   spaces", "<|begin|>hello<|end|>"]:
+        want = orig.encode(text).ids
+        got = tok(text, add_special_tokens=False)["input_ids"]
+        assert got == want, text
+        if "<|" not in text:
+            assert tok.decode(got) == text
