@@ -1,5 +1,6 @@
-"""Load a ``.gguf`` file straight into a low-bit model (llama, mistral, mixtral, qwen2, gemma, baichuan, yuan, bloom,
-falcon and mpt files) and generate.  Reference: python/llm/example/GPU/HuggingFace/Advanced-Quantizations/GGUF/generate.py
+"""Load a ``.gguf`` file straight into a low-bit model (llama, mistral, mixtral, qwen2, qwen3, gemma, gemma2, phi3,
+baichuan, yuan, bloom, falcon and mpt files; f32 / f16 / bf16 / q4_0 ... q8_0 / k-quant / i-quant tensors; sentencepiece
+and byte-level BPE vocabularies) and generate.  Reference: python/llm/example/GPU/HuggingFace/Advanced-Quantizations/GGUF/generate.py
 
     python examples/gguf.py --model model.gguf --prompt "What is AI?" --n-predict 32
 """
