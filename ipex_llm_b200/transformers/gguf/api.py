@@ -324,7 +324,13 @@ def load_gguf_model(fpath: str, dtype: torch.dtype = torch.float, low_bit: str =
 
     new_arch = bool(getattr(hf_cfg, "new_decoder_architecture", False))
 
+    rope_factors = []
+
     def process(name, tensor):
+        if name == "rope_freqs.weight":
+            # Llama-3.1 style long-context scaling: llama.cpp stores the per-frequency divisors as a tensor
+            rope_factors.append(tensor.float().reshape(-1))
+            return
         if gpt_like:
             target = get_gpt_module_name(arch, name, new_arch)
             if target is None or target not in params:
@@ -357,6 +363,13 @@ def load_gguf_model(fpath: str, dtype: torch.dtype = torch.float, low_bit: str =
     # buffers created on meta (rotary tables) are rebuilt by re-instantiating them
     from ..model import _rebuild_nonpersistent
     _rebuild_nonpersistent(model)
+    if rope_factors:
+        for mod in model.modules():
+            inv = getattr(mod, "inv_freq", None)
+            if inv is not None and inv.numel() == rope_factors[0].numel():
+                mod.inv_freq = inv / rope_factors[0].to(inv.device)
+                if hasattr(mod, "original_inv_freq"):
+                    mod.original_inv_freq = mod.inv_freq.clone()
     model = ggml_convert_low_bit(model.eval(), qt.qtype_from_name(low_bit), optimize_model=True)
     model = _attach_api(model, low_bit)
     try:

@@ -429,3 +429,40 @@ def test_byte_level_bpe_tokenizer_is_rebuilt_from_gguf_metadata(pre):
         assert got == want, text
         if "<|" not in text:
             assert tok.decode(got) == text
+
+
+def test_load_gguf_llama3_rope_factors(tmp_path):
+    """Llama-3.1 files carry their long-context rotary scaling as a ``rope_freqs.weight`` tensor of per-frequency
+    divisors: the loaded model rotates like the source model with ``rope_type = llama3``."""
+    import transformers
+    from ipex_llm.transformers import AutoModelForCausalLM
+    from ipex_llm_b200.transformers.gguf.gguf import GGUFFileLoader, write_gguf
+    rope = {"rope_type": "llama3", "rope_theta": 10000.0, "factor": 8.0, "low_freq_factor": 1.0,
+            "high_freq_factor": 4.0, "original_max_position_embeddings": 64}
+    cfg = transformers.LlamaConfig(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, vocab_size=320, max_position_embeddings=512,
+                                   rope_parameters=rope, tie_word_embeddings=False, bos_token_id=1, eos_token_id=2)
+    torch.manual_seed(0)
+    src = transformers.AutoModelForCausalLM.from_config(cfg).eval()
+    with torch.no_grad():
+        for p in src.parameters():
+            if p.dim() > 1:
+                p.normal_(0, 0.05)
+    plain = 1.0 / (10000.0 ** (torch.arange(0, 32, 2).float() / 32))
+    factors = plain / src.model.rotary_emb.inv_freq
+    assert factors.max() > 7.9 and factors.min() == 1.0
+    path = str(tmp_path / "l31.gguf")
+    _export_llama_cpp_style(src, "llama", path)
+    # add the factor tensor to the file
+    loader = GGUFFileLoader(path)
+    meta = dict(loader.config)
+    tensors = {n: (t, "f32" if t.dim() == 1 else "f16") for n, t in loader.tensors().items()}
+    loader.close()
+    tensors["rope_freqs.weight"] = (factors, "f32")
+    write_gguf(path, meta, tensors)
+    model, _ = AutoModelForCausalLM.from_gguf(path, low_bit="sym_int8")
+    ids = torch.randint(0, 320, (1, 200))                       # long enough for the scaled frequencies to matter
+    with torch.no_grad():
+        a = src(ids).logits[:, -1].float()
+        b = model(ids).logits[:, -1].float()
+    assert torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item() > 0.995
