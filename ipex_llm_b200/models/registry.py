@@ -75,9 +75,7 @@ def _moe_block_forward(self, hidden_states):
             import torch
             s = torch.sigmoid(sg(x)) * s
         out = out + s
-    tp = getattr(self.experts, "_tp_group", None)
-    if tp is not None:
-        out = tp.all_reduce(out)
+    # (under tensor parallelism the bank sums its partial outputs over the group itself, see parallel/tp.py)
     return out.reshape(bsz, seq, hid)
 
 

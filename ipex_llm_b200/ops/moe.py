@@ -87,6 +87,11 @@ def convert_fused_experts(module, qtype, device="cpu", convert_shape_only=False,
                           convert_shape_only=convert_shape_only, in_features=w.shape[-1],
                           enable_scale_search=enable_scale_search)
             lin._parameters["weight"] = p.to(device)
+    # a bank that auto_tp split along the intermediate dimension yields partial sums: they are summed over the group
+    # at the bank's output
+    if getattr(module, "_tp_group", None) is not None:
+        from ..parallel.tp import install_expert_allreduce
+        install_expert_allreduce(bank, module._tp_group)
     return bank
 
 
