@@ -84,7 +84,10 @@ def pipeline_parallel(model, pipeline_parallel_stages: int, torch_dtype=torch.fl
     world, rank = dist.get_world_size(), dist.get_rank()
     invalidInputError(world == pipeline_parallel_stages,
                       "Please make sure world size is same as `pipeline_parallel_stages`")
-    base = model.model
+    base = getattr(model, "model", None)
+    invalidInputError(base is not None and hasattr(base, "layers") and hasattr(base, "embed_tokens"),
+                      f"pipeline parallelism slices `model.model.layers`; {type(model).__name__} is laid out "
+                      "differently (GPT-2 / GPT-J / Bloom style `transformer.h`)")
     n_layers = model.config.num_hidden_layers
     start, end = stage_layer_range(n_layers, pipeline_parallel_stages, rank)
     for i in range(n_layers):
@@ -97,6 +100,10 @@ def pipeline_parallel(model, pipeline_parallel_stages: int, torch_dtype=torch.fl
                 attn.layer_idx = i - start
     if rank != 0:
         base.embed_tokens = Dummy_Embedding()
+        # models that scale their input embeddings inside the model forward (Granite, and MiniCPM checkpoints mapped
+        # to it) would scale the hidden states a later stage receives as `inputs_embeds` once more
+        if hasattr(base, "embedding_multiplier"):
+            base.embedding_multiplier = 1.0
     if rank != world - 1:
         base.norm = Dummy_Norm()
         model.lm_head = Dummy_Head()
@@ -331,12 +338,18 @@ def pipeline_parallel_generate(self, inputs: Optional[torch.Tensor] = None, max_
                     ids = torch.empty((rows[m], 1), dtype=torch.long, device=dev)
                     dist.recv(ids, src=world - 1, group=back)
                     out_new[b0:b1, step - 1] = ids[:, 0]
-                out = self(input_ids=ids, position_ids=position_ids, past_key_values=caches[m], use_cache=True)
+                kw = dict(input_ids=ids)
             else:
                 hid = torch.empty((rows[m], s_len, H), dtype=dtype, device=dev)
                 dist.recv(hid, src=rank - 1)
-                out = self(inputs_embeds=hid, position_ids=position_ids, past_key_values=caches[m], use_cache=True)
-            res = out.logits
+                kw = dict(inputs_embeds=hid)
+            if last:
+                res = self(position_ids=position_ids, past_key_values=caches[m], use_cache=True, **kw).logits
+            else:
+                # the hidden states themselves: a causal-LM wrapper may scale or soft-cap what it takes for logits
+                # (Cohere, Granite, Gemma-2), which must happen on the last stage only
+                res = self.model(position_ids=position_ids, past_key_values=caches[m], use_cache=True,
+                                 **kw).last_hidden_state
             if last:
                 nxt = torch.argmax(res[:, -1, :], dim=-1)
                 if eos_t is not None:

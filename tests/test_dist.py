@@ -53,6 +53,13 @@ def test_tensor_parallel_cpu_gloo(tp_llama_dir):
     assert res.stdout.count(": ok") == 2
 
 
+def test_pipeline_parallel_across_families_cpu_gloo():
+    """Wrappers that scale / divide / soft-cap their logits, MoE blocks, latent attention, fused qkv: see the worker."""
+    res = run_workers("pp_families_worker.py", 2, [], timeout=900)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert res.stdout.count(": ok") == 2
+
+
 def test_tensor_parallel_across_families_cpu_gloo():
     """Fused qkv / gate_up, expert banks, shared experts, replicated attention: see the worker's docstring."""
     res = run_workers("tp_families_worker.py", 2, [], timeout=900)
