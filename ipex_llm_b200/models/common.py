@@ -245,7 +245,9 @@ def scaled_dot_product_attention(query: torch.Tensor, key: torch.Tensor, value: 
         if sliding_window is not None:
             allowed = allowed & (ki > qi - sliding_window)
         w = w.masked_fill(~allowed, float("-inf"))
-    w = torch.softmax(w, dim=-1)
+    # a query row that may see no key at all (the rows of left padding under a sliding window) softmaxes to NaN,
+    # which would then leak into real rows through the next layer's keys: such rows attend to nothing instead
+    w = torch.nan_to_num(torch.softmax(w, dim=-1), nan=0.0)
     return torch.matmul(w, value.float()).to(query.dtype)
 
 

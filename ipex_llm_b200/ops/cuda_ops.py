@@ -681,7 +681,8 @@ def sdpa_prefill(q, k, v, mask, scale, softcap, sliding_window, causal=True):
             if sliding_window:
                 allowed = allowed & (ki > qi - sliding_window)
             w = w.masked_fill(~allowed, float("-inf"))
-        return torch.matmul(torch.softmax(w, dim=-1).to(q.dtype), vv)
+        # (rows without any visible key, e.g. left padding under a sliding window, attend to nothing instead of NaN)
+        return torch.matmul(torch.nan_to_num(torch.softmax(w, dim=-1), nan=0.0).to(q.dtype), vv)
     if mask is not None:
         m = mask[..., : k.shape[2]]
         if m.dtype != torch.bool and m.dtype != q.dtype:

@@ -499,3 +499,28 @@ def test_low_bit_checkpoint_round_trip_across_families(family, tmp_path):
     with torch.no_grad():
         a, b = m(ids).logits, again(ids).logits
     assert torch.equal(a, b) and a.abs().max() > 0
+
+
+@pytest.mark.parametrize("family", ["gemma2", "gemma3_text", "qwen3", "mixtral", "deepseek_v3", "gptj", "glm"])
+def test_left_padded_batch_generates_like_single_prompts(family):
+    """A short prompt left-padded beside a longer one generates the tokens it generates alone (position ids, padding
+    masks, and, under a sliding window, padding rows that see no key at all must not leak NaN into real rows)."""
+    import transformers
+    from ipex_llm.transformers import AutoModelForCausalLM
+    cls_name, extra = FAMILY_CONFIGS[family]
+    kw = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, vocab_size=1000, max_position_embeddings=256)
+    kw.update(extra)
+    torch.manual_seed(0)
+    m = AutoModelForCausalLM.from_config(getattr(transformers, cls_name)(**kw), load_in_low_bit="sym_int8",
+                                         device="cpu", torch_dtype=torch.float32)
+    m.generation_config.pad_token_id = 0
+    g = torch.Generator().manual_seed(0)
+    a, b = torch.randint(5, 900, (1, 9), generator=g), torch.randint(5, 900, (1, 16), generator=g)
+    batch = torch.cat([torch.cat([torch.zeros(1, 7, dtype=torch.long), a], 1), b], 0)
+    mask = torch.ones_like(batch)
+    mask[0, :7] = 0
+    both = m.generate(batch, attention_mask=mask, max_new_tokens=6, do_sample=False)
+    alone_a = m.generate(a, attention_mask=torch.ones_like(a), max_new_tokens=6, do_sample=False)
+    alone_b = m.generate(b, attention_mask=torch.ones_like(b), max_new_tokens=6, do_sample=False)
+    assert torch.equal(both[0, 16:], alone_a[0, 9:]) and torch.equal(both[1, 16:], alone_b[0, 16:])
