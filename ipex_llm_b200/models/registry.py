@@ -62,7 +62,7 @@ def _moe_block_forward(self, hidden_states):
     bsz, seq, hid = hidden_states.shape
     x = hidden_states.reshape(-1, hid)
     gate = self.gate
-    logits = F.linear(x, gate.weight)
+    logits = F.linear(x.to(gate.weight.dtype), gate.weight)     # (a disk-resident embedding hands out fp16 rows)
     top_k = getattr(gate, "top_k", None) or getattr(self, "top_k", 2)
     renorm = getattr(gate, "norm_topk_prob", True)
     _, w, idx = softmax_topk_router(logits, top_k, renorm)

@@ -14,6 +14,13 @@ from ..quant import qtypes as qt
 from ..quant.params import FP4Params, get_block_size, get_type_size
 
 
+def _scaled(module, out: Tensor) -> Tensor:
+    """Scaled word embeddings (Gemma family: rows times sqrt(hidden)) keep their factor when the table is replaced;
+    the converter stores it as ``embed_scale_value``."""
+    scale = getattr(module, "embed_scale_value", None)
+    return out if scale is None or scale == 1.0 else out * torch.tensor(scale, dtype=out.dtype, device=out.device)
+
+
 class CPUEmbedding(nn.Embedding):
     """Table pinned to host memory whatever ``.to(device)`` says; lookups return on the ids' device."""
 
@@ -28,7 +35,7 @@ class CPUEmbedding(nn.Embedding):
         return self
 
     def forward(self, x: Tensor):
-        return super().forward(x.to("cpu")).to(x.device)
+        return _scaled(self, super().forward(x.to("cpu")).to(x.device))
 
     @classmethod
     def from_embedding(cls, embedding: nn.Embedding):
@@ -133,13 +140,14 @@ class LowBitEmbedding(nn.Embedding):
             self._parameters["weight"] = w
         if w.data.is_cuda:
             from . import cuda_ops
-            return cuda_ops.dequantize_rows(x, w, self.embedding_dim, self.num_embeddings, self.torch_dtype)
+            return _scaled(self, cuda_ops.dequantize_rows(x, w, self.embedding_dim, self.num_embeddings,
+                                                          self.torch_dtype))
         rows, _ = self._row_view()
         ids = x.reshape(-1).cpu()
         picked = rows.index_select(0, ids).contiguous()
         from ..quant.params import ggml_convert_fp32
         out = ggml_convert_fp32(picked, (ids.numel(), self.embedding_dim), ids.numel() * self.embedding_dim, w.qtype)
-        return out.view(*x.shape, self.embedding_dim).to(self.torch_dtype).to(x.device)
+        return _scaled(self, out.view(*x.shape, self.embedding_dim).to(self.torch_dtype).to(x.device))
 
     @classmethod
     def from_embedding(cls, embedding: nn.Embedding, qtype, convert_shape_only=False, device="cpu"):

@@ -264,13 +264,18 @@ def _replace_with_low_bit_linear(model, qtype, modules_to_not_convert=None, conv
             model._modules[name] = new_linear
             has_been_replaced = True
             continue
-        if isinstance(module, nn.Embedding) and type(module) is nn.Embedding:
+        if isinstance(module, nn.Embedding) and (type(module) is nn.Embedding or hasattr(module, "scalar_embed_scale")):
+            new_emb = None
             if embedding_qtype is not None and not skip:
                 q = embedding_qtype if isinstance(embedding_qtype, int) else qt.qtype_from_name(embedding_qtype)
-                model._modules[name] = LowBitEmbedding.from_embedding(module, q, convert_shape_only, device)
+                new_emb = LowBitEmbedding.from_embedding(module, q, convert_shape_only, device)
                 has_been_replaced = True
             elif cpu_embedding:
-                model._modules[name] = CPUEmbedding.from_embedding(module)
+                new_emb = CPUEmbedding.from_embedding(module)
+            if new_emb is not None:
+                if hasattr(module, "scalar_embed_scale"):          # Gemma family: rows are scaled after the look-up
+                    new_emb.embed_scale_value = float(module.scalar_embed_scale)
+                model._modules[name] = new_emb
             continue
         if len(list(module.children())) > 0:
             _, flag = _replace_with_low_bit_linear(module, qtype, modules_to_not_convert, convert_shape_only,

@@ -524,3 +524,36 @@ def test_left_padded_batch_generates_like_single_prompts(family):
     alone_a = m.generate(a, attention_mask=torch.ones_like(a), max_new_tokens=6, do_sample=False)
     alone_b = m.generate(b, attention_mask=torch.ones_like(b), max_new_tokens=6, do_sample=False)
     assert torch.equal(both[0, 16:], alone_a[0, 9:]) and torch.equal(both[1, 16:], alone_b[0, 16:])
+
+
+@pytest.mark.parametrize("family", ["gemma2", "mixtral"])
+def test_embedding_variants_across_families(family, tmp_path, monkeypatch):
+    """``cpu_embedding``, ``disk_embedding`` and a packed ``embedding_qtype`` on a family with scaled word embeddings
+    (Gemma-2: the factor survives the replacement of the table) and on one whose router reads the hidden states
+    directly (Mixtral: a disk-resident table hands out fp16 rows)."""
+    import transformers
+    from ipex_llm.transformers import AutoModelForCausalLM
+    from ipex_llm_b200.ops.embedding import CPUEmbedding, DiskEmbedding, LowBitEmbedding
+    monkeypatch.chdir(tmp_path)                                # DiskEmbedding writes embeddings.bin beside the process
+    cls_name, extra = FAMILY_CONFIGS[family]
+    kw = dict(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, vocab_size=1000, max_position_embeddings=256)
+    kw.update(extra)
+    torch.manual_seed(0)
+    src = transformers.AutoModelForCausalLM.from_config(getattr(transformers, cls_name)(**kw)).eval()
+    d = str(tmp_path / "hf")
+    src.save_pretrained(d)
+    ids = torch.randint(0, 900, (2, 11))
+    with torch.no_grad():
+        ref = src(ids).logits[:, -1]
+    scaled = family == "gemma2"
+    for kwargs, cls, floor in ((dict(cpu_embedding=True), CPUEmbedding, 0.999),
+                               (dict(embedding_qtype="q4_k"), LowBitEmbedding, 0.99),
+                               (dict(disk_embedding=True), None if scaled else DiskEmbedding, 0.999)):
+        m = AutoModelForCausalLM.from_pretrained(d, load_in_low_bit="sym_int8", **kwargs)
+        if cls is not None:
+            assert isinstance(m.get_input_embeddings(), cls), kwargs
+            if scaled:
+                assert m.get_input_embeddings().embed_scale_value == 16.0
+        with torch.no_grad():
+            assert _cos(m(ids).logits[:, -1], ref) > floor, kwargs
