@@ -251,6 +251,16 @@ def scaled_dot_product_attention(query: torch.Tensor, key: torch.Tensor, value: 
     return torch.matmul(w, value.float()).to(query.dtype)
 
 
+def t5_dense_forward(self, hidden_states):
+    """``T5DenseActDense`` / ``T5DenseGatedActDense`` without the cast of the activations to ``wo.weight.dtype``: a
+    packed weight is a byte tensor, and the original forward would turn the hidden states into bytes."""
+    if hasattr(self, "wi_0"):
+        hidden_states = self.act(self.wi_0(hidden_states)) * self.wi_1(hidden_states)
+    else:
+        hidden_states = self.act(self.wi(hidden_states))
+    return self.wo(self.dropout(hidden_states))
+
+
 # ------------------------------------------------------------------------------------------------
 # attention interface of transformers 5: every model whose attention goes through ALL_ATTENTION_FUNCTIONS
 # ------------------------------------------------------------------------------------------------

@@ -140,6 +140,10 @@ FAMILIES = {
                           post_hook=P3.install),      # MiniCPM3 checkpoints arrive here with LongRoPE factors
     "phimoe": Family(post=[("LayerNorm", C.layer_norm_forward)]),
     "mllama": Family(post=[("MllamaTextRMSNorm", C.rms_norm_forward), ("MllamaTextMLP", C.mlp_silu_forward)]),
+    # encoder-decoder text models of the T5 line: their feed-forward casts activations to the weight's dtype
+    **{mt: Family(post=[(f"{prefix}DenseActDense", C.t5_dense_forward),
+                        (f"{prefix}DenseGatedActDense", C.t5_dense_forward)])
+       for mt, prefix in (("t5", "T5"), ("mt5", "MT5"), ("umt5", "UMT5"))},
     "rwkv": Family(pre=[R.rescale_before_quantization],
                    post=[("RwkvSelfAttention", R.rwkv4_attention_forward), ("RwkvFeedForward", R.rwkv4_ffn_forward)]),
     # LayerNorm families without a dedicated forward file: low-bit linears + the fused LayerNorm kernel

@@ -57,6 +57,11 @@ def is_auto_awq_available():
 
 
 def is_lm_head(name, model_config, out_features):
+    """The vocabulary projection of a generative model (reference convert.py:234-240): only its last position is needed
+    during generation.  A masked-LM decoder has the same shape but every position of its output is used."""
+    archs = getattr(model_config, "architectures", None) or []
+    if any(a.endswith("ForMaskedLM") or a.endswith("ForPreTraining") for a in archs):
+        return False
     if name == "lm_head" or getattr(model_config, "vocab_size", None) == out_features:
         return True
     return False
@@ -355,6 +360,17 @@ def convert_bigdl_other_module(model, dtype):
 # ------------------------------------------------------------------------------------------------
 # pre / post optimisation, driven by the family registry
 # ------------------------------------------------------------------------------------------------
+def _required_forward_fixes(model):
+    """Forward replacements that a packed model needs to be correct at all, applied even when the optimisations are
+    switched off: the T5 line's feed-forward casts its activations to ``wo.weight.dtype``, which is a byte type for
+    a packed weight."""
+    from ..models.common import t5_dense_forward
+    for mod in model.modules():
+        if type(mod).__name__.endswith(("DenseActDense", "DenseGatedActDense")) and hasattr(mod, "wo") and \
+                isinstance(getattr(mod.wo, "weight", None), FP4Params):
+            mod.forward = types.MethodType(t5_dense_forward, mod)
+
+
 def _optimize_pre(model, qtype=None):
     from ..models.registry import family_for
     fam = family_for(model)
@@ -441,6 +457,8 @@ def ggml_convert_low_bit(model, qtype, optimize_model=True, convert_shape_only=F
 
     if optimize_model:
         model = _optimize_post(model)
+    elif has_been_replaced:
+        _required_forward_fixes(model)
     if hasattr(model, "config") and model_type is not None:
         model._ipex_low_bit = qtype
     return model

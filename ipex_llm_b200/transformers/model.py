@@ -171,8 +171,15 @@ def _rebuild_nonpersistent(model, device="cpu"):
         if lost:
             fresh = None
             attempts = []
-            if hasattr(mod, "config"):
-                attempts += [((mod.config, getattr(mod, "layer_idx", None)), {}), ((mod.config,), {})]
+            configs = [mod.config] if hasattr(mod, "config") else []
+            # modules that do not keep their config (BERT's embeddings): the config of the nearest owner up the tree
+            parts = name.split(".")
+            for depth in range(len(parts) - 1, -1, -1):
+                owner = model.get_submodule(".".join(parts[:depth])) if depth else model
+                if hasattr(owner, "config") and all(owner.config is not c for c in configs):
+                    configs.append(owner.config)
+            for c in configs:
+                attempts += [((c, getattr(mod, "layer_idx", None)), {}), ((c,), {})]
             # small helper modules (vision rotary tables, ...) keep their constructor arguments as attributes
             import inspect
             try:
@@ -505,7 +512,11 @@ class _BaseAutoModelClass:
         invalidInputError(not real_missing, f"keys missing from the low-bit checkpoint: {real_missing[:8]}")
         _rebuild_nonpersistent(model, "cpu")
         if hasattr(model, "tie_weights") and getattr(config, "tie_word_embeddings", False):
-            model.tie_weights()
+            # a packed output layer came from the checkpoint as its own matrix: tying it to the embedding again
+            # would swap the packed parameter for the float table (T5 style maps do that)
+            head = model.get_output_embeddings() if hasattr(model, "get_output_embeddings") else None
+            if not isinstance(getattr(head, "weight", None), FP4Params):
+                model.tie_weights()
         model.eval()
         try:
             model.generation_config = transformers.GenerationConfig.from_pretrained(pretrained_model_name_or_path)

@@ -101,3 +101,59 @@ def test_attention_interface_serves_families_without_their_own_forward(name, mon
         assert calls["non_causal"] > 0          # bidirectional / cross attention must not be made causal
     cos = torch.nn.functional.cosine_similarity(out.flatten(), ref.flatten(), dim=0).item()
     assert cos > 0.995, (name, cos)
+
+
+AUTO_CASES = ["AutoModel", "AutoModelForMaskedLM", "AutoModelForSequenceClassification",
+              "AutoModelForTokenClassification", "AutoModelForQuestionAnswering", "AutoModelForNextSentencePrediction",
+              "AutoModelForMultipleChoice", "AutoModelForSeq2SeqLM", "AutoModelForSpeechSeq2Seq"]
+
+
+@pytest.mark.parametrize("auto", AUTO_CASES)
+def test_every_auto_class_converts_saves_and_reloads(auto, tmp_path):
+    """The Auto classes of the reference's API (model.py:788-830) beyond causal LM, on tiny BERT / T5 / Whisper
+    models: low-bit conversion keeps the outputs, ``save_low_bit`` / ``load_low_bit`` reproduce them bit for bit.
+    Covers a masked-LM decoder (every position of its output is used, so it is not treated as a generative head),
+    BERT's position-id buffers (in no checkpoint), T5's tied output layer and its feed-forward, which casts
+    activations to the weight's dtype."""
+    import transformers
+    import ipex_llm.transformers as IT
+    from ipex_llm_b200.ops.linear import LowBitLinear
+    bert = transformers.BertConfig(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                                   vocab_size=500, max_position_embeddings=64)
+    t5 = transformers.T5Config(d_model=128, d_ff=256, d_kv=32, num_layers=2, num_heads=4, vocab_size=500,
+                               decoder_start_token_id=0)
+    wh = transformers.WhisperConfig(d_model=128, encoder_layers=2, decoder_layers=2, encoder_attention_heads=4,
+                                    decoder_attention_heads=4, encoder_ffn_dim=256, decoder_ffn_dim=256,
+                                    num_mel_bins=16, max_source_positions=50, max_target_positions=64, vocab_size=500,
+                                    decoder_start_token_id=1, pad_token_id=0, bos_token_id=1, eos_token_id=2)
+    ids = torch.randint(0, 500, (2, 12))
+    table = {
+        "AutoModel": ("BertModel", bert, dict(input_ids=ids), "last_hidden_state"),
+        "AutoModelForMaskedLM": ("BertForMaskedLM", bert, dict(input_ids=ids), "logits"),
+        "AutoModelForSequenceClassification": ("BertForSequenceClassification", bert, dict(input_ids=ids), "logits"),
+        "AutoModelForTokenClassification": ("BertForTokenClassification", bert, dict(input_ids=ids), "logits"),
+        "AutoModelForQuestionAnswering": ("BertForQuestionAnswering", bert, dict(input_ids=ids), "start_logits"),
+        "AutoModelForNextSentencePrediction": ("BertForNextSentencePrediction", bert, dict(input_ids=ids), "logits"),
+        "AutoModelForMultipleChoice": ("BertForMultipleChoice", bert, dict(input_ids=ids.view(1, 2, 12)), "logits"),
+        "AutoModelForSeq2SeqLM": ("T5ForConditionalGeneration", t5,
+                                  dict(input_ids=ids, decoder_input_ids=ids[:, :5]), "logits"),
+        "AutoModelForSpeechSeq2Seq": ("WhisperForConditionalGeneration", wh,
+                                      dict(input_features=torch.randn(2, 16, 100), decoder_input_ids=ids[:, :5]),
+                                      "logits"),
+    }
+    hf_name, cfg, inputs, field = table[auto]
+    torch.manual_seed(0)
+    src = getattr(transformers, hf_name)(cfg).eval()
+    d0, d1 = str(tmp_path / "hf"), str(tmp_path / "low")
+    src.save_pretrained(d0)
+    cls = getattr(IT, auto)
+    low = cls.from_pretrained(d0, load_in_low_bit="sym_int8")
+    assert sum(isinstance(x, LowBitLinear) for x in low.modules()) >= 12
+    with torch.no_grad():
+        a, ref = getattr(low(**inputs), field), getattr(src(**inputs), field)
+    assert a.shape == ref.shape
+    assert torch.nn.functional.cosine_similarity(a.flatten().float(), ref.flatten().float(), dim=0) > 0.999
+    low.save_low_bit(d1)
+    again = cls.load_low_bit(d1)
+    with torch.no_grad():
+        assert torch.equal(getattr(again(**inputs), field), a)
