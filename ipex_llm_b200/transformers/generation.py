@@ -54,6 +54,11 @@ def ipex_generate(self, inputs=None, generation_config=None, logits_processor=No
             and assistant_model is None and _engine_ok(self, inputs, kwargs):
         from ..engine import engine_generate
         return engine_generate(self, inputs, generation_config=generation_config, streamer=streamer, **kwargs)
-    return self._hf_generate(inputs=inputs, generation_config=generation_config, logits_processor=logits_processor,
-                             stopping_criteria=stopping_criteria, prefix_allowed_tokens_fn=prefix_allowed_tokens_fn,
-                             synced_gpus=synced_gpus, assistant_model=assistant_model, streamer=streamer, **kwargs)
+    # only what the caller actually gave: some generate() overrides (Whisper) test for the presence of a keyword
+    optional = dict(generation_config=generation_config, logits_processor=logits_processor,
+                    stopping_criteria=stopping_criteria, prefix_allowed_tokens_fn=prefix_allowed_tokens_fn,
+                    synced_gpus=synced_gpus, assistant_model=assistant_model, streamer=streamer)
+    kwargs.update({k: v for k, v in optional.items() if v is not None})
+    if inputs is not None:
+        kwargs["inputs"] = inputs
+    return self._hf_generate(**kwargs)
