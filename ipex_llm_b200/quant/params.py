@@ -32,6 +32,10 @@ RTN_DTYPE = {qt.SYM_INT4_RTN: torch.uint8, qt.ASYM_INT4_RTN: torch.uint8, qt.SYM
 def get_block_size(qtype) -> int:
     if isinstance(qtype, str):
         qtype = qt.qtype_from_name(qtype)
+    if qtype == qt.MOFQ4:
+        return 64          # picks sym_int4 or fp4 per layer: both 64 values per block
+    if qtype == qt.MOFQ8:
+        return 128         # picks sym_int8 (64) or fp8_e4m3 (128): a layer must suit both
     return _nl.host_lib().ggml_qk_size(qtype)
 
 

@@ -76,6 +76,12 @@ def save_low_bit(self, save_directory, max_shard_size="10GB", **kwargs):
         if hasattr(self.config, "_pre_quantization_dtype"):
             delattr(self.config, "_pre_quantization_dtype")
     os.makedirs(save_directory, exist_ok=True)
+    if self.config.to_dict().get("bigdl_transformers_low_bit") in ("mixed_fp4", "mixed_fp8"):
+        # every layer chose between an integer and a float format of the same size by its own error: the bytes do
+        # not say which, so the choice is written down for load_low_bit
+        chosen = {n: qt.qtype_name(m.weight.qtype) for n, m in self.named_modules()
+                  if isinstance(getattr(m, "weight", None), FP4Params) and m.weight.quantized}
+        self.config.update({"bigdl_layer_qtypes": chosen})
     disk_embedding = getattr(self.config, "bigdl_disk_embedding", False)
     if disk_embedding:
         from ..ops.embedding import DiskEmbedding
@@ -354,6 +360,11 @@ class _BaseAutoModelClass:
                           f"fp4, fp6, fp8, fp8_e4m3, fp8_e5m2, fp16,  bf16, gguf_iq2_xxs, "
                           f"gguf_iq2_xs, gguf_iq1_s, gguf_q4k_m, gguf_q4k_s, q2_k, q4_k, q6_k, "
                           f"mixed_fp4 or mixed_fp8.")
+        if q_k.endswith("_rtn"):
+            # per-channel round-to-nearest containers belong to the NPU entry point of the reference; the same
+            # request here takes the blocked format of the same width, as ``transformers.npu_model`` does
+            warnings.warn(f"{q_k} is a per-channel NPU format; using {q_k[:-4]} blocks instead", UserWarning)
+            q_k = q_k[:-4]
         qtype = qt.qtype_from_name(q_k)
         imatrix_file = kwargs.pop("imatrix", None)
         if q_k in ("gguf_iq2_xxs", "gguf_iq2_xs", "gguf_iq1_s"):
@@ -503,6 +514,15 @@ class _BaseAutoModelClass:
                                      modules_to_not_convert=modules_to_not_convert, cpu_embedding=cpu_embedding,
                                      embedding_qtype=embedding_qtype, mixed_precision=mixed_precision,
                                      torch_dtype=torch_dtype)
+        for mod_name, q_name in (config_dict.get("bigdl_layer_qtypes") or {}).items():
+            try:
+                mod = model.get_submodule(mod_name)
+            except AttributeError:
+                continue
+            if isinstance(getattr(mod, "weight", None), FP4Params):
+                mod.weight.qtype = qt.qtype_from_name(q_name)
+                if hasattr(mod, "qtype"):
+                    mod.qtype = mod.weight.qtype
         sd = _load_state_dict_from_dir(pretrained_model_name_or_path)
         if saved_keys is not None:
             missing = saved_keys - set(sd.keys())

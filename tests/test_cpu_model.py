@@ -557,3 +557,38 @@ def test_embedding_variants_across_families(family, tmp_path, monkeypatch):
                 assert m.get_input_embeddings().embed_scale_value == 16.0
         with torch.no_grad():
             assert _cos(m(ids).logits[:, -1], ref) > floor, kwargs
+
+
+def test_mixed_formats_and_rtn_names(tmp_path):
+    """``mixed_fp4`` / ``mixed_fp8`` choose an integer or a float format per layer; the choice is stored with the
+    checkpoint (the bytes do not tell) so ``load_low_bit`` decodes every layer as it was packed.  The per-channel
+    ``*_rtn`` names of the NPU entry point are accepted on the main API as the blocked format of the same width."""
+    import transformers
+    from ipex_llm.transformers import AutoModelForCausalLM
+    from ipex_llm_b200.quant import qtypes as qt
+    cfg = transformers.LlamaConfig(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, vocab_size=500, max_position_embeddings=64,
+                                   tie_word_embeddings=False)
+    torch.manual_seed(0)
+    src = transformers.LlamaForCausalLM(cfg)
+    with torch.no_grad():
+        for n, p in src.named_parameters():
+            if "layers.0" in n and p.dim() > 1:
+                p.copy_(torch.randn_like(p) ** 3 * 0.02)         # heavy tails: the float format wins in this layer
+    d = str(tmp_path / "hf")
+    src.save_pretrained(d)
+    ids = torch.randint(0, 500, (1, 8))
+    m = AutoModelForCausalLM.from_pretrained(d, load_in_low_bit="mixed_fp4")
+    kinds = {m_.weight.qtype for m_ in m.modules() if getattr(getattr(m_, "weight", None), "quantized", False)}
+    assert kinds == {qt.SYM_INT4, qt.FP4}
+    low = str(tmp_path / "low")
+    m.save_low_bit(low)
+    again = AutoModelForCausalLM.load_low_bit(low)
+    with torch.no_grad():
+        assert torch.equal(again(ids).logits, m(ids).logits)
+    m8 = AutoModelForCausalLM.from_pretrained(d, load_in_low_bit="mixed_fp8")
+    with torch.no_grad():
+        assert torch.isfinite(m8(ids).logits).all()
+    with pytest.warns(UserWarning, match="per-channel NPU format"):
+        rtn = AutoModelForCausalLM.from_pretrained(d, load_in_low_bit="sym_int8_rtn")
+    assert rtn.config.bigdl_transformers_low_bit == "sym_int8"
