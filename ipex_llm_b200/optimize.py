@@ -34,8 +34,14 @@ def _save_low_bit(self, save_dir, *args, **kwargs):
         save_low_bit(self, save_dir, *args, **kwargs)
     else:
         torch.save(_plain_state_dict(self), os.path.join(save_dir, PYTORCH_MODEL_NAME))
+    cfg = dict(self._bigdl_config)
+    if cfg["bigdl_transformers_low_bit"] in ("mixed_fp4", "mixed_fp8"):
+        # the per-layer choice between the integer and the float format (the bytes do not tell which)
+        from .quant.params import FP4Params
+        cfg["bigdl_layer_qtypes"] = {n: qt.qtype_name(m.weight.qtype) for n, m in self.named_modules()
+                                     if isinstance(getattr(m, "weight", None), FP4Params) and m.weight.quantized}
     with open(os.path.join(save_dir, CONFIG_NAME), "w") as f:
-        json.dump(self._bigdl_config, f)
+        json.dump(cfg, f)
 
 
 def low_bit_sanity_check(model_path):
@@ -109,6 +115,18 @@ def load_low_bit(model, model_path):
         on_meta = any(p.device.type == "meta" for p in model.parameters())
         model = ggml_convert_low_bit(model, qtype=qtype, convert_shape_only=True,
                                      device="meta" if on_meta else "cpu")
+        with open(os.path.join(model_path, CONFIG_NAME)) as f:
+            chosen = json.load(f).get("bigdl_layer_qtypes") or {}
+        from .quant.params import FP4Params
+        for mod_name, q_name in chosen.items():
+            try:
+                mod = model.get_submodule(mod_name)
+            except AttributeError:
+                continue
+            if isinstance(getattr(mod, "weight", None), FP4Params):
+                mod.weight.qtype = qt.qtype_from_name(q_name)
+                if hasattr(mod, "qtype"):
+                    mod.qtype = mod.weight.qtype
     from .transformers.model import _load_state_dict_from_dir, _rebuild_nonpersistent
     sd = _load_state_dict_from_dir(model_path)
     for name, tensor in sd.items():
