@@ -15,13 +15,16 @@ def test_codebook_linear_on_gpu(name):
     q = qt.qtype_from_name(name)
     torch.manual_seed(0)
     w = torch.randn(96, 512)
-    # the same bytes whether the search ran on the CPU or on the GPU
+    # the search gives the same quality wherever it runs (near-ties between grid entries may fall differently between
+    # the two matmul implementations, so bytes are not compared)
     on_cpu = iq.quantize(w, q)
     on_gpu = iq.quantize(w.cuda(), q)
-    same = (on_cpu == on_gpu.cpu()).float().mean().item()
-    assert same > 0.9, same                            # ties in the arg-min may fall differently; the values agree
-    deq = iq.dequantize(on_gpu, w.shape, q)
-    assert ((deq.cpu() - iq.dequantize(on_cpu, w.shape, q)).norm() / w.norm()).item() < 0.05
+    assert on_gpu.is_cuda and on_gpu.numel() == on_cpu.numel()
+    err_cpu = ((iq.dequantize(on_cpu, w.shape, q) - w).norm() / w.norm()).item()
+    err_gpu = ((iq.dequantize(on_gpu, w.shape, q).cpu() - w).norm() / w.norm()).item()
+    assert abs(err_gpu - err_cpu) < 0.02 and err_gpu < 0.5, (err_cpu, err_gpu)
+    # the decoder itself is exact: the same bytes decode to the same values on both devices
+    assert torch.allclose(iq.dequantize(on_cpu.cuda(), w.shape, q).cpu(), iq.dequantize(on_cpu, w.shape, q), atol=1e-6)
     low = LowBitLinear(512, 96, q, bias=False)
     low._parameters["weight"] = FP4Params(w.clone(), qtype=q, in_features=512).to("cuda")
     assert low.weight.data.is_cuda and low.weight.data.numel() == 96 * 2 * iq.TYPE_SIZE[q]
