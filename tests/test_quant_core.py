@@ -253,3 +253,30 @@ def test_quantizers_survive_degenerate_and_extreme_blocks(name):
             assert y.abs().max().item() == 0, cname
         else:
             assert (y - x).abs().max().item() <= 1.01 * amax + 1e-38, cname      # (denormal scales lose bits)
+
+
+@pytest.mark.parametrize("name,type_size,tail_scale", [("gguf_iq2_xxs", 66, False), ("gguf_iq2_xs", 74, False),
+                                                        ("gguf_iq1_s", 50, False), ("gguf_iq1_m", 56, None)])
+def test_codebook_decoders_on_arbitrary_bytes(name, type_size, tail_scale):
+    """Random super-blocks (every bit pattern of indices, signs, scales and shift bits, not only those the quantizer
+    emits) decode to exactly what the ``gguf`` package's decoder gives."""
+    gq = pytest.importorskip("gguf.quants")
+    from gguf.constants import GGMLQuantizationType as T
+    from ipex_llm_b200.quant import iq_codebooks as iq
+    import numpy as np
+    rng = np.random.default_rng(11)
+    raw = rng.integers(0, 256, size=(64, type_size), dtype=np.uint8)
+    d = np.array([0.0173], dtype=np.float16).view(np.uint8)
+    if tail_scale is None:
+        # iq1_m spreads its fp16 scale over the top nibbles of four 16-bit words: keep it a small finite number
+        words = raw[:, 48:56].copy().view(np.uint16)
+        bits = int(np.array([0.0173], dtype=np.float16).view(np.uint16)[0])
+        for u in range(4):
+            words[:, u] = (words[:, u] & 0x0FFF) | (((bits >> (4 * u)) & 0xF) << 12)
+        raw[:, 48:56] = words.view(np.uint8)
+    else:
+        raw[:, :2] = d
+    q = qt.qtype_from_name(name)
+    ours = iq.dequantize(torch.from_numpy(raw.reshape(-1)), (64, 256), q)
+    theirs = torch.from_numpy(gq.dequantize(raw, getattr(T, name[5:].upper())))
+    assert torch.equal(ours, theirs)
