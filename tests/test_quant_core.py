@@ -280,3 +280,21 @@ def test_codebook_decoders_on_arbitrary_bytes(name, type_size, tail_scale):
     ours = iq.dequantize(torch.from_numpy(raw.reshape(-1)), (64, 256), q)
     theirs = torch.from_numpy(gq.dequantize(raw, getattr(T, name[5:].upper())))
     assert torch.equal(ours, theirs)
+
+
+@pytest.mark.parametrize("name,type_size,scale_at", [("q2_k", 84, (80, 82)), ("q4_k", 144, (0, 2)), ("q5_k", 176, (0, 2)),
+                                                      ("q6_k", 210, (208,))])
+def test_kquant_decoders_on_arbitrary_bytes(name, type_size, scale_at):
+    """The host library's k-quant decoders against the ``gguf`` package on random super-blocks (all scale / minimum /
+    high-bit patterns), i.e. the byte layouts are ggml's."""
+    gq = pytest.importorskip("gguf.quants")
+    from gguf.constants import GGMLQuantizationType as T
+    import numpy as np
+    rng = np.random.default_rng(5)
+    raw = rng.integers(0, 256, size=(48, type_size), dtype=np.uint8)
+    for off, val in zip(scale_at, (0.0131, 0.0077)):
+        raw[:, off:off + 2] = np.array([val], dtype=np.float16).view(np.uint8)
+    q = qt.qtype_from_name(name)
+    ours = ggml_convert_fp32(torch.from_numpy(raw.reshape(-1)), (48, 256), 48 * 256, q)
+    theirs = torch.from_numpy(gq.dequantize(raw, getattr(T, name.upper())))
+    assert torch.allclose(ours, theirs, atol=1e-6, rtol=1e-6)
