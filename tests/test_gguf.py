@@ -466,3 +466,31 @@ def test_load_gguf_llama3_rope_factors(tmp_path):
         a = src(ids).logits[:, -1].float()
         b = model(ids).logits[:, -1].float()
     assert torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item() > 0.995
+
+
+def test_files_written_here_open_in_the_official_reader(tmp_path):
+    """The package's writer and the native ``ipex-quantize`` produce files that ``gguf.GGUFReader`` opens: metadata
+    (non-ASCII strings, arrays, floats, booleans) and tensors (dense, q8_0, k-quant) come back as written."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants as gq
+    from ipex_llm_b200.ggml.quantize import quantize_gguf
+    from ipex_llm_b200.transformers.gguf.gguf import write_gguf
+    torch.manual_seed(0)
+    w = {"blk.0.attn_q.weight": (torch.randn(8, 256), "f32"), "blk.0.ffn_up.weight": (torch.randn(4, 512), "f16"),
+         "n.weight": (torch.randn(16), "f32"), "q.weight": (torch.randn(4, 64), "q8_0")}
+    src, dst = str(tmp_path / "a.gguf"), str(tmp_path / "b.gguf")
+    write_gguf(src, {"general.architecture": "llama", "llama.block_count": 1, "general.name": "tést",
+                     "arr.list": [1, 2, 3], "strs": ["a", "bb"], "f": 1.5, "flag": True}, w)
+    quantize_gguf(src, dst, "q4_k")
+    dense = (gguf.GGMLQuantizationType.F32, gguf.GGMLQuantizationType.F16)
+    for path, packed in ((src, False), (dst, True)):
+        r = gguf.GGUFReader(path)
+        assert bytes(r.fields["general.name"].parts[-1]).decode() == "tést"
+        seen = {}
+        for t in r.tensors:
+            data = np.asarray(t.data, dtype=np.float32) if t.tensor_type in dense else gq.dequantize(t.data, t.tensor_type)
+            ref = w[t.name][0].numpy()
+            seen[t.name] = (t.tensor_type.name, float(np.linalg.norm(data.reshape(ref.shape) - ref) / np.linalg.norm(ref)))
+        assert set(seen) == set(w)
+        assert seen["blk.0.attn_q.weight"][0] == ("Q4_K" if packed else "F32")
+        assert all(err < (0.1 if kind == "Q4_K" else 0.01) for kind, err in seen.values()), seen
