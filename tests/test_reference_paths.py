@@ -16,6 +16,12 @@ PATHS = [
     "utils.ipex_importer", "utils.lazy_load_torch", "transformers.npu_model", "transformers.patches",
     "transformers.streamer", "transformers.loader", "transformers.xgrammar", "ggml.quantize", "ggml.convert_model",
     "ggml.convert", "gptq.convert.convert_gptq_to_ggml", "transformers.convert_ipex",
+    "transformers.models.sd", "utils.glibc_checker", "serving.fastchat.bigdl_llm_model", "serving.fastchat.model_worker",
+    "serving.fastchat.vllm_worker", "serving.fastchat.tgi_api_server", "serving.fastchat.tgi_api_protocol",
+    "llamaindex.llms.bigdlllm", "langchain.llms.bigdlllm", "langchain.llms.transformersllm",
+    "langchain.llms.transformerspipelinellm", "langchain.embeddings.bigdlllm",
+    "langchain.embeddings.transformersembeddings", "langchain.vllm.vllm", "vllm.xpu.engine", "vllm.cpu.engine",
+    "vllm.xpu.entrypoints.openai.api_server", "vllm.cpu.entrypoints.openai.api_server",
 ]
 
 
