@@ -132,6 +132,7 @@ def load_low_bit(model, model_path):
     for name, tensor in sd.items():
         _set_tensor(model, name, tensor)
     _rebuild_nonpersistent(model, "cpu")
+    model.eval()           # a shell built from a config is in training mode (dropout, router jitter); this is inference
     if low_bit:
         model._bigdl_config = {"bigdl_transformers_low_bit": low_bit}
         model.save_low_bit = types.MethodType(_save_low_bit, model)
