@@ -93,6 +93,14 @@ def _hf_config(cfg: dict, arch: str, vocab: int):
     rope = g("rope.freq_base")
     if rope:
         common["rope_theta"] = float(rope)
+    # long-context variants: linear position interpolation or YaRN, as llama.cpp records them
+    scaling, factor = g("rope.scaling.type"), g("rope.scaling.factor")
+    if scaling in ("linear", "yarn") and factor and float(factor) != 1.0:
+        rp = {"rope_type": scaling, "factor": float(factor), "rope_theta": float(rope or 10000.0)}
+        if scaling == "yarn" and g("rope.scaling.original_context_length"):
+            rp["original_max_position_embeddings"] = int(g("rope.scaling.original_context_length"))
+        common["rope_parameters"] = rp
+        common.pop("rope_theta", None)
     name = str(cfg.get("general.name", "")).lower()
     if arch == "qwen2":
         return transformers.Qwen2Config(**common), "qwen2"

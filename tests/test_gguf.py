@@ -494,3 +494,34 @@ def test_files_written_here_open_in_the_official_reader(tmp_path):
         assert set(seen) == set(w)
         assert seen["blk.0.attn_q.weight"][0] == ("Q4_K" if packed else "F32")
         assert all(err < (0.1 if kind == "Q4_K" else 0.01) for kind, err in seen.values()), seen
+
+
+def test_load_gguf_rope_scaling_metadata(tmp_path):
+    """``<arch>.rope.scaling.type / factor`` (linear position interpolation) reaches the rebuilt model's rotary tables."""
+    import transformers
+    from ipex_llm.transformers import AutoModelForCausalLM
+    from ipex_llm_b200.transformers.gguf.gguf import GGUFFileLoader, write_gguf
+    cfg = transformers.LlamaConfig(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, vocab_size=320, max_position_embeddings=512,
+                                   rope_parameters={"rope_type": "linear", "factor": 4.0, "rope_theta": 10000.0},
+                                   tie_word_embeddings=False, bos_token_id=1, eos_token_id=2)
+    torch.manual_seed(0)
+    src = transformers.AutoModelForCausalLM.from_config(cfg).eval()
+    with torch.no_grad():
+        for p in src.parameters():
+            if p.dim() > 1:
+                p.normal_(0, 0.05)
+    path = str(tmp_path / "lin.gguf")
+    _export_llama_cpp_style(src, "llama", path)
+    loader = GGUFFileLoader(path)
+    meta = dict(loader.config)
+    tensors = {n: (t, "f32" if t.dim() == 1 else "f16") for n, t in loader.tensors().items()}
+    loader.close()
+    meta.update({"llama.rope.scaling.type": "linear", "llama.rope.scaling.factor": 4.0})
+    write_gguf(path, meta, tensors)
+    model, _ = AutoModelForCausalLM.from_gguf(path, low_bit="sym_int8")
+    assert torch.allclose(model.model.rotary_emb.inv_freq, src.model.rotary_emb.inv_freq)
+    ids = torch.randint(0, 320, (1, 120))
+    with torch.no_grad():
+        a, b = src(ids).logits[:, -1].float(), model(ids).logits[:, -1].float()
+    assert torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item() > 0.995
