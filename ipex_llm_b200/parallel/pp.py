@@ -322,13 +322,25 @@ def pipeline_parallel_generate(self, inputs: Optional[torch.Tensor] = None, max_
             h.wait()
 
     local_ids = {}        # world == 1: ids pass through this dict instead of the ring
+    # padded prompts: every stage masks the padding and counts positions from each row's first real token
+    mask = None
+    if attention_mask is not None and not bool(attention_mask.all()):
+        mask = torch.ones((B, S + max_new_tokens), dtype=torch.long, device=dev)
+        mask[:, :S] = attention_mask.to(dev)
+        prompt_pos = (mask[:, :S].cumsum(-1) - 1).clamp_(min=0)
+        prompt_len = mask[:, :S].sum(-1, keepdim=True)
     t_start = time.perf_counter()
     for step in range(max_new_tokens):
         s_len = S if step == 0 else 1
         pos = torch.arange(S) if step == 0 else torch.tensor([S + step - 1])
         for m in range(n_mb):
             b0, b1 = bounds[m], bounds[m + 1]
-            position_ids = pos.to(dev).unsqueeze(0).expand(rows[m], -1)
+            if mask is None:
+                position_ids = pos.to(dev).unsqueeze(0).expand(rows[m], -1)
+                mkw = {}
+            else:
+                position_ids = prompt_pos[b0:b1] if step == 0 else prompt_len[b0:b1] + (step - 1)
+                mkw = dict(attention_mask=mask[b0:b1, :S + step])
             if first:
                 if step == 0:
                     ids = input_ids[b0:b1]
@@ -344,12 +356,12 @@ def pipeline_parallel_generate(self, inputs: Optional[torch.Tensor] = None, max_
                 dist.recv(hid, src=rank - 1)
                 kw = dict(inputs_embeds=hid)
             if last:
-                res = self(position_ids=position_ids, past_key_values=caches[m], use_cache=True, **kw).logits
+                res = self(position_ids=position_ids, past_key_values=caches[m], use_cache=True, **kw, **mkw).logits
             else:
                 # the hidden states themselves: a causal-LM wrapper may scale or soft-cap what it takes for logits
                 # (Cohere, Granite, Gemma-2), which must happen on the last stage only
                 res = self.model(position_ids=position_ids, past_key_values=caches[m], use_cache=True,
-                                 **kw).last_hidden_state
+                                 **kw, **mkw).last_hidden_state
             if last:
                 nxt = torch.argmax(res[:, -1, :], dim=-1)
                 if eos_t is not None:

@@ -228,8 +228,18 @@ def main(argv=None):
     ap.add_argument("--host", type=str, default="0.0.0.0")
     ap.add_argument("--max-num-seqs", type=int, default=8)
     ap.add_argument("--model-type", type=str, default="normal")
+    ap.add_argument("--pipeline-parallel-stages", type=int, default=int(os.environ.get("WORLD_SIZE", "1")),
+                    help="under torchrun: one stage per rank; rank 0 serves HTTP, the others follow its batches "
+                         "(the reference's Pipeline-Parallel-Serving/pipeline_serving.py)")
     a = ap.parse_args(argv)
-    worker = ModelWorker(a.repo_id_or_model_path, a.low_bit, a.model_type, max_num_seqs=a.max_num_seqs)
+    if a.pipeline_parallel_stages > 1:
+        from .pp_worker import PPModelWorker
+        worker = PPModelWorker(a.repo_id_or_model_path, low_bit=a.low_bit, max_num_seqs=a.max_num_seqs)
+        if worker.rank != 0:
+            worker._serve_forever()                 # stages without the HTTP side follow rank 0 until it stops
+            return
+    else:
+        worker = ModelWorker(a.repo_id_or_model_path, a.low_bit, a.model_type, max_num_seqs=a.max_num_seqs)
     uvicorn.run(FastApp(worker).app, host=a.host, port=a.port)
 
 

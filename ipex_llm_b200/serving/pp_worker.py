@@ -137,10 +137,13 @@ class PPModelWorker(ModelWorker):
         if task.stopped:
             return False
         ids = torch.tensor(task.input_ids, dtype=torch.long)
+        # prompts are left-padded to the longest of the batch: the mask follows from the announced lengths
+        cols = torch.arange(ids.shape[1]).unsqueeze(0)
+        attn = (cols >= ids.shape[1] - torch.tensor(task.prompt_lengths).unsqueeze(1)).long()
         t0 = time.perf_counter()
         emitter = _TokenEmitter(self.tokenizer, batch) if self.rank == 0 else None
         out = self.model.generate(ids, max_new_tokens=task.max_tokens, do_sample=False, streamer=emitter,
-                                  eos_token_id=self.tokenizer.eos_token_id, pad_token_id=self.tokenizer.pad_token_id)
+                                  attention_mask=attn, eos_token_id=self.tokenizer.eos_token_id, pad_token_id=self.tokenizer.pad_token_id)
         if self.rank == 0:
             self.stats["first_token_s"].append(getattr(self.model, "first_token_time", 0.0))
             self.stats["next_token_s"].extend(getattr(self.model, "next_token_time", []))

@@ -60,6 +60,26 @@ def test_pipeline_parallel_across_families_cpu_gloo():
     assert res.stdout.count(": ok") == 2
 
 
+def test_pipeline_parallel_serving_cpu_gloo(tmp_path):
+    """``PPModelWorker`` end to end on two gloo stages (reference Pipeline-Parallel-Serving/pipeline_serving.py)."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import LlamaConfig, LlamaForCausalLM, PreTrainedTokenizerFast
+    words = ["<pad>", "<s>", "</s>", "<unk>"] + [f"w{i}" for i in range(60)]
+    tk = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tk.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    tok = PreTrainedTokenizerFast(tokenizer_object=tk, pad_token="<pad>", bos_token="<s>", eos_token="</s>",
+                                  unk_token="<unk>")
+    cfg = LlamaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=64, max_position_embeddings=256, tie_word_embeddings=False,
+                      eos_token_id=2, pad_token_id=0, bos_token_id=1)
+    torch.manual_seed(0)
+    LlamaForCausalLM(cfg).save_pretrained(tmp_path)
+    tok.save_pretrained(tmp_path)
+    res = run_workers("pp_serving_worker.py", 2, [str(tmp_path)], timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert res.stdout.count(": ok") == 2
+
+
 def test_tensor_parallel_across_families_cpu_gloo():
     """Fused qkv / gate_up, expert banks, shared experts, replicated attention: see the worker's docstring."""
     res = run_workers("tp_families_worker.py", 2, [], timeout=900)
