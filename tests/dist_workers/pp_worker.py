@@ -32,6 +32,11 @@ def main():
     if cuda:
         full = full.to(dev)
     ref = full.generate(ids.to(dev), max_new_tokens=8, do_sample=False)
+    # a left-padded batch (rows of 17, 9 and 4 real tokens)
+    pad_mask = torch.ones_like(ids)
+    pad_mask[1, :8] = 0
+    pad_mask[2, :13] = 0
+    ref_pad = None if cuda else full.generate(ids, attention_mask=pad_mask, max_new_tokens=8, do_sample=False)
     del full
 
     staged = AutoModelForCausalLM.from_pretrained(args.model_dir, load_in_low_bit="sym_int8", torch_dtype=dtype,
@@ -45,6 +50,9 @@ def main():
     # fp16 stage hand-offs on the GPU can flip a near-tie late in a sequence; the CPU path is fp32 and exact
     assert match == 1.0 if not cuda else match > 0.9, (match, out, ref)
     assert staged.first_token_time > 0 and len(staged.next_token_time) == 7
+    if ref_pad is not None:
+        out_pad = staged.generate(ids, attention_mask=pad_mask, max_new_tokens=8, do_sample=False)
+        assert torch.equal(out_pad, ref_pad), (out_pad, ref_pad)
 
     # token-level streaming from the first stage: the prompt, then one put per step with every sequence's token
     class _Collect:
