@@ -1,10 +1,14 @@
 """Hugging Face ``transformers``-style API (reference: python/llm/src/ipex_llm/transformers/__init__.py)."""
-from .convert import ggml_convert_low_bit  # noqa: F401
+from .convert import convert_model_hybrid, get_enable_ipex, ggml_convert_low_bit  # noqa: F401
 from .model import (AutoModel, AutoModelForCausalLM, AutoModelForMaskedLM, AutoModelForMultipleChoice,  # noqa: F401
                     AutoModelForNextSentencePrediction, AutoModelForQuestionAnswering,
                     AutoModelForSeq2SeqLM, AutoModelForSequenceClassification, AutoModelForSpeechSeq2Seq,
                     AutoModelForTokenClassification, AutoModelForVision2Seq,
                     Qwen2VLModelForConditionalGeneration)
+from .modelling_bigdl import (BigdlNativeForCausalLM, BloomForCausalLM, ChatGLMForCausalLM,  # noqa: F401
+                              GptneoxForCausalLM, LlamaForCausalLM, StarcoderForCausalLM)
+
+Qwen2VLForConditionalGeneration = Qwen2VLModelForConditionalGeneration   # the name the reference package exports
 
 
 def __getattr__(name):

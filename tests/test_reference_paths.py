@@ -50,6 +50,15 @@ def test_names_behind_the_paths():
     assert lin.weight.device.type == "meta"
     import bigdl.llm.transformers.low_bit_linear as legacy
     assert legacy.LowBitLinear is impl
+    # everything the reference's ``ipex_llm.transformers`` package exports (transformers/__init__.py:17-32)
+    import ipex_llm.transformers as pkg
+    for name in ("ggml_convert_low_bit", "get_enable_ipex", "convert_model_hybrid", "AutoModelForCausalLM", "AutoModel",
+                 "AutoModelForSeq2SeqLM", "AutoModelForSpeechSeq2Seq", "AutoModelForQuestionAnswering",
+                 "AutoModelForSequenceClassification", "AutoModelForMaskedLM", "AutoModelForNextSentencePrediction",
+                 "AutoModelForMultipleChoice", "AutoModelForTokenClassification", "Qwen2VLForConditionalGeneration",
+                 "BigdlNativeForCausalLM", "LlamaForCausalLM", "ChatGLMForCausalLM", "GptneoxForCausalLM",
+                 "BloomForCausalLM", "StarcoderForCausalLM", "init_pipeline_parallel", "PPModelWorker"):
+        assert hasattr(pkg, name), name
 
 
 def test_torch_library_ops_have_fake_kernels_and_match_eager():
