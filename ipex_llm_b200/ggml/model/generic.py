@@ -13,8 +13,10 @@ import time
 import uuid
 from typing import Iterator, List, Optional, Union
 
+from .generation import GenerationMixin
 
-class GenericModel:
+
+class GenericModel(GenerationMixin):
     family = "llama"
 
     def __init__(self, model_path: str, n_ctx: int = 512, n_threads: int = -1, seed: int = -1, n_batch: int = 512,
@@ -99,14 +101,18 @@ class GenericModel:
     def __call__(self, prompt: str, **kwargs):
         return self.create_completion(prompt, **kwargs)
 
-    def generate(self, tokens: List[int], top_k: int = 40, top_p: float = 0.95, temp: float = 0.0,
-                 repeat_penalty: float = 1.0, max_tokens: int = 128, **kwargs) -> Iterator[int]:
+    def _generate_ids(self, tokens: List[int], max_tokens, temp, top_p, top_k, repeat_penalty) -> List[int]:
         import torch
         dev = next(self.model.parameters()).device
         ids = torch.tensor([tokens], device=dev)
         with torch.no_grad():
             out = self.model.generate(ids, **self._gen_kwargs(max_tokens, temp, top_p, top_k, repeat_penalty))
-        yield from out[0][len(tokens):].tolist()
+        return out[0][len(tokens):].tolist()
+
+    def _generate(self, tokens: List[int], top_k: int = 40, top_p: float = 0.95, temp: float = 0.0,
+                  repeat_penalty: float = 1.0, max_tokens: int = 128, **kwargs) -> Iterator[int]:
+        """Generator over the new tokens of one prompt (the llama-cpp form of ``generate``)."""
+        yield from self._generate_ids(tokens, max_tokens, temp, top_p, top_k, repeat_penalty)
 
     def embed(self, text: str) -> List[float]:
         import torch

@@ -102,6 +102,18 @@ def test_native_style_classes_and_legacy_names(tiny):
     assert pieces[-1]["choices"][0]["finish_reason"] in ("length", "stop")
     emb = llm.create_embedding("w3 w4")
     assert len(emb["data"][0]["embedding"]) == 64
+    # the transformers-flavoured token API of the same classes (ggml/model/generation/utils.py:28-180)
+    from ipex_llm.ggml.model.generation import GenerationMixin
+    from ipex_llm.ggml.model.llama import Llama as ByPath
+    assert ByPath is Llama and isinstance(llm, GenerationMixin)
+    for fam in ("gptneox", "bloom", "starcoder", "chatglm"):
+        __import__(f"ipex_llm.ggml.model.{fam}")
+    new = llm.generate(toks, max_new_tokens=4, temperature=0.0)
+    assert len(new) == 1 and 1 <= len(new[0]) <= 4
+    assert new == llm.generate([toks], max_new_tokens=4, temperature=0.0)
+    assert new[0] == list(llm._generate(toks, max_tokens=4))
+    assert llm.batch_decode(new) == [llm.decode(new[0])] and isinstance(llm.batch_decode(new[0]), str)
+    assert llm.generate([]) is None
 
 
 def test_ggml_quantize_module(tiny_llama_dir, tmp_path):
