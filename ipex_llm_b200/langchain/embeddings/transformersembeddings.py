@@ -40,3 +40,17 @@ class TransformersEmbeddings:
 
     def embed_query(self, text: str, **kwargs) -> List[float]:
         return self.embed(text.replace("\n", " "), **kwargs)
+
+
+class TransformersBgeEmbeddings(TransformersEmbeddings):
+    """BGE-style sentence vector: the first token's last hidden state, L2-normalised (reference
+    transformersembeddings.py:188-195)."""
+
+    def embed(self, text: str, **kwargs) -> List[float]:
+        import torch
+        dev = next(self.model.parameters()).device
+        enc = self.tokenizer(text, return_tensors="pt", **{**self.encode_kwargs, **kwargs})
+        with torch.no_grad():
+            out = self.model(input_ids=enc["input_ids"].to(dev), output_hidden_states=True)
+        hidden = out.hidden_states[-1] if getattr(out, "hidden_states", None) is not None else out.last_hidden_state
+        return torch.nn.functional.normalize(hidden[:, 0].float(), p=2, dim=1)[0].cpu().tolist()

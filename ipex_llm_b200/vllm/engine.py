@@ -9,8 +9,8 @@ format and then defers to vLLM with every other argument untouched.
 The patches live on classes of this process.  vLLM's V1 engine core normally runs in a child process that would import
 those classes afresh, so unless the caller decided otherwise the core is kept in-process
 (``VLLM_ENABLE_V1_MULTIPROCESSING=0``); tensor-parallel workers are forked by default and inherit the patches.  The
-multiprocessing front end of older releases (``MQLLMEngine`` / ``run_mp_engine``) does not exist in current vLLM and
-has no counterpart here.
+multiprocessing front end of older releases (``MQLLMEngine``) does not exist in current vLLM: ``run_mp_engine`` serves
+through it where the installed vLLM still has it and says so otherwise.
 """
 from __future__ import annotations
 
@@ -57,6 +57,31 @@ def _build(name):
     body["__module__"] = __name__
     new = type(name, (base,), body)
     return new
+
+
+def run_mp_engine(engine_args, usage_context, ipc_path: str, load_in_low_bit: str, engine_alive):
+    """Body of the engine process of vLLM's ZeroMQ front end (reference engine.py:224-242): build the engine with the
+    low-bit loader patches installed and serve until SIGTERM; ``engine_alive.value`` turns False on failure."""
+    import importlib
+    import signal
+    from ..utils.common import invalidInputError
+    try:
+        base = importlib.import_module("vllm.engine.multiprocessing.engine").MQLLMEngine
+    except (ImportError, AttributeError):
+        invalidInputError(False, "the installed vLLM has no MQLLMEngine front end; use IPEXLLMAsyncV1Engine "
+                                 "(ipex_llm.vllm.entrypoints.openai.api_server does)")
+
+    def on_term(*_):
+        raise KeyboardInterrupt("MQLLMEngine terminated")
+
+    try:
+        signal.signal(signal.SIGTERM, on_term)
+        _convert(load_in_low_bit)
+        engine = base.from_engine_args(engine_args=engine_args, usage_context=usage_context, ipc_path=ipc_path)
+        engine.start()
+    except BaseException:
+        engine_alive.value = False
+        raise
 
 
 def __getattr__(name):

@@ -37,6 +37,10 @@ def test_langchain_and_llamaindex(tiny):
     emb = TransformersEmbeddings.from_model_id(tiny, model_kwargs={"torch_dtype": torch.float32}, device_map="cpu")
     v = emb.embed_query("w1 w2")
     assert len(v) == 64 and len(emb.embed_documents(["w1", "w2 w3"])) == 2
+    from ipex_llm.langchain.embeddings import TransformersBgeEmbeddings
+    bge = TransformersBgeEmbeddings(model=emb.model, tokenizer=emb.tokenizer)
+    b = torch.tensor(bge.embed_query("w1 w2"))
+    assert b.shape == (64,) and abs(float(b.norm()) - 1.0) < 1e-4          # first token's state, unit length
     li = IpexLLM(model_name=tiny, device_map="cpu", max_new_tokens=4, model_kwargs={"torch_dtype": torch.float32})
     r = li.complete("w5 w6")
     assert isinstance(r.text, str)

@@ -59,6 +59,12 @@ def test_names_behind_the_paths():
                  "BigdlNativeForCausalLM", "LlamaForCausalLM", "ChatGLMForCausalLM", "GptneoxForCausalLM",
                  "BloomForCausalLM", "StarcoderForCausalLM", "init_pipeline_parallel", "PPModelWorker"):
         assert hasattr(pkg, name), name
+    from ipex_llm.transformers.gguf import load_gguf_model  # noqa: F401
+    from ipex_llm.utils.common import LazyImport
+    from ipex_llm.vllm.xpu.engine import run_mp_engine  # noqa: F401
+    lazy_fn = LazyImport("ipex_llm.transformers.low_bit_linear.ggml_convert_qtype")
+    assert lazy_fn(torch.randn(2, 64), ggml_tensor_qtype["sym_int8"]).dtype == torch.uint8
+    assert LazyImport("ipex_llm.ggml.quantize").ggml_tensor_qtype["sym_int4"] == 2
 
 
 def test_torch_library_ops_have_fake_kernels_and_match_eager():
