@@ -6,6 +6,11 @@ import pytest
 import torch
 
 PATHS = [
+    "serving.fastapi.api_server", "serving.fastapi.model_worker",
+    "serving.fastapi.openai_protocol", "serving.fastapi.tgi_protocol",
+    "vllm.xpu.engine.engine", "vllm.cpu.engine.engine",
+    "ggml.model.llama", "ggml.model.gptneox", "ggml.model.bloom",
+    "ggml.model.starcoder", "ggml.model.generation", "utils.common.lazyimport",
     "transformers.low_bit_linear", "transformers.embedding", "transformers.kv", "transformers.utils",
     "transformers.convert", "transformers.models.utils", "transformers.models.common", "utils.common",
     "utils.common.log4Error", "transformers.modelling_bigdl", "transformers.training_patch", "transformers.qlora",
